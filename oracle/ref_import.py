@@ -1,0 +1,121 @@
+"""Import the unmodified reference modules for pinning the oracle.  TEST INFRASTRUCTURE ONLY.
+
+The reference's package ``__init__`` files pull in its data pipeline and
+Lightning, which are not installed here.  Registering empty parent packages
+whose ``__path__`` points at the reference directories lets
+``crosslayer_transcoder/model/{clt,jumprelu,topk,standardize}.py`` import
+exactly as they are; three small stand-in modules (``lightning``,
+``torchmetrics``, ``nnsight``) are enough for
+``crosslayer_transcoder/model/clt_lightning.py`` too.
+
+Used only where the reference tree exists (the development container): by
+``tests/golden/make_golden.py`` and ``tests/test_oracle_vs_reference.py``.
+"""
+from __future__ import annotations
+
+import importlib
+import os
+import sys
+import types
+from pathlib import Path
+
+import torch
+
+REF_ROOT = Path(os.environ.get("CLT_REFERENCE_ROOT", "/root/reference"))
+
+
+def available() -> bool:
+    return (REF_ROOT / "crosslayer_transcoder" / "model" / "clt.py").exists()
+
+
+def _pkg(name: str, path: Path) -> types.ModuleType:
+    m = types.ModuleType(name)
+    m.__path__ = [str(path)]
+    sys.modules[name] = m
+    return m
+
+
+def _shim_lightning():
+    if "lightning" in sys.modules:
+        return
+    L = types.ModuleType("lightning")
+
+    class _Trainer:
+        max_steps = 1
+        num_devices = 1
+
+    class LightningModule(torch.nn.Module):
+        def __init__(self, *a, **k):
+            super().__init__()
+            self.trainer = _Trainer()
+            self.global_step = 0
+            self.logger = None
+            self.logged = {}
+
+        def log(self, name, value, *a, **k):
+            self.logged[name] = value
+
+        def save_hyperparameters(self, *a, **k):
+            pass
+
+    class Callback:
+        pass
+
+    class LightningDataModule:
+        pass
+
+    L.LightningModule = LightningModule
+    L.Callback = Callback
+    L.LightningDataModule = LightningDataModule
+    sys.modules["lightning"] = L
+
+    tm = types.ModuleType("torchmetrics")
+
+    class Metric(torch.nn.Module):
+        def __init__(self, *a, **k):
+            super().__init__()
+
+        def add_state(self, name, default, dist_reduce_fx=None):
+            self.register_buffer(name, default)
+
+    tm.Metric = Metric
+    sys.modules["torchmetrics"] = tm
+    sys.modules.setdefault("nnsight", types.ModuleType("nnsight"))
+    if "wandb" not in sys.modules:
+        try:
+            import wandb  # noqa: F401
+        except Exception:
+            w = types.ModuleType("wandb")
+            w.wandb_run = types.SimpleNamespace(Run=type("Run", (), {}))
+            sys.modules["wandb"] = w
+
+
+_loaded = {}
+
+
+def load(with_lightning: bool = False) -> types.SimpleNamespace:
+    """Return a namespace with the reference's model modules (``clt``, ``jumprelu``,
+    ``topk``, ``standardize`` and, optionally, ``clt_lightning``)."""
+    if not available():
+        raise RuntimeError(f"reference tree not found at {REF_ROOT}")
+    key = bool(with_lightning)
+    if key in _loaded:
+        return _loaded[key]
+    base = REF_ROOT / "crosslayer_transcoder"
+    if "crosslayer_transcoder" not in sys.modules:
+        _pkg("crosslayer_transcoder", base)
+        _pkg("crosslayer_transcoder.model", base / "model")
+        _pkg("crosslayer_transcoder.metrics", base / "metrics")
+        utils = _pkg("crosslayer_transcoder.utils", base / "utils")
+        uu = types.ModuleType("crosslayer_transcoder.utils.utils")
+        uu.get_webtext_dataloader = lambda *a, **k: None
+        sys.modules["crosslayer_transcoder.utils.utils"] = uu
+        utils.utils = uu
+    ns = types.SimpleNamespace()
+    for name in ("serializable_module", "standardize", "jumprelu", "topk", "clt"):
+        setattr(ns, name, importlib.import_module(f"crosslayer_transcoder.model.{name}"))
+    if with_lightning:
+        _shim_lightning()
+        ns.clt_lightning = importlib.import_module("crosslayer_transcoder.model.clt_lightning")
+    _loaded[key] = ns
+    return ns

@@ -1,0 +1,139 @@
+"""Generate the golden vectors under ``tests/golden/`` by running the UNMODIFIED
+reference modules (imported with ``oracle/ref_import.py``) on seeded inputs.
+
+Run where the reference tree is present:
+
+    python tests/golden/make_golden.py
+
+Each ``<case>.pt`` holds the case's spec, its inputs (batch, weights, state) and
+what the reference's ``training_step`` + ``backward`` + one ``Adam`` step gave:
+loss, pre-activations, features, normalised reconstruction, every parameter's
+gradient and the parameters after the optimizer step.
+"""
+from __future__ import annotations
+
+import contextlib
+import sys
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+
+from crosslayer_transcoder_b200 import synthetic  # noqa: E402
+from oracle import ref_import  # noqa: E402
+
+HERE = Path(__file__).resolve().parent
+
+
+def cases():
+    base = dict(n_layers=3, d_acts=32, d_features=64, batch=48, rank_u=8, n_outlier=2)
+    S = synthetic.WorkloadSpec
+    out = []
+    for bf16 in (False, True):
+        sfx = "bf16" if bf16 else "fp32"
+        out += [
+            S(f"jumprelu_clt_{sfx}", kind="jumprelu", crosslayer=True, bf16=bf16, lambda_sparsity=4e-4,
+              pre_actv_loss=3e-6, lr=1e-3, **base),
+            S(f"jumprelu_plt_{sfx}", kind="jumprelu", crosslayer=False, bf16=bf16, lambda_sparsity=2e-4,
+              c_sparsity=0.5, pre_actv_loss=3e-6, lr=1e-3, **base),
+            S(f"topk_clt_{sfx}", kind="topk", crosslayer=True, bf16=bf16, k=4, k_aux=8, aux_loss_scale=1 / 32,
+              tokens_till_dead=1000, dead_fraction=0.3, lr=1e-3, **base),
+            S(f"batchtopk_clt_{sfx}", kind="batchtopk", crosslayer=True, bf16=bf16, k=3, e=0.1, lr=1e-3, **base),
+        ]
+    return out
+
+
+def build_reference_module(ref, spec, weights, last_active):
+    clt, jr, tk, st, cl = ref.clt, ref.jumprelu, ref.topk, ref.standardize, ref.clt_lightning
+    L, D, F = spec.n_layers, spec.d_acts, spec.d_features
+    enc = clt.Encoder(D, F, L)
+    dec = (clt.CrosslayerDecoder if spec.crosslayer else clt.Decoder)(D, F, L)
+    if spec.kind == "jumprelu":
+        nl = jr.JumpReLU(theta=spec.theta, bandwidth=spec.bandwidth, n_layers=L, d_features=F)
+    elif spec.kind == "topk":
+        nl = tk.PerLayerTopK(k=spec.k)
+    else:
+        nl = tk.BatchTopK(k=spec.k, e=spec.e)
+    model = clt.CrossLayerTranscoder(nl, enc, dec, st.DimensionwiseInputStandardizer(L, D),
+                                     st.DimensionwiseOutputStandardizer(L, D))
+    with torch.no_grad():
+        enc.W.copy_(weights["W_enc"])
+        enc.b.copy_(weights["b_enc"])
+        dec.b.copy_(weights["b_dec"])
+        if spec.crosslayer:
+            for t in range(L):
+                dec.get_parameter(f"W_{t}").copy_(weights["W_dec"][t])
+        else:
+            dec.W.copy_(weights["W_dec"])
+    common = dict(model=model, learning_rate=spec.lr, log_metrics_every=10 ** 9)
+    if spec.kind == "jumprelu":
+        mod = cl.JumpReLUCrossLayerTranscoderModule(lambda_sparsity=spec.lambda_sparsity, c_sparsity=spec.c_sparsity,
+                                                    use_tanh=spec.use_tanh, pre_actv_loss=spec.pre_actv_loss, **common)
+        mod.trainer.max_steps = 1
+        mod.global_step = 1          # lambda ramp factor global_step / max_steps = 1
+    elif spec.kind == "topk":
+        mod = cl.TopKCrossLayerTranscoderModule(topk_aux=tk.PerLayerTopK(k=spec.k_aux),
+                                                tokens_till_dead=spec.tokens_till_dead,
+                                                aux_loss_scale=spec.aux_loss_scale, **common)
+        mod.last_active.copy_(last_active)
+    else:
+        mod = cl.CrossLayerTranscoderModule(**common)
+    return mod
+
+
+def run_case(ref, spec):
+    batch = synthetic.make_batch(spec, seed=11)
+    weights = synthetic.make_weights(spec, seed=12)
+    # non-zero biases so that every term of the arithmetic is exercised
+    g = torch.Generator().manual_seed(13)
+    weights["b_enc"] = 0.02 * torch.randn(weights["b_enc"].shape, generator=g)
+    weights["b_dec"] = 0.02 * torch.randn(weights["b_dec"].shape, generator=g)
+    last_active = synthetic.make_last_active(spec, seed=14)
+    mod = build_reference_module(ref, spec, weights, last_active)
+    mod.model.initialize_standardizers(batch)
+    ctx = torch.autocast("cpu", dtype=torch.bfloat16) if spec.bf16 else contextlib.nullcontext()
+    with ctx:
+        # the forward tuple, for the intermediate tensors
+        pre, feat, recons_norm, recons = mod.forward(batch[:, 0])
+    thr0 = mod.model.nonlinearity.threshold.clone() if spec.kind == "batchtopk" else None
+    if thr0 is not None:
+        mod.model.nonlinearity.threshold = torch.zeros(1)     # undo the forward's EMA update
+    with ctx:
+        loss = mod.training_step(batch, 1)
+    loss.backward()
+    names = [n for n, _ in mod.named_parameters()]
+    grads = {n: (p.grad.detach().clone() if p.grad is not None else torch.zeros_like(p))
+             for n, p in mod.named_parameters()}
+    opt = mod.configure_optimizers()
+    opt.step()
+    after = {n: p.detach().clone() for n, p in mod.named_parameters()}
+    out = {
+        "spec": dict(spec.__dict__),
+        "batch": batch, "weights": weights, "last_active_in": last_active,
+        "names": names,
+        "loss": loss.detach(), "pre": pre.detach().float(), "feat": feat.detach().float(),
+        "recons_norm": recons_norm.detach().float(), "recons": recons.detach().float(),
+        "grads": grads, "params_after_adam": after,
+        "logged": {k: (v.detach().clone() if torch.is_tensor(v) else v) for k, v in mod.logged.items()},
+        "last_active_out": mod.last_active.clone(),
+        "stats": {"mu_in": mod.model.input_standardizer.mean.clone(), "sd_in": mod.model.input_standardizer.std.clone(),
+                  "mu_out": mod.model.output_standardizer.mean.clone(), "sd_out": mod.model.output_standardizer.std.clone()},
+    }
+    if spec.kind == "batchtopk":
+        out["threshold_out"] = mod.model.nonlinearity.threshold.detach().clone()
+    return out
+
+
+def main():
+    ref = ref_import.load(with_lightning=True)
+    torch.set_num_threads(1)          # fixed reduction order
+    for spec in cases():
+        out = run_case(ref, spec)
+        torch.save(out, HERE / f"{spec.name}.pt")
+        print(f"{spec.name}: loss={out['loss'].item():.6f}  nnz={int((out['feat'] > 0).sum())}")
+
+
+if __name__ == "__main__":
+    main()
