@@ -1,0 +1,383 @@
+// HBM-bound kernels of the training step that are not contractions:
+// standardise + cast of the input batch, reconstruction loss forward and
+// backward, decoder row norms, the dead-feature counters and the fused Adam step.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace clt {
+
+template <class T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <class T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_float<__half>(__half v) { return __half2float(v); }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+// ---------------------------------------------------------------------------------
+// Input preparation: xn[l, b, d] = (batch[b, 0, l, d] - mu[l, d]) / sd[l, d], cast to TOut.
+// The layer-major output makes every layer's [B, D] matrix one contiguous GEMM operand.
+// ---------------------------------------------------------------------------------
+template <class TIn, class TOut>
+__global__ void prep_input_kernel(const TIn* __restrict__ batch, const float* __restrict__ mu,
+                                  const float* __restrict__ sd, TOut* __restrict__ xn, int B, int L, int D) {
+  const long long total = (long long)B * L * D;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int d = (int)(i % D);
+    const long long r = i / D;
+    const int l = (int)(r % L);
+    const long long b = r / L;
+    const float x = to_float<TIn>(batch[((b * 2 + 0) * L + l) * D + d]);
+    const float v = (x - mu[l * D + d]) / sd[l * D + d];
+    xn[((long long)l * B + b) * D + d] = from_float<TOut>(v);
+  }
+}
+
+template <class TIn, class TOut>
+static int prep_input_t(const void* batch, const float* mu, const float* sd, void* xn, int B, int L, int D,
+                        cudaStream_t s) {
+  const long long total = (long long)B * L * D;
+  const int threads = 256;
+  const int blocks = (int)min((total + threads - 1) / threads, (long long)148 * 16);
+  prep_input_kernel<TIn, TOut><<<blocks, threads, 0, s>>>((const TIn*)batch, mu, sd, (TOut*)xn, B, L, D);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int prep_input(const void* batch, int in_dtype, const float* mu, const float* sd, void* xn, int out_bf16, int B, int L,
+               int D, cudaStream_t s) {
+  if (B <= 0) return 0;
+  switch (in_dtype * 2 + (out_bf16 ? 1 : 0)) {
+    case 0: return prep_input_t<float, float>(batch, mu, sd, xn, B, L, D, s);
+    case 1: return prep_input_t<float, __nv_bfloat16>(batch, mu, sd, xn, B, L, D, s);
+    case 2: return prep_input_t<__half, float>(batch, mu, sd, xn, B, L, D, s);
+    case 3: return prep_input_t<__half, __nv_bfloat16>(batch, mu, sd, xn, B, L, D, s);
+    case 4: return prep_input_t<__nv_bfloat16, float>(batch, mu, sd, xn, B, L, D, s);
+    case 5: return prep_input_t<__nv_bfloat16, __nv_bfloat16>(batch, mu, sd, xn, B, L, D, s);
+  }
+  set_error("prep_input: unknown input dtype %d", in_dtype);
+  return 1;
+}
+
+// ---------------------------------------------------------------------------------
+// Reconstruction loss.
+//   diff[b,l,d] = recon[b,l,d] - (batch[b,1,l,d] - mu_o[l,d]) / sd_o[l,d]
+// forward : acc[0] += sum diff^2
+// backward: drecon[l,b,d] = 2 diff * gscale / (B L D)   (cast to TOut, layer-major)
+//           db_dec[l,d]  += sum_b of the same (fp32)
+// A CTA owns a strip of 32 consecutive (l, d) columns and walks the batch, so the
+// bias gradient needs one atomic per column per CTA.
+// With aux != null (TopK auxiliary loss) the residual target is err = -diff and
+//   adiff = aux[b,l,d] - err = aux + diff ;  acc[1] += sum adiff^2  (NaNs count as 0)
+//   d recon = 2 diff gs/(BLD) + 2 adiff a_scale gs/(BLD) ; d aux = 2 adiff a_scale gs/(BLD)
+// ---------------------------------------------------------------------------------
+template <class TIn>
+__global__ void loss_fwd_kernel(const float* __restrict__ recon, const float* __restrict__ aux,
+                                const TIn* __restrict__ batch, const float* __restrict__ mu,
+                                const float* __restrict__ sd, float* __restrict__ acc, int B, int L, int D) {
+  const long long total = (long long)B * L * D;
+  float s0 = 0.f, s1 = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(i % ((long long)L * D));
+    const long long b = i / ((long long)L * D);
+    const float y = (to_float<TIn>(batch[(b * 2 + 1) * L * D + c]) - mu[c]) / sd[c];
+    const float diff = recon[i] - y;
+    s0 += diff * diff;
+    if (aux != nullptr) {
+      const float ad = aux[i] + diff;
+      const float sq = ad * ad;
+      s1 += (sq == sq) ? sq : 0.f;
+    }
+  }
+  s0 = warp_sum(s0);
+  s1 = warp_sum(s1);
+  __shared__ float sh[2][32];
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) sh[0][w] = s0, sh[1][w] = s1;
+  __syncthreads();
+  if (w == 0) {
+    const int nw = blockDim.x >> 5;
+    s0 = warp_sum(lane < nw ? sh[0][lane] : 0.f);
+    s1 = warp_sum(lane < nw ? sh[1][lane] : 0.f);
+    if (lane == 0) {
+      atomicAdd(acc + 0, s0);
+      if (aux != nullptr) atomicAdd(acc + 1, s1);
+    }
+  }
+}
+
+int loss_fwd(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu, const float* sd,
+             float* acc, int B, int L, int D, cudaStream_t s) {
+  if (B <= 0) return 0;
+  const long long total = (long long)B * L * D;
+  const int threads = 256;
+  const int blocks = (int)min((total + threads - 1) / threads, (long long)148 * 8);
+  if (in_dtype == 0)
+    loss_fwd_kernel<float><<<blocks, threads, 0, s>>>(recon, aux, (const float*)batch, mu, sd, acc, B, L, D);
+  else if (in_dtype == 1)
+    loss_fwd_kernel<__half><<<blocks, threads, 0, s>>>(recon, aux, (const __half*)batch, mu, sd, acc, B, L, D);
+  else
+    loss_fwd_kernel<__nv_bfloat16>
+        <<<blocks, threads, 0, s>>>(recon, aux, (const __nv_bfloat16*)batch, mu, sd, acc, B, L, D);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+template <class TIn, class TOut>
+__global__ void loss_bwd_kernel(const float* __restrict__ recon, const float* __restrict__ aux,
+                                const TIn* __restrict__ batch, const float* __restrict__ mu,
+                                const float* __restrict__ sd, const float* __restrict__ gscale, float aux_scale,
+                                TOut* __restrict__ drecon, TOut* __restrict__ daux, float* __restrict__ db_dec, int B,
+                                int L, int D, int rows_per_cta) {
+  // blockDim = (32, 8): x walks 32 columns of the flattened (l, d) axis, y walks batch rows
+  const int LD = L * D;
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  const int b0 = blockIdx.y * rows_per_cta;
+  const int b1 = min(B, b0 + rows_per_cta);
+  const float gs = (gscale != nullptr ? *gscale : 1.f) / ((float)B * (float)L * (float)D);
+  float colsum = 0.f;
+  if (c < LD) {
+    const int l = c / D, d = c % D;
+    const float m = mu[c], sdv = sd[c];
+    for (int b = b0 + threadIdx.y; b < b1; b += blockDim.y) {
+      const long long i = (long long)b * LD + c;
+      const float y = (to_float<TIn>(batch[((long long)b * 2 + 1) * LD + c]) - m) / sdv;
+      const float diff = recon[i] - y;
+      float g = 2.f * diff * gs;
+      const long long o = ((long long)l * B + b) * D + d;
+      if (aux != nullptr) {
+        const float ad = aux[i] + diff;
+        float ga = 2.f * ad * aux_scale * gs;
+        if (!(ad * ad == ad * ad)) ga = 0.f;  // nan_to_num on the squared error
+        g += ga;
+        daux[o] = from_float<TOut>(ga);
+        colsum += ga;  // the auxiliary reconstruction carries the decoder bias too
+      }
+      drecon[o] = from_float<TOut>(g);
+      colsum += g;
+    }
+  }
+  __shared__ float sh[8][33];
+  sh[threadIdx.y][threadIdx.x] = colsum;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < LD) {
+    float t = 0.f;
+    for (int j = 0; j < (int)blockDim.y; ++j) t += sh[j][threadIdx.x];
+    if (t != 0.f) atomicAdd(db_dec + c, t);
+  }
+}
+
+int loss_bwd(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu, const float* sd,
+             const float* gscale, float aux_scale, void* drecon, void* daux, int out_bf16, float* db_dec, int B, int L,
+             int D, cudaStream_t s) {
+  if (B <= 0) return 0;
+  const int LD = L * D;
+  const int rows_per_cta = 256;
+  dim3 grid((LD + 31) / 32, (B + rows_per_cta - 1) / rows_per_cta), block(32, 8);
+#define CLT_LB(TI, TO)                                                                                          \
+  loss_bwd_kernel<TI, TO><<<grid, block, 0, s>>>(recon, aux, (const TI*)batch, mu, sd, gscale, aux_scale,       \
+                                                 (TO*)drecon, (TO*)daux, db_dec, B, L, D, rows_per_cta)
+  switch (in_dtype * 2 + (out_bf16 ? 1 : 0)) {
+    case 0: CLT_LB(float, float); break;
+    case 1: CLT_LB(float, __nv_bfloat16); break;
+    case 2: CLT_LB(__half, float); break;
+    case 3: CLT_LB(__half, __nv_bfloat16); break;
+    case 4: CLT_LB(__nv_bfloat16, float); break;
+    case 5: CLT_LB(__nv_bfloat16, __nv_bfloat16); break;
+    default: set_error("loss_bwd: unknown input dtype %d", in_dtype); return 1;
+  }
+#undef CLT_LB
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// Decoder row norms  n[s, f] = sqrt( sum over blocks (t, s) of |W[pair(t,s), f, :]|^2 ).
+// crosslayer = 0: one block per layer (per-layer decoder), n[l, f] = |W[l, f, :]|.
+// One warp per (s, f).
+// ---------------------------------------------------------------------------------
+__global__ void dec_norm_kernel(const float* __restrict__ W, float* __restrict__ out, int L, int F, int D,
+                                int crosslayer) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= L * F) return;
+  const int s = warp / F, f = warp % F;
+  float acc = 0.f;
+  const int t_end = crosslayer ? L : s + 1;
+  for (int t = s; t < t_end; ++t) {
+    const long long p = crosslayer ? (long long)t * (t + 1) / 2 + s : s;
+    const float* row = W + (p * F + f) * D;
+    for (int d = lane; d < D; d += 32) {
+      const float w = row[d];
+      acc = fmaf(w, w, acc);
+    }
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) out[warp] = sqrtf(acc);
+}
+
+int dec_norms(const float* W, float* out, int L, int F, int D, int crosslayer, cudaStream_t s) {
+  const long long warps = (long long)L * F;
+  if (warps <= 0) return 0;
+  const int threads = 256;
+  const long long blocks = (warps * 32 + threads - 1) / threads;
+  dec_norm_kernel<<<(unsigned)blocks, threads, 0, s>>>(W, out, L, F, D, crosslayer);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// rowcoef[s, f] = dnorm[s, f] / n[s, f]  (0 where the norm is 0)
+__global__ void norm_coef_kernel(const float* dnorm, const float* n, float* out, int count) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) out[i] = n[i] > 0.f ? dnorm[i] / n[i] : 0.f;
+}
+int norm_coef(const float* dnorm, const float* n, float* out, int count, cudaStream_t s) {
+  if (count <= 0) return 0;
+  norm_coef_kernel<<<(count + 255) / 256, 256, 0, s>>>(dnorm, n, out, count);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// Dead-feature counters: last_active[fired] = 0; last_active += B; dead = last_active > limit.
+// Clears the fired flags for the next step.
+// ---------------------------------------------------------------------------------
+__global__ void dead_update_kernel(long long* last_active, int* fired, unsigned char* dead, long long B,
+                                   long long limit, int count) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  long long v = fired[i] ? 0 : last_active[i];
+  v += B;
+  last_active[i] = v;
+  fired[i] = 0;
+  if (dead != nullptr) dead[i] = v > limit ? 1 : 0;
+}
+int dead_update(long long* last_active, int* fired, unsigned char* dead, long long B, long long limit, int count,
+                cudaStream_t s) {
+  if (count <= 0) return 0;
+  dead_update_kernel<<<(count + 255) / 256, 256, 0, s>>>(last_active, fired, dead, B, limit, count);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// Fused Adam over one flat fp32 buffer, optionally refreshing the bf16 copy that
+// the tensor-core kernels read.  28 bytes of traffic per parameter (+2 for the copy).
+// ---------------------------------------------------------------------------------
+struct AdamScalars {
+  float lr, beta1, beta2, eps, inv_bc1, inv_sqrt_bc2, weight_decay;
+  int decoupled;
+};
+
+__device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, const AdamScalars& a) {
+  if (a.weight_decay != 0.f) {
+    if (a.decoupled)
+      p *= 1.f - a.lr * a.weight_decay;
+    else
+      g = fmaf(a.weight_decay, p, g);
+  }
+  m = a.beta1 * m + (1.f - a.beta1) * g;
+  v = a.beta2 * v + (1.f - a.beta2) * g * g;
+  const float denom = sqrtf(v) * a.inv_sqrt_bc2 + a.eps;
+  p -= (a.lr * a.inv_bc1) * (m / denom);
+}
+
+__global__ void __launch_bounds__(256) adam_kernel(float* __restrict__ p, const float* __restrict__ g,
+                                                   float* __restrict__ m, float* __restrict__ v,
+                                                   __nv_bfloat16* __restrict__ shadow, long long n, AdamScalars a) {
+  const long long n4 = n / 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += stride) {
+    float4 pp = reinterpret_cast<float4*>(p)[i];
+    const float4 gg = __ldcs(reinterpret_cast<const float4*>(g) + i);
+    float4 mm = reinterpret_cast<float4*>(m)[i];
+    float4 vv = reinterpret_cast<float4*>(v)[i];
+    adam_one(pp.x, gg.x, mm.x, vv.x, a);
+    adam_one(pp.y, gg.y, mm.y, vv.y, a);
+    adam_one(pp.z, gg.z, mm.z, vv.z, a);
+    adam_one(pp.w, gg.w, mm.w, vv.w, a);
+    reinterpret_cast<float4*>(p)[i] = pp;
+    reinterpret_cast<float4*>(m)[i] = mm;
+    reinterpret_cast<float4*>(v)[i] = vv;
+    if (shadow != nullptr) {
+      uint2 s;
+      s.x = pack_bf16x2(pp.x, pp.y);
+      s.y = pack_bf16x2(pp.z, pp.w);
+      reinterpret_cast<uint2*>(shadow)[i] = s;
+    }
+  }
+  // tail (n not a multiple of 4)
+  for (long long i = n4 * 4 + blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride) {
+    float pp = p[i], mm = m[i], vv = v[i];
+    adam_one(pp, g[i], mm, vv, a);
+    p[i] = pp, m[i] = mm, v[i] = vv;
+    if (shadow != nullptr) shadow[i] = __float2bfloat16_rn(pp);
+  }
+}
+
+int adam_step(float* p, const float* g, float* m, float* v, void* shadow_bf16, long long n, float lr, float beta1,
+              float beta2, float eps, float weight_decay, int decoupled, long long step, int num_sms, cudaStream_t s) {
+  if (n <= 0) return 0;
+  CLT_CHECK_ARG(step >= 1, "adam_step: step counts from 1 (got %lld)", step);
+  CLT_CHECK_ARG(((uintptr_t)p | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) % 16 == 0,
+                "adam_step: buffers must be 16-byte aligned");
+  AdamScalars a;
+  a.lr = lr, a.beta1 = beta1, a.beta2 = beta2, a.eps = eps, a.weight_decay = weight_decay, a.decoupled = decoupled;
+  const double bc1 = 1.0 - pow((double)beta1, (double)step);
+  const double bc2 = 1.0 - pow((double)beta2, (double)step);
+  a.inv_bc1 = (float)(1.0 / bc1);
+  a.inv_sqrt_bc2 = (float)(1.0 / sqrt(bc2));
+  const int threads = 256;
+  const long long want = (n / 4 + threads - 1) / threads + 1;
+  const long long cap = (long long)num_sms * 8;
+  adam_kernel<<<(unsigned)(want < cap ? want : cap), threads, 0, s>>>(p, g, m, v, (__nv_bfloat16*)shadow_bf16, n, a);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// fp32 -> bf16 copy (initial shadows, and after a state-dict load)
+__global__ void cast_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += stride)
+    dst[i] = __float2bfloat16_rn(src[i]);
+}
+int cast_bf16(const float* src, void* dst, long long n, cudaStream_t s) {
+  if (n <= 0) return 0;
+  const long long want = (n + 255) / 256;
+  cast_bf16_kernel<<<(unsigned)(want < 148 * 16 ? want : 148 * 16), 256, 0, s>>>(src, (__nv_bfloat16*)dst, n);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// Scalar loss assembly on the device (no host round trip):
+//   loss = acc[0] / (B L D) + lam * acc_sp / B + pal * acc_pre / (B L) + aux_scale * acc[1] / (B L D)
+// terms[0..3] receive the four summands.
+// ---------------------------------------------------------------------------------
+__global__ void finalize_loss_kernel(const float* mse_acc, const float* enc_acc, float* loss, float* terms, float inv_bld,
+                                     float lam_over_b, float pal_over_bl, float aux_scale) {
+  const float mse = mse_acc[0] * inv_bld;
+  const float aux = aux_scale != 0.f ? aux_scale * mse_acc[1] * inv_bld : 0.f;
+  const float pre = enc_acc != nullptr ? pal_over_bl * enc_acc[0] : 0.f;
+  const float sp = enc_acc != nullptr ? lam_over_b * enc_acc[1] : 0.f;
+  terms[0] = mse, terms[1] = sp, terms[2] = pre, terms[3] = aux;
+  loss[0] = mse + sp + pre + aux;
+}
+int finalize_loss(const float* mse_acc, const float* enc_acc, float* loss, float* terms, float inv_bld, float lam_over_b,
+                  float pal_over_bl, float aux_scale, cudaStream_t s) {
+  finalize_loss_kernel<<<1, 1, 0, s>>>(mse_acc, enc_acc, loss, terms, inv_bld, lam_over_b, pal_over_bl, aux_scale);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace clt

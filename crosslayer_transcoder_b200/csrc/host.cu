@@ -1,0 +1,143 @@
+// Host-side plumbing of the library: error string, device queries, TMA tensor-map
+// encoding, and the C entry points that are thin wrappers over elementwise kernels.
+#include <cuda.h>
+#include <stdarg.h>
+#include <string.h>
+
+#include "../../include/clt_b200.h"
+#include "common.cuh"
+#include "gemm_tc.cuh"
+#include "kernels.h"
+
+namespace clt {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+const char* last_error() { return g_error; }
+
+int device_sm_count() {
+  static int cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+namespace tc {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 3-D bf16 tensor map (contiguous axis, rows, stacked matrices) with the 128-byte swizzle.
+// K-major operands use one box of 64 x tile_rows; MN-major operands boxes of 64 x 64.
+int encode_operand_map(CUtensorMap* map, const TcOperand& o, int tile_rows_if_k_major) {
+  EncodeTiledFn fn = encode_fn();
+  CLT_CHECK_ARG(fn != nullptr, "cuTensorMapEncodeTiled is not available from this driver");
+  CLT_CHECK_ARG(((uintptr_t)o.ptr & 15) == 0, "tensor-core operand must be 16-byte aligned");
+  CLT_CHECK_ARG(o.row_stride % 8 == 0 && o.z_stride % 8 == 0,
+                "tensor-core operand strides must be multiples of 8 elements (row %lld, matrix %lld)", o.row_stride,
+                o.z_stride);
+  CLT_CHECK_ARG(o.inner > 0 && o.rows > 0 && o.z_count > 0, "empty tensor-core operand");
+  cuuint64_t dims[3] = {(cuuint64_t)o.inner, (cuuint64_t)o.rows, (cuuint64_t)o.z_count};
+  cuuint64_t strides[2] = {(cuuint64_t)o.row_stride * 2, (cuuint64_t)(o.z_count > 1 ? o.z_stride : o.row_stride * o.rows) * 2};
+  if (strides[1] == 0) strides[1] = strides[0];
+  cuuint32_t box[3] = {64, (cuuint32_t)(o.mn_major ? 64 : tile_rows_if_k_major), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(o.ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  CLT_CHECK_ARG(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code %d (inner %lld rows %lld z %lld)", (int)r,
+                o.inner, o.rows, o.z_count);
+  return 0;
+}
+
+}  // namespace tc
+}  // namespace clt
+
+using namespace clt;
+
+extern "C" {
+
+int clt_version(void) { return 1; }
+const char* clt_last_error(void) { return last_error(); }
+
+int clt_device_check(void) {
+  int dev = 0;
+  CLT_CHECK_CUDA(cudaGetDevice(&dev));
+  int major = 0;
+  CLT_CHECK_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  CLT_CHECK_ARG(major == 10, "this library is built for sm_100a only; device %d has compute capability %d.x", dev,
+                major);
+  return 0;
+}
+
+int clt_prep_input(const void* batch, int in_dtype, const float* mu, const float* sd, void* xn, int bf16, int B, int L,
+                   int D, clt_stream_t stream) {
+  return prep_input(batch, in_dtype, mu, sd, xn, bf16, B, L, D, (cudaStream_t)stream);
+}
+
+int clt_loss_fwd(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu_out,
+                 const float* sd_out, float* acc, int B, int L, int D, clt_stream_t stream) {
+  return loss_fwd(recon, aux, batch, in_dtype, mu_out, sd_out, acc, B, L, D, (cudaStream_t)stream);
+}
+
+int clt_finalize_loss(const float* mse_acc, const float* enc_acc, float* loss, float* terms, float inv_bld,
+                      float lam_over_b, float pal_over_bl, float aux_scale, clt_stream_t stream) {
+  return finalize_loss(mse_acc, enc_acc, loss, terms, inv_bld, lam_over_b, pal_over_bl, aux_scale,
+                       (cudaStream_t)stream);
+}
+
+int clt_loss_bwd(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu_out,
+                 const float* sd_out, const float* gscale, float aux_scale, void* drecon, void* daux, int bf16,
+                 float* db_dec, int B, int L, int D, clt_stream_t stream) {
+  return loss_bwd(recon, aux, batch, in_dtype, mu_out, sd_out, gscale, aux_scale, drecon, daux, bf16, db_dec, B, L, D,
+                  (cudaStream_t)stream);
+}
+
+int clt_dec_norms(const float* W_dec, float* out, int L, int F, int D, int crosslayer, clt_stream_t stream) {
+  return dec_norms(W_dec, out, L, F, D, crosslayer, (cudaStream_t)stream);
+}
+
+int clt_norm_coef(const float* dnorm, const float* norm, float* out, int count, clt_stream_t stream) {
+  return norm_coef(dnorm, norm, out, count, (cudaStream_t)stream);
+}
+
+int clt_dead_update(int64_t* last_active, int* fired, uint8_t* dead, int64_t B, int64_t limit, int count,
+                    clt_stream_t stream) {
+  return dead_update((long long*)last_active, fired, dead, B, limit, count, (cudaStream_t)stream);
+}
+
+int clt_adam_step(float* p, const float* g, float* m, float* v, void* shadow_bf16, int64_t n, float lr, float beta1,
+                  float beta2, float eps, float weight_decay, int decoupled, int64_t step, clt_stream_t stream) {
+  return adam_step(p, g, m, v, shadow_bf16, n, lr, beta1, beta2, eps, weight_decay, decoupled, step,
+                   device_sm_count(), (cudaStream_t)stream);
+}
+
+int clt_cast_bf16(const float* src, void* dst, int64_t n, clt_stream_t stream) {
+  return cast_bf16(src, dst, n, (cudaStream_t)stream);
+}
+
+}  // extern "C"

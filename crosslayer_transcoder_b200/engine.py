@@ -1,0 +1,400 @@
+"""Fused training step of the crosslayer transcoder on B200.
+
+``StepEngine`` runs the reference's ``training_step`` arithmetic
+(crosslayer_transcoder/model/clt_lightning.py:290-312, 420-475, 519-567) as a
+sequence of calls into ``libclt_b200.so``: forward kernels inside
+``StepEngine.forward``, backward kernels inside the autograd node it returns, so
+that the caller's ``loss.backward()`` / ``optimizer.step()`` work unchanged.
+
+All parameters of the module live in one flat fp32 buffer (the ``nn.Parameter``s
+are views into it), with a flat gradient buffer and, in bf16 mode, a flat bf16 copy
+that the tensor-core kernels read and the fused Adam step refreshes.  PyTorch is used
+for allocation, streams and autograd plumbing only; there is no eager fallback.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from . import _lib
+from ._lib import DTYPE_CODE, CltError, lib, stream_ptr
+from .model.clt import CrosslayerDecoder
+
+_ALIGN = 64  # elements; keeps every segment 256-byte aligned in fp32 and 128-byte aligned in bf16
+
+
+def _round_up(n: int, a: int = _ALIGN) -> int:
+    return (n + a - 1) // a * a
+
+
+class FlatParams:
+    """One flat fp32 buffer holding every parameter of a module, plus matching flat
+    buffers for gradients, Adam moments and the bf16 operand copy."""
+
+    def __init__(self, module: torch.nn.Module, device: torch.device, want_bf16: bool):
+        self.params: List[torch.nn.Parameter] = [p for p in module.parameters()]
+        if not self.params:
+            raise CltError("module has no parameters")
+        for p in self.params:
+            if p.dtype != torch.float32:
+                raise CltError(f"parameters must be fp32 master weights (got {p.dtype})")
+        self.offsets: Dict[int, int] = {}
+        off = 0
+        for p in self.params:
+            self.offsets[id(p)] = off
+            off += _round_up(p.numel())
+        self.numel = off
+        self.device = device
+        self.flat = torch.zeros(off, dtype=torch.float32, device=device)
+        self.grad = torch.zeros(off, dtype=torch.float32, device=device)
+        self.shadow: Optional[torch.Tensor] = None
+        self.exp_avg: Optional[torch.Tensor] = None
+        self.exp_avg_sq: Optional[torch.Tensor] = None
+        with torch.no_grad():
+            for p in self.params:
+                view = self.view_of(p, self.flat)
+                view.copy_(p.data)
+                p.data = view
+        self._shadow_version = None
+        if want_bf16:
+            self.ensure_shadow()
+
+    def view_of(self, p: torch.nn.Parameter, buf: torch.Tensor) -> torch.Tensor:
+        o = self.offsets[id(p)]
+        return buf[o:o + p.numel()].view(p.shape)
+
+    def is_packed(self) -> bool:
+        base = self.flat.data_ptr()
+        return all(p.data_ptr() == base + 4 * self.offsets[id(p)] for p in self.params)
+
+    def _version(self):
+        return tuple(p._version for p in self.params)
+
+    def ensure_shadow(self):
+        """(Re)build the bf16 copy when parameters were changed by anything but the fused Adam step."""
+        v = self._version()
+        if self.shadow is None:
+            self.shadow = torch.empty(self.numel, dtype=torch.bfloat16, device=self.device)
+            self._shadow_version = None
+        if self._shadow_version != v:
+            lib().call("clt_cast_bf16", self.flat, self.shadow, self.numel, stream_ptr())
+            self._shadow_version = v
+
+    def ensure_moments(self):
+        if self.exp_avg is None:
+            self.exp_avg = torch.zeros_like(self.flat)
+            self.exp_avg_sq = torch.zeros_like(self.flat)
+
+
+class _Workspace:
+    """Per-batch-size activation buffers, reused between steps."""
+
+    def __init__(self):
+        self.key = None
+        self.buf: Dict[str, torch.Tensor] = {}
+
+    def get(self, name, shape, dtype, device, zero=False):
+        t = self.buf.get(name)
+        if t is None or t.shape != torch.Size(shape) or t.dtype != dtype or t.device != device:
+            t = (torch.zeros if zero else torch.empty)(shape, dtype=dtype, device=device)
+            self.buf[name] = t
+        return t
+
+
+class StepEngine:
+    def __init__(self, module):
+        self.module = module                      # a CrossLayerTranscoderModule
+        self.flat: Optional[FlatParams] = None
+        self.ws = _Workspace()
+        self.status: Optional[torch.Tensor] = None
+        self.fired: Optional[torch.Tensor] = None
+        self.launches = 0                         # kernels launched by this engine (for reporting)
+        self.last_terms: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ setup
+    def _call(self, name, *args):
+        lib().call(name, *args)
+        self.launches += 1
+
+    def _precision(self, batch) -> bool:
+        """True for the bf16 tensor-core path.  ``module.precision`` forces it ("bf16" / "fp32");
+        "auto" follows the autocast state the trainer set up (bf16-mixed -> bf16)."""
+        mode = getattr(self.module, "precision", "auto")
+        if mode == "bf16":
+            return True
+        if mode == "fp32":
+            return False
+        if torch.is_autocast_enabled("cuda"):
+            dt = torch.get_autocast_dtype("cuda")
+            if dt == torch.bfloat16:
+                return True
+            raise NotImplementedError(f"autocast dtype {dt} is not supported by the fused step (bf16 or fp32 only)")
+        return False
+
+    def prepare(self, device: torch.device, bf16: bool):
+        lib().check_device()
+        if self.flat is None or self.flat.device != device or not self.flat.is_packed():
+            old = self.flat
+            self.flat = FlatParams(self.module, device, bf16)
+            if old is not None and old.exp_avg is not None and old.numel == self.flat.numel and old.device == device:
+                self.flat.exp_avg, self.flat.exp_avg_sq = old.exp_avg, old.exp_avg_sq
+        if bf16:
+            self.flat.ensure_shadow()
+        if self.status is None or self.status.device != device:
+            self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        enc = self.module.model.encoder
+        if self.fired is None or self.fired.device != device:
+            self.fired = torch.zeros(enc.n_layers, enc.d_features, dtype=torch.int32, device=device)
+
+    def check_status(self, where=""):
+        if self.status is not None:
+            _lib.check_status(self.status, where)
+
+    # ------------------------------------------------------------------ helpers
+    def _operand(self, p: torch.nn.Parameter, bf16: bool) -> torch.Tensor:
+        """The tensor a contraction reads for parameter ``p``: its bf16 copy or the fp32 master."""
+        return self.flat.view_of(p, self.flat.shadow) if bf16 else p.data
+
+    def _dec_flat(self, bf16: bool):
+        """(operand buffer [P,F,D], fp32 master [P,F,D], gradient [P,F,D]) of the decoder blocks;
+        they are adjacent in the flat buffer in block order."""
+        dec = self.module.model.decoder
+        blocks = dec.blocks()
+        F, D = dec.d_features, dec.d_acts
+        o0 = self.flat.offsets[id(blocks[0])]
+        n = 0
+        for w in blocks:
+            if self.flat.offsets[id(w)] != o0 + n:
+                raise CltError("decoder blocks are not adjacent in the flat parameter buffer")
+            n += _round_up(w.numel())
+            if w.numel() % _ALIGN:
+                raise CltError("decoder block size must be a multiple of 64 elements")
+        P = n // (F * D)
+        sl = slice(o0, o0 + n)
+        op = (self.flat.shadow if bf16 else self.flat.flat)[sl].view(P, F, D)
+        return op, self.flat.flat[sl].view(P, F, D), self.flat.grad[sl].view(P, F, D)
+
+    def _stats(self):
+        m = self.module.model
+        ins, outs = m.input_standardizer, m.output_standardizer
+        if ins is None or outs is None:
+            raise CltError("the fused step needs both standardizers")
+        if not (ins.is_initialized and outs.is_initialized):
+            raise ValueError("Standardizer not initialized")
+        f = lambda t: t.detach().float().contiguous()
+        return f(ins.mean), f(ins.std), f(outs.mean), f(outs.std)
+
+    def _bandwidth(self, nl) -> float:
+        """JumpReLU bandwidth as a host number, read from the device buffer once."""
+        if getattr(self, "_bw_cache", None) is None:
+            self._bw_cache = float(nl.bandwidth)
+        return self._bw_cache
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, batch: torch.Tensor, hyper: dict) -> torch.Tensor:
+        """Run the forward half of the step on ``batch`` ``[B, 2, L, D]`` and return the scalar
+        loss, connected to the parameters through an autograd node that runs the backward half."""
+        if not batch.is_cuda:
+            raise CltError("the fused training step runs on CUDA tensors only (no CPU fallback)")
+        if batch.dtype not in DTYPE_CODE:
+            raise CltError(f"unsupported batch dtype {batch.dtype}")
+        batch = batch.contiguous()
+        bf16 = self._precision(batch)
+        self.prepare(batch.device, bf16)
+        kind = hyper["kind"]
+        if kind in ("jumprelu", "relu"):
+            ctx = self._forward_dense(batch, hyper, bf16)
+        else:
+            raise NotImplementedError(f"nonlinearity kind {kind!r}")
+        self.last_terms = ctx["out"][1:5]          # mse, sparsity, pre-activation, auxiliary summands
+        params = self.flat.params
+        return _StepFunction.apply(self, ctx, *params)
+
+    def _forward_dense(self, batch, h, bf16):
+        mod = self.module
+        model = mod.model
+        enc, dec, nl = model.encoder, model.decoder, model.nonlinearity
+        B, L, D, F = batch.shape[0], enc.n_layers, enc.d_acts, enc.d_features
+        dev = batch.device
+        T = torch.bfloat16 if bf16 else torch.float32
+        s = stream_ptr()
+        crosslayer = 1 if isinstance(dec, CrosslayerDecoder) else 0
+        mu_i, sd_i, mu_o, sd_o = self._stats()
+        ws = self.ws
+        xn = ws.get("xn", (L, B, D), T, dev)
+        z = ws.get("z", (L, B, F), T, dev)
+        feat = ws.get("feat", (L, B, F), T, dev)
+        recon = ws.get("recon", (B, L, D), torch.float32, dev)
+        acc = ws.get("acc", (8,), torch.float32, dev)
+        out = torch.empty(5, dtype=torch.float32, device=dev)       # loss + 4 terms
+        acc.zero_()
+        in_code = DTYPE_CODE[batch.dtype]
+        self._call("clt_prep_input", batch, in_code, mu_i, sd_i, xn, int(bf16), B, L, D, s)
+        theta = nl.theta.data if h["kind"] == "jumprelu" else None
+        lam = float(h.get("lambda_sparsity", 0.0))
+        norm = None
+        W_op, W_master, _ = self._dec_flat(bf16)
+        if lam != 0.0:
+            norm = ws.get("dec_norm", (L, F), torch.float32, dev)
+            self._call("clt_dec_norms", W_master, norm, L, F, D, crosslayer, s)
+        self._call("clt_encoder_fwd_act", xn, self._operand(enc.W, bf16), enc.b.data, theta, norm, z, feat,
+                   self.fired, acc[0:2], float(h.get("c_sparsity", 1.0)), int(h.get("use_tanh", True)), B, L, D, F,
+                   int(bf16), self.status, s)
+        self._call("clt_decoder_dense_fwd", feat, W_op, dec.b.data, recon, B, L, D, F, crosslayer, int(bf16),
+                   self.status, s)
+        self._call("clt_loss_fwd", recon, None, batch, in_code, mu_o, sd_o, acc[2:4], B, L, D, s)
+        pal = float(h.get("pre_actv_loss", 0.0))
+        self._call("clt_finalize_loss", acc[2:4], acc[0:2], out[0:1], out[1:5], 1.0 / (B * L * D), lam / B,
+                   pal / (B * L), 0.0, s)
+        self._call("clt_dead_update", mod.last_active, self.fired, None, B, int(mod.tokens_till_dead), L * F, s)
+        return dict(kind=h["kind"], bf16=bf16, batch=batch, B=B, L=L, D=D, F=F, crosslayer=crosslayer, lam=lam,
+                    pal=pal, c=float(h.get("c_sparsity", 1.0)), use_tanh=int(h.get("use_tanh", True)),
+                    bandwidth=self._bandwidth(nl) if h["kind"] == "jumprelu" else 1.0, out=out,
+                    stats=(mu_i, sd_i, mu_o, sd_o), norm=norm, in_code=in_code)
+
+    # ------------------------------------------------------------------ backward
+    def backward(self, ctx: dict, gscale: torch.Tensor):
+        if ctx["kind"] in ("jumprelu", "relu"):
+            self._backward_dense(ctx, gscale)
+        else:
+            raise NotImplementedError(ctx["kind"])
+
+    def _zero_small_grads(self):
+        """Gradients accumulated with atomics start from zero; contraction outputs are overwritten."""
+        model = self.module.model
+        small = [model.encoder.b, model.decoder.b]
+        if hasattr(model.nonlinearity, "theta"):
+            small.append(model.nonlinearity.theta)
+        for p in small:
+            self.flat.view_of(p, self.flat.grad).zero_()
+
+    def _backward_dense(self, c, gscale):
+        model = self.module.model
+        enc, dec, nl = model.encoder, model.decoder, model.nonlinearity
+        B, L, D, F, bf16 = c["B"], c["L"], c["D"], c["F"], c["bf16"]
+        dev = c["batch"].device
+        T = torch.bfloat16 if bf16 else torch.float32
+        s = stream_ptr()
+        ws = self.ws
+        xn, z, feat, recon = ws.buf["xn"], ws.buf["z"], ws.buf["feat"], ws.buf["recon"]
+        drecon = ws.get("drecon", (L, B, D), T, dev)
+        dpre = ws.get("dpre", (L, B, F), T, dev)
+        _, _, mu_o, sd_o = c["stats"]
+        g = self.flat.grad
+        gview = lambda p: self.flat.view_of(p, g)
+        self._zero_small_grads()
+        gs = gscale.detach().to(torch.float32).reshape(1).contiguous()
+        self._call("clt_loss_bwd", recon, None, c["batch"], c["in_code"], mu_o, sd_o, gs, 0.0, drecon, None,
+                   int(bf16), gview(dec.b), B, L, D, s)
+        W_op, W_master, dW_dec = self._dec_flat(bf16)
+        theta = nl.theta.data if c["kind"] == "jumprelu" else None
+        dtheta = gview(nl.theta) if c["kind"] == "jumprelu" else None
+        norm = c["norm"]
+        dnorm = None
+        if norm is not None:
+            dnorm = ws.get("dnorm", (L, F), torch.float32, dev)
+            dnorm.zero_()
+        self._call("clt_decoder_dense_bwd_dfeat", drecon, W_op, z, enc.b.data, theta, norm, dpre, dtheta,
+                   gview(enc.b), dnorm, c["bandwidth"], c["lam"] / B, c["c"], c["pal"] / (B * L), c["use_tanh"], gs,
+                   B, L, D, F, c["crosslayer"], int(bf16), self.status, s)
+        rowcoef = None
+        if norm is not None:
+            rowcoef = ws.get("rowcoef", (L, F), torch.float32, dev)
+            self._call("clt_norm_coef", dnorm, norm, rowcoef, L * F, s)
+        self._call("clt_decoder_dense_bwd_dw", feat, drecon, dW_dec, rowcoef, W_master if rowcoef is not None else None,
+                   B, L, D, F, c["crosslayer"], int(bf16), self.status, s)
+        self._call("clt_encoder_dense_bwd_dw", xn, dpre, gview(enc.W), B, L, D, F, int(bf16), self.status, s)
+
+
+class _StepFunction(torch.autograd.Function):
+    """Autograd node of the fused step: forward already ran; backward launches the gradient
+    kernels and hands each parameter its slice of the flat gradient buffer."""
+
+    @staticmethod
+    def forward(ctx, engine: StepEngine, step_ctx: dict, *params):
+        ctx.engine, ctx.step_ctx = engine, step_ctx
+        ctx.n = len(params)
+        return step_ctx["out"][0].clone()
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        eng: StepEngine = ctx.engine
+        eng.backward(ctx.step_ctx, grad_out)
+        grads = []
+        for p in eng.flat.params:
+            gv = eng.flat.view_of(p, eng.flat.grad)
+            # a parameter that already holds a gradient would be accumulated into in place;
+            # hand it a copy so the flat buffer can be reused by the next step
+            grads.append(gv.clone() if p.grad is not None else gv)
+        return (None, None, *grads)
+
+
+class FusedAdam(torch.optim.Optimizer):
+    """Adam / AdamW with the update of ``torch.optim.Adam`` (reference
+    clt_lightning.py:339-352), run as one kernel over the engine's flat parameter
+    buffer; the same kernel refreshes the bf16 operand copy."""
+
+    def __init__(self, params, engine: StepEngine, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0,
+                 decoupled=False):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, decoupled=decoupled))
+        self.engine = engine
+        self._step = 0
+
+    def _flat_ready(self, group) -> bool:
+        fp = self.engine.flat
+        if fp is None or not fp.is_packed() or len(group["params"]) != len(fp.params):
+            return False
+        base = fp.grad.data_ptr()
+        for p in group["params"]:
+            if id(p) not in fp.offsets or p.grad is None or p.grad.data_ptr() != base + 4 * fp.offsets[id(p)]:
+                return False
+        return True
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        self._step += 1
+        L = lib()
+        s = stream_ptr()
+        for group in self.param_groups:
+            b1, b2 = group["betas"]
+            args = (float(group["lr"]), float(b1), float(b2), float(group["eps"]), float(group["weight_decay"]),
+                    int(group["decoupled"]), self._step, s)
+            if len(self.param_groups) == 1 and self._flat_ready(group):
+                fp = self.engine.flat
+                fp.ensure_moments()
+                L.call("clt_adam_step", fp.flat, fp.grad, fp.exp_avg, fp.exp_avg_sq, fp.shadow, fp.numel, *args)
+                self.engine.launches += 1
+                for p in group["params"]:
+                    st = self.state[p]
+                    if "exp_avg" not in st:
+                        st["exp_avg"] = fp.view_of(p, fp.exp_avg)
+                        st["exp_avg_sq"] = fp.view_of(p, fp.exp_avg_sq)
+                    st["step"] = self._step
+                continue
+            # general path: one launch per parameter (still the CUDA kernel)
+            fp = self.engine.flat
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                if not p.is_cuda:
+                    raise CltError("FusedAdam updates CUDA parameters only")
+                st = self.state[p]
+                if "exp_avg" not in st:
+                    if fp is not None and id(p) in fp.offsets and fp.is_packed():
+                        fp.ensure_moments()
+                        st["exp_avg"], st["exp_avg_sq"] = fp.view_of(p, fp.exp_avg), fp.view_of(p, fp.exp_avg_sq)
+                    else:
+                        st["exp_avg"], st["exp_avg_sq"] = torch.zeros_like(p), torch.zeros_like(p)
+                st["step"] = self._step
+                shadow = None
+                if fp is not None and fp.shadow is not None and id(p) in fp.offsets and fp.is_packed():
+                    shadow = fp.view_of(p, fp.shadow)
+                gr = p.grad.contiguous()
+                L.call("clt_adam_step", p.data, gr, st["exp_avg"], st["exp_avg_sq"], shadow, p.numel(), *args)
+                self.engine.launches += 1
+        return loss

@@ -1,0 +1,167 @@
+"""Training modules with the reference's constructor arguments, buffers and logged
+scalar names (crosslayer_transcoder/model/clt_lightning.py:29-567).  ``training_step``
+hands the batch to the fused CUDA step of ``crosslayer_transcoder_b200.engine`` and
+returns its scalar loss; ``loss.backward()`` then runs the fused backward kernels and
+``configure_optimizers()`` returns the fused Adam.  Logging-only parts of the reference
+(the W&B metric dump every ``log_metrics_every`` steps, the replacement-model
+validation) are not part of the training step and are left to the caller.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..engine import FusedAdam, StepEngine
+from .clt import CrossLayerTranscoder
+from .jumprelu import JumpReLU, ReLU
+from .topk import BatchTopK, PerLayerBatchTopK, PerLayerTopK
+
+try:  # Lightning is optional: with it the classes are real LightningModules
+    import lightning as L
+
+    _Base = L.LightningModule
+except Exception:  # pragma: no cover - depends on the environment
+
+    class _Trainer:
+        max_steps = 1
+        num_devices = 1
+
+    class _Base(torch.nn.Module):
+        """Stand-in with the few LightningModule members the step uses."""
+
+        def __init__(self, *args, **kwargs):
+            super().__init__()
+            self.trainer = _Trainer()
+            self.global_step = 0
+            self.logged = {}
+
+        def log(self, name, value, *args, **kwargs):
+            self.logged[name] = value
+
+        def save_hyperparameters(self, *args, **kwargs):
+            pass
+
+
+class CrossLayerTranscoderModule(_Base):
+    def __init__(self, model: CrossLayerTranscoder, replacement_model=None, dead_features=None,
+                 learning_rate: float = 1e-3, compile: bool = False, warmup_steps: int = 0, lr_decay_step: int = 0,
+                 lr_decay_factor: float = 1.0, compute_dead_features: bool = False,
+                 compute_dead_features_every: int = 100, tokens_till_dead: int = 1_000_000, optimizer: str = "adam",
+                 beta1: Optional[float] = None, beta2: Optional[float] = None, log_metrics_every: int = 50,
+                 *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.save_hyperparameters(ignore=["model", "replacement_model", "dead_features"])
+        self.model, self.replacement_model, self.dead_features = model, replacement_model, dead_features
+        self.learning_rate, self.compile, self.tokens_till_dead = learning_rate, compile, tokens_till_dead
+        self.warmup_steps, self.lr_decay_step, self.lr_decay_factor = warmup_steps, lr_decay_step, lr_decay_factor
+        self.compute_dead_features = compute_dead_features
+        self.compute_dead_features_every = compute_dead_features_every
+        self.optimizer, self.beta1, self.beta2 = optimizer, beta1, beta2
+        self.log_metrics_every = log_metrics_every
+        assert model.encoder.n_layers == model.decoder.n_layers, \
+            "Encoder and decoder must have the same number of layers"
+        self.register_buffer("last_active",
+                             torch.zeros(model.encoder.n_layers, model.encoder.d_features, dtype=torch.long))
+        #: "auto" follows torch.autocast (bf16-mixed -> tensor cores); "bf16" / "fp32" force a path
+        self.precision = "auto"
+        self._engine = StepEngine(self)
+
+    # ---- nonlinearity -> step kind -----------------------------------------------------
+    def _kind(self) -> str:
+        nl = self.model.nonlinearity
+        if isinstance(nl, JumpReLU):
+            return "jumprelu"
+        if isinstance(nl, (ReLU, torch.nn.ReLU)):
+            return "relu"
+        if isinstance(nl, PerLayerTopK):
+            return "topk"
+        if isinstance(nl, BatchTopK):
+            return "batchtopk"
+        if isinstance(nl, PerLayerBatchTopK):
+            return "perlayer_batchtopk"
+        raise NotImplementedError(f"nonlinearity {type(nl).__name__} has no fused training step")
+
+    def _hyper(self) -> dict:
+        return {"kind": self._kind()}
+
+    def forward(self, acts_norm):
+        return self.model(acts_norm)
+
+    def configure_model(self):
+        """Nothing to shard or compile here: feature-axis sharding is set up by constructing the
+        module on each rank with its own feature slice (see ``parallel.py``)."""
+
+    def _run_step(self, batch, batch_idx):
+        if batch_idx == 0:
+            self.model.initialize_standardizers(batch)
+        loss = self._engine.forward(batch, self._hyper())
+        terms = self._engine.last_terms
+        self.log("training/loss", loss.detach())
+        return loss, terms
+
+    def training_step(self, batch, batch_idx):
+        loss, _ = self._run_step(batch, batch_idx)
+        return loss
+
+    def validation_step(self, batch, batch_idx):
+        pass
+
+    def configure_optimizers(self):
+        b1 = 0.9 if self.beta1 is None else self.beta1
+        b2 = 0.999 if self.beta2 is None else self.beta2
+        self.beta1, self.beta2 = b1, b2
+        if self.optimizer not in ("adam", "adamw"):
+            raise ValueError(f"Optimizer {self.optimizer} not supported")
+        decoupled = self.optimizer == "adamw"
+        opt = FusedAdam(self.parameters(), self._engine, lr=self.learning_rate, betas=(b1, b2),
+                        weight_decay=1e-2 if decoupled else 0.0, decoupled=decoupled)
+        if self.warmup_steps > 0:
+            sched = torch.optim.lr_scheduler.LinearLR(opt, start_factor=1e-7, end_factor=1.0,
+                                                      total_iters=self.warmup_steps)
+            return {"optimizer": opt, "lr_scheduler": {"scheduler": sched, "interval": "step", "frequency": 1,
+                                                       "name": "warmup"}}
+        if self.lr_decay_step > 0:
+            sched = torch.optim.lr_scheduler.MultiStepLR(opt, milestones=[self.lr_decay_step],
+                                                         gamma=self.lr_decay_factor)
+            return {"optimizer": opt, "lr_scheduler": {"scheduler": sched, "interval": "step", "frequency": 1,
+                                                       "name": "step_decay"}}
+        return opt
+
+
+class JumpReLUCrossLayerTranscoderModule(CrossLayerTranscoderModule):
+    def __init__(self, lambda_sparsity: float = 0.0002, c_sparsity: float = 0.1, use_tanh: bool = True,
+                 pre_actv_loss: float = 0.0, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self._lambda, self.c, self.use_tanh, self.pre_actv_loss = lambda_sparsity, c_sparsity, use_tanh, pre_actv_loss
+
+    def current_sparsity_penalty(self):
+        """Linear ramp lambda * global_step / max_steps (reference clt_lightning.py:411-418)."""
+        cur = self._lambda * (self.global_step / self.trainer.max_steps)
+        self.log("training/sparsity_penalty", cur)
+        return cur
+
+    def _hyper(self) -> dict:
+        return {"kind": self._kind(), "lambda_sparsity": self.current_sparsity_penalty(), "c_sparsity": self.c,
+                "use_tanh": self.use_tanh, "pre_actv_loss": self.pre_actv_loss, "with_penalties": True}
+
+    def training_step(self, batch, batch_idx):
+        loss, terms = self._run_step(batch, batch_idx)
+        self.log("training/sparsity_loss", terms[1])
+        self.log("training/pre_actv_loss", terms[2])
+        return loss
+
+
+class TopKCrossLayerTranscoderModule(CrossLayerTranscoderModule):
+    def __init__(self, topk_aux: torch.nn.Module, tokens_till_dead: int = 100_000, aux_loss_scale: float = 1 / 32,
+                 *args, **kwargs):
+        super().__init__(*args, **kwargs)
+        self.tokens_till_dead, self.topk_aux, self.aux_loss_scale = tokens_till_dead, topk_aux, aux_loss_scale
+
+    def _hyper(self) -> dict:
+        return {"kind": self._kind(), "k_aux": int(self.topk_aux.k), "aux_loss_scale": float(self.aux_loss_scale)}
+
+    def training_step(self, batch, batch_idx):
+        loss, terms = self._run_step(batch, batch_idx)
+        self.log("training/aux_loss", terms[3])
+        return loss

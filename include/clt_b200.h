@@ -1,0 +1,127 @@
+/* C ABI of the B200 crosslayer-transcoder training-step library (libclt_b200.so).
+ *
+ * The reference project is pure Python and has no native interface; each entry
+ * point below names the reference code it replaces (file:line, paths relative to
+ * the reference project root).  All pointers are device pointers unless stated
+ * otherwise; the library allocates and frees nothing, keeps no state between
+ * calls except per-function launch attributes, and launches on the stream it is
+ * given.  Every function returns 0 when its kernels were launched, non-zero when
+ * an argument was rejected or a launch failed (then clt_last_error() holds the
+ * reason).  Kernels never trap: a kernel that gives up on a bounded wait or meets
+ * an out-of-range index writes a code to the `status` word passed by the caller
+ * (one int in device memory, zero before the call) and returns.
+ *
+ * Shapes:  B tokens, L layers, D = d_acts, F = d_features held by this rank,
+ *          P = number of decoder blocks (L (L+1)/2 crosslayer, L per-layer).
+ * `bf16`:  0 = fp32 operands, CUDA-core contraction; 1 = bf16 operands, tcgen05
+ *          tensor-core contraction with fp32 accumulation.  T below is float or
+ *          __nv_bfloat16 accordingly.
+ * Layouts: xn, drecon [L, B, D];  z, feat, dpre [L, B, F];  recon [B, L, D] fp32;
+ *          W_enc [L, D, F];  W_dec flat [P, F, D], block (source s -> target t) at
+ *          p = t (t+1)/2 + s (crosslayer) or p = layer (per-layer).
+ * in_dtype of the raw batch [B, 2, L, D]: 0 = fp32, 1 = fp16, 2 = bf16.
+ */
+#ifndef CLT_B200_H
+#define CLT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* clt_stream_t; /* a cudaStream_t */
+
+int clt_version(void);
+const char* clt_last_error(void);
+/* 0 when the current device is compute capability 10.x; non-zero (with an error string) otherwise. */
+int clt_device_check(void);
+
+/* DimensionwiseInputStandardizer.forward (crosslayer_transcoder/model/standardize.py:49-59):
+ * xn[l,b,d] = (batch[b,0,l,d] - mu[l,d]) / sd[l,d], cast to T, layer-major. */
+int clt_prep_input(const void* batch, int in_dtype, const float* mu, const float* sd, void* xn, int bf16,
+                   int B, int L, int D, clt_stream_t stream);
+
+/* Encoder.forward + JumpReLU / ReLU forward (crosslayer_transcoder/model/clt.py:157-165,
+ * crosslayer_transcoder/model/jumprelu.py:21-22, 33-38), plus the sums of the pre-activation
+ * loss and sparsity penalty (crosslayer_transcoder/model/clt_lightning.py:450-465) and the
+ * per-feature "fired" flags of update_dead_features (clt_lightning.py:284).
+ * z = round_T(xn W_enc), pre = z + b_enc, feat = pre [pre > theta and pre > 0].
+ * theta == NULL selects ReLU; dec_norm == NULL skips the sparsity sum; fired may be NULL.
+ * loss_acc[0] += sum relu(-pre); loss_acc[1] += sum tanh(feat dec_norm c) (or the product). */
+int clt_encoder_fwd_act(const void* xn, const void* W_enc, const float* b_enc, const float* theta,
+                        const float* dec_norm, void* z_out, void* feat_out, int* fired, float* loss_acc,
+                        float c_sparsity, int use_tanh, int B, int L, int D, int F, int bf16, int* status,
+                        clt_stream_t stream);
+
+/* Encoder.forward alone (clt.py:157-162), for the TopK / BatchTopK selections that follow:
+ * z = round_T(xn W_enc), no bias. */
+int clt_encoder_fwd_store(const void* xn, const void* W_enc, void* z_out, int B, int L, int D, int F, int bf16,
+                          int* status, clt_stream_t stream);
+
+/* CrosslayerDecoder.forward (clt.py:334-343) / Decoder.forward (clt.py:241-248):
+ * recon[b,t,:] = sum_{s<=t} feat[s,b,:] W_dec[pair(t,s)] (+ b_dec[t]); b_dec may be NULL. */
+int clt_decoder_dense_fwd(const void* feat, const void* W_dec, const float* b_dec, float* recon, int B, int L,
+                          int D, int F, int crosslayer, int bf16, int* status, clt_stream_t stream);
+
+/* Reconstruction MSE (clt_lightning.py:303-304) and, with aux != NULL, the TopK auxiliary
+ * loss (clt_lightning.py:548-551).  acc[0] += sum diff^2, acc[1] += sum (aux + diff)^2. */
+int clt_loss_fwd(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu_out,
+                 const float* sd_out, float* acc, int B, int L, int D, clt_stream_t stream);
+
+/* loss = acc terms scaled as the reference's means (clt_lightning.py:304, 459-468, 553);
+ * terms[0..3] = mse, sparsity, pre-activation, auxiliary summands. enc_acc may be NULL. */
+int clt_finalize_loss(const float* mse_acc, const float* enc_acc, float* loss, float* terms, float inv_bld,
+                      float lam_over_b, float pal_over_bl, float aux_scale, clt_stream_t stream);
+
+/* Backward of the losses w.r.t. the reconstruction(s) (what autograd derives from
+ * clt_lightning.py:303-304, 548-553): drecon (and daux) [L,B,D] in T, db_dec[l,d] += column sums.
+ * gscale: device scalar dLoss (NULL = 1). */
+int clt_loss_bwd(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu_out,
+                 const float* sd_out, const float* gscale, float aux_scale, void* drecon, void* daux, int bf16,
+                 float* db_dec, int B, int L, int D, clt_stream_t stream);
+
+/* Backward of the decoder w.r.t. the features fused with the JumpReLU / ReLU backward
+ * (jumprelu.py:41-48), the sparsity-penalty and pre-activation-loss gradients
+ * (clt_lightning.py:450-465):  dfeat[s] = sum_{t>=s} drecon[t] W_dec[pair(t,s)]^T, then
+ * dpre, dtheta, db_enc, d dec_norm as documented in csrc/epilogues.cuh.
+ * lam = lambda / B, pal = pre_actv_loss / (B L). */
+int clt_decoder_dense_bwd_dfeat(const void* drecon, const void* W_dec, const void* z_in, const float* b_enc,
+                                const float* theta, const float* dec_norm, void* dpre_out, float* dtheta,
+                                float* dbenc, float* dnorm, float bandwidth, float lam, float c_sparsity,
+                                float pal, int use_tanh, const float* gscale, int B, int L, int D, int F,
+                                int crosslayer, int bf16, int* status, clt_stream_t stream);
+
+/* Decoder weight gradient: dW_dec[pair(t,s)] = feat[s]^T drecon[t] (+ rowcoef[s,f] W_dec[p,f,:],
+ * the gradient through the decoder norms of clt_lightning.py:438-448); fp32 output [P,F,D]. */
+int clt_decoder_dense_bwd_dw(const void* feat, const void* drecon, float* dW, const float* rowcoef,
+                             const float* W_master, int B, int L, int D, int F, int crosslayer, int bf16,
+                             int* status, clt_stream_t stream);
+
+/* Encoder weight gradient: dW_enc[l] = xn[l]^T dpre[l]; fp32 output [L,D,F]. */
+int clt_encoder_dense_bwd_dw(const void* xn, const void* dpre, float* dW, int B, int L, int D, int F, int bf16,
+                             int* status, clt_stream_t stream);
+
+/* Decoder norms of the sparsity penalty (clt_lightning.py:438-448): out[s,f]. */
+int clt_dec_norms(const float* W_dec, float* out, int L, int F, int D, int crosslayer, clt_stream_t stream);
+/* out = dnorm / norm (0 where norm == 0) */
+int clt_norm_coef(const float* dnorm, const float* norm, float* out, int count, clt_stream_t stream);
+
+/* update_dead_features (clt_lightning.py:282-288): last_active[fired]=0; last_active+=B;
+ * dead = last_active > limit (dead may be NULL). Clears fired. */
+int clt_dead_update(int64_t* last_active, int* fired, uint8_t* dead, int64_t B, int64_t limit, int count,
+                    clt_stream_t stream);
+
+/* torch.optim.Adam / AdamW step (clt_lightning.py:339-352) over one flat fp32 buffer; `step`
+ * counts from 1.  shadow_bf16 (may be NULL) receives the bf16 copy of the new parameters. */
+int clt_adam_step(float* p, const float* g, float* m, float* v, void* shadow_bf16, int64_t n, float lr,
+                  float beta1, float beta2, float eps, float weight_decay, int decoupled, int64_t step,
+                  clt_stream_t stream);
+
+/* fp32 -> bf16 copy of a parameter buffer (the tensor-core operands). */
+int clt_cast_bf16(const float* src, void* dst, int64_t n, clt_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CLT_B200_H */

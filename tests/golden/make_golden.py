@@ -22,13 +22,13 @@ ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
 
 from crosslayer_transcoder_b200 import synthetic  # noqa: E402
-from oracle import ref_import  # noqa: E402
+from oracle import ref_import  # noqa: E402  (only main() needs the reference)
 
 HERE = Path(__file__).resolve().parent
 
 
 def cases():
-    base = dict(n_layers=3, d_acts=32, d_features=64, batch=48, rank_u=8, n_outlier=2)
+    base = dict(n_layers=3, d_acts=64, d_features=64, batch=136, rank_u=8, n_outlier=2)
     S = synthetic.WorkloadSpec
     out = []
     for bf16 in (False, True):
@@ -83,7 +83,8 @@ def build_reference_module(ref, spec, weights, last_active):
     return mod
 
 
-def run_case(ref, spec):
+def case_inputs(spec):
+    """Inputs of a golden case, regenerated from fixed seeds (also used by the tests)."""
     batch = synthetic.make_batch(spec, seed=11)
     weights = synthetic.make_weights(spec, seed=12)
     # non-zero biases so that every term of the arithmetic is exercised
@@ -91,6 +92,17 @@ def run_case(ref, spec):
     weights["b_enc"] = 0.02 * torch.randn(weights["b_enc"].shape, generator=g)
     weights["b_dec"] = 0.02 * torch.randn(weights["b_dec"].shape, generator=g)
     last_active = synthetic.make_last_active(spec, seed=14)
+    return batch, weights, last_active
+
+
+def checksum(batch, weights):
+    ts = [batch, weights["W_enc"], weights["b_enc"], weights["b_dec"]]
+    ts += list(weights["W_dec"]) if isinstance(weights["W_dec"], list) else [weights["W_dec"]]
+    return torch.stack([torch.stack([t.double().sum(), t.double().abs().sum()]) for t in ts])
+
+
+def run_case(ref, spec):
+    batch, weights, last_active = case_inputs(spec)
     mod = build_reference_module(ref, spec, weights, last_active)
     mod.model.initialize_standardizers(batch)
     ctx = torch.autocast("cpu", dtype=torch.bfloat16) if spec.bf16 else contextlib.nullcontext()
@@ -111,11 +123,11 @@ def run_case(ref, spec):
     after = {n: p.detach().clone() for n, p in mod.named_parameters()}
     out = {
         "spec": dict(spec.__dict__),
-        "batch": batch, "weights": weights, "last_active_in": last_active,
+        "input_checksum": checksum(batch, weights),
         "names": names,
         "loss": loss.detach(), "pre": pre.detach().float(), "feat": feat.detach().float(),
-        "recons_norm": recons_norm.detach().float(), "recons": recons.detach().float(),
-        "grads": grads, "params_after_adam": after,
+        "recons_norm": recons_norm.detach().float(),
+        "grads": grads, "params_after_adam": after if not spec.bf16 else None,
         "logged": {k: (v.detach().clone() if torch.is_tensor(v) else v) for k, v in mod.logged.items()},
         "last_active_out": mod.last_active.clone(),
         "stats": {"mu_in": mod.model.input_standardizer.mean.clone(), "sd_in": mod.model.input_standardizer.std.clone(),
