@@ -1,0 +1,409 @@
+"""Benchmark of the crosslayer-transcoder training step (forward + backward + Adam).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+
+Prints ONE JSON line (rank 0).  ``value`` is training tokens/s with the batch already
+resident in HBM; ``e2e`` is the same metric through the public module API with the batch
+copied from pinned host memory and the loss read back every step; ``roofline`` describes
+the kernel with the largest share of the timed region; ``cpu_baseline`` is the CPU oracle
+(a restatement of the reference's step) timed on this host on a bounded sample.
+
+For N > 1 launch with ``python -m torch.distributed.run --nproc-per-node N bench.py --gpus N``:
+the feature axis is sharded over the ranks, every rank sees the same batch (strong scaling).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from crosslayer_transcoder_b200 import synthetic  # noqa: E402
+
+METRIC = "clt_train_tokens_per_s"
+UNIT = "tokens/s"
+DEFAULT_WORKLOAD = "c2_plt_bf16"
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels from
+# the ncu captures summarised under profiles/; None where no capture has been taken.
+NCU_TRAFFIC = {}
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------------------
+# clocks
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.lines = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------
+# workload construction
+# --------------------------------------------------------------------------------------
+def build_on_device(spec: synthetic.WorkloadSpec, dev, rank: int, world: int):
+    """The package's training module for this rank's feature shard, weights drawn on the device."""
+    import crosslayer_transcoder_b200.model as M
+    from crosslayer_transcoder_b200 import parallel
+
+    L, D, F = spec.n_layers, spec.d_acts, spec.d_features
+    lo, hi = parallel.feature_shard(F, rank, world)
+    Fl = hi - lo
+    with torch.device(dev):
+        enc = M.Encoder(D, Fl, L)
+        dec = (M.CrosslayerDecoder if spec.crosslayer else M.Decoder)(D, Fl, L)
+        if spec.kind == "jumprelu":
+            nl = M.JumpReLU(theta=spec.theta, bandwidth=spec.bandwidth, n_layers=L, d_features=Fl)
+        elif spec.kind == "topk":
+            nl = M.PerLayerTopK(k=spec.k)
+        else:
+            nl = M.BatchTopK(k=spec.k, e=spec.e)
+        model = M.CrossLayerTranscoder(nl, enc, dec, M.DimensionwiseInputStandardizer(L, D),
+                                       M.DimensionwiseOutputStandardizer(L, D))
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    with torch.no_grad():
+        enc.W.copy_((torch.rand(enc.W.shape, device=dev, generator=g) * 2 - 1) / D ** 0.5)
+        bound = (L * F) ** -0.5 if spec.crosslayer else F ** -0.5
+        for w in dec.blocks():
+            w.copy_((torch.rand(w.shape, device=dev, generator=g) * 2 - 1) * bound)
+    common = dict(model=model, learning_rate=spec.lr, tokens_till_dead=spec.tokens_till_dead)
+    if spec.kind == "jumprelu":
+        mod = M.JumpReLUCrossLayerTranscoderModule(lambda_sparsity=spec.lambda_sparsity, c_sparsity=spec.c_sparsity,
+                                                   use_tanh=spec.use_tanh, pre_actv_loss=spec.pre_actv_loss, **common)
+        mod.trainer.max_steps = 1
+        mod.global_step = 1
+    elif spec.kind == "topk":
+        mod = M.TopKCrossLayerTranscoderModule(topk_aux=M.PerLayerTopK(k=spec.k_aux),
+                                               aux_loss_scale=spec.aux_loss_scale, **common)
+        mod.last_active.copy_(synthetic.make_last_active(spec, f_lo=lo, f_hi=hi))
+    else:
+        mod = M.CrossLayerTranscoderModule(**common)
+    mod = mod.to(dev)
+    mod.precision = "bf16" if spec.bf16 else "fp32"
+    if world > 1:
+        parallel.attach(mod)
+    return mod
+
+
+def algorithmic_work(spec, Fl: int, n_params: int, batch_bytes_per_elem: int):
+    """Per-launch algorithmic FLOPs / bytes of every entry point, for this rank's shard."""
+    B, L, D = spec.batch, spec.n_layers, spec.d_acts
+    P = L * (L + 1) // 2 if spec.crosslayer else L
+    e = 2 if spec.bf16 else 4
+    enc = 2.0 * B * L * D * Fl
+    dec = 2.0 * B * P * Fl * D
+    bld = float(B) * L * D
+    return {
+        "clt_encoder_fwd_act": ("tensor", enc), "clt_encoder_fwd_store": ("tensor", enc),
+        "clt_encoder_dense_bwd_dw": ("tensor", enc), "clt_decoder_dense_fwd": ("tensor", dec),
+        "clt_decoder_dense_bwd_dfeat": ("tensor", dec), "clt_decoder_dense_bwd_dw": ("tensor", dec),
+        "clt_adam_step": ("hbm", n_params * (28.0 + (2 if spec.bf16 else 0))),
+        "clt_prep_input": ("hbm", bld * (batch_bytes_per_elem + e)),
+        "clt_loss_fwd": ("hbm", bld * (4 + batch_bytes_per_elem)),
+        "clt_loss_bwd": ("hbm", bld * (4 + batch_bytes_per_elem + e)),
+        "clt_dec_norms": ("hbm", float(P) * Fl * D * 4),
+    }
+
+
+# --------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference's step on the host cores
+# --------------------------------------------------------------------------------------
+def cpu_sample_spec(spec):
+    """A bounded sample of the workload for the CPU: same B, D, F and step structure, two layers."""
+    return synthetic.scaled(spec, n_layers=2, name=spec.name + "_cpu_sample")
+
+
+def time_cpu_oracle(spec, steps: int, warmup: int):
+    from oracle import clt_oracle as O
+
+    sample = cpu_sample_spec(spec)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    batch = synthetic.make_batch(sample, seed=5)
+    g = torch.Generator().manual_seed(6)
+    L, D, F = sample.n_layers, sample.d_acts, sample.d_features
+    W_enc = (torch.rand(L, D, F, generator=g) * 2 - 1) / D ** 0.5
+    if sample.crosslayer:
+        W_dec = [(torch.rand(t + 1, F, D, generator=g) * 2 - 1) / (spec.n_layers * F) ** 0.5 for t in range(L)]
+    else:
+        W_dec = (torch.rand(L, F, D, generator=g) * 2 - 1) / F ** 0.5
+    theta = torch.full((1, L, F), sample.theta) if sample.kind == "jumprelu" else None
+    P = O.Params(W_enc, torch.zeros(L, F), W_dec, torch.zeros(L, D), theta)
+    H = O.Hyper(kind=sample.kind, bf16=sample.bf16, bandwidth=sample.bandwidth,
+                lambda_sparsity=sample.lambda_sparsity, c_sparsity=sample.c_sparsity, use_tanh=sample.use_tanh,
+                pre_actv_loss=sample.pre_actv_loss, k=sample.k, k_aux=sample.k_aux,
+                aux_loss_scale=sample.aux_loss_scale, tokens_till_dead=sample.tokens_till_dead, e=sample.e)
+    stats = O.standardizer_stats(batch)
+    kw = {}
+    if sample.kind == "topk":
+        kw["last_active"] = synthetic.make_last_active(sample)
+    if sample.kind == "batchtopk":
+        kw["threshold"] = torch.zeros(1)
+    state = [(torch.zeros_like(t), torch.zeros_like(t)) for t in P.tensors()]
+    times = []
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        out, grads = O.step_with_grads(P, batch, stats, H, **kw)
+        new = []
+        for t, gr, (m, v) in zip(P.tensors(), grads, state):
+            p2, m2, v2 = O.adam_step(t, gr, m, v, i + 1, sample.lr)
+            t.copy_(p2)
+            new.append((m2, v2))
+        state = new
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt)
+    # the sample has 2 of the workload's layers; dense work per layer pair grows with the number of
+    # decoder blocks, so scale the step time by the dense-FLOP ratio of the full workload
+    def flops(s):
+        Pn = s.n_layers * (s.n_layers + 1) // 2 if s.crosslayer else s.n_layers
+        return 4.0 * s.batch * s.n_layers * s.d_acts * s.d_features + 6.0 * s.batch * Pn * s.d_features * s.d_acts
+    scale = flops(spec) / flops(sample)
+    t_med = statistics.median(times)
+    return {"tokens_per_s": spec.batch / (t_med * scale), "cores": cores, "sample_step_s": t_med, "scale": scale,
+            "sample": f"{sample.n_layers} of {spec.n_layers} layers at full B/D/F, step time scaled by the dense-FLOP "
+                      f"ratio {scale:.1f} (extrapolated)"}
+
+
+# --------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(synthetic.WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--override", default="", help="comma-separated field=value changes to the workload "
+                    "(reduced shapes for profiler captures; the result is then not a benchmark value)")
+    args = ap.parse_args()
+    spec = synthetic.WORKLOADS[args.workload]
+    if args.override:
+        over = {}
+        for kv in args.override.split(","):
+            k, v = kv.split("=")
+            over[k] = type(getattr(spec, k))(v)
+        spec = synthetic.scaled(spec, name=spec.name + "[" + args.override + "]", **over)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    config = {"workload": spec.name, "kind": spec.kind, "decoder": "crosslayer" if spec.crosslayer else "per-layer",
+              "n_layers": spec.n_layers, "d_acts": spec.d_acts, "d_features": spec.d_features,
+              "batch_tokens": spec.batch, "sharding": f"d_features/{world}",
+              "l2": "inputs_larger_than_l2 (batch and activations are hundreds of MB to GB per step)"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        steps = max(1, min(args.steps, 3))
+        r = time_cpu_oracle(spec, steps=steps, warmup=min(args.warmup, 1))
+        line = {"impl": "reference", "metric": METRIC, "value": r["tokens_per_s"], "unit": UNIT, "n_gpus": args.gpus,
+                "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * r["sample_step_s"] * r["scale"],
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "bf16" if spec.bf16 else "fp32", "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": r["tokens_per_s"], "unit": UNIT, "cores": r["cores"], "kind": "port",
+                                 "sample": r["sample"]},
+                "e2e": {"value": r["tokens_per_s"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    import torch.distributed as dist
+
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    dev = torch.device(f"cuda:{local_rank}")
+    torch.cuda.set_device(dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    mod = build_on_device(spec, dev, rank, world)
+    opt = mod.configure_optimizers()
+    eng = mod._engine
+    batch_host = synthetic.make_batch(spec, seed=0).half().pin_memory()      # fp16, the reference's activation dtype
+    batch_dev = batch_host.to(dev, non_blocking=True)
+    torch.cuda.synchronize()
+
+    def step(b, idx):
+        opt.zero_grad(set_to_none=True)
+        loss = mod.training_step(b, idx)
+        loss.backward()
+        opt.step()
+        return loss
+
+    for i in range(max(args.warmup, 3)):
+        step(batch_dev, i)
+    eng.check_status("warm-up")
+
+    # ---- device-resident timing, per-kernel events collected in the same region --------------
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = eng.launches
+    eng.profile = {}
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(batch_dev, 100 + i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    prof = eng.profile_summary()
+    eng.profile = None
+    launches = eng.launches - launches0
+    clocks = sampler.stop() if rank == 0 else None
+    eng.check_status("timed region")
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t)
+
+    # ---- end to end: pinned host batch -> device every step (prefetched on a copy stream), loss read back
+    copy_stream = torch.cuda.Stream()
+    bufs = [torch.empty_like(batch_dev), torch.empty_like(batch_dev)]
+    ready = [torch.cuda.Event(), torch.cuda.Event()]
+    freed = [torch.cuda.Event(), torch.cuda.Event()]
+
+    def upload(slot):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(freed[slot])
+            bufs[slot].copy_(batch_host, non_blocking=True)
+            ready[slot].record(copy_stream)
+
+    for f in freed:
+        f.record()
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    upload(0)
+    last = 0.0
+    for i in range(args.steps):
+        slot = i & 1
+        if i + 1 < args.steps:
+            upload(slot ^ 1)
+        torch.cuda.current_stream().wait_event(ready[slot])
+        loss = step(bufs[slot], 200 + i)
+        freed[slot].record()
+        last = float(loss.detach())             # device -> host read of the step's result
+    t1.record()
+    barrier()
+    e2e_ms = t0.elapsed_time(t1)
+    t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t)
+    eng.check_status("end-to-end region")
+
+    if rank == 0:
+        peaks = load_peaks()
+        Fl = spec.d_features // world
+        work = algorithmic_work(spec, Fl, eng.flat.numel, batch_host.element_size())
+        kernels = {}
+        for name, st in prof.items():
+            bound, amount = work.get(name, (None, None))
+            entry = {"launches": st["launches"], "ms_avg": round(st["ms_avg"], 4),
+                     "share": round(st["ms_total"] / ms, 4)}
+            if bound == "tensor":
+                ach = amount / (st["ms_avg"] * 1e-3) / 1e12
+                entry.update(bound="tensor", achieved=round(ach, 1), unit="TFLOP/s",
+                             frac=round(ach / peaks["bf16_tflops"], 4))
+            elif bound == "hbm":
+                ach = amount / (st["ms_avg"] * 1e-3) / 1e9
+                entry.update(bound="hbm", achieved=round(ach, 1), unit="GB/s", frac=round(ach / peaks["hbm_gbs"], 4))
+            kernels[name] = entry
+        top = max((k for k in kernels if "bound" in kernels[k]), key=lambda k: kernels[k]["share"])
+        tk = kernels[top]
+        roofline = {"kernel": top, "bound": tk["bound"], "achieved": tk["achieved"],
+                    "peak": peaks["bf16_tflops"] if tk["bound"] == "tensor" else peaks["hbm_gbs"],
+                    "unit": tk["unit"], "frac": tk["frac"], "peak_source": peaks["source"],
+                    "traffic": NCU_TRAFFIC.get((spec.name, top))}
+        line = {"metric": METRIC, "value": spec.batch * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "bf16" if spec.bf16 else "fp32", "data": "synthetic", "config": config,
+                "clocks": clocks,
+                "e2e": {"value": spec.batch * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
+                        "h2d_bytes_per_step": batch_host.numel() * batch_host.element_size(),
+                        "d2h_bytes_per_step": 4, "last_loss": last},
+                "gpu_launches": launches, "roofline": roofline, "kernels": kernels}
+        if world == 1 and not args.no_cpu_baseline:
+            r = time_cpu_oracle(spec, steps=1, warmup=1)
+            line["cpu_baseline"] = {"value": r["tokens_per_s"], "unit": UNIT, "cores": r["cores"], "kind": "port",
+                                    "sample": r["sample"]}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

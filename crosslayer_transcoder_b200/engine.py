@@ -111,11 +111,30 @@ class StepEngine:
         self.fired: Optional[torch.Tensor] = None
         self.launches = 0                         # kernels launched by this engine (for reporting)
         self.last_terms: Optional[torch.Tensor] = None
+        self.profile: Optional[dict] = None
 
     # ------------------------------------------------------------------ setup
     def _call(self, name, *args):
-        lib().call(name, *args)
+        """One C-ABI call = one kernel launch on the current stream.  With ``self.profile`` set to a
+        dict, CUDA events around the call collect per-entry-point device time."""
+        if self.profile is None:
+            lib().call(name, *args)
+        else:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            lib().call(name, *args)
+            e1.record()
+            self.profile.setdefault(name, []).append((e0, e1))
         self.launches += 1
+
+    def profile_summary(self) -> Dict[str, dict]:
+        """{entry point: {"launches", "ms_total", "ms_avg"}} from the collected events (synchronises)."""
+        torch.cuda.synchronize()
+        out = {}
+        for name, evs in (self.profile or {}).items():
+            ms = [a.elapsed_time(b) for a, b in evs]
+            out[name] = {"launches": len(ms), "ms_total": sum(ms), "ms_avg": sum(ms) / max(1, len(ms))}
+        return out
 
     def _precision(self, batch) -> bool:
         """True for the bf16 tensor-core path.  ``module.precision`` forces it ("bf16" / "fp32");
@@ -225,10 +244,14 @@ class StepEngine:
         xn = ws.get("xn", (L, B, D), T, dev)
         z = ws.get("z", (L, B, F), T, dev)
         feat = ws.get("feat", (L, B, F), T, dev)
-        recon = ws.get("recon", (B, L, D), torch.float32, dev)
-        acc = ws.get("acc", (8,), torch.float32, dev)
+        # reconstruction buffer with an 8-float tail: [0:2] encoder-side loss sums (summed over
+        # feature shards together with the partial reconstructions), [2:4] reconstruction-loss sums
+        rbuf = ws.get("recon", (B * L * D + 8,), torch.float32, dev)
+        recon, acc = rbuf[: B * L * D].view(B, L, D), rbuf[B * L * D:]
         out = torch.empty(5, dtype=torch.float32, device=dev)       # loss + 4 terms
         acc.zero_()
+        world, group = getattr(mod, "tp_world", 1), getattr(mod, "tp_group", None)
+        first_rank = getattr(mod, "tp_rank", 0) == 0
         in_code = DTYPE_CODE[batch.dtype]
         self._call("clt_prep_input", batch, in_code, mu_i, sd_i, xn, int(bf16), B, L, D, s)
         theta = nl.theta.data if h["kind"] == "jumprelu" else None
@@ -241,8 +264,12 @@ class StepEngine:
         self._call("clt_encoder_fwd_act", xn, self._operand(enc.W, bf16), enc.b.data, theta, norm, z, feat,
                    self.fired, acc[0:2], float(h.get("c_sparsity", 1.0)), int(h.get("use_tanh", True)), B, L, D, F,
                    int(bf16), self.status, s)
-        self._call("clt_decoder_dense_fwd", feat, W_op, dec.b.data, recon, B, L, D, F, crosslayer, int(bf16),
-                   self.status, s)
+        self._call("clt_decoder_dense_fwd", feat, W_op, dec.b.data if first_rank else None, recon, B, L, D, F,
+                   crosslayer, int(bf16), self.status, s)
+        if world > 1:
+            from .parallel import all_reduce_sum
+
+            all_reduce_sum(rbuf[: B * L * D + 2], group)      # partial reconstructions + encoder-side sums
         self._call("clt_loss_fwd", recon, None, batch, in_code, mu_o, sd_o, acc[2:4], B, L, D, s)
         pal = float(h.get("pre_actv_loss", 0.0))
         self._call("clt_finalize_loss", acc[2:4], acc[0:2], out[0:1], out[1:5], 1.0 / (B * L * D), lam / B,
@@ -277,7 +304,8 @@ class StepEngine:
         T = torch.bfloat16 if bf16 else torch.float32
         s = stream_ptr()
         ws = self.ws
-        xn, z, feat, recon = ws.buf["xn"], ws.buf["z"], ws.buf["feat"], ws.buf["recon"]
+        xn, z, feat = ws.buf["xn"], ws.buf["z"], ws.buf["feat"]
+        recon = ws.buf["recon"][: B * L * D].view(B, L, D)
         drecon = ws.get("drecon", (L, B, D), T, dev)
         dpre = ws.get("dpre", (L, B, F), T, dev)
         _, _, mu_o, sd_o = c["stats"]
@@ -358,7 +386,6 @@ class FusedAdam(torch.optim.Optimizer):
             with torch.enable_grad():
                 loss = closure()
         self._step += 1
-        L = lib()
         s = stream_ptr()
         for group in self.param_groups:
             b1, b2 = group["betas"]
@@ -367,8 +394,8 @@ class FusedAdam(torch.optim.Optimizer):
             if len(self.param_groups) == 1 and self._flat_ready(group):
                 fp = self.engine.flat
                 fp.ensure_moments()
-                L.call("clt_adam_step", fp.flat, fp.grad, fp.exp_avg, fp.exp_avg_sq, fp.shadow, fp.numel, *args)
-                self.engine.launches += 1
+                self.engine._call("clt_adam_step", fp.flat, fp.grad, fp.exp_avg, fp.exp_avg_sq, fp.shadow, fp.numel,
+                                  *args)
                 for p in group["params"]:
                     st = self.state[p]
                     if "exp_avg" not in st:
@@ -395,6 +422,6 @@ class FusedAdam(torch.optim.Optimizer):
                 if fp is not None and fp.shadow is not None and id(p) in fp.offsets and fp.is_packed():
                     shadow = fp.view_of(p, fp.shadow)
                 gr = p.grad.contiguous()
-                L.call("clt_adam_step", p.data, gr, st["exp_avg"], st["exp_avg_sq"], shadow, p.numel(), *args)
-                self.engine.launches += 1
+                self.engine._call("clt_adam_step", p.data, gr, st["exp_avg"], st["exp_avg_sq"], shadow, p.numel(),
+                                  *args)
         return loss

@@ -1,0 +1,42 @@
+"""Feature-axis sharding of the training step over the GPUs of one node.
+
+The reference shards ``d_features`` with DTensor styles (column-parallel encoder,
+sharded nonlinearity, row-parallel decoder whose partial outputs are all-reduced:
+crosslayer_transcoder/model/parallel.py:157-339).  Here each rank simply constructs
+its module with its own contiguous slice of the feature axis
+
+    encoder.W[:, :, lo:hi]  encoder.b[:, lo:hi]  theta[:, :, lo:hi]  decoder.W_t[:, lo:hi, :]
+
+(``decoder.b`` and the standardizers are replicated), every rank receives the same
+batch, and the step's one exchange is the sum of the partial normalised
+reconstructions (NCCL all-reduce over NVLink).  Backward needs no collective: the
+reconstruction gradient is replicated and every parameter gradient is shard-local.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def feature_shard(d_features: int, rank: int, world: int) -> Tuple[int, int]:
+    """Contiguous slice [lo, hi) of the feature axis owned by ``rank``."""
+    if d_features % world:
+        raise ValueError(f"d_features={d_features} is not divisible by the {world} ranks")
+    per = d_features // world
+    return rank * per, (rank + 1) * per
+
+
+def attach(module, group: Optional[dist.ProcessGroup] = None) -> None:
+    """Mark ``module`` (built with this rank's feature slice) as one shard of a group.  With no
+    group the default process group is used."""
+    if not dist.is_initialized():
+        raise RuntimeError("torch.distributed is not initialised")
+    module.tp_group = group if group is not None else dist.group.WORLD
+    module.tp_rank = dist.get_rank(module.tp_group)
+    module.tp_world = dist.get_world_size(module.tp_group)
+
+
+def all_reduce_sum(buf: torch.Tensor, group) -> None:
+    dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
