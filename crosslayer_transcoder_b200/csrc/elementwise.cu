@@ -250,22 +250,31 @@ int norm_coef(const float* dnorm, const float* n, float* out, int count, cudaStr
 
 // ---------------------------------------------------------------------------------
 // Dead-feature counters: last_active[fired] = 0; last_active += B; dead = last_active > limit.
-// Clears the fired flags for the next step.
+// fired_bits holds one bit per feature ([L, ceil(F/32)] words, set by the encoder or
+// selection kernels); the words are cleared here for the next step.
 // ---------------------------------------------------------------------------------
-__global__ void dead_update_kernel(long long* last_active, int* fired, unsigned char* dead, long long B,
-                                   long long limit, int count) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= count) return;
-  long long v = fired[i] ? 0 : last_active[i];
-  v += B;
-  last_active[i] = v;
-  fired[i] = 0;
-  if (dead != nullptr) dead[i] = v > limit ? 1 : 0;
+__global__ void dead_update_kernel(long long* last_active, unsigned* fired_bits, unsigned char* dead, long long B,
+                                   long long limit, int F) {
+  const int l = blockIdx.y;
+  const int f = blockIdx.x * blockDim.x + threadIdx.x;  // a warp covers one 32-feature word
+  const int words = (F + 31) / 32;
+  unsigned word = 0u;
+  if (f < F) word = fired_bits[(size_t)l * words + f / 32];
+  __syncwarp();
+  if (f < F) {
+    const size_t i = (size_t)l * F + f;
+    long long v = ((word >> (f & 31)) & 1u) ? 0 : last_active[i];
+    v += B;
+    last_active[i] = v;
+    if (dead != nullptr) dead[i] = v > limit ? 1 : 0;
+    if ((f & 31) == 0) fired_bits[(size_t)l * words + f / 32] = 0u;
+  }
 }
-int dead_update(long long* last_active, int* fired, unsigned char* dead, long long B, long long limit, int count,
-                cudaStream_t s) {
-  if (count <= 0) return 0;
-  dead_update_kernel<<<(count + 255) / 256, 256, 0, s>>>(last_active, fired, dead, B, limit, count);
+int dead_update(long long* last_active, unsigned* fired_bits, unsigned char* dead, long long B, long long limit, int L,
+                int F, cudaStream_t s) {
+  if (L <= 0 || F <= 0) return 0;
+  dim3 grid((F + 255) / 256, L);
+  dead_update_kernel<<<grid, 256, 0, s>>>(last_active, fired_bits, dead, B, limit, F);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

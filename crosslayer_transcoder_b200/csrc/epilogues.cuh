@@ -5,12 +5,18 @@
 // tile, each lane one row, and passes 32 consecutive columns of that row at a
 // time.  Column reductions over the batch axis are therefore warp shuffles.
 //
+// Per-column parameters (biases, thresholds, norms) are staged by the kernel in
+// shared memory once per tile and read by every row as broadcasts.
+//
 //   struct Epi {
 //     struct Params;                      // pointers and scalars, passed by value
 //     struct State;                       // per-thread registers living for the whole kernel
+//     static constexpr int kColArrays;    // per-column parameter arrays to stage
+//     static float col_value(const Params&, int arr, int z, int n, int N);   // array arr at column n < N
 //     static void init(State&);
-//     static void apply(const Params&, State&, int z, int row, bool row_ok,
-//                       int n0, int M, int N, float (&v)[32]);
+//     template <int CS>                   // CS = stride between staged arrays (columns per tile)
+//     static void apply(const Params&, State&, int z, int row, bool row_ok, int n0, int M, int N,
+//                       float (&v)[32], const float* colp);   // colp[arr * CS + i], i = 0..31
 //     static void finish(const Params&, State&);   // once per thread, warp-converged
 //   };
 #pragma once
@@ -121,9 +127,12 @@ struct StoreZ {
     T* out;  // [nz, M, N]
   };
   struct State {};
+  static constexpr int kColArrays = 0;
+  __device__ static float col_value(const Params&, int, int, int, int) { return 0.f; }
   __device__ static void init(State&) {}
+  template <int CS>
   __device__ static void apply(const Params& p, State&, int z, int row, bool row_ok, int n0, int M, int N,
-                               float (&v)[32]) {
+                               float (&v)[32], const float*) {
     if (!row_ok) return;
     T* dst = p.out + ((size_t)z * M + row) * N + n0;
     store32<T>(dst, N - n0, can_vec<T>(n0, N), v);
@@ -139,15 +148,17 @@ struct DecOut {
     long long ld, zstride;
   };
   struct State {};
+  static constexpr int kColArrays = 1;
+  __device__ static float col_value(const Params& p, int, int z, int n, int N) {
+    return p.bias != nullptr ? __ldg(p.bias + (size_t)z * N + n) : 0.f;
+  }
   __device__ static void init(State&) {}
+  template <int CS>
   __device__ static void apply(const Params& p, State&, int z, int row, bool row_ok, int n0, int M, int N,
-                               float (&v)[32]) {
+                               float (&v)[32], const float* colp) {
     if (!row_ok) return;
-    if (p.bias != nullptr) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (n0 + i < N) v[i] += __ldg(p.bias + (size_t)z * N + n0 + i);
-    }
+    for (int i = 0; i < 32; ++i) v[i] += colp[i];
     float* dst = p.out + (size_t)row * p.ld + (size_t)z * p.zstride + n0;
     const bool vec = (n0 + 32 <= N) && (p.ld % 4 == 0) && (p.zstride % 4 == 0);
     store32<float>(dst, N - n0, vec, v);
@@ -166,9 +177,12 @@ struct GradOut {
     int coef_by_source;    // 1: z is a (target, source) pair and rowcoef is indexed by its source layer
   };
   struct State {};
+  static constexpr int kColArrays = 0;
+  __device__ static float col_value(const Params&, int, int, int, int) { return 0.f; }
   __device__ static void init(State&) {}
+  template <int CS>
   __device__ static void apply(const Params& p, State&, int z, int row, bool row_ok, int n0, int M, int N,
-                               float (&v)[32]) {
+                               float (&v)[32], const float*) {
     if (!row_ok) return;
     const size_t off = ((size_t)z * M + row) * N + n0;
     const bool vec = can_vec<float>(n0, N);
@@ -193,10 +207,11 @@ struct GradOut {
 // Encoder forward with the (Jump)ReLU fused
 // =====================================================================================
 // acc -> z = round_T(acc); pre = z + b; feat = pre * [pre > theta and pre > 0].
-// Stores z and feat, marks columns that fired, and accumulates the two scalar
-// loss terms that depend on every pre-activation:
-//   sum relu(-pre)                       (pre-activation loss)
+// Stores z and feat, marks (one bit per column) the columns that fired, and
+// accumulates the two scalar loss terms that depend on every pre-activation:
+//   sum relu(-pre)                       (pre-activation loss; skipped when want_pre == 0)
 //   sum tanh(feat * dec_norm * c)        (sparsity penalty; without tanh: the product itself)
+// Staged columns: 0 = b, 1 = theta (0 for ReLU), 2 = dec_norm * c.
 template <class T>
 struct EncJumpReLU {
   struct Params {
@@ -205,44 +220,56 @@ struct EncJumpReLU {
     const float* dec_norm;  // [nz, N] or null (no sparsity term)
     T* z_out;               // [nz, M, N]
     T* feat_out;            // [nz, M, N]
-    int* fired;             // [nz, N] or null
+    unsigned* fired_bits;   // [nz, ceil(N/32)] packed flags, or null
     float* loss_acc;        // [0] += sum relu(-pre), [1] += sum of the sparsity summand
     float c_sparsity;
     int use_tanh;
+    int want_pre;           // accumulate sum relu(-pre)
   };
   struct State {
     float s_pre, s_sp;
   };
+  static constexpr int kColArrays = 3;
+  __device__ static float col_value(const Params& p, int arr, int z, int n, int N) {
+    const size_t i = (size_t)z * N + n;
+    if (arr == 0) return __ldg(p.b_enc + i);
+    if (arr == 1) return p.theta != nullptr ? __ldg(p.theta + i) : 0.f;
+    return p.dec_norm != nullptr ? __ldg(p.dec_norm + i) * p.c_sparsity : 0.f;
+  }
   __device__ static void init(State& s) { s.s_pre = 0.f, s.s_sp = 0.f; }
+  template <int CS>
   __device__ static void apply(const Params& p, State& st, int z, int row, bool row_ok, int n0, int M, int N,
-                               float (&v)[32]) {
-    const int lane = threadIdx.x & 31;
-    const size_t cz = (size_t)z * N + n0;
+                               float (&v)[32], const float* colp) {
+    const bool full = n0 + 32 <= N;
+    const bool sp = p.dec_norm != nullptr;
     float feat[32];
+    unsigned mask = 0u;
+    float s_pre = 0.f, s_sp = 0.f;
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-      const bool ok = row_ok && (n0 + i < N);
       const float zr = round_to<T>(v[i]);
-      const float b = ok ? __ldg(p.b_enc + cz + i) : 0.f;
-      const float th = (ok && p.theta != nullptr) ? __ldg(p.theta + cz + i) : 0.f;
-      const float pre = zr + b;
-      const float f = (ok && pre > th && pre > 0.f) ? pre : 0.f;
+      const float pre = zr + colp[i];
+      float f = (pre > colp[CS + i] && pre > 0.f) ? pre : 0.f;
+      if (!(row_ok && (full || n0 + i < N))) f = 0.f;
       v[i] = zr;
       feat[i] = f;
-      if (ok) {
-        st.s_pre += fmaxf(-pre, 0.f);
-        if (p.dec_norm != nullptr) {
-          const float w = f * __ldg(p.dec_norm + cz + i) * p.c_sparsity;
-          st.s_sp += p.use_tanh ? tanhf(w) : w;
-        }
+      mask |= (f > 0.f) ? (1u << i) : 0u;
+      if (p.want_pre) s_pre += fmaxf(-pre, 0.f);
+      if (sp) {
+        const float w = f * colp[2 * CS + i];
+        s_sp += p.use_tanh ? tanhf(w) : w;
       }
     }
-    if (p.fired != nullptr) {
+    if (p.want_pre && !full) {  // ragged edge: redo the sum with the column guard
+      s_pre = 0.f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const unsigned any = __ballot_sync(0xffffffffu, feat[i] > 0.f);
-        if (lane == i && any != 0u && n0 + i < N) p.fired[cz + i] = 1;
-      }
+      for (int i = 0; i < 32; ++i)
+        if (n0 + i < N) s_pre += fmaxf(-(v[i] + colp[i]), 0.f);
+    }
+    if (row_ok) st.s_pre += s_pre, st.s_sp += s_sp;
+    if (p.fired_bits != nullptr) {
+      mask = __reduce_or_sync(0xffffffffu, mask);
+      if ((threadIdx.x & 31) == 0 && mask != 0u) atomicOr(p.fired_bits + (size_t)z * ((N + 31) / 32) + n0 / 32, mask);
     }
     if (!row_ok) return;
     const size_t off = ((size_t)z * M + row) * N + n0;
@@ -270,6 +297,8 @@ struct EncJumpReLU {
 //   dnorm  += lam * (1 - tanh^2(w)) * feat * c
 //   db_enc += dpre
 // dpre is stored rounded to T (the operand type of the encoder weight-gradient contraction).
+// Staged columns: 0 = b, 1 = theta (0 for ReLU), 2 = dec_norm * c, 3 = -theta / bw.
+// rect is evaluated as -bw/2 < pre - theta <= bw/2, the same set without the division.
 template <class T>
 struct DFeatJumpReLU {
   struct Params {
@@ -289,11 +318,20 @@ struct DFeatJumpReLU {
     const float* gscale;  // device scalar: gradient of the loss w.r.t. itself (null = 1)
   };
   struct State {};
+  static constexpr int kColArrays = 4;
+  __device__ static float col_value(const Params& p, int arr, int z, int n, int N) {
+    const size_t i = (size_t)z * N + n;
+    if (arr == 0) return __ldg(p.b_enc + i);
+    if (arr == 1) return p.theta != nullptr ? __ldg(p.theta + i) : 0.f;
+    if (arr == 2) return p.dec_norm != nullptr ? __ldg(p.dec_norm + i) * p.c_sparsity : 0.f;
+    return p.theta != nullptr ? -__ldg(p.theta + i) / p.bandwidth : 0.f;
+  }
   __device__ static void init(State&) {}
+  template <int CS>
   __device__ static void apply(const Params& p, State&, int z, int row, bool row_ok, int n0, int M, int N,
-                               float (&v)[32]) {
-    const size_t cz = (size_t)z * N + n0;
+                               float (&v)[32], const float* colp) {
     const size_t off = ((size_t)z * M + (row_ok ? row : 0)) * N + n0;
+    const bool full = n0 + 32 <= N;
     const bool vec = can_vec<T>(n0, N);
     float zv[32];
     load32<T>(p.z_in + off, row_ok ? N - n0 : 0, vec && row_ok, zv);
@@ -302,35 +340,33 @@ struct DFeatJumpReLU {
     const bool sp = p.dec_norm != nullptr;
     const float gsc = p.gscale != nullptr ? __ldg(p.gscale) : 1.f;
     const float lam = p.lam * gsc, pal = p.pal * gsc;
+    const float hb = 0.5f * p.bandwidth;
 #pragma unroll
     for (int i = 0; i < 32; ++i) {
-      const bool ok = row_ok && (n0 + i < N);
-      const float b = ok ? __ldg(p.b_enc + cz + i) : 0.f;
-      const float th = (ok && !relu) ? __ldg(p.theta + cz + i) : 0.f;
-      const float pre = zv[i] + b;
-      const float f = (pre > th && pre > 0.f) ? pre : 0.f;
+      const bool ok = row_ok && (full || n0 + i < N);
+      const float th = colp[CS + i];
+      const float pre = zv[i] + colp[i];
       float gs = v[i];
       float dn = 0.f;
       if (sp) {
-        const float n = ok ? __ldg(p.dec_norm + cz + i) : 0.f;
-        const float w = f * n * p.c_sparsity;
+        const float f = (pre > th && pre > 0.f) ? pre : 0.f;
+        const float nc = colp[2 * CS + i];
         float d1 = 1.f;
         if (p.use_tanh) {
-          const float tw = tanhf(w);
+          const float tw = tanhf(f * nc);
           d1 = 1.f - tw * tw;
         }
-        gs += lam * d1 * n * p.c_sparsity;
+        gs = fmaf(lam * d1, nc, gs);
         dn = lam * d1 * f * p.c_sparsity;
       }
-      const float u = (pre - th) / p.bandwidth;
-      const float rect = ((u + 0.5f > 0.f) ? 1.f : 0.f) - ((u - 0.5f > 0.f) ? 1.f : 0.f);
+      const float d = pre - th;
+      const bool rect = (d > -hb) && !(d > hb);
       const bool pass = relu ? (pre > 0.f) : !(pre < 0.f);
       float dp = pass ? gs : 0.f;
       if (pre < 0.f) dp -= pal;
-      dp = ok ? dp : 0.f;
-      dth[i] = ok ? -(th / p.bandwidth) * rect * gs : 0.f;
+      v[i] = ok ? dp : 0.f;
+      dth[i] = (ok && rect) ? colp[3 * CS + i] * gs : 0.f;
       dnr[i] = ok ? dn : 0.f;
-      v[i] = dp;
     }
     if (row_ok) store32<T>(p.dpre_out + off, N - n0, vec, v);
     col_atomic_add(p.dbenc + (size_t)z * N, n0, N, warp_colsum32(v));

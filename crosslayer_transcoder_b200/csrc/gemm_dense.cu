@@ -63,17 +63,17 @@ bool dims_ok(int B, int L, int D, int F) { return B > 0 && L > 0 && D > 0 && F >
 extern "C" {
 
 int clt_encoder_fwd_act(const void* xn, const void* W_enc, const float* b_enc, const float* theta,
-                        const float* dec_norm, void* z_out, void* feat_out, int* fired, float* loss_acc,
-                        float c_sparsity, int use_tanh, int B, int L, int D, int F, int bf16, int* status,
-                        clt_stream_t stream) {
+                        const float* dec_norm, void* z_out, void* feat_out, uint32_t* fired_bits, float* loss_acc,
+                        float c_sparsity, int use_tanh, int want_pre, int B, int L, int D, int F, int bf16,
+                        int* status, clt_stream_t stream) {
   CLT_CHECK_ARG(dims_ok(B, L, D, F), "encoder_fwd_act: bad dims B=%d L=%d D=%d F=%d", B, L, D, F);
   CLT_CHECK_ARG(xn && W_enc && b_enc && z_out && feat_out && loss_acc, "encoder_fwd_act: null pointer");
   GemmGeom g{kBatched, B, F, D, L, L};
   Operand a{xn, 1, B, D, L}, b{W_enc, 0, F, D, L};
-  epi::EncJumpReLU<float>::Params p32{b_enc, theta, dec_norm, (float*)z_out, (float*)feat_out, fired, loss_acc,
-                                      c_sparsity, use_tanh};
-  epi::EncJumpReLU<bf16_t>::Params p16{b_enc, theta, dec_norm, (bf16_t*)z_out, (bf16_t*)feat_out, fired, loss_acc,
-                                       c_sparsity, use_tanh};
+  epi::EncJumpReLU<float>::Params p32{b_enc, theta, dec_norm, (float*)z_out, (float*)feat_out, fired_bits, loss_acc,
+                                      c_sparsity, use_tanh, want_pre};
+  epi::EncJumpReLU<bf16_t>::Params p16{b_enc, theta, dec_norm, (bf16_t*)z_out, (bf16_t*)feat_out, fired_bits,
+                                       loss_acc, c_sparsity, use_tanh, want_pre};
   return run_gemm<epi::EncJumpReLU<float>, epi::EncJumpReLU<bf16_t>>(g, a, b, p32, p16, bf16, status,
                                                                       (cudaStream_t)stream);
 }

@@ -82,6 +82,16 @@ __global__ void __launch_bounds__(128) gemm_simt_kernel(GemmGeom g, SimtOperands
     }
   }
 
+  // per-column parameters of this tile, staged once and read as broadcasts
+  constexpr int kCols = Epi::kColArrays > 0 ? Epi::kColArrays : 1;
+  __shared__ float colp[kCols][kSimtBN];
+  if (Epi::kColArrays > 0) {
+    for (int e = tid; e < Epi::kColArrays * kSimtBN; e += 128) {
+      const int arr = e / kSimtBN, j = e % kSimtBN;
+      colp[arr][j] = (n0 + j < g.N) ? Epi::col_value(ep, arr, z, n0 + j, g.N) : 0.f;
+    }
+    __syncthreads();
+  }
   typename Epi::State st;
   Epi::init(st);
 #pragma unroll
@@ -90,7 +100,7 @@ __global__ void __launch_bounds__(128) gemm_simt_kernel(GemmGeom g, SimtOperands
       float v[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = acc[32 * c + i];
-      Epi::apply(ep, st, z, row, row_ok, n0 + 32 * c, g.M, g.N, v);
+      Epi::template apply<kSimtBN>(ep, st, z, row, row_ok, n0 + 32 * c, g.M, g.N, v, &colp[0][32 * c]);
     }
   }
   Epi::finish(ep, st);

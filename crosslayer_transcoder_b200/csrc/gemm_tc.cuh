@@ -1,10 +1,11 @@
 // bf16 contraction on the 5th-generation tensor cores (tcgen05), fp32 accumulators
 // in tensor memory, operands staged in shared memory by TMA.
 //
-// One persistent CTA per SM, 192 threads:
+// One persistent CTA per SM, 320 threads:
 //   warp 0      TMA producer (one elected lane)
 //   warp 1      tensor-memory allocation, MMA issue (one elected lane)
-//   warps 2..5  epilogue: warp w reads the 32 tensor-memory lanes of quarter w % 4
+//   warps 2..9  epilogue: warp w reads the 32 tensor-memory lanes of quarter w % 4;
+//               warps 2..5 take columns 0..127 of the tile, warps 6..9 columns 128..255
 // A CTA walks output tiles of 128 x 256 (tile index = blockIdx.x + i * gridDim.x).
 // Four 48 KB stages (A 128x64, B 256x64 bf16) are handed from the producer to the
 // MMA lane through full/empty mbarriers; two 256-column accumulators in tensor
@@ -39,9 +40,13 @@ constexpr int kStages = 4;
 constexpr int kABytes = kBM * kBK * 2;  // 16 KB
 constexpr int kBBytes = kBN * kBK * 2;  // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kThreads = 64 + kEpiThreads;
 constexpr int kTmemCols = 512;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kMaxColArrays = 4;
+constexpr int kColBytes = 2 * kMaxColArrays * kBN * 4;  // staged per-column parameters, double-buffered
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kColBytes;
 constexpr long long kWaitCycles = 4000000000ll;  // about two seconds
 
 // ---- PTX wrappers ---------------------------------------------------------------
@@ -193,7 +198,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&bars->tmem_full[i]), 1);
-      mbar_init(smem_u32(&bars->tmem_empty[i]), 4);  // one arrival per epilogue warp
+      mbar_init(smem_u32(&bars->tmem_empty[i]), kEpiWarps);  // one arrival per epilogue warp
     }
     bars->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -298,7 +303,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     __syncwarp();
   } else {
     // ------------------------------ epilogue ----------------------------------
-    const int quarter = warp & 3;  // tensor-memory lanes 32*quarter .. +31
+    static_assert(Epi::kColArrays <= kMaxColArrays, "too many per-column parameter arrays");
+    float* colp_base = reinterpret_cast<float*>(smem + kStages * kStageBytes + 256);
+    const int et = threadIdx.x - 64;          // 0..255 among the epilogue threads
+    const int quarter = warp & 3;             // tensor-memory lanes 32*quarter .. +31
+    const int half = (warp - 2) >> 2;         // which 128 columns of the tile
     typename Epi::State st;
     Epi::init(st);
     uint32_t acc_phase[2] = {0, 0};
@@ -309,22 +318,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       const int r = tile % tiles_per_slab;
       const int m0 = (r % m_tiles) * kBM;
       const int n0 = (r / m_tiles) * kBN;
-      bool ok = true;
+      float* colp = colp_base + buf * (kMaxColArrays * kBN);
+      // stage this tile's per-column parameters while its main loop is still running
+#pragma unroll
+      for (int a = 0; a < Epi::kColArrays; ++a)
+        colp[a * kBN + et] = (n0 + et < g.N) ? Epi::col_value(ep, a, z, n0 + et, g.N) : 0.f;
+      int bad = 0;
       if (lane == 0)
-        ok = mbar_wait(smem_u32(&bars->tmem_full[buf]), acc_phase[buf], abort_flag, status, kTimeoutTmemFull);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) break;
+        bad = mbar_wait(smem_u32(&bars->tmem_full[buf]), acc_phase[buf], abort_flag, status, kTimeoutTmemFull) ? 0 : 1;
+      // one barrier over the epilogue threads: publishes the staged columns and makes the
+      // give-up decision uniform, so no warp is left behind at a later barrier
+      int any_bad;
+      asm volatile(
+          "{\n\t.reg .pred p, q;\n\t"
+          "setp.ne.b32 p, %1, 0;\n\t"
+          "bar.red.or.pred q, 1, %2, p;\n\t"
+          "selp.u32 %0, 1, 0, q;\n\t}"
+          : "=r"(any_bad)
+          : "r"(bad), "n"(kEpiThreads)
+          : "memory");
+      if (any_bad) break;
       acc_phase[buf] ^= 1;
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < g.M;
 #pragma unroll 1
-      for (int c = 0; c < kBN / 32; ++c) {
+      for (int cc = 0; cc < kBN / 64; ++cc) {
+        const int c = half * (kBN / 64) + cc;
         const int n = n0 + 32 * c;
         if (n >= g.N) break;
         float v[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kBN + 32 * c), v);
-        Epi::apply(ep, st, z, row, row_ok, n, g.M, g.N, v);
+        Epi::template apply<kBN>(ep, st, z, row, row_ok, n, g.M, g.N, v, colp + 32 * c);
       }
       tc_fence_before();
       __syncwarp();

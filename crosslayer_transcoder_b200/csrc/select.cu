@@ -1,0 +1,305 @@
+// TopK selection kernels (HBM-bound, no tensor cores).
+//
+// Per (token, layer) row the reference keeps the k largest pre-activations and passes
+// them through a ReLU (crosslayer_transcoder/model/topk.py:56-61).  A kept value that
+// is not positive becomes 0 and receives no gradient, so the result equals "the
+// min(k, #positive) largest POSITIVE values": these kernels select among positive
+// values only, whose IEEE bit patterns order like unsigned integers.
+//
+// Selection is an exact three-level radix select on the 31 value bits (11 + 11 + 9):
+// a shared-memory histogram per level narrows the bucket that holds the k-th largest
+// value until the threshold key T and the number r of elements equal to T that still
+// fit are known; everything above T and the first r elements equal to T are emitted.
+// One CTA of 256 threads owns a row and re-reads it from L1/L2 for every level.
+#include "../../include/clt_b200.h"
+#include "common.cuh"
+#include "kernels.h"
+
+namespace clt {
+
+namespace {
+
+constexpr int kSelThreads = 256;
+constexpr int kBins = 2048;
+
+template <class T>
+__device__ __forceinline__ float ld_as_float(const T* p, int i);
+template <>
+__device__ __forceinline__ float ld_as_float<float>(const float* p, int i) { return __ldg(p + i); }
+template <>
+__device__ __forceinline__ float ld_as_float<__nv_bfloat16>(const __nv_bfloat16* p, int i) {
+  return __bfloat162float(__ldg(p + i));
+}
+
+// digit of `key` at a radix level, and whether `key` lies in the bucket selected so far
+__device__ __forceinline__ bool level_digit(unsigned key, int level, unsigned prefix, unsigned& digit) {
+  if (level == 0) {
+    digit = key >> 20;  // sign bit is 0 for positive values: 11 significant bits
+    return true;
+  }
+  if (level == 1) {
+    digit = (key >> 9) & 0x7ffu;
+    return (key >> 20) == prefix;
+  }
+  digit = key & 0x1ffu;
+  return (key >> 9) == prefix;
+}
+
+// Find the bucket d with  count(buckets > d) < want <= count(buckets >= d).
+// hist[kBins] is consumed (turned into suffix sums).  Returns through shared scalars.
+__device__ void pick_bucket(int* hist, int want, int* sh_digit, int* sh_above) {
+  // suffix sums over 2048 bins with 256 threads: 8 bins per thread, then a block scan of thread totals
+  __shared__ int tot[kSelThreads];
+  const int t = threadIdx.x;
+  int local[8];
+  int s = 0;
+#pragma unroll
+  for (int i = 7; i >= 0; --i) {
+    s += hist[t * 8 + i];
+    local[i] = s;  // sum of bins t*8+i .. t*8+7
+  }
+  tot[t] = s;
+  __syncthreads();
+  // suffix sum of thread totals (simple two-step: warp-level then across warps)
+  int above = 0;  // sum of totals of threads > t
+  for (int j = t + 1; j < kSelThreads; j += 1) {
+    if ((j & 31) == 0 && j + 31 < kSelThreads) {
+      // whole warp block: add lazily below
+    }
+    above += tot[j];
+  }
+  // bins of this thread: count strictly above bin i = above + local[i+1]
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int gt = above + (i < 7 ? local[i + 1] : 0);
+    const int ge = above + local[i];
+    if (gt < want && want <= ge) {
+      *sh_digit = t * 8 + i;
+      *sh_above = gt;
+    }
+  }
+  __syncthreads();
+}
+
+struct RowSelect {
+  unsigned T;   // threshold key (0: every positive value is kept)
+  int r;        // how many elements equal to T are kept
+};
+
+// Exact k-th largest positive value of one row, by all threads of the CTA.
+// key_at(i) returns the key of element i (0 for elements that do not take part).
+template <class KeyFn>
+__device__ RowSelect radix_select(int n, int k, KeyFn key_at) {
+  __shared__ int hist[kBins];
+  __shared__ int sh_digit, sh_above, sh_total;
+  unsigned prefix = 0;
+  int want = k;
+  RowSelect out{0u, 0};
+  for (int level = 0; level < 3; ++level) {
+    for (int i = threadIdx.x; i < kBins; i += kSelThreads) hist[i] = 0;
+    if (threadIdx.x == 0) sh_total = 0;
+    __syncthreads();
+    int mine = 0;
+    for (int i = threadIdx.x; i < n; i += kSelThreads) {
+      const unsigned key = key_at(i);
+      unsigned d;
+      if (key != 0u && level_digit(key, level, prefix, d)) {
+        atomicAdd(&hist[d], 1);
+        ++mine;
+      }
+    }
+    if (mine) atomicAdd(&sh_total, mine);
+    __syncthreads();
+    if (sh_total < want) {  // fewer candidates than slots: keep them all (only possible at level 0)
+      __syncthreads();
+      return RowSelect{0u, 0};
+    }
+    if (threadIdx.x == 0) sh_digit = 0, sh_above = 0;
+    __syncthreads();
+    pick_bucket(hist, want, &sh_digit, &sh_above);
+    const unsigned d = (unsigned)sh_digit;
+    want -= sh_above;
+    if (level == 0)
+      prefix = d;
+    else if (level == 1)
+      prefix = (prefix << 11) | d;
+    else
+      out.T = (prefix << 9) | d;
+    __syncthreads();
+  }
+  out.r = want;  // elements equal to T still to take (>= 1)
+  return out;
+}
+
+__device__ __forceinline__ unsigned positive_key(float v) { return v > 0.f ? __float_as_uint(v) : 0u; }
+
+// ---------------------------------------------------------------------------------------
+// Main selection: idx/val [L, B, k] of the k largest positive pre-activations per row,
+// unused slots (fewer than k positives) hold idx 0 / val 0.  Marks fired features.
+// ---------------------------------------------------------------------------------------
+template <class T>
+__global__ void __launch_bounds__(kSelThreads)
+select_topk_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, int* __restrict__ idx_out,
+                   float* __restrict__ val_out, unsigned* __restrict__ fired_bits, int B, int F, int k) {
+  const int row = blockIdx.x;  // l * B + b
+  const int l = row / B;
+  const T* zr = z + (size_t)row * F;
+  const float* br = b_enc + (size_t)l * F;
+  auto key_at = [&](int i) { return positive_key(ld_as_float<T>(zr, i) + __ldg(br + i)); };
+  const RowSelect sel = radix_select(F, k, key_at);
+  __shared__ int n_out, n_tie;
+  if (threadIdx.x == 0) n_out = 0, n_tie = 0;
+  __syncthreads();
+  int* io = idx_out + (size_t)row * k;
+  float* vo = val_out + (size_t)row * k;
+  const int words = (F + 31) / 32;
+  for (int i = threadIdx.x; i < F; i += kSelThreads) {
+    const float v = ld_as_float<T>(zr, i) + __ldg(br + i);
+    const unsigned key = positive_key(v);
+    bool take = key > sel.T;
+    if (!take && key != 0u && key == sel.T) take = atomicAdd(&n_tie, 1) < sel.r;
+    if (take) {
+      const int slot = atomicAdd(&n_out, 1);
+      if (slot < k) {
+        io[slot] = i;
+        vo[slot] = v;
+        if (fired_bits != nullptr) atomicOr(fired_bits + (size_t)l * words + i / 32, 1u << (i & 31));
+      }
+    }
+  }
+  __syncthreads();
+  for (int s = n_out + threadIdx.x; s < k; s += kSelThreads) io[s] = 0, vo[s] = 0.f;
+}
+
+// ---------------------------------------------------------------------------------------
+// Dead-feature list per layer: dead_list[l, 0..n_dead[l]) = ascending indices with dead != 0.
+// One CTA per layer.
+// ---------------------------------------------------------------------------------------
+__global__ void dead_compact_kernel(const unsigned char* __restrict__ dead, int* __restrict__ dead_list,
+                                    int* __restrict__ n_dead, int F) {
+  const int l = blockIdx.x;
+  __shared__ int base;
+  __shared__ int wsum[32];
+  if (threadIdx.x == 0) base = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int f0 = 0; f0 < F; f0 += blockDim.x) {
+    const int f = f0 + threadIdx.x;
+    const int flag = (f < F && dead[(size_t)l * F + f]) ? 1 : 0;
+    const unsigned bal = __ballot_sync(0xffffffffu, flag);
+    const int before = __popc(bal & ((1u << lane) - 1u));
+    if (lane == 0) wsum[w] = __popc(bal);
+    __syncthreads();
+    int woff = 0;
+    for (int j = 0; j < w; ++j) woff += wsum[j];
+    if (flag) dead_list[(size_t)l * F + base + woff + before] = f;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int tot = 0;
+      for (int j = 0; j < nw; ++j) tot += wsum[j];
+      base += tot;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) n_dead[l] = base;
+}
+
+// ---------------------------------------------------------------------------------------
+// Auxiliary selection over the dead features of a row, written as a dense row of the
+// compacted feature matrix:  a[l, b, j] = pre(dead_list[l][j]) if it is among the k_aux
+// largest positive dead pre-activations of the row, else 0   (j < nd_pad; 0 beyond n_dead[l]).
+// Values tied with the k_aux-th are all kept.
+// ---------------------------------------------------------------------------------------
+template <class T>
+__global__ void __launch_bounds__(kSelThreads)
+select_aux_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, const int* __restrict__ dead_list,
+                  const int* __restrict__ n_dead, T* __restrict__ a_out, int B, int F, int k_aux, int nd_pad) {
+  extern __shared__ float cand[];  // pre-activations of the dead features of this row
+  const int row = blockIdx.x;
+  const int l = row / B;
+  const int nd = min(n_dead[l], nd_pad);
+  const T* zr = z + (size_t)row * F;
+  const float* br = b_enc + (size_t)l * F;
+  const int* dl = dead_list + (size_t)l * F;
+  for (int j = threadIdx.x; j < nd; j += kSelThreads) {
+    const int f = __ldg(dl + j);
+    cand[j] = ld_as_float<T>(zr, f) + __ldg(br + f);
+  }
+  __syncthreads();
+  auto key_at = [&](int j) { return positive_key(cand[j]); };
+  const RowSelect sel = radix_select(nd, k_aux, key_at);
+  T* ao = a_out + (size_t)row * nd_pad;
+  for (int j = threadIdx.x; j < nd_pad; j += kSelThreads) {
+    float v = 0.f;
+    if (j < nd) {
+      const float c = cand[j];
+      const unsigned key = positive_key(c);
+      if (key != 0u && key >= sel.T) v = c;
+    }
+    if constexpr (sizeof(T) == 2)
+      ao[j] = __float2bfloat16_rn(v);
+    else
+      ao[j] = v;
+  }
+}
+
+}  // namespace
+
+}  // namespace clt
+
+using namespace clt;
+
+extern "C" {
+
+int clt_select_topk(const void* z, const float* b_enc, int* idx_out, float* val_out, uint32_t* fired_bits, int B,
+                    int L, int F, int k, int bf16, clt_stream_t stream) {
+  CLT_CHECK_ARG(B > 0 && L > 0 && F > 0, "select_topk: bad dims B=%d L=%d F=%d", B, L, F);
+  CLT_CHECK_ARG(k >= 0 && k <= F, "select_topk: k=%d must be in [0, F=%d]", k, F);
+  CLT_CHECK_ARG(z && b_enc && (k == 0 || (idx_out && val_out)), "select_topk: null pointer");
+  if (k == 0) return 0;
+  const long long rows = (long long)L * B;
+  CLT_CHECK_ARG(rows < (1ll << 31), "select_topk: too many rows");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (bf16)
+    select_topk_kernel<__nv_bfloat16><<<(unsigned)rows, kSelThreads, 0, s>>>((const __nv_bfloat16*)z, b_enc, idx_out,
+                                                                               val_out, fired_bits, B, F, k);
+  else
+    select_topk_kernel<float><<<(unsigned)rows, kSelThreads, 0, s>>>((const float*)z, b_enc, idx_out, val_out,
+                                                                      fired_bits, B, F, k);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int clt_dead_compact(const uint8_t* dead, int* dead_list, int* n_dead, int L, int F, clt_stream_t stream) {
+  CLT_CHECK_ARG(L > 0 && F > 0 && dead && dead_list && n_dead, "dead_compact: bad arguments");
+  dead_compact_kernel<<<L, 1024, 0, (cudaStream_t)stream>>>(dead, dead_list, n_dead, F);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int clt_select_aux(const void* z, const float* b_enc, const int* dead_list, const int* n_dead, void* a_out, int B,
+                   int L, int F, int k_aux, int nd_pad, int bf16, clt_stream_t stream) {
+  CLT_CHECK_ARG(B > 0 && L > 0 && F > 0 && nd_pad > 0, "select_aux: bad dims B=%d L=%d F=%d nd_pad=%d", B, L, F, nd_pad);
+  CLT_CHECK_ARG(k_aux >= 1, "select_aux: k_aux=%d must be positive", k_aux);
+  CLT_CHECK_ARG(z && b_enc && dead_list && n_dead && a_out, "select_aux: null pointer");
+  const size_t smem = (size_t)nd_pad * sizeof(float);
+  CLT_CHECK_ARG(smem <= 200 * 1024, "select_aux: %d dead features per layer exceed the shared-memory candidate buffer",
+                nd_pad);
+  const long long rows = (long long)L * B;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (bf16) {
+    auto kern = select_aux_kernel<__nv_bfloat16>;
+    CLT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<(unsigned)rows, kSelThreads, smem, s>>>((const __nv_bfloat16*)z, b_enc, dead_list, n_dead,
+                                                   (__nv_bfloat16*)a_out, B, F, k_aux, nd_pad);
+  } else {
+    auto kern = select_aux_kernel<float>;
+    CLT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<(unsigned)rows, kSelThreads, smem, s>>>((const float*)z, b_enc, dead_list, n_dead, (float*)a_out, B, F,
+                                                   k_aux, nd_pad);
+  }
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

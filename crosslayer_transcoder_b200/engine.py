@@ -164,7 +164,8 @@ class StepEngine:
             self.status = torch.zeros(1, dtype=torch.int32, device=device)
         enc = self.module.model.encoder
         if self.fired is None or self.fired.device != device:
-            self.fired = torch.zeros(enc.n_layers, enc.d_features, dtype=torch.int32, device=device)
+            # one bit per feature, set by the kernels that see the features of a step
+            self.fired = torch.zeros(enc.n_layers, (enc.d_features + 31) // 32, dtype=torch.int32, device=device)
 
     def check_status(self, where=""):
         if self.status is not None:
@@ -262,8 +263,8 @@ class StepEngine:
             norm = ws.get("dec_norm", (L, F), torch.float32, dev)
             self._call("clt_dec_norms", W_master, norm, L, F, D, crosslayer, s)
         self._call("clt_encoder_fwd_act", xn, self._operand(enc.W, bf16), enc.b.data, theta, norm, z, feat,
-                   self.fired, acc[0:2], float(h.get("c_sparsity", 1.0)), int(h.get("use_tanh", True)), B, L, D, F,
-                   int(bf16), self.status, s)
+                   self.fired, acc[0:2], float(h.get("c_sparsity", 1.0)), int(h.get("use_tanh", True)),
+                   int(float(h.get("pre_actv_loss", 0.0)) != 0.0), B, L, D, F, int(bf16), self.status, s)
         self._call("clt_decoder_dense_fwd", feat, W_op, dec.b.data if first_rank else None, recon, B, L, D, F,
                    crosslayer, int(bf16), self.status, s)
         if world > 1:
@@ -274,7 +275,7 @@ class StepEngine:
         pal = float(h.get("pre_actv_loss", 0.0))
         self._call("clt_finalize_loss", acc[2:4], acc[0:2], out[0:1], out[1:5], 1.0 / (B * L * D), lam / B,
                    pal / (B * L), 0.0, s)
-        self._call("clt_dead_update", mod.last_active, self.fired, None, B, int(mod.tokens_till_dead), L * F, s)
+        self._call("clt_dead_update", mod.last_active, self.fired, None, B, int(mod.tokens_till_dead), L, F, s)
         return dict(kind=h["kind"], bf16=bf16, batch=batch, B=B, L=L, D=D, F=F, crosslayer=crosslayer, lam=lam,
                     pal=pal, c=float(h.get("c_sparsity", 1.0)), use_tanh=int(h.get("use_tanh", True)),
                     bandwidth=self._bandwidth(nl) if h["kind"] == "jumprelu" else 1.0, out=out,

@@ -47,12 +47,14 @@ int clt_prep_input(const void* batch, int in_dtype, const float* mu, const float
  * loss and sparsity penalty (crosslayer_transcoder/model/clt_lightning.py:450-465) and the
  * per-feature "fired" flags of update_dead_features (clt_lightning.py:284).
  * z = round_T(xn W_enc), pre = z + b_enc, feat = pre [pre > theta and pre > 0].
- * theta == NULL selects ReLU; dec_norm == NULL skips the sparsity sum; fired may be NULL.
- * loss_acc[0] += sum relu(-pre); loss_acc[1] += sum tanh(feat dec_norm c) (or the product). */
+ * theta == NULL selects ReLU; dec_norm == NULL skips the sparsity sum; fired_bits
+ * ([L, ceil(F/32)] words, one bit per feature, OR-ed into) may be NULL.
+ * loss_acc[0] += sum relu(-pre) (when want_pre != 0); loss_acc[1] += sum tanh(feat dec_norm c)
+ * (or the product). */
 int clt_encoder_fwd_act(const void* xn, const void* W_enc, const float* b_enc, const float* theta,
-                        const float* dec_norm, void* z_out, void* feat_out, int* fired, float* loss_acc,
-                        float c_sparsity, int use_tanh, int B, int L, int D, int F, int bf16, int* status,
-                        clt_stream_t stream);
+                        const float* dec_norm, void* z_out, void* feat_out, uint32_t* fired_bits,
+                        float* loss_acc, float c_sparsity, int use_tanh, int want_pre, int B, int L, int D,
+                        int F, int bf16, int* status, clt_stream_t stream);
 
 /* Encoder.forward alone (clt.py:157-162), for the TopK / BatchTopK selections that follow:
  * z = round_T(xn W_enc), no bias. */
@@ -108,9 +110,10 @@ int clt_dec_norms(const float* W_dec, float* out, int L, int F, int D, int cross
 int clt_norm_coef(const float* dnorm, const float* norm, float* out, int count, clt_stream_t stream);
 
 /* update_dead_features (clt_lightning.py:282-288): last_active[fired]=0; last_active+=B;
- * dead = last_active > limit (dead may be NULL). Clears fired. */
-int clt_dead_update(int64_t* last_active, int* fired, uint8_t* dead, int64_t B, int64_t limit, int count,
-                    clt_stream_t stream);
+ * dead = last_active > limit (dead may be NULL).  fired_bits is [L, ceil(F/32)] words, one bit
+ * per feature, and is cleared for the next step. */
+int clt_dead_update(int64_t* last_active, uint32_t* fired_bits, uint8_t* dead, int64_t B, int64_t limit, int L,
+                    int F, clt_stream_t stream);
 
 /* torch.optim.Adam / AdamW step (clt_lightning.py:339-352) over one flat fp32 buffer; `step`
  * counts from 1.  shadow_bf16 (may be NULL) receives the bf16 copy of the new parameters. */

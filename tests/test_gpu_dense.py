@@ -38,6 +38,7 @@ def test_golden_step(case, prec):
                           module_grad_list(mod), golden_grad_list(g)):
         assert a is not None, name
         assert rel_err(a.cpu(), b) < tol, name
+    assert torch.equal(mod.last_active.cpu(), g["last_active_out"])     # dead-feature counters, bit-exact
     if prec == "fp32":
         opt = mod.configure_optimizers()
         opt.step()
