@@ -149,24 +149,40 @@ def build_on_device(spec: synthetic.WorkloadSpec, dev, rank: int, world: int):
     return mod
 
 
-def algorithmic_work(spec, Fl: int, n_params: int, batch_bytes_per_elem: int):
-    """Per-launch algorithmic FLOPs / bytes of every entry point, for this rank's shard."""
+def algorithmic_work(spec, Fl: int, n_params: int, batch_bytes_per_elem: int, nd_pad: int = 0):
+    """Per-launch algorithmic FLOPs / bytes of every entry point, for this rank's shard.
+    Dense contractions: 2 M N K.  HBM-bound kernels: the bytes the operation has to move once
+    (gathers count every row they fetch; L2-resident re-reads are not counted)."""
     B, L, D = spec.batch, spec.n_layers, spec.d_acts
     P = L * (L + 1) // 2 if spec.crosslayer else L
     e = 2 if spec.bf16 else 4
+    Fd = nd_pad if spec.kind == "topk" else Fl        # width of the dense decoder-side contractions
     enc = 2.0 * B * L * D * Fl
-    dec = 2.0 * B * P * Fl * D
+    dec = 2.0 * B * P * Fd * D
     bld = float(B) * L * D
-    return {
+    k = max(spec.k, 1)
+    rows = float(B) * k * P                            # decoder rows fetched by the sparse forward
+    work = {
         "clt_encoder_fwd_act": ("tensor", enc), "clt_encoder_fwd_store": ("tensor", enc),
-        "clt_encoder_dense_bwd_dw": ("tensor", enc), "clt_decoder_dense_fwd": ("tensor", dec),
+        "clt_encoder_dense_bwd_dw": ("tensor", 2.0 * B * L * D * Fd if spec.kind == "topk" else enc),
+        "clt_decoder_dense_fwd": ("tensor", dec),
         "clt_decoder_dense_bwd_dfeat": ("tensor", dec), "clt_decoder_dense_bwd_dw": ("tensor", dec),
         "clt_adam_step": ("hbm", n_params * (28.0 + (2 if spec.bf16 else 0))),
         "clt_prep_input": ("hbm", bld * (batch_bytes_per_elem + e)),
-        "clt_loss_fwd": ("hbm", bld * (4 + batch_bytes_per_elem)),
-        "clt_loss_bwd": ("hbm", bld * (4 + batch_bytes_per_elem + e)),
+        "clt_loss_fwd": ("hbm", bld * (4 + batch_bytes_per_elem + (4 if spec.k_aux else 0))),
+        "clt_loss_bwd": ("hbm", bld * (4 + batch_bytes_per_elem + e + ((4 + e) if spec.k_aux else 0))),
         "clt_dec_norms": ("hbm", float(P) * Fl * D * 4),
+        "clt_select_topk": ("hbm", float(L) * B * Fl * e + float(L) * B * k * 8),
+        "clt_select_aux": ("hbm", float(L) * B * nd_pad * e * 2),
+        "clt_sparse_decoder_fwd": ("hbm", rows * D * e + bld * 4),
+        "clt_sparse_bwd_dec": ("hbm", float(P) * Fl * D * (e + 4)),
+        "clt_sparse_bwd_enc": ("hbm", float(L) * D * Fl * 4 + float(L) * B * k * D * e),
+        "clt_gather_rows": ("hbm", float(P) * nd_pad * D * e * 2),
+        "clt_scatter_rows": ("hbm", float(P) * nd_pad * D * 4 * 3),
+        "clt_scatter_cols": ("hbm", float(L) * nd_pad * D * 4 * 3),
+        "clt_csc_build": ("hbm", float(L) * B * k * 8 * 2 + float(L) * Fl * 4 * 3),
     }
+    return work
 
 
 # --------------------------------------------------------------------------------------
@@ -367,7 +383,9 @@ def main():
     if rank == 0:
         peaks = load_peaks()
         Fl = spec.d_features // world
-        work = algorithmic_work(spec, Fl, eng.flat.numel, batch_host.element_size())
+        a_aux = eng.ws.buf.get("a_aux")
+        work = algorithmic_work(spec, Fl, eng.flat.numel, batch_host.element_size(),
+                                nd_pad=int(a_aux.shape[-1]) if a_aux is not None else 0)
         kernels = {}
         for name, st in prof.items():
             bound, amount = work.get(name, (None, None))

@@ -45,12 +45,11 @@ __device__ __forceinline__ bool level_digit(unsigned key, int level, unsigned pr
   return (key >> 9) == prefix;
 }
 
-// Find the bucket d with  count(buckets > d) < want <= count(buckets >= d).
-// hist[kBins] is consumed (turned into suffix sums).  Returns through shared scalars.
-__device__ void pick_bucket(int* hist, int want, int* sh_digit, int* sh_above) {
-  // suffix sums over 2048 bins with 256 threads: 8 bins per thread, then a block scan of thread totals
-  __shared__ int tot[kSelThreads];
-  const int t = threadIdx.x;
+// Find the bucket d with  count(buckets > d) < want <= count(buckets >= d) and the count
+// strictly above it.  256 threads, 8 bins each; suffix sums by warp shuffles.
+__device__ void pick_bucket(const int* hist, int want, int* sh_digit, int* sh_above) {
+  __shared__ int wtot[kSelThreads / 32];
+  const int t = threadIdx.x, lane = t & 31, w = t >> 5;
   int local[8];
   int s = 0;
 #pragma unroll
@@ -58,17 +57,16 @@ __device__ void pick_bucket(int* hist, int want, int* sh_digit, int* sh_above) {
     s += hist[t * 8 + i];
     local[i] = s;  // sum of bins t*8+i .. t*8+7
   }
-  tot[t] = s;
-  __syncthreads();
-  // suffix sum of thread totals (simple two-step: warp-level then across warps)
-  int above = 0;  // sum of totals of threads > t
-  for (int j = t + 1; j < kSelThreads; j += 1) {
-    if ((j & 31) == 0 && j + 31 < kSelThreads) {
-      // whole warp block: add lazily below
-    }
-    above += tot[j];
+  int x = s;  // becomes the sum over lanes >= lane of this warp
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int y = __shfl_down_sync(0xffffffffu, x, o);
+    if (lane + o < 32) x += y;
   }
-  // bins of this thread: count strictly above bin i = above + local[i+1]
+  if (lane == 0) wtot[w] = x;
+  __syncthreads();
+  int above = x - s;  // threads after this one in the warp
+  for (int j = w + 1; j < kSelThreads / 32; ++j) above += wtot[j];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int gt = above + (i < 7 ? local[i + 1] : 0);

@@ -1,0 +1,498 @@
+// Sparse half of the TopK training step (HBM / L2 bound, no tensor cores).
+//
+// The selection leaves k (index, value) pairs per (layer, token) row.  The decoder
+// forward gathers decoder rows token by token; the backward works feature by feature
+// from a transposed (feature-major) copy of the selection so that every decoder row is
+// read once, every gradient row is written once and no pre-zeroing or atomics on the
+// large gradient buffers are needed.
+//
+// Layouts: idx / val / dval [L, B, k];  col_ptr [L, F+1];  ent [L, B*k] (slot = b*k + j);
+//          W_dec flat [P, F, D];  recon [B, L, D];  drecon, xn [L, B, D].
+#include "../../include/clt_b200.h"
+#include "common.cuh"
+#include "gemm.cuh"
+#include "kernels.h"
+
+namespace clt {
+namespace {
+
+// ---- 8-wide row chunks ------------------------------------------------------------------
+template <class T>
+struct Vec8;
+template <>
+struct Vec8<__nv_bfloat16> {
+  static constexpr int kElems = 8;
+  __device__ static __forceinline__ void load(const __nv_bfloat16* p, float (&o)[8]) {
+    const uint4 t = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      o[2 * j] = __uint_as_float(w[j] << 16);
+      o[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+    }
+  }
+};
+template <>
+struct Vec8<float> {
+  static constexpr int kElems = 8;
+  __device__ static __forceinline__ void load(const float* p, float (&o)[8]) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    o[0] = a.x, o[1] = a.y, o[2] = a.z, o[3] = a.w, o[4] = b.x, o[5] = b.y, o[6] = b.z, o[7] = b.w;
+  }
+};
+
+// =========================================================================================
+// Decoder forward, token-major gather.  One CTA per (token b, target layer t):
+//   recon[b, t, :] = b_dec[t] + sum_{s <= t} sum_j val[s,b,j] * W[pair(t,s), idx[s,b,j], :]
+// Each of the 4 warps takes every 4th selected row; lanes hold D/8/32 chunks of 8 columns.
+// =========================================================================================
+template <class T, int VPL>
+__global__ void __launch_bounds__(128)
+sparse_dec_fwd_kernel(const int* __restrict__ idx, const float* __restrict__ val, const T* __restrict__ W,
+                      const float* __restrict__ b_dec, float* __restrict__ recon, int B, int L, int D, int F, int k,
+                      int crosslayer, int* status) {
+  extern __shared__ float red[];  // [4][D]
+  const int b = blockIdx.x, t = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = D / 8;
+  float acc[VPL][8];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+  const int s_lo = crosslayer ? 0 : t;
+  const int nrows = (t - s_lo + 1) * k;
+  for (int r = warp; r < nrows; r += 4) {
+    const int s = s_lo + r / k, j = r % k;
+    const size_t e = ((size_t)s * B + b) * k + j;
+    const float v = __ldg(val + e);
+    if (v == 0.f) continue;
+    const int f = __ldg(idx + e);
+    if (f < 0 || f >= F) {
+      report_status(status, kBadIndex);
+      continue;
+    }
+    const size_t p = crosslayer ? (size_t)pair_index(t, s) : (size_t)t;
+    const T* row = W + (p * F + f) * D;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nvec) {
+        float w[8];
+        Vec8<T>::load(row + 8 * c, w);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[i][q] = fmaf(v, w[q], acc[i][q]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nvec) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) red[warp * D + 8 * c + q] = acc[i][q];
+    }
+  }
+  __syncthreads();
+  float* out = recon + ((size_t)b * L + t) * D;
+  for (int d = threadIdx.x; d < D; d += 128) {
+    float sum = red[d] + red[D + d] + red[2 * D + d] + red[3 * D + d];
+    if (b_dec != nullptr) sum += __ldg(b_dec + (size_t)t * D + d);
+    out[d] = sum;
+  }
+}
+
+// =========================================================================================
+// Feature-major copy of the selection (counting sort per layer).
+// =========================================================================================
+__global__ void csc_count_kernel(const int* __restrict__ idx, const float* __restrict__ val, int* __restrict__ count,
+                                 long long n_per_layer, int F, int L, int* status) {
+  const long long total = n_per_layer * L;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    if (val[i] == 0.f) continue;
+    const int l = (int)(i / n_per_layer);
+    const int f = idx[i];
+    if (f < 0 || f >= F) {
+      report_status(status, kBadIndex);
+      continue;
+    }
+    atomicAdd(count + (size_t)l * (F + 1) + f, 1);
+  }
+}
+
+// exclusive scan of count[l, 0..F) in place -> col_ptr[l, 0..F]; cursor[l, f] = col_ptr[l, f]
+__global__ void csc_scan_kernel(int* __restrict__ col_ptr, int* __restrict__ cursor, int F) {
+  const int l = blockIdx.x;
+  int* cp = col_ptr + (size_t)l * (F + 1);
+  int* cur = cursor + (size_t)l * F;
+  __shared__ int wsum[32];
+  __shared__ int carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int f0 = 0; f0 < F; f0 += blockDim.x) {
+    const int f = f0 + threadIdx.x;
+    const int c = f < F ? cp[f] : 0;
+    int x = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) wsum[w] = x;
+    __syncthreads();
+    int woff = 0;
+    for (int j = 0; j < w; ++j) woff += wsum[j];
+    const int excl = carry + woff + x - c;
+    __syncthreads();
+    if (f < F) cp[f] = excl, cur[f] = excl;
+    if (threadIdx.x == blockDim.x - 1) carry = excl + c;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) cp[F] = carry;
+}
+
+__global__ void csc_fill_kernel(const int* __restrict__ idx, const float* __restrict__ val, int* __restrict__ cursor,
+                                int* __restrict__ ent, long long n_per_layer, int F, int L) {
+  const long long total = n_per_layer * L;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    if (val[i] == 0.f) continue;
+    const int l = (int)(i / n_per_layer);
+    const int f = idx[i];
+    if (f < 0 || f >= F) continue;
+    const int pos = atomicAdd(cursor + (size_t)l * F + f, 1);
+    ent[(size_t)l * n_per_layer + pos] = (int)(i - (long long)l * n_per_layer);
+  }
+}
+
+// =========================================================================================
+// Decoder backward, feature-major.  One warp per (source layer s, feature f):
+//   for every target t >= s:  w = W[pair(t,s), f, :]
+//       for every token b that selected f:  dval[s,b,j] += w . drecon[t,b,:]
+//                                           dW row       += val[s,b,j] * drecon[t,b,:]
+//       dW[pair(t,s), f, :] = dW row   (zeros when nobody selected f)
+// =========================================================================================
+template <class T, int VPL>
+__global__ void __launch_bounds__(128)
+sparse_bwd_dec_kernel(const int* __restrict__ col_ptr, const int* __restrict__ ent, const float* __restrict__ val,
+                      const T* __restrict__ W, const T* __restrict__ drecon, float* __restrict__ dW,
+                      float* __restrict__ dval, int B, int L, int D, int F, int k, int crosslayer) {
+  const long long wid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= (long long)L * F) return;
+  const int s = (int)(wid / F), f = (int)(wid % F);
+  const int nvec = D / 8;
+  const int* cp = col_ptr + (size_t)s * (F + 1);
+  const int e0 = cp[f], e1 = cp[f + 1];
+  const size_t npl = (size_t)B * k;
+  const int t_end = crosslayer ? L : s + 1;
+  for (int t = s; t < t_end; ++t) {
+    const size_t p = crosslayer ? (size_t)pair_index(t, s) : (size_t)s;
+    const size_t roff = (p * F + f) * D;
+    float w[VPL][8], g[VPL][8];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int c = lane + 32 * i;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) g[i][q] = 0.f, w[i][q] = 0.f;
+      if (e1 > e0 && c < nvec) Vec8<T>::load(W + roff + 8 * c, w[i]);
+    }
+    for (int e = e0; e < e1; ++e) {
+      const int slot = __ldg(ent + (size_t)s * npl + e);
+      const int b = slot / k;
+      const float v = __ldg(val + (size_t)s * npl + slot);
+      const T* dr = drecon + ((size_t)t * B + b) * D;
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int c = lane + 32 * i;
+        if (c < nvec) {
+          float x[8];
+          Vec8<T>::load(dr + 8 * c, x);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            dot = fmaf(w[i][q], x[q], dot);
+            g[i][q] = fmaf(v, x[q], g[i][q]);
+          }
+        }
+      }
+      dot = warp_sum(dot);
+      if (lane == 0) atomicAdd(dval + (size_t)s * npl + slot, dot);
+    }
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nvec) {
+        float4* o = reinterpret_cast<float4*>(dW + roff + 8 * c);
+        o[0] = make_float4(g[i][0], g[i][1], g[i][2], g[i][3]);
+        o[1] = make_float4(g[i][4], g[i][5], g[i][6], g[i][7]);
+      }
+    }
+  }
+}
+
+// =========================================================================================
+// Encoder backward, feature-major.  One CTA per (layer l, 32 features, 768 input dims):
+//   dW_enc[l, d, f] = sum over tokens b that selected f of dval[l,b,j] * xn[l,b,d]
+//   db_enc[l, f]    = sum of the same dval
+// Thread t owns dims d0 + t, d0 + t + 256, d0 + t + 512 and all 32 features of the block,
+// so every store is a 128-byte run of the F-contiguous gradient.
+// =========================================================================================
+template <class T>
+__global__ void __launch_bounds__(256)
+sparse_bwd_enc_kernel(const int* __restrict__ col_ptr, const int* __restrict__ ent, const float* __restrict__ dval,
+                      const T* __restrict__ xn, float* __restrict__ dW, float* __restrict__ db, int B, int D, int F,
+                      int k) {
+  const int l = blockIdx.y, f0 = blockIdx.x * 32, d0 = blockIdx.z * 768;
+  const int* cp = col_ptr + (size_t)l * (F + 1);
+  const size_t npl = (size_t)B * k;
+  float acc[3][32];
+#pragma unroll
+  for (int i = 0; i < 3; ++i)
+#pragma unroll
+    for (int q = 0; q < 32; ++q) acc[i][q] = 0.f;
+  float bsum = 0.f;
+#pragma unroll
+  for (int q = 0; q < 32; ++q) {
+    const int f = f0 + q;
+    if (f >= F) break;
+    const int e0 = cp[f], e1 = cp[f + 1];
+    float bs = 0.f;
+    for (int e = e0; e < e1; ++e) {
+      const int slot = __ldg(ent + (size_t)l * npl + e);
+      const float g = __ldg(dval + (size_t)l * npl + slot);
+      const T* x = xn + ((size_t)l * B + slot / k) * D;
+      bs += g;
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        const int d = d0 + threadIdx.x + 256 * i;
+        if (d < D) acc[i][q] = fmaf(g, ToFloat<T>::get(x[d]), acc[i][q]);
+      }
+    }
+    if ((int)threadIdx.x == q) bsum = bs;
+  }
+  const bool vec = (F % 4 == 0) && (f0 + 32 <= F);
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    const int d = d0 + threadIdx.x + 256 * i;
+    if (d >= D) continue;
+    float* o = dW + ((size_t)l * D + d) * F + f0;
+    if (vec) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        reinterpret_cast<float4*>(o)[q] = make_float4(acc[i][4 * q], acc[i][4 * q + 1], acc[i][4 * q + 2], acc[i][4 * q + 3]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 32; ++q)
+        if (f0 + q < F) o[q] = acc[i][q];
+    }
+  }
+  if (blockIdx.z == 0 && threadIdx.x < 32 && f0 + (int)threadIdx.x < F) db[(size_t)l * F + f0 + threadIdx.x] = bsum;
+}
+
+// =========================================================================================
+// Compaction helpers of the auxiliary (dead-feature) path.
+// =========================================================================================
+// out[p, j, :] = W[p, dead_list[s(p)][j], :] for j < n_dead[s(p)], else 0
+template <class T>
+__global__ void gather_rows_kernel(const T* __restrict__ W, const int* __restrict__ dead_list,
+                                   const int* __restrict__ n_dead, T* __restrict__ out, int F, int D, int nd_pad,
+                                   int crosslayer) {
+  const int j = blockIdx.x, p = blockIdx.y;
+  int s = p, t = p;
+  if (crosslayer) pair_split(p, t, s);
+  const bool live = j < n_dead[s];
+  const int f = live ? dead_list[(size_t)s * F + j] : 0;
+  const uint4* src = reinterpret_cast<const uint4*>(W + ((size_t)p * F + f) * D);
+  uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)p * nd_pad + j) * D);
+  const int nv = D * (int)sizeof(T) / 16;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) dst[i] = live ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+}
+
+// dst[p, dead_list[s(p)][j], :] += src[p, j, :]   (fp32 gradients)
+__global__ void scatter_rows_kernel(const float* __restrict__ src, const int* __restrict__ dead_list,
+                                    const int* __restrict__ n_dead, float* __restrict__ dst, int F, int D, int nd_pad,
+                                    int crosslayer) {
+  const int j = blockIdx.x, p = blockIdx.y;
+  int s = p, t = p;
+  if (crosslayer) pair_split(p, t, s);
+  if (j >= n_dead[s]) return;
+  const int f = dead_list[(size_t)s * F + j];
+  const float4* a = reinterpret_cast<const float4*>(src + ((size_t)p * nd_pad + j) * D);
+  float4* o = reinterpret_cast<float4*>(dst + ((size_t)p * F + f) * D);
+  for (int i = threadIdx.x; i < D / 4; i += blockDim.x) {
+    float4 x = o[i];
+    const float4 y = a[i];
+    x.x += y.x, x.y += y.y, x.z += y.z, x.w += y.w;
+    o[i] = x;
+  }
+}
+
+// dW_enc[l, d, dead_list[l][j]] += src[l, d, j];  db_enc[l, dead_list[l][j]] += db_src[l, j]
+__global__ void scatter_cols_kernel(const float* __restrict__ src, const float* __restrict__ db_src,
+                                    const int* __restrict__ dead_list, const int* __restrict__ n_dead,
+                                    float* __restrict__ dW, float* __restrict__ db, int D, int F, int nd_pad) {
+  const int l = blockIdx.y;
+  const int nd = n_dead[l];
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= nd) return;
+  const int f = dead_list[(size_t)l * F + j];
+  for (int d = 0; d < D; ++d) dW[((size_t)l * D + d) * F + f] += src[((size_t)l * D + d) * nd_pad + j];
+  db[(size_t)l * F + f] += db_src[(size_t)l * nd_pad + j];
+}
+
+template <class T>
+int launch_dec_fwd(const int* idx, const float* val, const void* W, const float* b_dec, float* recon, int B, int L,
+                   int D, int F, int k, int crosslayer, int* status, cudaStream_t s) {
+  const int vpl = (D / 8 + 31) / 32;
+  dim3 grid(B, L);
+  const size_t smem = 4 * (size_t)D * sizeof(float);
+#define CLT_DEC_FWD(V)                                                                                              \
+  case V:                                                                                                           \
+    CLT_CHECK_CUDA(cudaFuncSetAttribute(sparse_dec_fwd_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                        (int)smem));                                                                \
+    sparse_dec_fwd_kernel<T, V><<<grid, 128, smem, s>>>(idx, val, (const T*)W, b_dec, recon, B, L, D, F, k,         \
+                                                        crosslayer, status);                                        \
+    break;
+  switch (vpl) {
+    CLT_DEC_FWD(1) CLT_DEC_FWD(2) CLT_DEC_FWD(3) CLT_DEC_FWD(4) CLT_DEC_FWD(6) CLT_DEC_FWD(8) CLT_DEC_FWD(9)
+    CLT_DEC_FWD(12)
+    default:
+      set_error("sparse decoder: d_acts=%d is not supported (needs D/256 in {1,2,3,4,6,8,9,12} after rounding up)", D);
+      return 1;
+  }
+#undef CLT_DEC_FWD
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+template <class T>
+int launch_bwd_dec(const int* col_ptr, const int* ent, const float* val, const void* W, const void* drecon, float* dW,
+                   float* dval, int B, int L, int D, int F, int k, int crosslayer, cudaStream_t s) {
+  const int vpl = (D / 8 + 31) / 32;
+  const long long warps = (long long)L * F;
+  const unsigned grid = (unsigned)((warps + 3) / 4);
+#define CLT_BWD_DEC(V)                                                                                            \
+  case V:                                                                                                         \
+    sparse_bwd_dec_kernel<T, V><<<grid, 128, 0, s>>>(col_ptr, ent, val, (const T*)W, (const T*)drecon, dW, dval, \
+                                                     B, L, D, F, k, crosslayer);                                  \
+    break;
+  switch (vpl) {
+    CLT_BWD_DEC(1) CLT_BWD_DEC(2) CLT_BWD_DEC(3) CLT_BWD_DEC(4) CLT_BWD_DEC(6) CLT_BWD_DEC(8) CLT_BWD_DEC(9)
+    CLT_BWD_DEC(12)
+    default:
+      set_error("sparse decoder backward: d_acts=%d is not supported", D);
+      return 1;
+  }
+#undef CLT_BWD_DEC
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace
+}  // namespace clt
+
+using namespace clt;
+
+extern "C" {
+
+int clt_sparse_decoder_fwd(const int* idx, const float* val, const void* W_dec, const float* b_dec, float* recon, int B,
+                           int L, int D, int F, int k, int crosslayer, int bf16, int* status, clt_stream_t stream) {
+  CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && F > 0 && k > 0, "sparse_decoder_fwd: bad dims B=%d L=%d D=%d F=%d k=%d", B,
+                L, D, F, k);
+  CLT_CHECK_ARG(D % 8 == 0, "sparse_decoder_fwd: d_acts=%d must be a multiple of 8", D);
+  CLT_CHECK_ARG(idx && val && W_dec && recon, "sparse_decoder_fwd: null pointer");
+  CLT_CHECK_ARG(B <= 2147483647 && L <= 65535, "sparse_decoder_fwd: grid too large");
+  if (bf16)
+    return launch_dec_fwd<__nv_bfloat16>(idx, val, W_dec, b_dec, recon, B, L, D, F, k, crosslayer, status,
+                                         (cudaStream_t)stream);
+  return launch_dec_fwd<float>(idx, val, W_dec, b_dec, recon, B, L, D, F, k, crosslayer, status, (cudaStream_t)stream);
+}
+
+int clt_csc_build(const int* idx, const float* val, int* col_ptr, int* cursor, int* ent, int B, int L, int F, int k,
+                  int* status, clt_stream_t stream) {
+  CLT_CHECK_ARG(B > 0 && L > 0 && F > 0 && k > 0, "csc_build: bad dims B=%d L=%d F=%d k=%d", B, L, F, k);
+  CLT_CHECK_ARG(idx && val && col_ptr && cursor && ent, "csc_build: null pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long npl = (long long)B * k;
+  CLT_CHECK_ARG(npl < (1ll << 31), "csc_build: B*k too large");
+  CLT_CHECK_CUDA(cudaMemsetAsync(col_ptr, 0, sizeof(int) * (size_t)L * (F + 1), s));
+  const long long total = npl * L;
+  const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+  csc_count_kernel<<<blocks, 256, 0, s>>>(idx, val, col_ptr, npl, F, L, status);
+  csc_scan_kernel<<<L, 1024, 0, s>>>(col_ptr, cursor, F);
+  csc_fill_kernel<<<blocks, 256, 0, s>>>(idx, val, cursor, ent, npl, F, L);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int clt_sparse_bwd_dec(const int* col_ptr, const int* ent, const float* val, const void* W_dec, const void* drecon,
+                       float* dW, float* dval, int B, int L, int D, int F, int k, int crosslayer, int bf16,
+                       clt_stream_t stream) {
+  CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && F > 0 && k > 0, "sparse_bwd_dec: bad dims");
+  CLT_CHECK_ARG(D % 8 == 0, "sparse_bwd_dec: d_acts=%d must be a multiple of 8", D);
+  CLT_CHECK_ARG(col_ptr && ent && val && W_dec && drecon && dW && dval, "sparse_bwd_dec: null pointer");
+  CLT_CHECK_CUDA(cudaMemsetAsync(dval, 0, sizeof(float) * (size_t)L * B * k, (cudaStream_t)stream));
+  if (bf16)
+    return launch_bwd_dec<__nv_bfloat16>(col_ptr, ent, val, W_dec, drecon, dW, dval, B, L, D, F, k, crosslayer,
+                                         (cudaStream_t)stream);
+  return launch_bwd_dec<float>(col_ptr, ent, val, W_dec, drecon, dW, dval, B, L, D, F, k, crosslayer,
+                               (cudaStream_t)stream);
+}
+
+int clt_sparse_bwd_enc(const int* col_ptr, const int* ent, const float* dval, const void* xn, float* dW_enc,
+                       float* db_enc, int B, int L, int D, int F, int k, int bf16, clt_stream_t stream) {
+  CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && F > 0 && k > 0, "sparse_bwd_enc: bad dims");
+  CLT_CHECK_ARG(col_ptr && ent && dval && xn && dW_enc && db_enc, "sparse_bwd_enc: null pointer");
+  dim3 grid((F + 31) / 32, L, (D + 767) / 768);
+  CLT_CHECK_ARG(grid.y <= 65535 && grid.z <= 65535, "sparse_bwd_enc: grid too large");
+  if (bf16)
+    sparse_bwd_enc_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>(
+        col_ptr, ent, dval, (const __nv_bfloat16*)xn, dW_enc, db_enc, B, D, F, k);
+  else
+    sparse_bwd_enc_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(col_ptr, ent, dval, (const float*)xn, dW_enc,
+                                                                        db_enc, B, D, F, k);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int clt_gather_rows(const void* W_dec, const int* dead_list, const int* n_dead, void* out, int L, int F, int D,
+                    int nd_pad, int crosslayer, int bf16, clt_stream_t stream) {
+  CLT_CHECK_ARG(L > 0 && F > 0 && D > 0 && nd_pad > 0, "gather_rows: bad dims");
+  CLT_CHECK_ARG((D * (bf16 ? 2 : 4)) % 16 == 0, "gather_rows: rows must be multiples of 16 bytes");
+  const int P = crosslayer ? L * (L + 1) / 2 : L;
+  dim3 grid(nd_pad, P);
+  if (bf16)
+    gather_rows_kernel<__nv_bfloat16><<<grid, 128, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)W_dec, dead_list, n_dead, (__nv_bfloat16*)out, F, D, nd_pad, crosslayer);
+  else
+    gather_rows_kernel<float><<<grid, 128, 0, (cudaStream_t)stream>>>((const float*)W_dec, dead_list, n_dead,
+                                                                     (float*)out, F, D, nd_pad, crosslayer);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int clt_scatter_rows(const float* src, const int* dead_list, const int* n_dead, float* dW_dec, int L, int F, int D,
+                     int nd_pad, int crosslayer, clt_stream_t stream) {
+  CLT_CHECK_ARG(L > 0 && F > 0 && D > 0 && nd_pad > 0 && D % 4 == 0, "scatter_rows: bad dims");
+  const int P = crosslayer ? L * (L + 1) / 2 : L;
+  dim3 grid(nd_pad, P);
+  scatter_rows_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(src, dead_list, n_dead, dW_dec, F, D, nd_pad, crosslayer);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int clt_scatter_cols(const float* src, const float* db_src, const int* dead_list, const int* n_dead, float* dW_enc,
+                     float* db_enc, int L, int D, int F, int nd_pad, clt_stream_t stream) {
+  CLT_CHECK_ARG(L > 0 && F > 0 && D > 0 && nd_pad > 0, "scatter_cols: bad dims");
+  dim3 grid((nd_pad + 127) / 128, L);
+  scatter_cols_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(src, db_src, dead_list, n_dead, dW_enc, db_enc, D, F,
+                                                              nd_pad);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

@@ -19,7 +19,6 @@ import torch
 
 from . import _lib
 from ._lib import DTYPE_CODE, CltError, lib, stream_ptr
-from .model.clt import CrosslayerDecoder
 
 _ALIGN = 64  # elements; keeps every segment 256-byte aligned in fp32 and 128-byte aligned in bf16
 
@@ -225,6 +224,8 @@ class StepEngine:
         kind = hyper["kind"]
         if kind in ("jumprelu", "relu"):
             ctx = self._forward_dense(batch, hyper, bf16)
+        elif kind == "topk":
+            ctx = self._forward_topk(batch, hyper, bf16)
         else:
             raise NotImplementedError(f"nonlinearity kind {kind!r}")
         self.last_terms = ctx["out"][1:5]          # mse, sparsity, pre-activation, auxiliary summands
@@ -239,7 +240,7 @@ class StepEngine:
         dev = batch.device
         T = torch.bfloat16 if bf16 else torch.float32
         s = stream_ptr()
-        crosslayer = 1 if isinstance(dec, CrosslayerDecoder) else 0
+        crosslayer = 1 if dec.crosslayer else 0
         mu_i, sd_i, mu_o, sd_o = self._stats()
         ws = self.ws
         xn = ws.get("xn", (L, B, D), T, dev)
@@ -285,6 +286,8 @@ class StepEngine:
     def backward(self, ctx: dict, gscale: torch.Tensor):
         if ctx["kind"] in ("jumprelu", "relu"):
             self._backward_dense(ctx, gscale)
+        elif ctx["kind"] == "topk":
+            self._backward_topk(ctx, gscale)
         else:
             raise NotImplementedError(ctx["kind"])
 
@@ -334,6 +337,124 @@ class StepEngine:
         self._call("clt_decoder_dense_bwd_dw", feat, drecon, dW_dec, rowcoef, W_master if rowcoef is not None else None,
                    B, L, D, F, c["crosslayer"], int(bf16), self.status, s)
         self._call("clt_encoder_dense_bwd_dw", xn, dpre, gview(enc.W), B, L, D, F, int(bf16), self.status, s)
+
+
+
+    # ------------------------------------------------------------------ TopK path
+    def _forward_topk(self, batch, h, bf16):
+        """PerLayerTopK step (reference clt_lightning.py:519-567): encoder contraction, exact per-row
+        selection, sparse decoder gather; the auxiliary dead-feature loss runs as dense contractions
+        over the compacted dead features."""
+        mod = self.module
+        model = mod.model
+        enc, dec, nl = model.encoder, model.decoder, model.nonlinearity
+        B, L, D, F = batch.shape[0], enc.n_layers, enc.d_acts, enc.d_features
+        k = int(nl.k)
+        assert k <= F                                   # reference topk.py:56
+        k_aux = int(h.get("k_aux", 0))
+        assert k_aux <= F
+        dev = batch.device
+        T = torch.bfloat16 if bf16 else torch.float32
+        s = stream_ptr()
+        crosslayer = 1 if dec.crosslayer else 0
+        mu_i, sd_i, mu_o, sd_o = self._stats()
+        ws = self.ws
+        xn = ws.get("xn", (L, B, D), T, dev)
+        z = ws.get("z", (L, B, F), T, dev)
+        rbuf = ws.get("recon", (B * L * D + 8,), torch.float32, dev)
+        recon, acc = rbuf[: B * L * D].view(B, L, D), rbuf[B * L * D:]
+        out = torch.empty(5, dtype=torch.float32, device=dev)
+        acc.zero_()
+        in_code = DTYPE_CODE[batch.dtype]
+        W_op, _, _ = self._dec_flat(bf16)
+        self._call("clt_prep_input", batch, in_code, mu_i, sd_i, xn, int(bf16), B, L, D, s)
+        self._call("clt_encoder_fwd_store", xn, self._operand(enc.W, bf16), z, B, L, D, F, int(bf16), self.status, s)
+        kk = max(k, 1)
+        idx = ws.get("idx", (L, B, kk), torch.int32, dev)
+        val = ws.get("val", (L, B, kk), torch.float32, dev)
+        if k > 0:
+            self._call("clt_select_topk", z, enc.b.data, idx, val, self.fired, B, L, F, k, int(bf16), s)
+        else:
+            idx.zero_()
+            val.zero_()
+        dead = ws.get("dead", (L, F), torch.uint8, dev)
+        self._call("clt_dead_update", mod.last_active, self.fired, dead, B, int(mod.tokens_till_dead), L, F, s)
+        aux = None
+        aux_recon = None
+        aux_scale = float(h.get("aux_loss_scale", 0.0))
+        if k_aux > 0:
+            dead_list = ws.get("dead_list", (L, F), torch.int32, dev)
+            n_dead = ws.get("n_dead", (L,), torch.int32, dev)
+            self._call("clt_dead_compact", dead, dead_list, n_dead, L, F, s)
+            nd = int(n_dead.max())                      # host read: sizes the compacted contractions
+            nd_pad = max(64, _round_up(nd, 64))
+            a_aux = ws.get("a_aux", (L, B, nd_pad), T, dev)
+            self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, a_aux, B, L, F, k_aux, nd_pad, int(bf16), s)
+            P = W_op.shape[0]
+            w_c = ws.get("w_c", (P, nd_pad, D), T, dev)
+            self._call("clt_gather_rows", W_op, dead_list, n_dead, w_c, L, F, D, nd_pad, crosslayer, int(bf16), s)
+            aux_recon = ws.get("aux_recon", (B, L, D), torch.float32, dev)
+            self._call("clt_decoder_dense_fwd", a_aux, w_c, dec.b.data, aux_recon, B, L, D, nd_pad, crosslayer,
+                       int(bf16), self.status, s)
+            aux = dict(dead_list=dead_list, n_dead=n_dead, nd_pad=nd_pad, a_aux=a_aux, w_c=w_c)
+        self._call("clt_sparse_decoder_fwd", idx, val, W_op, dec.b.data, recon, B, L, D, F, kk, crosslayer, int(bf16),
+                   self.status, s)
+        self._call("clt_loss_fwd", recon, aux_recon, batch, in_code, mu_o, sd_o, acc[2:4], B, L, D, s)
+        self._call("clt_finalize_loss", acc[2:4], None, out[0:1], out[1:5], 1.0 / (B * L * D), 0.0, 0.0,
+                   aux_scale if aux is not None else 0.0, s)
+        return dict(kind="topk", bf16=bf16, batch=batch, B=B, L=L, D=D, F=F, k=kk, crosslayer=crosslayer, out=out,
+                    stats=(mu_i, sd_i, mu_o, sd_o), in_code=in_code, aux=aux, aux_scale=aux_scale, idx=idx, val=val)
+
+    def _backward_topk(self, c, gscale):
+        model = self.module.model
+        enc, dec = model.encoder, model.decoder
+        B, L, D, F, k, bf16 = c["B"], c["L"], c["D"], c["F"], c["k"], c["bf16"]
+        cross = c["crosslayer"]
+        dev = c["batch"].device
+        T = torch.bfloat16 if bf16 else torch.float32
+        s = stream_ptr()
+        ws = self.ws
+        xn = ws.buf["xn"]
+        recon = ws.buf["recon"][: B * L * D].view(B, L, D)
+        aux = c["aux"]
+        drecon = ws.get("drecon", (L, B, D), T, dev)
+        daux = ws.get("daux", (L, B, D), T, dev) if aux is not None else None
+        _, _, mu_o, sd_o = c["stats"]
+        g = self.flat.grad
+        gview = lambda p: self.flat.view_of(p, g)
+        gview(dec.b).zero_()
+        gs = gscale.detach().to(torch.float32).reshape(1).contiguous()
+        self._call("clt_loss_bwd", recon, ws.buf["aux_recon"] if aux is not None else None, c["batch"], c["in_code"],
+                   mu_o, sd_o, gs, c["aux_scale"] if aux is not None else 0.0, drecon, daux, int(bf16), gview(dec.b),
+                   B, L, D, s)
+        W_op, _, dW_dec = self._dec_flat(bf16)
+        idx, val = c["idx"], c["val"]
+        col_ptr = ws.get("col_ptr", (L, F + 1), torch.int32, dev)
+        cursor = ws.get("cursor", (L, F), torch.int32, dev)
+        ent = ws.get("ent", (L, B * k), torch.int32, dev)
+        dval = ws.get("dval", (L, B, k), torch.float32, dev)
+        self._call("clt_csc_build", idx, val, col_ptr, cursor, ent, B, L, F, k, self.status, s)
+        self._call("clt_sparse_bwd_dec", col_ptr, ent, val, W_op, drecon, dW_dec, dval, B, L, D, F, k, cross,
+                   int(bf16), s)
+        self._call("clt_sparse_bwd_enc", col_ptr, ent, dval, xn, gview(enc.W), gview(enc.b), B, L, D, F, k, int(bf16), s)
+        if aux is not None:
+            nd_pad, a_aux, w_c = aux["nd_pad"], aux["a_aux"], aux["w_c"]
+            dl, n_dead = aux["dead_list"], aux["n_dead"]
+            P = w_c.shape[0]
+            zeros_b = ws.get("zeros_b", (L, nd_pad), torch.float32, dev, zero=True)
+            dpre_c = ws.get("dpre_c", (L, B, nd_pad), T, dev)
+            db_c = ws.get("db_c", (L, nd_pad), torch.float32, dev)
+            db_c.zero_()
+            # gradient w.r.t. the auxiliary features, ReLU-masked by the selection (a_aux > 0)
+            self._call("clt_decoder_dense_bwd_dfeat", daux, w_c, a_aux, zeros_b, None, None, dpre_c, None, db_c, None,
+                       1.0, 0.0, 1.0, 0.0, 0, None, B, L, D, nd_pad, cross, int(bf16), self.status, s)
+            dW_c = ws.get("dW_c", (P, nd_pad, D), torch.float32, dev)
+            self._call("clt_decoder_dense_bwd_dw", a_aux, daux, dW_c, None, None, B, L, D, nd_pad, cross, int(bf16),
+                       self.status, s)
+            self._call("clt_scatter_rows", dW_c, dl, n_dead, dW_dec, L, F, D, nd_pad, cross, s)
+            dWe_c = ws.get("dWe_c", (L, D, nd_pad), torch.float32, dev)
+            self._call("clt_encoder_dense_bwd_dw", xn, dpre_c, dWe_c, B, L, D, nd_pad, int(bf16), self.status, s)
+            self._call("clt_scatter_cols", dWe_c, db_c, dl, n_dead, gview(enc.W), gview(enc.b), L, D, F, nd_pad, s)
 
 
 class _StepFunction(torch.autograd.Function):

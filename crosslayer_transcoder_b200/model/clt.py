@@ -67,6 +67,8 @@ class Encoder(_Layered):
 class Decoder(_Layered):
     """Per-layer decoder: layer l's features write only to layer l's output."""
 
+    crosslayer = False
+
     def __init__(self, d_acts: int, d_features: int, n_layers: int):
         super().__init__(d_acts, d_features, n_layers)
         self.W = nn.Parameter(torch.empty(n_layers, d_features, d_acts))
@@ -103,6 +105,8 @@ class Decoder(_Layered):
 
 class CrosslayerDecoder(_Layered):
     """Features of source layer s write to every target layer t >= s through ``W_t[s]``."""
+
+    crosslayer = True
 
     def __init__(self, d_acts: int, d_features: int, n_layers: int):
         super().__init__(d_acts, d_features, n_layers)

@@ -115,6 +115,62 @@ int clt_norm_coef(const float* dnorm, const float* norm, float* out, int count, 
 int clt_dead_update(int64_t* last_active, uint32_t* fired_bits, uint8_t* dead, int64_t B, int64_t limit, int L,
                     int F, clt_stream_t stream);
 
+/* ---- TopK path --------------------------------------------------------------------------- */
+
+/* PerLayerTopK._training_forward (crosslayer_transcoder/model/topk.py:53-63) on pre = z + b_enc:
+ * idx / val [L, B, k] hold the (at most k) largest positive pre-activations of every row, unused
+ * slots idx 0 / val 0 (a kept value that is not positive is zero after the ReLU and gets no
+ * gradient, so it is not stored).  fired_bits as in clt_encoder_fwd_act; may be NULL. */
+int clt_select_topk(const void* z, const float* b_enc, int* idx_out, float* val_out, uint32_t* fired_bits,
+                    int B, int L, int F, int k, int bf16, clt_stream_t stream);
+
+/* Ascending list of the dead features of every layer: dead_list [L, F], n_dead [L]
+ * (idxs_dead of clt_lightning.py:286, compacted). */
+int clt_dead_compact(const uint8_t* dead, int* dead_list, int* n_dead, int L, int F, clt_stream_t stream);
+
+/* topk_aux(where(dead, pre, -inf)) (clt_lightning.py:544-546) written as the dense matrix of the
+ * compacted dead features: a_out[l, b, j] = pre[l, b, dead_list[l][j]] if it is among the k_aux
+ * largest positive dead pre-activations of the row (ties with the k_aux-th are all kept), else 0;
+ * [L, B, nd_pad] in T, columns j >= n_dead[l] are 0. */
+int clt_select_aux(const void* z, const float* b_enc, const int* dead_list, const int* n_dead, void* a_out,
+                   int B, int L, int F, int k_aux, int nd_pad, int bf16, clt_stream_t stream);
+
+/* CrosslayerDecoder.forward / Decoder.forward (clt.py:334-343, 241-248) on the selected features:
+ * recon[b,t,:] = b_dec[t] + sum_{s<=t} sum_j val[s,b,j] W_dec[pair(t,s), idx[s,b,j], :]. */
+int clt_sparse_decoder_fwd(const int* idx, const float* val, const void* W_dec, const float* b_dec, float* recon,
+                           int B, int L, int D, int F, int k, int crosslayer, int bf16, int* status,
+                           clt_stream_t stream);
+
+/* Feature-major copy of the selection: col_ptr [L, F+1], ent [L, B*k] (entry = b*k + j, grouped by
+ * feature).  cursor [L, F] is scratch. */
+int clt_csc_build(const int* idx, const float* val, int* col_ptr, int* cursor, int* ent, int B, int L, int F,
+                  int k, int* status, clt_stream_t stream);
+
+/* Backward of the decoder on the selected features (autograd of clt.py:334-343 restricted to the
+ * non-zero features): dval[s,b,j] = sum_{t>=s} drecon[t,b,:] . W_dec[pair(t,s), idx, :] and
+ * dW_dec[pair(t,s), f, :] = sum_{(b,j): idx = f} val drecon[t,b,:]; every row of dW is written. */
+int clt_sparse_bwd_dec(const int* col_ptr, const int* ent, const float* val, const void* W_dec,
+                       const void* drecon, float* dW, float* dval, int B, int L, int D, int F, int k,
+                       int crosslayer, int bf16, clt_stream_t stream);
+
+/* Backward of the encoder on the selected features (autograd of clt.py:157-165 through the TopK
+ * scatter): dW_enc[l,:,f] = sum_{(b,j): idx = f} dval xn[l,b,:], db_enc[l,f] = sum dval; every
+ * element of both is written. */
+int clt_sparse_bwd_enc(const int* col_ptr, const int* ent, const float* dval, const void* xn, float* dW_enc,
+                       float* db_enc, int B, int L, int D, int F, int k, int bf16, clt_stream_t stream);
+
+/* Compaction helpers of the auxiliary dead-feature path (clt_lightning.py:544-549 run as dense
+ * contractions over the dead features only):
+ * gather_rows : out[p, j, :] = W_dec[p, dead_list[s(p)][j], :]              (T, [P, nd_pad, D])
+ * scatter_rows: dW_dec[p, dead_list[s(p)][j], :] += src[p, j, :]            (fp32)
+ * scatter_cols: dW_enc[l, :, dead_list[l][j]] += src[l, :, j]; db_enc likewise (fp32) */
+int clt_gather_rows(const void* W_dec, const int* dead_list, const int* n_dead, void* out, int L, int F, int D,
+                    int nd_pad, int crosslayer, int bf16, clt_stream_t stream);
+int clt_scatter_rows(const float* src, const int* dead_list, const int* n_dead, float* dW_dec, int L, int F,
+                     int D, int nd_pad, int crosslayer, clt_stream_t stream);
+int clt_scatter_cols(const float* src, const float* db_src, const int* dead_list, const int* n_dead,
+                     float* dW_enc, float* db_enc, int L, int D, int F, int nd_pad, clt_stream_t stream);
+
 /* torch.optim.Adam / AdamW step (clt_lightning.py:339-352) over one flat fp32 buffer; `step`
  * counts from 1.  shadow_bf16 (may be NULL) receives the bf16 copy of the new parameters. */
 int clt_adam_step(float* p, const float* g, float* m, float* v, void* shadow_bf16, int64_t n, float lr,
