@@ -208,10 +208,15 @@ __global__ void dead_compact_kernel(const unsigned char* __restrict__ dead, int*
 // largest positive dead pre-activations of the row, else 0   (j < nd_pad; 0 beyond n_dead[l]).
 // Values tied with the k_aux-th are all kept.
 // ---------------------------------------------------------------------------------------
+// mode 0: threshold computed here, dense row written (single GPU)
+// mode 1: only the row's candidates are written: cand_out[row, 0..k_aux) = its k_aux largest positive
+//         dead pre-activations (0-padded), for the exchange between feature shards
+// mode 2: threshold given (thr[row], from the exchanged candidates), dense row written
 template <class T>
 __global__ void __launch_bounds__(kSelThreads)
 select_aux_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, const int* __restrict__ dead_list,
-                  const int* __restrict__ n_dead, T* __restrict__ a_out, int B, int F, int k_aux, int nd_pad) {
+                  const int* __restrict__ n_dead, T* __restrict__ a_out, float* __restrict__ cand_out,
+                  const float* __restrict__ thr, int mode, int B, int F, int k_aux, int nd_pad) {
   extern __shared__ float cand[];  // pre-activations of the dead features of this row
   const int row = blockIdx.x;
   const int l = row / B;
@@ -224,8 +229,32 @@ select_aux_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, cons
     cand[j] = ld_as_float<T>(zr, f) + __ldg(br + f);
   }
   __syncthreads();
-  auto key_at = [&](int j) { return positive_key(cand[j]); };
-  const RowSelect sel = radix_select(nd, k_aux, key_at);
+  RowSelect sel{0u, 0};
+  if (mode == 2) {
+    sel.T = positive_key(thr[row]);
+  } else {
+    auto key_at = [&](int j) { return positive_key(cand[j]); };
+    sel = radix_select(nd, k_aux, key_at);
+  }
+  if (mode == 1) {
+    __shared__ int n_out, n_tie;
+    if (threadIdx.x == 0) n_out = 0, n_tie = 0;
+    __syncthreads();
+    float* co = cand_out + (size_t)row * k_aux;
+    for (int j = threadIdx.x; j < nd; j += kSelThreads) {
+      const float c = cand[j];
+      const unsigned key = positive_key(c);
+      bool take = key > sel.T;
+      if (!take && key != 0u && key == sel.T) take = atomicAdd(&n_tie, 1) < sel.r;
+      if (take) {
+        const int slot = atomicAdd(&n_out, 1);
+        if (slot < k_aux) co[slot] = c;
+      }
+    }
+    __syncthreads();
+    for (int s = n_out + threadIdx.x; s < k_aux; s += kSelThreads) co[s] = 0.f;
+    return;
+  }
   T* ao = a_out + (size_t)row * nd_pad;
   for (int j = threadIdx.x; j < nd_pad; j += kSelThreads) {
     float v = 0.f;
@@ -238,6 +267,39 @@ select_aux_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, cons
       ao[j] = __float2bfloat16_rn(v);
     else
       ao[j] = v;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Exchange between feature shards: every rank contributes its k best values of a row;
+// thr[row] = the k-th largest positive value among all R * k of them (0 when there are fewer
+// than k positive ones, i.e. every positive value stays).  vals [R, rows, k].
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kSelThreads)
+topk_threshold_kernel(const float* __restrict__ vals, float* __restrict__ thr, long long rows, int R, int k) {
+  const long long row = blockIdx.x;
+  auto key_at = [&](int i) { return positive_key(__ldg(vals + ((size_t)(i / k) * rows + row) * k + i % k)); };
+  const RowSelect sel = radix_select(R * k, k, key_at);
+  if (threadIdx.x == 0) thr[row] = __uint_as_float(sel.T);
+}
+
+// Keep the local candidates at or above the exchanged threshold (ties are all kept), clear the
+// others, mark the fired features.
+__global__ void topk_apply_threshold_kernel(const int* __restrict__ idx, float* __restrict__ val,
+                                            const float* __restrict__ thr, unsigned* __restrict__ fired_bits,
+                                            long long total, int B, int F, int k) {
+  const int words = (F + 31) / 32;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / k;
+    const float v = val[i];
+    if (v <= 0.f) continue;
+    if (positive_key(v) < positive_key(thr[row])) {
+      val[i] = 0.f;
+    } else if (fired_bits != nullptr) {
+      const int l = (int)(row / B), f = idx[i];
+      atomicOr(fired_bits + (size_t)l * words + f / 32, 1u << (f & 31));
+    }
   }
 }
 
@@ -275,11 +337,15 @@ int clt_dead_compact(const uint8_t* dead, int* dead_list, int* n_dead, int L, in
   return 0;
 }
 
-int clt_select_aux(const void* z, const float* b_enc, const int* dead_list, const int* n_dead, void* a_out, int B,
-                   int L, int F, int k_aux, int nd_pad, int bf16, clt_stream_t stream) {
+int clt_select_aux(const void* z, const float* b_enc, const int* dead_list, const int* n_dead, void* a_out,
+                   float* cand_out, const float* thr, int mode, int B, int L, int F, int k_aux, int nd_pad, int bf16,
+                   clt_stream_t stream) {
   CLT_CHECK_ARG(B > 0 && L > 0 && F > 0 && nd_pad > 0, "select_aux: bad dims B=%d L=%d F=%d nd_pad=%d", B, L, F, nd_pad);
   CLT_CHECK_ARG(k_aux >= 1, "select_aux: k_aux=%d must be positive", k_aux);
-  CLT_CHECK_ARG(z && b_enc && dead_list && n_dead && a_out, "select_aux: null pointer");
+  CLT_CHECK_ARG(mode >= 0 && mode <= 2, "select_aux: unknown mode %d", mode);
+  CLT_CHECK_ARG(z && b_enc && dead_list && n_dead, "select_aux: null pointer");
+  CLT_CHECK_ARG(mode == 1 ? cand_out != nullptr : a_out != nullptr, "select_aux: missing output for mode %d", mode);
+  CLT_CHECK_ARG(mode != 2 || thr != nullptr, "select_aux: mode 2 needs the thresholds");
   const size_t smem = (size_t)nd_pad * sizeof(float);
   CLT_CHECK_ARG(smem <= 200 * 1024, "select_aux: %d dead features per layer exceed the shared-memory candidate buffer",
                 nd_pad);
@@ -289,13 +355,33 @@ int clt_select_aux(const void* z, const float* b_enc, const int* dead_list, cons
     auto kern = select_aux_kernel<__nv_bfloat16>;
     CLT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<(unsigned)rows, kSelThreads, smem, s>>>((const __nv_bfloat16*)z, b_enc, dead_list, n_dead,
-                                                   (__nv_bfloat16*)a_out, B, F, k_aux, nd_pad);
+                                                   (__nv_bfloat16*)a_out, cand_out, thr, mode, B, F, k_aux, nd_pad);
   } else {
     auto kern = select_aux_kernel<float>;
     CLT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<(unsigned)rows, kSelThreads, smem, s>>>((const float*)z, b_enc, dead_list, n_dead, (float*)a_out, B, F,
-                                                   k_aux, nd_pad);
+    kern<<<(unsigned)rows, kSelThreads, smem, s>>>((const float*)z, b_enc, dead_list, n_dead, (float*)a_out, cand_out,
+                                                   thr, mode, B, F, k_aux, nd_pad);
   }
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int clt_topk_threshold(const float* vals, float* thr, int64_t rows, int R, int k, clt_stream_t stream) {
+  CLT_CHECK_ARG(rows > 0 && R > 0 && k > 0 && rows < (1ll << 31), "topk_threshold: bad dims");
+  CLT_CHECK_ARG(vals && thr, "topk_threshold: null pointer");
+  topk_threshold_kernel<<<(unsigned)rows, kSelThreads, 0, (cudaStream_t)stream>>>(vals, thr, rows, R, k);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int clt_topk_apply_threshold(const int* idx, float* val, const float* thr, uint32_t* fired_bits, int B, int L, int F,
+                             int k, clt_stream_t stream) {
+  CLT_CHECK_ARG(B > 0 && L > 0 && F > 0 && k > 0, "topk_apply_threshold: bad dims");
+  CLT_CHECK_ARG(idx && val && thr, "topk_apply_threshold: null pointer");
+  const long long total = (long long)L * B * k;
+  const long long want = (total + 255) / 256;
+  topk_apply_threshold_kernel<<<(unsigned)(want < 148 * 16 ? want : 148 * 16), 256, 0, (cudaStream_t)stream>>>(
+      idx, val, thr, fired_bits, total, B, F, k);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

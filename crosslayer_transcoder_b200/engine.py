@@ -361,10 +361,15 @@ class StepEngine:
         ws = self.ws
         xn = ws.get("xn", (L, B, D), T, dev)
         z = ws.get("z", (L, B, F), T, dev)
-        rbuf = ws.get("recon", (B * L * D + 8,), torch.float32, dev)
-        recon, acc = rbuf[: B * L * D].view(B, L, D), rbuf[B * L * D:]
+        # [reconstruction | auxiliary reconstruction | 8-float tail of loss sums]: the first two are
+        # partial sums over this rank's features and are reduced together across feature shards
+        n_rec = B * L * D
+        rbuf = ws.get("recon2", (2 * n_rec + 8,), torch.float32, dev)
+        recon, aux_recon_buf, acc = rbuf[:n_rec].view(B, L, D), rbuf[n_rec:2 * n_rec].view(B, L, D), rbuf[2 * n_rec:]
         out = torch.empty(5, dtype=torch.float32, device=dev)
         acc.zero_()
+        world, group = getattr(mod, "tp_world", 1), getattr(mod, "tp_group", None)
+        bias = dec.b.data if getattr(mod, "tp_rank", 0) == 0 else None      # added once, not per shard
         in_code = DTYPE_CODE[batch.dtype]
         W_op, _, _ = self._dec_flat(bf16)
         self._call("clt_prep_input", batch, in_code, mu_i, sd_i, xn, int(bf16), B, L, D, s)
@@ -373,7 +378,18 @@ class StepEngine:
         idx = ws.get("idx", (L, B, kk), torch.int32, dev)
         val = ws.get("val", (L, B, kk), torch.float32, dev)
         if k > 0:
-            self._call("clt_select_topk", z, enc.b.data, idx, val, self.fired, B, L, F, k, int(bf16), s)
+            self._call("clt_select_topk", z, enc.b.data, idx, val, self.fired if world == 1 else None, B, L, F, k,
+                       int(bf16), s)
+            if world > 1:
+                # every shard offers its k best values per row; the k-th largest of all of them is the
+                # row's threshold, and each shard keeps its candidates at or above it
+                from .parallel import all_gather
+
+                val_all = ws.get("val_all", (world, L, B, kk), torch.float32, dev)
+                all_gather(val_all, val, group)
+                thr = ws.get("thr_main", (L, B), torch.float32, dev)
+                self._call("clt_topk_threshold", val_all, thr, L * B, world, k, s)
+                self._call("clt_topk_apply_threshold", idx, val, thr, self.fired, B, L, F, k, s)
         else:
             idx.zero_()
             val.zero_()
@@ -389,16 +405,34 @@ class StepEngine:
             nd = int(n_dead.max())                      # host read: sizes the compacted contractions
             nd_pad = max(64, _round_up(nd, 64))
             a_aux = ws.get("a_aux", (L, B, nd_pad), T, dev)
-            self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, a_aux, B, L, F, k_aux, nd_pad, int(bf16), s)
+            if world == 1:
+                self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, a_aux, None, None, 0, B, L, F, k_aux,
+                           nd_pad, int(bf16), s)
+            else:
+                from .parallel import all_gather
+
+                cand = ws.get("aux_cand", (L, B, k_aux), torch.float32, dev)
+                self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, None, cand, None, 1, B, L, F, k_aux,
+                           nd_pad, int(bf16), s)
+                cand_all = ws.get("aux_cand_all", (world, L, B, k_aux), torch.float32, dev)
+                all_gather(cand_all, cand, group)
+                thr_aux = ws.get("thr_aux", (L, B), torch.float32, dev)
+                self._call("clt_topk_threshold", cand_all, thr_aux, L * B, world, k_aux, s)
+                self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, a_aux, None, thr_aux, 2, B, L, F, k_aux,
+                           nd_pad, int(bf16), s)
             P = W_op.shape[0]
             w_c = ws.get("w_c", (P, nd_pad, D), T, dev)
             self._call("clt_gather_rows", W_op, dead_list, n_dead, w_c, L, F, D, nd_pad, crosslayer, int(bf16), s)
-            aux_recon = ws.get("aux_recon", (B, L, D), torch.float32, dev)
-            self._call("clt_decoder_dense_fwd", a_aux, w_c, dec.b.data, aux_recon, B, L, D, nd_pad, crosslayer,
+            aux_recon = aux_recon_buf
+            self._call("clt_decoder_dense_fwd", a_aux, w_c, bias, aux_recon, B, L, D, nd_pad, crosslayer,
                        int(bf16), self.status, s)
             aux = dict(dead_list=dead_list, n_dead=n_dead, nd_pad=nd_pad, a_aux=a_aux, w_c=w_c)
-        self._call("clt_sparse_decoder_fwd", idx, val, W_op, dec.b.data, recon, B, L, D, F, kk, crosslayer, int(bf16),
+        self._call("clt_sparse_decoder_fwd", idx, val, W_op, bias, recon, B, L, D, F, kk, crosslayer, int(bf16),
                    self.status, s)
+        if world > 1:
+            from .parallel import all_reduce_sum
+
+            all_reduce_sum(rbuf[: (2 if aux is not None else 1) * n_rec], group)
         self._call("clt_loss_fwd", recon, aux_recon, batch, in_code, mu_o, sd_o, acc[2:4], B, L, D, s)
         self._call("clt_finalize_loss", acc[2:4], None, out[0:1], out[1:5], 1.0 / (B * L * D), 0.0, 0.0,
                    aux_scale if aux is not None else 0.0, s)
@@ -415,7 +449,9 @@ class StepEngine:
         s = stream_ptr()
         ws = self.ws
         xn = ws.buf["xn"]
-        recon = ws.buf["recon"][: B * L * D].view(B, L, D)
+        n_rec = B * L * D
+        recon = ws.buf["recon2"][:n_rec].view(B, L, D)
+        aux_recon = ws.buf["recon2"][n_rec:2 * n_rec].view(B, L, D)
         aux = c["aux"]
         drecon = ws.get("drecon", (L, B, D), T, dev)
         daux = ws.get("daux", (L, B, D), T, dev) if aux is not None else None
@@ -424,7 +460,7 @@ class StepEngine:
         gview = lambda p: self.flat.view_of(p, g)
         gview(dec.b).zero_()
         gs = gscale.detach().to(torch.float32).reshape(1).contiguous()
-        self._call("clt_loss_bwd", recon, ws.buf["aux_recon"] if aux is not None else None, c["batch"], c["in_code"],
+        self._call("clt_loss_bwd", recon, aux_recon if aux is not None else None, c["batch"], c["in_code"],
                    mu_o, sd_o, gs, c["aux_scale"] if aux is not None else 0.0, drecon, daux, int(bf16), gview(dec.b),
                    B, L, D, s)
         W_op, _, dW_dec = self._dec_flat(bf16)

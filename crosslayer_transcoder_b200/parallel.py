@@ -8,8 +8,10 @@ its module with its own contiguous slice of the feature axis
     encoder.W[:, :, lo:hi]  encoder.b[:, lo:hi]  theta[:, :, lo:hi]  decoder.W_t[:, lo:hi, :]
 
 (``decoder.b`` and the standardizers are replicated), every rank receives the same
-batch, and the step's one exchange is the sum of the partial normalised
-reconstructions (NCCL all-reduce over NVLink).  Backward needs no collective: the
+batch, and the step's exchange is the sum of the partial normalised reconstructions
+(NCCL all-reduce over NVLink).  The TopK selections, which the reference's plan does not
+support, add one all-gather of each shard's k best values per row, from which every
+rank derives the row's global threshold.  Backward needs no collective: the
 reconstruction gradient is replicated and every parameter gradient is shard-local.
 """
 from __future__ import annotations
@@ -40,3 +42,11 @@ def attach(module, group: Optional[dist.ProcessGroup] = None) -> None:
 
 def all_reduce_sum(buf: torch.Tensor, group) -> None:
     dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
+
+
+def all_gather(out: torch.Tensor, part: torch.Tensor, group) -> None:
+    """out[r] = rank r's ``part`` (out has a leading axis of the group size)."""
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(out, part.contiguous(), group=group)
+    else:
+        dist.all_gather(list(out.unbind(0)), part.contiguous(), group=group)

@@ -131,9 +131,20 @@ int clt_dead_compact(const uint8_t* dead, int* dead_list, int* n_dead, int L, in
 /* topk_aux(where(dead, pre, -inf)) (clt_lightning.py:544-546) written as the dense matrix of the
  * compacted dead features: a_out[l, b, j] = pre[l, b, dead_list[l][j]] if it is among the k_aux
  * largest positive dead pre-activations of the row (ties with the k_aux-th are all kept), else 0;
- * [L, B, nd_pad] in T, columns j >= n_dead[l] are 0. */
+ * [L, B, nd_pad] in T, columns j >= n_dead[l] are 0.
+ * mode 0: as above.  mode 1 (feature shards): write only cand_out [L, B, k_aux], this shard's k_aux
+ * best values per row (0-padded).  mode 2: a_out from the exchanged per-row threshold thr [L, B]. */
 int clt_select_aux(const void* z, const float* b_enc, const int* dead_list, const int* n_dead, void* a_out,
-                   int B, int L, int F, int k_aux, int nd_pad, int bf16, clt_stream_t stream);
+                   float* cand_out, const float* thr, int mode, int B, int L, int F, int k_aux, int nd_pad,
+                   int bf16, clt_stream_t stream);
+
+/* Selection across feature shards (the reference has no counterpart: its tensor-parallel plan
+ * rejects TopK, crosslayer_transcoder/model/parallel.py:269-274).  vals [R, rows, k] holds every
+ * shard's k best values per row; thr[row] = the k-th largest positive one (0: keep all). */
+int clt_topk_threshold(const float* vals, float* thr, int64_t rows, int R, int k, clt_stream_t stream);
+/* Clear the local candidates below thr (ties stay), mark the fired features. */
+int clt_topk_apply_threshold(const int* idx, float* val, const float* thr, uint32_t* fired_bits, int B, int L,
+                             int F, int k, clt_stream_t stream);
 
 /* CrosslayerDecoder.forward / Decoder.forward (clt.py:334-343, 241-248) on the selected features:
  * recon[b,t,:] = b_dec[t] + sum_{s<=t} sum_j val[s,b,j] W_dec[pair(t,s), idx[s,b,j], :]. */

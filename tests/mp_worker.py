@@ -1,0 +1,84 @@
+"""Worker of the multi-GPU parity test: one process per GPU (launched by torch.distributed.run),
+each holding one feature shard; rank 0 compares the gathered result with the unsharded CPU oracle."""
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+
+from crosslayer_transcoder_b200 import parallel, synthetic  # noqa: E402
+from oracle import clt_oracle as O  # noqa: E402
+from tests.helpers import build_module, oracle_for_spec, rel_err, spec_inputs  # noqa: E402
+
+
+def shard_weights(w, lo, hi, crosslayer):
+    out = {"W_enc": w["W_enc"][:, :, lo:hi].contiguous(), "b_enc": w["b_enc"][:, lo:hi].contiguous(),
+           "b_dec": w["b_dec"]}
+    out["W_dec"] = [x[:, lo:hi].contiguous() for x in w["W_dec"]] if crosslayer else w["W_dec"][:, lo:hi].contiguous()
+    if "theta" in w:
+        out["theta"] = w["theta"][:, :, lo:hi].contiguous()
+    return out
+
+
+def main():
+    kind, prec = sys.argv[1], sys.argv[2]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+    dev = torch.device(f"cuda:{local}")
+    bf16 = prec == "bf16"
+    if kind == "jumprelu":
+        spec = synthetic.WorkloadSpec("mp_jr", 3, 128, 512, 200, "jumprelu", True, bf16, rank_u=16, n_outlier=2,
+                                      lambda_sparsity=4e-4, pre_actv_loss=3e-6, lr=1e-3)
+    else:
+        spec = synthetic.WorkloadSpec("mp_topk", 3, 128, 1024, 200, "topk", True, bf16, rank_u=16, n_outlier=2, k=8,
+                                      k_aux=32, aux_loss_scale=1 / 32, tokens_till_dead=1000, dead_fraction=0.2,
+                                      lr=1e-3)
+    batch, w, la = spec_inputs(spec)
+    lo, hi = parallel.feature_shard(spec.d_features, rank, world)
+    mod = build_module(spec, shard_weights(w, lo, hi, spec.crosslayer), dev, last_active=la[:, lo:hi].contiguous())
+    parallel.attach(mod)
+    loss = mod.training_step(batch.to(dev), 0)
+    loss.backward()
+    mod._engine.check_status("multi-GPU step")
+    m = mod.model
+    # gather the feature-sharded gradients on every rank
+    def gather(t, dim):
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t.contiguous())
+        return torch.cat(parts, dim=dim).cpu()
+
+    g_enc = gather(m.encoder.W.grad, 2)
+    g_benc = gather(m.encoder.b.grad, 1)
+    g_dec = [gather(x.grad, 1) for x in m.decoder.blocks()]
+    g_bdec = m.decoder.b.grad.cpu()
+    la_out = gather(mod.last_active, 1)
+    ok = True
+    if rank == 0:
+        P, H, stats, kw = oracle_for_spec(spec, batch, w, la)
+        ref, rg = O.step_with_grads(P, batch, stats, H, **kw)
+        tol = 2e-2 if bf16 else 1e-4
+        errs = {"loss": rel_err(loss.detach().cpu(), ref.loss), "W_enc": rel_err(g_enc, rg[0]),
+                "b_enc": rel_err(g_benc, rg[1]), "b_dec": rel_err(g_bdec, rg[2 + len(g_dec)])}
+        for t, g in enumerate(g_dec):
+            errs[f"W_dec{t}"] = rel_err(g, rg[2 + t])
+        bad = {k: v for k, v in errs.items() if not v < tol}
+        if kind == "topk" and not torch.equal(la_out, ref.last_active):
+            bad["last_active"] = 1.0
+        print("errors", errs)
+        ok = not bad
+        if bad:
+            print("FAILED", bad)
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.broadcast(flag, 0)
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag) else 1)
+
+
+if __name__ == "__main__":
+    main()

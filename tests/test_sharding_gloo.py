@@ -1,0 +1,76 @@
+"""The feature-sharding exchange steps on CPU ranks (gloo, world size 2): partial reconstructions
+summed by all-reduce, and the TopK threshold derived from the all-gathered per-shard candidates,
+both against the unsharded oracle."""
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, str(ROOT))
+    from crosslayer_transcoder_b200 import parallel, synthetic
+    from oracle import clt_oracle as O
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        spec = synthetic.WorkloadSpec("gloo", 3, 32, 64, 40, "topk", True, False, rank_u=8, n_outlier=1, k=4)
+        batch = synthetic.make_batch(spec, seed=3)
+        w = synthetic.make_weights(spec, seed=4)
+        lo, hi = parallel.feature_shard(spec.d_features, rank, world)
+        ws = synthetic.make_weights(spec, seed=4, f_lo=lo, f_hi=hi)          # this rank's slice, drawn independently
+        assert torch.equal(ws["W_enc"], w["W_enc"][:, :, lo:hi])
+        assert all(torch.equal(a, b[:, lo:hi]) for a, b in zip(ws["W_dec"], w["W_dec"]))
+        stats = O.standardizer_stats(batch)
+        xn = (batch[:, 0] - stats[0]) / stats[1]
+        full = O.Params(w["W_enc"], w["b_enc"], w["W_dec"], w["b_dec"])
+        part = O.Params(ws["W_enc"], ws["b_enc"], ws["W_dec"], torch.zeros_like(ws["b_dec"]))
+        pre_full = O.encoder_fwd(xn, full, False)
+        feat_full = O.per_layer_topk(pre_full, spec.k)
+        # --- selection across shards: all-gather the k best values per row, threshold, filter
+        pre = O.encoder_fwd(xn, part, False)
+        vals = torch.topk(pre, spec.k, dim=-1).values.clamp_min(0).permute(1, 0, 2).contiguous()    # [L, B, k]
+        allv = torch.empty(world, *vals.shape)
+        parallel.all_gather(allv, vals, dist.group.WORLD)
+        merged = allv.permute(1, 2, 0, 3).reshape(*vals.shape[:2], -1)                              # [L, B, R k]
+        thr = torch.topk(merged, spec.k, dim=-1).values[..., -1].permute(1, 0).unsqueeze(-1)        # [B, L, 1]
+        feat = torch.where((pre >= thr) & (pre > 0), pre, torch.zeros_like(pre))
+        assert torch.equal(feat, feat_full[:, :, lo:hi])
+        # --- partial reconstructions: sum over shards == unsharded decoder
+        recon = O.decoder_fwd(feat, part, False).contiguous()
+        parallel.all_reduce_sum(recon, dist.group.WORLD)
+        recon = recon + w["b_dec"]
+        ref = O.decoder_fwd(feat_full, full, False)
+        assert torch.allclose(recon, ref, rtol=1e-5, atol=1e-6)
+        q.put((rank, "ok"))
+    except Exception as e:  # pragma: no cover
+        q.put((rank, repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_cpu_ranks_exchange():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, 29611, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=30)
+    assert all(v == "ok" for _, v in res), res
+
+
+def test_feature_shard_bounds():
+    from crosslayer_transcoder_b200 import parallel
+    import pytest
+
+    assert parallel.feature_shard(32768, 3, 8) == (12288, 16384)
+    with pytest.raises(ValueError):
+        parallel.feature_shard(100, 0, 8)
