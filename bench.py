@@ -139,7 +139,14 @@ def build_on_device(spec: synthetic.WorkloadSpec, dev, rank: int, world: int):
     elif spec.kind == "topk":
         mod = M.TopKCrossLayerTranscoderModule(topk_aux=M.PerLayerTopK(k=spec.k_aux),
                                                aux_loss_scale=spec.aux_loss_scale, **common)
-        mod.last_active.copy_(synthetic.make_last_active(spec, f_lo=lo, f_hi=hi))
+        la = synthetic.make_last_active(spec, f_lo=lo, f_hi=hi)
+        mod.last_active.copy_(la)
+        # Features marked dead get an encoder bias of -1: like dead features in a real run they stay out of
+        # the top-k (so they stay dead) while a few per cent of their pre-activations are still positive,
+        # which is what the auxiliary loss works on.  With the plain random weights every "dead" feature
+        # would fire within a step and the auxiliary path would see almost no dead features.
+        with torch.no_grad():
+            enc.b[(la > spec.tokens_till_dead).to(enc.b.device)] = -1.0
     else:
         mod = M.CrossLayerTranscoderModule(**common)
     mod = mod.to(dev)

@@ -134,7 +134,50 @@ __device__ __forceinline__ unsigned positive_key(float v) { return v > 0.f ? __f
 // ---------------------------------------------------------------------------------------
 // Main selection: idx/val [L, B, k] of the k largest positive pre-activations per row,
 // unused slots (fewer than k positives) hold idx 0 / val 0.  Marks fired features.
+//
+// Fast path (k <= 256): two sweeps over the row and no histogram.
+//   sweep 1  every thread keeps the maximum of its strided share of the row; the k-th
+//            largest of the 256 thread maxima is a lower bound T_lo of the row's k-th
+//            largest value (the maxima are 256 distinct elements of the row)
+//   sweep 2  the elements >= T_lo (k of them at least, a few more in expectation) go to
+//            a shared-memory candidate list
+//   finish   rank the candidates by counting; rank < k is the selection, slot = rank
+// A row whose candidate list overflows (masses of equal values) falls back to the exact
+// radix select above.
 // ---------------------------------------------------------------------------------------
+constexpr int kCandCap = 1024;
+
+template <class T>
+struct RowReader;
+template <>
+struct RowReader<__nv_bfloat16> {
+  // 8 consecutive elements starting at a multiple of 8
+  __device__ static __forceinline__ void load8(const __nv_bfloat16* z, const float* b, int i, float (&o)[8]) {
+    const uint4 t = __ldg(reinterpret_cast<const uint4*>(z + i));
+    const float4 b0 = __ldg(reinterpret_cast<const float4*>(b + i));
+    const float4 b1 = __ldg(reinterpret_cast<const float4*>(b + i) + 1);
+    o[0] = __uint_as_float(t.x << 16) + b0.x;
+    o[1] = __uint_as_float(t.x & 0xffff0000u) + b0.y;
+    o[2] = __uint_as_float(t.y << 16) + b0.z;
+    o[3] = __uint_as_float(t.y & 0xffff0000u) + b0.w;
+    o[4] = __uint_as_float(t.z << 16) + b1.x;
+    o[5] = __uint_as_float(t.z & 0xffff0000u) + b1.y;
+    o[6] = __uint_as_float(t.w << 16) + b1.z;
+    o[7] = __uint_as_float(t.w & 0xffff0000u) + b1.w;
+  }
+};
+template <>
+struct RowReader<float> {
+  __device__ static __forceinline__ void load8(const float* z, const float* b, int i, float (&o)[8]) {
+    const float4 z0 = __ldg(reinterpret_cast<const float4*>(z + i));
+    const float4 z1 = __ldg(reinterpret_cast<const float4*>(z + i) + 1);
+    const float4 b0 = __ldg(reinterpret_cast<const float4*>(b + i));
+    const float4 b1 = __ldg(reinterpret_cast<const float4*>(b + i) + 1);
+    o[0] = z0.x + b0.x, o[1] = z0.y + b0.y, o[2] = z0.z + b0.z, o[3] = z0.w + b0.w;
+    o[4] = z1.x + b1.x, o[5] = z1.y + b1.y, o[6] = z1.z + b1.z, o[7] = z1.w + b1.w;
+  }
+};
+
 template <class T>
 __global__ void __launch_bounds__(kSelThreads)
 select_topk_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, int* __restrict__ idx_out,
@@ -143,15 +186,84 @@ select_topk_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, int
   const int l = row / B;
   const T* zr = z + (size_t)row * F;
   const float* br = b_enc + (size_t)l * F;
-  auto key_at = [&](int i) { return positive_key(ld_as_float<T>(zr, i) + __ldg(br + i)); };
-  const RowSelect sel = radix_select(F, k, key_at);
-  __shared__ int n_out, n_tie;
-  if (threadIdx.x == 0) n_out = 0, n_tie = 0;
-  __syncthreads();
   int* io = idx_out + (size_t)row * k;
   float* vo = val_out + (size_t)row * k;
   const int words = (F + 31) / 32;
-  for (int i = threadIdx.x; i < F; i += kSelThreads) {
+  const int tid = threadIdx.x;
+
+  __shared__ float tmax[kSelThreads];
+  __shared__ float cand_v[kCandCap];
+  __shared__ int cand_i[kCandCap];
+  __shared__ int n_cand;
+  __shared__ float t_lo;
+
+  bool fast = (k <= kSelThreads) && (F % 8 == 0) && (F >= 8 * kSelThreads);
+  if (fast) {
+    // ---- sweep 1: per-thread maxima
+    float m = 0.f;
+    for (int i = 8 * tid; i < F; i += 8 * kSelThreads) {
+      float v[8];
+      RowReader<T>::load8(zr, br, i, v);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) m = fmaxf(m, v[q]);
+    }
+    tmax[tid] = m;  // 0 when the thread saw no positive value
+    if (tid == 0) n_cand = 0, t_lo = 0.f;
+    __syncthreads();
+    // k-th largest of the 256 maxima by rank counting (ties ordered by thread id)
+    int rank = 0;
+    for (int j = 0; j < kSelThreads; ++j) {
+      const float o = tmax[j];
+      rank += (o > m || (o == m && j < tid)) ? 1 : 0;
+    }
+    if (rank == k - 1) t_lo = m;
+    __syncthreads();
+    const float lo = t_lo;  // 0: fewer than k threads saw a positive value -> take every positive
+    // ---- sweep 2: candidates
+    for (int i = 8 * tid; i < F; i += 8 * kSelThreads) {
+      float v[8];
+      RowReader<T>::load8(zr, br, i, v);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        if (v[q] > 0.f && v[q] >= lo) {
+          const int c = atomicAdd(&n_cand, 1);
+          if (c < kCandCap) cand_v[c] = v[q], cand_i[c] = i + q;
+        }
+      }
+    }
+    __syncthreads();
+    const int nc = n_cand;
+    if (nc > kCandCap) {
+      fast = false;  // uniform: n_cand is shared
+    } else {
+      // ---- finish: rank by counting, rank < k selected, slot = rank
+      for (int c = tid; c < nc; c += kSelThreads) {
+        const float v = cand_v[c];
+        const int fi = cand_i[c];
+        int r = 0;
+        for (int j = 0; j < nc; ++j) {
+          const float o = cand_v[j];
+          r += (o > v || (o == v && cand_i[j] < fi)) ? 1 : 0;
+        }
+        if (r < k) {
+          io[r] = fi;
+          vo[r] = v;
+          if (fired_bits != nullptr) atomicOr(fired_bits + (size_t)l * words + fi / 32, 1u << (fi & 31));
+        }
+      }
+      for (int s2 = nc + tid; s2 < k; s2 += kSelThreads) io[s2] = 0, vo[s2] = 0.f;
+      return;
+    }
+  }
+  __syncthreads();
+
+  // ---- exact radix select (general k, ragged F, or heavy ties)
+  auto key_at = [&](int i) { return positive_key(ld_as_float<T>(zr, i) + __ldg(br + i)); };
+  const RowSelect sel = radix_select(F, k, key_at);
+  __shared__ int n_out, n_tie;
+  if (tid == 0) n_out = 0, n_tie = 0;
+  __syncthreads();
+  for (int i = tid; i < F; i += kSelThreads) {
     const float v = ld_as_float<T>(zr, i) + __ldg(br + i);
     const unsigned key = positive_key(v);
     bool take = key > sel.T;
@@ -166,7 +278,7 @@ select_topk_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, int
     }
   }
   __syncthreads();
-  for (int s = n_out + threadIdx.x; s < k; s += kSelThreads) io[s] = 0, vo[s] = 0.f;
+  for (int s2 = n_out + tid; s2 < k; s2 += kSelThreads) io[s2] = 0, vo[s2] = 0.f;
 }
 
 // ---------------------------------------------------------------------------------------

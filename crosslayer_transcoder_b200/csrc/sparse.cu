@@ -169,67 +169,68 @@ __global__ void csc_fill_kernel(const int* __restrict__ idx, const float* __rest
 }
 
 // =========================================================================================
-// Decoder backward, feature-major.  One warp per (source layer s, feature f):
-//   for every target t >= s:  w = W[pair(t,s), f, :]
-//       for every token b that selected f:  dval[s,b,j] += w . drecon[t,b,:]
-//                                           dW row       += val[s,b,j] * drecon[t,b,:]
-//       dW[pair(t,s), f, :] = dW row   (zeros when nobody selected f)
+// Decoder backward, feature-major.  One warp per decoder row (block p = (target t, source s),
+// feature f):   w = W[p, f, :]
+//   for every token b that selected feature f of layer s:
+//       dval[s,b,j] += w . drecon[t,b,:]            (one atomic per token and target)
+//       g           += val[s,b,j] * drecon[t,b,:]
+//   dW[p, f, :] = g                                 (zeros when nobody selected f)
+// The reconstruction gradient (tens of MB) stays resident in L2; W is read once and dW
+// written once.
 // =========================================================================================
 template <class T, int VPL>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 sparse_bwd_dec_kernel(const int* __restrict__ col_ptr, const int* __restrict__ ent, const float* __restrict__ val,
                       const T* __restrict__ W, const T* __restrict__ drecon, float* __restrict__ dW,
-                      float* __restrict__ dval, int B, int L, int D, int F, int k, int crosslayer) {
+                      float* __restrict__ dval, int B, int L, int D, int F, int k, int crosslayer, long long n_rows) {
   const long long wid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (wid >= (long long)L * F) return;
-  const int s = (int)(wid / F), f = (int)(wid % F);
+  if (wid >= n_rows) return;
+  const int p = (int)(wid / F), f = (int)(wid % F);
+  int s = p, t = p;
+  if (crosslayer) pair_split(p, t, s);
   const int nvec = D / 8;
   const int* cp = col_ptr + (size_t)s * (F + 1);
-  const int e0 = cp[f], e1 = cp[f + 1];
+  const int e0 = __ldg(cp + f), e1 = __ldg(cp + f + 1);
   const size_t npl = (size_t)B * k;
-  const int t_end = crosslayer ? L : s + 1;
-  for (int t = s; t < t_end; ++t) {
-    const size_t p = crosslayer ? (size_t)pair_index(t, s) : (size_t)s;
-    const size_t roff = (p * F + f) * D;
-    float w[VPL][8], g[VPL][8];
+  const size_t roff = ((size_t)p * F + f) * D;
+  float w[VPL][8], g[VPL][8];
 #pragma unroll
-    for (int i = 0; i < VPL; ++i) {
-      const int c = lane + 32 * i;
+  for (int i = 0; i < VPL; ++i) {
+    const int c = lane + 32 * i;
 #pragma unroll
-      for (int q = 0; q < 8; ++q) g[i][q] = 0.f, w[i][q] = 0.f;
-      if (e1 > e0 && c < nvec) Vec8<T>::load(W + roff + 8 * c, w[i]);
-    }
-    for (int e = e0; e < e1; ++e) {
-      const int slot = __ldg(ent + (size_t)s * npl + e);
-      const int b = slot / k;
-      const float v = __ldg(val + (size_t)s * npl + slot);
-      const T* dr = drecon + ((size_t)t * B + b) * D;
-      float dot = 0.f;
-#pragma unroll
-      for (int i = 0; i < VPL; ++i) {
-        const int c = lane + 32 * i;
-        if (c < nvec) {
-          float x[8];
-          Vec8<T>::load(dr + 8 * c, x);
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            dot = fmaf(w[i][q], x[q], dot);
-            g[i][q] = fmaf(v, x[q], g[i][q]);
-          }
-        }
-      }
-      dot = warp_sum(dot);
-      if (lane == 0) atomicAdd(dval + (size_t)s * npl + slot, dot);
-    }
+    for (int q = 0; q < 8; ++q) g[i][q] = 0.f, w[i][q] = 0.f;
+    if (e1 > e0 && c < nvec) Vec8<T>::load(W + roff + 8 * c, w[i]);
+  }
+  for (int e = e0; e < e1; ++e) {
+    const int slot = __ldg(ent + (size_t)s * npl + e);
+    const int b = slot / k;
+    const float v = __ldg(val + (size_t)s * npl + slot);
+    const T* dr = drecon + ((size_t)t * B + b) * D;
+    float dot = 0.f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
       const int c = lane + 32 * i;
       if (c < nvec) {
-        float4* o = reinterpret_cast<float4*>(dW + roff + 8 * c);
-        o[0] = make_float4(g[i][0], g[i][1], g[i][2], g[i][3]);
-        o[1] = make_float4(g[i][4], g[i][5], g[i][6], g[i][7]);
+        float x[8];
+        Vec8<T>::load(dr + 8 * c, x);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          dot = fmaf(w[i][q], x[q], dot);
+          g[i][q] = fmaf(v, x[q], g[i][q]);
+        }
       }
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) atomicAdd(dval + (size_t)s * npl + slot, dot);
+  }
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nvec) {
+      float4* o = reinterpret_cast<float4*>(dW + roff + 8 * c);
+      __stcs(o, make_float4(g[i][0], g[i][1], g[i][2], g[i][3]));
+      __stcs(o + 1, make_float4(g[i][4], g[i][5], g[i][6], g[i][7]));
     }
   }
 }
@@ -373,12 +374,15 @@ template <class T>
 int launch_bwd_dec(const int* col_ptr, const int* ent, const float* val, const void* W, const void* drecon, float* dW,
                    float* dval, int B, int L, int D, int F, int k, int crosslayer, cudaStream_t s) {
   const int vpl = (D / 8 + 31) / 32;
-  const long long warps = (long long)L * F;
-  const unsigned grid = (unsigned)((warps + 3) / 4);
+  const int P = crosslayer ? L * (L + 1) / 2 : L;
+  const long long rows = (long long)P * F;
+  const long long blocks = (rows + 7) / 8;
+  CLT_CHECK_ARG(blocks < (1ll << 31), "sparse decoder backward: too many rows");
+  const unsigned grid = (unsigned)blocks;
 #define CLT_BWD_DEC(V)                                                                                            \
   case V:                                                                                                         \
-    sparse_bwd_dec_kernel<T, V><<<grid, 128, 0, s>>>(col_ptr, ent, val, (const T*)W, (const T*)drecon, dW, dval, \
-                                                     B, L, D, F, k, crosslayer);                                  \
+    sparse_bwd_dec_kernel<T, V><<<grid, 256, 0, s>>>(col_ptr, ent, val, (const T*)W, (const T*)drecon, dW, dval, \
+                                                     B, L, D, F, k, crosslayer, rows);                            \
     break;
   switch (vpl) {
     CLT_BWD_DEC(1) CLT_BWD_DEC(2) CLT_BWD_DEC(3) CLT_BWD_DEC(4) CLT_BWD_DEC(6) CLT_BWD_DEC(8) CLT_BWD_DEC(9)

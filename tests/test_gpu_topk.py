@@ -79,6 +79,7 @@ CASES = [
     ("clt_no_dead", 2, 64, 256, 129, True, 4, 8, 0.0),
     ("clt_few_dead", 3, 64, 512, 150, True, 16, 64, 0.05),      # fewer dead features than k_aux
     ("clt_no_aux", 2, 64, 256, 100, True, 4, 0, 0.0),
+    ("clt_wide", 2, 64, 4096, 130, True, 32, 64, 0.1),          # wide rows: the two-sweep selection path
 ]
 
 
@@ -115,22 +116,33 @@ def test_selection_edge_cases():
 
     dev = torch.device("cuda:0")
     lib().check_device()
-    L, B, F = 2, 5, 96
-    g = torch.Generator().manual_seed(0)
-    z = torch.randn(L, B, F, generator=g)
-    z[1, 3] = -z[1, 3].abs() - 0.1                                   # an all-negative row
-    zb = z.to(dev)
-    bias = torch.zeros(L, F, device=dev)
-    for k in (1, 7, F):
-        idx = torch.empty(L, B, k, dtype=torch.int32, device=dev)
-        val = torch.empty(L, B, k, device=dev)
-        lib().call("clt_select_topk", zb, bias, idx, val, None, B, L, F, k, 0, stream_ptr())
-        dense = torch.zeros(L, B, F).scatter_add_(2, idx.long().cpu(), val.cpu())
-        ref = O.per_layer_topk(z.permute(1, 0, 2).contiguous(), k).permute(1, 0, 2)
-        assert torch.equal(dense, ref)
-        assert (dense >= 0).all() and float(dense[1, 3].abs().sum()) == 0.0
+    for L, B, F, ks in ((2, 5, 96, (1, 7, 96)), (2, 5, 4096, (1, 32, 256, 300, 4096))):
+        _check_selection(dev, L, B, F, ks)
     spec = synthetic.WorkloadSpec("kbig", 2, 64, 64, 16, "topk", True, False, rank_u=8, n_outlier=1, k=65, k_aux=0)
     batch, w, la = spec_inputs(spec)
     mod = build_module(spec, w, dev, last_active=la)
     with pytest.raises(AssertionError):
         mod.training_step(batch.to(dev), 0)
+
+
+def _check_selection(dev, L, B, F, ks):
+    from crosslayer_transcoder_b200._lib import lib, stream_ptr
+
+    g = torch.Generator().manual_seed(0)
+    z = torch.randn(L, B, F, generator=g)
+    z[1, 3] = -z[1, 3].abs() - 0.1                                   # an all-negative row
+    z[0, 1, F // 2:] = -1.0                                          # positives in half of the row only
+    z[0, 2] = torch.where(z[0, 2] > 0, torch.full_like(z[0, 2], 0.5), z[0, 2])   # masses of equal values
+    zb = z.to(dev)
+    bias = torch.zeros(L, F, device=dev)
+    for k in ks:
+        idx = torch.empty(L, B, k, dtype=torch.int32, device=dev)
+        val = torch.empty(L, B, k, device=dev)
+        lib().call("clt_select_topk", zb, bias, idx, val, None, B, L, F, k, 0, stream_ptr())
+        dense = torch.zeros(L, B, F).scatter_add_(2, idx.long().cpu(), val.cpu())
+        ref = O.per_layer_topk(z.permute(1, 0, 2).contiguous(), k).permute(1, 0, 2)
+        tie_row = torch.zeros(L, B, dtype=torch.bool)
+        tie_row[0, 2] = True                                         # which of the equal values win is unspecified
+        assert torch.equal(dense[~tie_row], ref[~tie_row])
+        assert torch.equal(dense[tie_row].sort(dim=-1).values, ref[tie_row].sort(dim=-1).values)
+        assert (dense >= 0).all() and float(dense[1, 3].abs().sum()) == 0.0
