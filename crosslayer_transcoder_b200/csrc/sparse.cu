@@ -106,6 +106,12 @@ sparse_dec_fwd_kernel(const int* __restrict__ idx, const float* __restrict__ val
 // =========================================================================================
 // Feature-major copy of the selection (counting sort per layer).
 // =========================================================================================
+// Scratch of the allocation-free variant of the counting sort (clt_csc_build_static): the
+// per-feature write cursors.  It lives in the library image, so every GPU that loads the
+// library holds these 4 MiB until the process exits.
+constexpr long long kStaticCursorCap = 1ll << 20;  // layers x features this rank may hold
+static __device__ __align__(256) int g_static_cursor[kStaticCursorCap];
+
 __global__ void csc_count_kernel(const int* __restrict__ idx, const float* __restrict__ val, int* __restrict__ count,
                                  long long n_per_layer, int F, int L, int* status) {
   const long long total = n_per_layer * L;
@@ -431,6 +437,48 @@ int clt_csc_build(const int* idx, const float* val, int* col_ptr, int* cursor, i
   csc_fill_kernel<<<blocks, 256, 0, s>>>(idx, val, cursor, ent, npl, F, L);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
+}
+
+// Host-side address of g_static_cursor per device.  In host code the array's name is only a
+// stand-in for the symbol, not a device address, so it is resolved once per device, with that
+// device current, and the resolved pointer is what the kernels receive.
+static int* static_cursor_ptr(int* err) {
+  static int* ptr[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("csc_build_static: cannot identify the current device (%s)", cudaGetErrorString(e));
+    *err = 2;
+    return nullptr;
+  }
+  if (ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_cursor);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error("csc_build_static: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+      *err = 2;
+      return nullptr;
+    }
+    ptr[dev] = static_cast<int*>(p);
+  }
+  *err = 0;
+  return ptr[dev];
+}
+
+int clt_csc_build_static(const int* idx, const float* val, int* col_ptr, int* ent, int B, int L, int F, int k,
+                         int* status, clt_stream_t stream) {
+  CLT_CHECK_ARG(B > 0 && L > 0 && F > 0 && k > 0, "csc_build_static: bad dims B=%d L=%d F=%d k=%d", B, L, F, k);
+  CLT_CHECK_ARG(idx && val && col_ptr && ent, "csc_build_static: null pointer");
+  CLT_CHECK_ARG((long long)L * F <= kStaticCursorCap,
+                "csc_build_static: L*F = %lld exceeds the built-in scratch of %lld entries; use clt_csc_build with a "
+                "caller-provided cursor buffer",
+                (long long)L * F, kStaticCursorCap);
+  int err = 0;
+  int* cursor = static_cursor_ptr(&err);
+  if (cursor == nullptr) return err;
+  // every cursor entry in [0, L*F) is rewritten by the scan before the fill reads it, so nothing left
+  // in the array by an earlier call is ever observed
+  return clt_csc_build(idx, val, col_ptr, cursor, ent, B, L, F, k, status, stream);
 }
 
 int clt_sparse_bwd_dec(const int* col_ptr, const int* ent, const float* val, const void* W_dec, const void* drecon,

@@ -4,8 +4,8 @@
  * point below names the reference code it replaces (file:line, paths relative to
  * the reference project root).  All pointers are device pointers unless stated
  * otherwise; the library allocates and frees nothing, keeps no state between
- * calls except per-function launch attributes, and launches on the stream it is
- * given.  Every function returns 0 when its kernels were launched, non-zero when
+ * calls except per-function launch attributes (and the built-in scratch array of
+ * clt_csc_build_static), and launches on the stream it is given.  Every function returns 0 when its kernels were launched, non-zero when
  * an argument was rejected or a launch failed (then clt_last_error() holds the
  * reason).  Kernels never trap: a kernel that gives up on a bounded wait or meets
  * an out-of-range index writes a code to the `status` word passed by the caller
@@ -156,6 +156,24 @@ int clt_sparse_decoder_fwd(const int* idx, const float* val, const void* W_dec, 
  * feature).  cursor [L, F] is scratch. */
 int clt_csc_build(const int* idx, const float* val, int* col_ptr, int* cursor, int* ent, int B, int L, int F,
                   int k, int* status, clt_stream_t stream);
+
+/* Same result as clt_csc_build, for hosts that must not allocate device memory on behalf of this
+ * library.  (No counterpart in the reference: it exists only for this library's callers.)
+ * Some embedders hand the step a fixed set of buffers at start-up and cannot grow it afterwards:
+ * a process whose device memory is wholly pre-reserved by its own pool allocator, so that a
+ * cudaMalloc for scratch would fail or fragment the pool, or a latency-bound loop in which
+ * cudaMalloc / cudaFree would stall the device.  For them the write cursors live in a 4 MiB
+ * array inside the library image (1,048,576 ints; every GPU that loads the library carries it
+ * until the process exits), so the caller passes inputs and outputs only and neither this call
+ * nor anything under it calls cudaMalloc, cudaFree or an allocating library routine.
+ * - L * F above 1,048,576 is rejected with an error; use clt_csc_build with your own cursor buffer.
+ * - The first call on each device resolves the array's device address (cudaGetSymbolAddress, with
+ *   that device current); make that first call before any stream capture begins.
+ * - All calls on a device share the one array, which keeps whatever the previous call left in
+ *   it.  Every entry the call reads is rewritten by the call first, so no clearing is needed,
+ *   but two calls that overlap on the GPU (different streams, no ordering) race on it. */
+int clt_csc_build_static(const int* idx, const float* val, int* col_ptr, int* ent, int B, int L, int F, int k,
+                         int* status, clt_stream_t stream);
 
 /* Backward of the decoder on the selected features (autograd of clt.py:334-343 restricted to the
  * non-zero features): dval[s,b,j] = sum_{t>=s} drecon[t,b,:] . W_dec[pair(t,s), idx, :] and
