@@ -32,7 +32,7 @@ from crosslayer_transcoder_b200 import synthetic  # noqa: E402
 
 METRIC = "clt_train_tokens_per_s"
 UNIT = "tokens/s"
-DEFAULT_WORKLOAD = "c2_plt_bf16"
+DEFAULT_WORKLOAD = "c3_clt_topk_bf16"
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels from
 # the ncu captures summarised under profiles/; None where no capture has been taken.
