@@ -42,13 +42,84 @@ __global__ void prep_input_kernel(const TIn* __restrict__ batch, const float* __
   }
 }
 
+// ---- 8-element vector I/O for the streaming kernels -------------------------------------
+template <class T>
+__device__ __forceinline__ void load8(const T* p, float (&o)[8]);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&o)[8]) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  o[0] = a.x, o[1] = a.y, o[2] = a.z, o[3] = a.w, o[4] = b.x, o[5] = b.y, o[6] = b.z, o[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__half>(const __half* p, float (&o)[8]) {
+  const uint4 t = __ldg(reinterpret_cast<const uint4*>(p));
+  const __half2* h = reinterpret_cast<const __half2*>(&t);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __half22float2(h[j]);
+    o[2 * j] = f.x, o[2 * j + 1] = f.y;
+  }
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&o)[8]) {
+  const uint4 t = __ldg(reinterpret_cast<const uint4*>(p));
+  const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    o[2 * j] = __uint_as_float(w[j] << 16);
+    o[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+  }
+}
+template <class T>
+__device__ __forceinline__ void store8(T* p, const float (&v)[8]);
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float (&v)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 t;
+  t.x = pack_bf16x2(v[0], v[1]), t.y = pack_bf16x2(v[2], v[3]);
+  t.z = pack_bf16x2(v[4], v[5]), t.w = pack_bf16x2(v[6], v[7]);
+  *reinterpret_cast<uint4*>(p) = t;
+}
+
+// same as prep_input_kernel, 8 consecutive d per thread (needs D % 8 == 0)
+template <class TIn, class TOut>
+__global__ void prep_input_vec_kernel(const TIn* __restrict__ batch, const float* __restrict__ mu,
+                                      const float* __restrict__ sd, TOut* __restrict__ xn, int B, int L, int D) {
+  const int dv = D / 8;
+  const long long total = (long long)B * L * dv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int d = (int)(i % dv) * 8;
+    const long long r = i / dv;
+    const int l = (int)(r % L);
+    const long long b = r / L;
+    float x[8], m[8], s[8];
+    load8<TIn>(batch + ((b * 2 + 0) * L + l) * D + d, x);
+    load8<float>(mu + l * D + d, m);
+    load8<float>(sd + l * D + d, s);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) x[q] = (x[q] - m[q]) / s[q];
+    store8<TOut>(xn + ((long long)l * B + b) * D + d, x);
+  }
+}
+
 template <class TIn, class TOut>
 static int prep_input_t(const void* batch, const float* mu, const float* sd, void* xn, int B, int L, int D,
                         cudaStream_t s) {
-  const long long total = (long long)B * L * D;
   const int threads = 256;
-  const int blocks = (int)min((total + threads - 1) / threads, (long long)148 * 16);
-  prep_input_kernel<TIn, TOut><<<blocks, threads, 0, s>>>((const TIn*)batch, mu, sd, (TOut*)xn, B, L, D);
+  if (D % 8 == 0 && ((uintptr_t)batch | (uintptr_t)xn | (uintptr_t)mu | (uintptr_t)sd) % 16 == 0) {
+    const long long total = (long long)B * L * (D / 8);
+    const int blocks = (int)min((total + threads - 1) / threads, (long long)148 * 16);
+    prep_input_vec_kernel<TIn, TOut><<<blocks, threads, 0, s>>>((const TIn*)batch, mu, sd, (TOut*)xn, B, L, D);
+  } else {
+    const long long total = (long long)B * L * D;
+    const int blocks = (int)min((total + threads - 1) / threads, (long long)148 * 16);
+    prep_input_kernel<TIn, TOut><<<blocks, threads, 0, s>>>((const TIn*)batch, mu, sd, (TOut*)xn, B, L, D);
+  }
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -116,19 +187,79 @@ __global__ void loss_fwd_kernel(const float* __restrict__ recon, const float* __
   }
 }
 
+// same sums, 8 consecutive (l, d) columns per thread (needs L*D % 8 == 0)
+template <class TIn>
+__global__ void loss_fwd_vec_kernel(const float* __restrict__ recon, const float* __restrict__ aux,
+                                    const TIn* __restrict__ batch, const float* __restrict__ mu,
+                                    const float* __restrict__ sd, float* __restrict__ acc, int B, int L, int D) {
+  const long long LD = (long long)L * D;
+  const long long total = (long long)B * LD / 8;
+  float s0 = 0.f, s1 = 0.f;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long e = i * 8;
+    const long long c = e % LD, b = e / LD;
+    float y[8], m[8], sdv[8], r[8];
+    load8<TIn>(batch + (b * 2 + 1) * LD + c, y);
+    load8<float>(mu + c, m);
+    load8<float>(sd + c, sdv);
+    load8<float>(recon + e, r);
+    float diff[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      diff[q] = r[q] - (y[q] - m[q]) / sdv[q];
+      s0 = fmaf(diff[q], diff[q], s0);
+    }
+    if (aux != nullptr) {
+      float a[8];
+      load8<float>(aux + e, a);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float ad = a[q] + diff[q];
+        const float sq = ad * ad;
+        s1 += (sq == sq) ? sq : 0.f;
+      }
+    }
+  }
+  s0 = warp_sum(s0);
+  s1 = warp_sum(s1);
+  __shared__ float sh[2][32];
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) sh[0][w] = s0, sh[1][w] = s1;
+  __syncthreads();
+  if (w == 0) {
+    const int nw = blockDim.x >> 5;
+    s0 = warp_sum(lane < nw ? sh[0][lane] : 0.f);
+    s1 = warp_sum(lane < nw ? sh[1][lane] : 0.f);
+    if (lane == 0) {
+      atomicAdd(acc + 0, s0);
+      if (aux != nullptr) atomicAdd(acc + 1, s1);
+    }
+  }
+}
+
 int loss_fwd(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu, const float* sd,
              float* acc, int B, int L, int D, cudaStream_t s) {
   if (B <= 0) return 0;
   const long long total = (long long)B * L * D;
   const int threads = 256;
-  const int blocks = (int)min((total + threads - 1) / threads, (long long)148 * 8);
-  if (in_dtype == 0)
-    loss_fwd_kernel<float><<<blocks, threads, 0, s>>>(recon, aux, (const float*)batch, mu, sd, acc, B, L, D);
-  else if (in_dtype == 1)
-    loss_fwd_kernel<__half><<<blocks, threads, 0, s>>>(recon, aux, (const __half*)batch, mu, sd, acc, B, L, D);
-  else
-    loss_fwd_kernel<__nv_bfloat16>
-        <<<blocks, threads, 0, s>>>(recon, aux, (const __nv_bfloat16*)batch, mu, sd, acc, B, L, D);
+  const bool vec = ((long long)L * D) % 8 == 0 &&
+                   ((uintptr_t)recon | (uintptr_t)aux | (uintptr_t)batch | (uintptr_t)mu | (uintptr_t)sd) % 16 == 0;
+  const long long work = vec ? total / 8 : total;
+  const int blocks = (int)min((work + threads - 1) / threads, (long long)148 * 8);
+#define CLT_LF(TI)                                                                                               \
+  if (vec)                                                                                                       \
+    loss_fwd_vec_kernel<TI><<<blocks, threads, 0, s>>>(recon, aux, (const TI*)batch, mu, sd, acc, B, L, D);      \
+  else                                                                                                           \
+    loss_fwd_kernel<TI><<<blocks, threads, 0, s>>>(recon, aux, (const TI*)batch, mu, sd, acc, B, L, D)
+  if (in_dtype == 0) {
+    CLT_LF(float);
+  } else if (in_dtype == 1) {
+    CLT_LF(__half);
+  } else {
+    CLT_LF(__nv_bfloat16);
+  }
+#undef CLT_LF
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -17,29 +17,56 @@ namespace clt {
 namespace {
 
 // ---- 8-wide row chunks ------------------------------------------------------------------
+// load_raw keeps a chunk in its storage format (4 registers for bf16); unpack widens it to fp32
+// at the point of use, which keeps rows that are in flight cheap in registers.
 template <class T>
 struct Vec8;
 template <>
 struct Vec8<__nv_bfloat16> {
-  static constexpr int kElems = 8;
-  __device__ static __forceinline__ void load(const __nv_bfloat16* p, float (&o)[8]) {
-    const uint4 t = __ldg(reinterpret_cast<const uint4*>(p));
-    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+  struct Raw {
+    uint4 v;
+  };
+  __device__ static __forceinline__ Raw load_raw(const __nv_bfloat16* p) {
+    Raw r;
+    r.v = __ldg(reinterpret_cast<const uint4*>(p));
+    return r;
+  }
+  __device__ static __forceinline__ Raw zero() {
+    Raw r;
+    r.v = make_uint4(0, 0, 0, 0);
+    return r;
+  }
+  __device__ static __forceinline__ void unpack(const Raw& r, float (&o)[8]) {
+    const uint32_t w[4] = {r.v.x, r.v.y, r.v.z, r.v.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       o[2 * j] = __uint_as_float(w[j] << 16);
       o[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
     }
   }
+  __device__ static __forceinline__ void load(const __nv_bfloat16* p, float (&o)[8]) { unpack(load_raw(p), o); }
 };
 template <>
 struct Vec8<float> {
-  static constexpr int kElems = 8;
-  __device__ static __forceinline__ void load(const float* p, float (&o)[8]) {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(p));
-    const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
-    o[0] = a.x, o[1] = a.y, o[2] = a.z, o[3] = a.w, o[4] = b.x, o[5] = b.y, o[6] = b.z, o[7] = b.w;
+  struct Raw {
+    float4 a, b;
+  };
+  __device__ static __forceinline__ Raw load_raw(const float* p) {
+    Raw r;
+    r.a = __ldg(reinterpret_cast<const float4*>(p));
+    r.b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    return r;
   }
+  __device__ static __forceinline__ Raw zero() {
+    Raw r;
+    r.a = make_float4(0.f, 0.f, 0.f, 0.f);
+    r.b = r.a;
+    return r;
+  }
+  __device__ static __forceinline__ void unpack(const Raw& r, float (&o)[8]) {
+    o[0] = r.a.x, o[1] = r.a.y, o[2] = r.a.z, o[3] = r.a.w, o[4] = r.b.x, o[5] = r.b.y, o[6] = r.b.z, o[7] = r.b.w;
+  }
+  __device__ static __forceinline__ void load(const float* p, float (&o)[8]) { unpack(load_raw(p), o); }
 };
 
 // =========================================================================================
@@ -185,7 +212,7 @@ __global__ void csc_fill_kernel(const int* __restrict__ idx, const float* __rest
 // written once.
 // =========================================================================================
 template <class T, int VPL>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 sparse_bwd_dec_kernel(const int* __restrict__ col_ptr, const int* __restrict__ ent, const float* __restrict__ val,
                       const T* __restrict__ W, const T* __restrict__ drecon, float* __restrict__ dW,
                       float* __restrict__ dval, int B, int L, int D, int F, int k, int crosslayer, long long n_rows) {
@@ -200,35 +227,69 @@ sparse_bwd_dec_kernel(const int* __restrict__ col_ptr, const int* __restrict__ e
   const int e0 = __ldg(cp + f), e1 = __ldg(cp + f + 1);
   const size_t npl = (size_t)B * k;
   const size_t roff = ((size_t)p * F + f) * D;
-  float w[VPL][8], g[VPL][8];
+  using V = Vec8<T>;
+  constexpr bool kTwo = VPL <= 4;  // two rows in flight while the register budget allows it
+  typename V::Raw w[VPL];
+  float g[VPL][8];
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     const int c = lane + 32 * i;
 #pragma unroll
-    for (int q = 0; q < 8; ++q) g[i][q] = 0.f, w[i][q] = 0.f;
-    if (e1 > e0 && c < nvec) Vec8<T>::load(W + roff + 8 * c, w[i]);
+    for (int q = 0; q < 8; ++q) g[i][q] = 0.f;
+    w[i] = (e1 > e0 && c < nvec) ? V::load_raw(W + roff + 8 * c) : V::zero();
   }
-  for (int e = e0; e < e1; ++e) {
-    const int slot = __ldg(ent + (size_t)s * npl + e);
-    const int b = slot / k;
-    const float v = __ldg(val + (size_t)s * npl + slot);
-    const T* dr = drecon + ((size_t)t * B + b) * D;
-    float dot = 0.f;
+  // entries in groups of 32: one coalesced load of the group's slots and values, then the rows
+  // (two at a time where possible, so that two independent row fetches are in flight per warp)
+  for (int eb = e0; eb < e1; eb += 32) {
+    const int n = min(32, e1 - eb);
+    int my_slot = 0;
+    float my_val = 0.f;
+    if (lane < n) {
+      my_slot = __ldg(ent + (size_t)s * npl + eb + lane);
+      my_val = __ldg(val + (size_t)s * npl + my_slot);
+    }
+    for (int j = 0; j < n; j += (kTwo ? 2 : 1)) {
+      const bool two = kTwo && (j + 1 < n);
+      const int slot0 = __shfl_sync(0xffffffffu, my_slot, j);
+      const int slot1 = __shfl_sync(0xffffffffu, my_slot, two ? j + 1 : j);
+      const float v0 = __shfl_sync(0xffffffffu, my_val, j);
+      const float v1 = two ? __shfl_sync(0xffffffffu, my_val, j + 1) : 0.f;
+      const T* dr0 = drecon + ((size_t)t * B + slot0 / k) * D;
+      const T* dr1 = drecon + ((size_t)t * B + slot1 / k) * D;
+      typename V::Raw x0[VPL], x1[kTwo ? VPL : 1];
 #pragma unroll
-    for (int i = 0; i < VPL; ++i) {
-      const int c = lane + 32 * i;
-      if (c < nvec) {
-        float x[8];
-        Vec8<T>::load(dr + 8 * c, x);
+      for (int i = 0; i < VPL; ++i) {
+        const int c = lane + 32 * i;
+        x0[i] = c < nvec ? V::load_raw(dr0 + 8 * c) : V::zero();
+        if (kTwo) x1[i] = (two && c < nvec) ? V::load_raw(dr1 + 8 * c) : V::zero();
+      }
+      float dot0 = 0.f, dot1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        float wf[8], xf[8];
+        V::unpack(w[i], wf);
+        V::unpack(x0[i], xf);
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
-          dot = fmaf(w[i][q], x[q], dot);
-          g[i][q] = fmaf(v, x[q], g[i][q]);
+          dot0 = fmaf(wf[q], xf[q], dot0);
+          g[i][q] = fmaf(v0, xf[q], g[i][q]);
+        }
+        if (kTwo) {
+          V::unpack(x1[i], xf);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            dot1 = fmaf(wf[q], xf[q], dot1);
+            g[i][q] = fmaf(v1, xf[q], g[i][q]);
+          }
         }
       }
+      dot0 = warp_sum(dot0);
+      if (kTwo) dot1 = warp_sum(dot1);
+      if (lane == 0) {
+        atomicAdd(dval + (size_t)s * npl + slot0, dot0);
+        if (two) atomicAdd(dval + (size_t)s * npl + slot1, dot1);
+      }
     }
-    dot = warp_sum(dot);
-    if (lane == 0) atomicAdd(dval + (size_t)s * npl + slot, dot);
   }
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
@@ -242,31 +303,34 @@ sparse_bwd_dec_kernel(const int* __restrict__ col_ptr, const int* __restrict__ e
 }
 
 // =========================================================================================
-// Encoder backward, feature-major.  One CTA per (layer l, 32 features, 768 input dims):
+// Encoder backward, feature-major.  One CTA per (layer l, 8 features, 768 input dims):
 //   dW_enc[l, d, f] = sum over tokens b that selected f of dval[l,b,j] * xn[l,b,d]
 //   db_enc[l, f]    = sum of the same dval
-// Thread t owns dims d0 + t, d0 + t + 256, d0 + t + 512 and all 32 features of the block,
-// so every store is a 128-byte run of the F-contiguous gradient.
+// Thread t owns dims d0 + t, d0 + t + 256, d0 + t + 512 and the 8 features of the block, so every
+// store is a full 32-byte sector of the F-contiguous gradient; the small register footprint
+// keeps many CTAs resident to hide the latency of the dependent entry -> row loads.
 // =========================================================================================
+constexpr int kEncFB = 8;
+
 template <class T>
 __global__ void __launch_bounds__(256)
 sparse_bwd_enc_kernel(const int* __restrict__ col_ptr, const int* __restrict__ ent, const float* __restrict__ dval,
                       const T* __restrict__ xn, float* __restrict__ dW, float* __restrict__ db, int B, int D, int F,
                       int k) {
-  const int l = blockIdx.y, f0 = blockIdx.x * 32, d0 = blockIdx.z * 768;
+  const int l = blockIdx.y, f0 = blockIdx.x * kEncFB, d0 = blockIdx.z * 768;
   const int* cp = col_ptr + (size_t)l * (F + 1);
   const size_t npl = (size_t)B * k;
-  float acc[3][32];
+  float acc[3][kEncFB];
 #pragma unroll
   for (int i = 0; i < 3; ++i)
 #pragma unroll
-    for (int q = 0; q < 32; ++q) acc[i][q] = 0.f;
+    for (int q = 0; q < kEncFB; ++q) acc[i][q] = 0.f;
   float bsum = 0.f;
 #pragma unroll
-  for (int q = 0; q < 32; ++q) {
+  for (int q = 0; q < kEncFB; ++q) {
     const int f = f0 + q;
     if (f >= F) break;
-    const int e0 = cp[f], e1 = cp[f + 1];
+    const int e0 = __ldg(cp + f), e1 = __ldg(cp + f + 1);
     float bs = 0.f;
     for (int e = e0; e < e1; ++e) {
       const int slot = __ldg(ent + (size_t)l * npl + e);
@@ -281,7 +345,7 @@ sparse_bwd_enc_kernel(const int* __restrict__ col_ptr, const int* __restrict__ e
     }
     if ((int)threadIdx.x == q) bsum = bs;
   }
-  const bool vec = (F % 4 == 0) && (f0 + 32 <= F);
+  const bool vec = (F % 4 == 0) && (f0 + kEncFB <= F);
 #pragma unroll
   for (int i = 0; i < 3; ++i) {
     const int d = d0 + threadIdx.x + 256 * i;
@@ -289,15 +353,17 @@ sparse_bwd_enc_kernel(const int* __restrict__ col_ptr, const int* __restrict__ e
     float* o = dW + ((size_t)l * D + d) * F + f0;
     if (vec) {
 #pragma unroll
-      for (int q = 0; q < 8; ++q)
-        reinterpret_cast<float4*>(o)[q] = make_float4(acc[i][4 * q], acc[i][4 * q + 1], acc[i][4 * q + 2], acc[i][4 * q + 3]);
+      for (int q = 0; q < kEncFB / 4; ++q)
+        __stcs(reinterpret_cast<float4*>(o) + q,
+               make_float4(acc[i][4 * q], acc[i][4 * q + 1], acc[i][4 * q + 2], acc[i][4 * q + 3]));
     } else {
 #pragma unroll
-      for (int q = 0; q < 32; ++q)
+      for (int q = 0; q < kEncFB; ++q)
         if (f0 + q < F) o[q] = acc[i][q];
     }
   }
-  if (blockIdx.z == 0 && threadIdx.x < 32 && f0 + (int)threadIdx.x < F) db[(size_t)l * F + f0 + threadIdx.x] = bsum;
+  if (blockIdx.z == 0 && threadIdx.x < kEncFB && f0 + (int)threadIdx.x < F)
+    db[(size_t)l * F + f0 + threadIdx.x] = bsum;
 }
 
 // =========================================================================================
@@ -339,16 +405,18 @@ __global__ void scatter_rows_kernel(const float* __restrict__ src, const int* __
 }
 
 // dW_enc[l, d, dead_list[l][j]] += src[l, d, j];  db_enc[l, dead_list[l][j]] += db_src[l, j]
+// blockDim (32, 8): x walks the dead features (coalesced reads of src), y walks input dims.
 __global__ void scatter_cols_kernel(const float* __restrict__ src, const float* __restrict__ db_src,
                                     const int* __restrict__ dead_list, const int* __restrict__ n_dead,
                                     float* __restrict__ dW, float* __restrict__ db, int D, int F, int nd_pad) {
   const int l = blockIdx.y;
   const int nd = n_dead[l];
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  const int j = blockIdx.x * 32 + threadIdx.x;
   if (j >= nd) return;
   const int f = dead_list[(size_t)l * F + j];
-  for (int d = 0; d < D; ++d) dW[((size_t)l * D + d) * F + f] += src[((size_t)l * D + d) * nd_pad + j];
-  db[(size_t)l * F + f] += db_src[(size_t)l * nd_pad + j];
+  for (int d = blockIdx.z * 8 + threadIdx.y; d < D; d += 8 * gridDim.z)
+    dW[((size_t)l * D + d) * F + f] += src[((size_t)l * D + d) * nd_pad + j];
+  if (blockIdx.z == 0 && threadIdx.y == 0) db[(size_t)l * F + f] += db_src[(size_t)l * nd_pad + j];
 }
 
 template <class T>
@@ -382,12 +450,12 @@ int launch_bwd_dec(const int* col_ptr, const int* ent, const float* val, const v
   const int vpl = (D / 8 + 31) / 32;
   const int P = crosslayer ? L * (L + 1) / 2 : L;
   const long long rows = (long long)P * F;
-  const long long blocks = (rows + 7) / 8;
+  const long long blocks = (rows + 3) / 4;
   CLT_CHECK_ARG(blocks < (1ll << 31), "sparse decoder backward: too many rows");
   const unsigned grid = (unsigned)blocks;
 #define CLT_BWD_DEC(V)                                                                                            \
   case V:                                                                                                         \
-    sparse_bwd_dec_kernel<T, V><<<grid, 256, 0, s>>>(col_ptr, ent, val, (const T*)W, (const T*)drecon, dW, dval, \
+    sparse_bwd_dec_kernel<T, V><<<grid, 128, 0, s>>>(col_ptr, ent, val, (const T*)W, (const T*)drecon, dW, dval, \
                                                      B, L, D, F, k, crosslayer, rows);                            \
     break;
   switch (vpl) {
@@ -499,7 +567,7 @@ int clt_sparse_bwd_enc(const int* col_ptr, const int* ent, const float* dval, co
                        float* db_enc, int B, int L, int D, int F, int k, int bf16, clt_stream_t stream) {
   CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && F > 0 && k > 0, "sparse_bwd_enc: bad dims");
   CLT_CHECK_ARG(col_ptr && ent && dval && xn && dW_enc && db_enc, "sparse_bwd_enc: null pointer");
-  dim3 grid((F + 31) / 32, L, (D + 767) / 768);
+  dim3 grid((F + kEncFB - 1) / kEncFB, L, (D + 767) / 768);
   CLT_CHECK_ARG(grid.y <= 65535 && grid.z <= 65535, "sparse_bwd_enc: grid too large");
   if (bf16)
     sparse_bwd_enc_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>(
@@ -540,9 +608,9 @@ int clt_scatter_rows(const float* src, const int* dead_list, const int* n_dead, 
 int clt_scatter_cols(const float* src, const float* db_src, const int* dead_list, const int* n_dead, float* dW_enc,
                      float* db_enc, int L, int D, int F, int nd_pad, clt_stream_t stream) {
   CLT_CHECK_ARG(L > 0 && F > 0 && D > 0 && nd_pad > 0, "scatter_cols: bad dims");
-  dim3 grid((nd_pad + 127) / 128, L);
-  scatter_cols_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(src, db_src, dead_list, n_dead, dW_enc, db_enc, D, F,
-                                                              nd_pad);
+  dim3 grid((nd_pad + 31) / 32, L, 16), block(32, 8);
+  scatter_cols_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, db_src, dead_list, n_dead, dW_enc, db_enc, D, F,
+                                                                nd_pad);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -398,6 +398,8 @@ class StepEngine:
         aux = None
         aux_recon = None
         aux_scale = float(h.get("aux_loss_scale", 0.0))
+        pending = []                                    # collectives in flight (feature shards only)
+        h_gather = None
         if k_aux > 0:
             dead_list = ws.get("dead_list", (L, F), torch.int32, dev)
             n_dead = ws.get("n_dead", (L,), torch.int32, dev)
@@ -405,17 +407,28 @@ class StepEngine:
             nd = int(n_dead.max())                      # host read: sizes the compacted contractions
             nd_pad = max(64, _round_up(nd, 64))
             a_aux = ws.get("a_aux", (L, B, nd_pad), T, dev)
-            if world == 1:
-                self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, a_aux, None, None, 0, B, L, F, k_aux,
-                           nd_pad, int(bf16), s)
-            else:
+            if world > 1:
+                # offer this shard's k_aux best dead values per row; the gather runs while the main
+                # decoder works
                 from .parallel import all_gather
 
                 cand = ws.get("aux_cand", (L, B, k_aux), torch.float32, dev)
                 self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, None, cand, None, 1, B, L, F, k_aux,
                            nd_pad, int(bf16), s)
                 cand_all = ws.get("aux_cand_all", (world, L, B, k_aux), torch.float32, dev)
-                all_gather(cand_all, cand, group)
+                h_gather = all_gather(cand_all, cand, group, async_op=True)
+        self._call("clt_sparse_decoder_fwd", idx, val, W_op, bias, recon, B, L, D, F, kk, crosslayer, int(bf16),
+                   self.status, s)
+        if world > 1:
+            from .parallel import all_reduce_sum
+
+            pending.append(all_reduce_sum(rbuf[:n_rec], group, async_op=True))
+        if k_aux > 0:
+            if world == 1:
+                self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, a_aux, None, None, 0, B, L, F, k_aux,
+                           nd_pad, int(bf16), s)
+            else:
+                h_gather.wait()
                 thr_aux = ws.get("thr_aux", (L, B), torch.float32, dev)
                 self._call("clt_topk_threshold", cand_all, thr_aux, L * B, world, k_aux, s)
                 self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, a_aux, None, thr_aux, 2, B, L, F, k_aux,
@@ -427,12 +440,10 @@ class StepEngine:
             self._call("clt_decoder_dense_fwd", a_aux, w_c, bias, aux_recon, B, L, D, nd_pad, crosslayer,
                        int(bf16), self.status, s)
             aux = dict(dead_list=dead_list, n_dead=n_dead, nd_pad=nd_pad, a_aux=a_aux, w_c=w_c)
-        self._call("clt_sparse_decoder_fwd", idx, val, W_op, bias, recon, B, L, D, F, kk, crosslayer, int(bf16),
-                   self.status, s)
-        if world > 1:
-            from .parallel import all_reduce_sum
-
-            all_reduce_sum(rbuf[: (2 if aux is not None else 1) * n_rec], group)
+            if world > 1:
+                pending.append(all_reduce_sum(rbuf[n_rec:2 * n_rec], group, async_op=True))
+        for h_ in pending:
+            h_.wait()
         self._call("clt_loss_fwd", recon, aux_recon, batch, in_code, mu_o, sd_o, acc[2:4], B, L, D, s)
         self._call("clt_finalize_loss", acc[2:4], None, out[0:1], out[1:5], 1.0 / (B * L * D), 0.0, 0.0,
                    aux_scale if aux is not None else 0.0, s)

@@ -40,13 +40,14 @@ def attach(module, group: Optional[dist.ProcessGroup] = None) -> None:
     module.tp_world = dist.get_world_size(module.tp_group)
 
 
-def all_reduce_sum(buf: torch.Tensor, group) -> None:
-    dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group)
+def all_reduce_sum(buf: torch.Tensor, group, async_op: bool = False):
+    """Sum ``buf`` over the group in place.  With ``async_op`` the collective is only enqueued and a
+    work handle is returned; ``handle.wait()`` orders the current stream after it."""
+    return dist.all_reduce(buf, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
 
 
-def all_gather(out: torch.Tensor, part: torch.Tensor, group) -> None:
+def all_gather(out: torch.Tensor, part: torch.Tensor, group, async_op: bool = False):
     """out[r] = rank r's ``part`` (out has a leading axis of the group size)."""
     if dist.get_backend(group) == "nccl":
-        dist.all_gather_into_tensor(out, part.contiguous(), group=group)
-    else:
-        dist.all_gather(list(out.unbind(0)), part.contiguous(), group=group)
+        return dist.all_gather_into_tensor(out, part.contiguous(), group=group, async_op=async_op)
+    return dist.all_gather(list(out.unbind(0)), part.contiguous(), group=group, async_op=async_op)
