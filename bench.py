@@ -64,7 +64,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -256,7 +256,7 @@ def time_cpu_oracle(spec, steps: int, warmup: int):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(synthetic.WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
@@ -352,14 +352,28 @@ def main():
 
     # ---- end to end: pinned host batch -> device every step (prefetched on a copy stream), loss read back
     copy_stream = torch.cuda.Stream()
-    bufs = [torch.empty_like(batch_dev), torch.empty_like(batch_dev)]
+    if world > 1:
+        from crosslayer_transcoder_b200 import parallel
+
+        chunk = (spec.batch + world - 1) // world
+        shape = (world * chunk, *batch_dev.shape[1:])
+        bufs = [torch.empty(shape, dtype=batch_dev.dtype, device=dev) for _ in range(2)]
+    else:
+        bufs = [torch.empty_like(batch_dev), torch.empty_like(batch_dev)]
     ready = [torch.cuda.Event(), torch.cuda.Event()]
     freed = [torch.cuda.Event(), torch.cuda.Event()]
+    views = [None, None]
 
     def upload(slot):
         with torch.cuda.stream(copy_stream):
             copy_stream.wait_event(freed[slot])
-            bufs[slot].copy_(batch_host, non_blocking=True)
+            if world > 1:
+                # every rank holds the batch on the host; each uploads 1/R of the rows and the rest
+                # arrives over NVLink
+                views[slot] = parallel.upload_batch(batch_host, bufs[slot], mod.tp_group)
+            else:
+                bufs[slot].copy_(batch_host, non_blocking=True)
+                views[slot] = bufs[slot]
             ready[slot].record(copy_stream)
 
     for f in freed:
@@ -375,7 +389,7 @@ def main():
         if i + 1 < args.steps:
             upload(slot ^ 1)
         torch.cuda.current_stream().wait_event(ready[slot])
-        loss = step(bufs[slot], 200 + i)
+        loss = step(views[slot], 200 + i)
         freed[slot].record()
         last = float(loss.detach())             # device -> host read of the step's result
     t1.record()
@@ -418,7 +432,7 @@ def main():
                 "dtype": "bf16" if spec.bf16 else "fp32", "data": "synthetic", "config": config,
                 "clocks": clocks,
                 "e2e": {"value": spec.batch * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
-                        "h2d_bytes_per_step": batch_host.numel() * batch_host.element_size(),
+                        "h2d_bytes_per_step": batch_host.numel() * batch_host.element_size() // world,
                         "d2h_bytes_per_step": 4, "last_loss": last},
                 "gpu_launches": launches, "roofline": roofline, "kernels": kernels}
         if world == 1 and not args.no_cpu_baseline:

@@ -308,16 +308,86 @@ __global__ void loss_bwd_kernel(const float* __restrict__ recon, const float* __
   }
 }
 
+// same computation, 4 consecutive columns per thread (needs D % 4 == 0): blockDim (32, 8) covers
+// 128 columns; 16-byte loads of the reconstruction, 8-byte loads/stores of the 16-bit tensors
+template <class TIn, class TOut>
+__global__ void loss_bwd_vec_kernel(const float* __restrict__ recon, const float* __restrict__ aux,
+                                    const TIn* __restrict__ batch, const float* __restrict__ mu,
+                                    const float* __restrict__ sd, const float* __restrict__ gscale, float aux_scale,
+                                    TOut* __restrict__ drecon, TOut* __restrict__ daux, float* __restrict__ db_dec,
+                                    int B, int L, int D, int rows_per_cta) {
+  const int LD = L * D;
+  const int c = (blockIdx.x * 32 + threadIdx.x) * 4;
+  const int b0 = blockIdx.y * rows_per_cta;
+  const int b1 = min(B, b0 + rows_per_cta);
+  const float gs = (gscale != nullptr ? *gscale : 1.f) / ((float)B * (float)L * (float)D);
+  float cs[4] = {0.f, 0.f, 0.f, 0.f};
+  if (c < LD) {
+    const int l = c / D, d = c % D;
+    const float4 m = *reinterpret_cast<const float4*>(mu + c), sv = *reinterpret_cast<const float4*>(sd + c);
+    const float mm[4] = {m.x, m.y, m.z, m.w}, ss[4] = {sv.x, sv.y, sv.z, sv.w};
+    for (int b = b0 + threadIdx.y; b < b1; b += blockDim.y) {
+      const long long i = (long long)b * LD + c;
+      const TIn* yp = batch + ((long long)b * 2 + 1) * LD + c;
+      const float4 r4 = *reinterpret_cast<const float4*>(recon + i);
+      const float rr[4] = {r4.x, r4.y, r4.z, r4.w};
+      float aa[4] = {0.f, 0.f, 0.f, 0.f};
+      if (aux != nullptr) {
+        const float4 a4 = *reinterpret_cast<const float4*>(aux + i);
+        aa[0] = a4.x, aa[1] = a4.y, aa[2] = a4.z, aa[3] = a4.w;
+      }
+      float g[4], ga[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float y = (to_float<TIn>(yp[q]) - mm[q]) / ss[q];
+        const float diff = rr[q] - y;
+        g[q] = 2.f * diff * gs;
+        ga[q] = 0.f;
+        if (aux != nullptr) {
+          const float ad = aa[q] + diff;
+          ga[q] = (ad * ad == ad * ad) ? 2.f * ad * aux_scale * gs : 0.f;
+          g[q] += ga[q];
+          cs[q] += ga[q];
+        }
+        cs[q] += g[q];
+      }
+      const long long o = ((long long)l * B + b) * D + d;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        drecon[o + q] = from_float<TOut>(g[q]);
+        if (aux != nullptr) daux[o + q] = from_float<TOut>(ga[q]);
+      }
+    }
+  }
+  __shared__ float sh[8][32][4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) sh[threadIdx.y][threadIdx.x][q] = cs[q];
+  __syncthreads();
+  if (threadIdx.y == 0 && c < LD) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float t = 0.f;
+      for (int j = 0; j < (int)blockDim.y; ++j) t += sh[j][threadIdx.x][q];
+      if (t != 0.f) atomicAdd(db_dec + c + q, t);
+    }
+  }
+}
+
 int loss_bwd(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu, const float* sd,
              const float* gscale, float aux_scale, void* drecon, void* daux, int out_bf16, float* db_dec, int B, int L,
              int D, cudaStream_t s) {
   if (B <= 0) return 0;
   const int LD = L * D;
   const int rows_per_cta = 256;
-  dim3 grid((LD + 31) / 32, (B + rows_per_cta - 1) / rows_per_cta), block(32, 8);
-#define CLT_LB(TI, TO)                                                                                          \
-  loss_bwd_kernel<TI, TO><<<grid, block, 0, s>>>(recon, aux, (const TI*)batch, mu, sd, gscale, aux_scale,       \
-                                                 (TO*)drecon, (TO*)daux, db_dec, B, L, D, rows_per_cta)
+  const bool vec = D % 4 == 0 && ((uintptr_t)recon | (uintptr_t)aux | (uintptr_t)mu | (uintptr_t)sd) % 16 == 0;
+  dim3 grid(vec ? (LD / 4 + 31) / 32 : (LD + 31) / 32, (B + rows_per_cta - 1) / rows_per_cta), block(32, 8);
+#define CLT_LB(TI, TO)                                                                                            \
+  if (vec)                                                                                                        \
+    loss_bwd_vec_kernel<TI, TO><<<grid, block, 0, s>>>(recon, aux, (const TI*)batch, mu, sd, gscale, aux_scale,   \
+                                                       (TO*)drecon, (TO*)daux, db_dec, B, L, D, rows_per_cta);    \
+  else                                                                                                            \
+    loss_bwd_kernel<TI, TO><<<grid, block, 0, s>>>(recon, aux, (const TI*)batch, mu, sd, gscale, aux_scale,       \
+                                                   (TO*)drecon, (TO*)daux, db_dec, B, L, D, rows_per_cta)
   switch (in_dtype * 2 + (out_bf16 ? 1 : 0)) {
     case 0: CLT_LB(float, float); break;
     case 1: CLT_LB(float, __nv_bfloat16); break;

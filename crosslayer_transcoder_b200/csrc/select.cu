@@ -282,6 +282,126 @@ select_topk_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, int
 }
 
 // ---------------------------------------------------------------------------------------
+// Main selection for short rows (a feature shard's slice): one WARP per row, 8 rows per CTA,
+// so that the per-row launch and synchronisation overhead does not dominate when F is a few
+// thousand.  Same scheme as above with 32 lanes instead of 256 threads (k <= 32):
+//   sweep 1  lane maxima; T_lo = k-th largest of the 32 maxima
+//   sweep 2  elements >= T_lo appended to the warp's shared-memory list (ballot offsets)
+//   finish   rank by counting, slot = rank
+// If the list overflows (masses of equal values) the exact k-th value is found by bisection on
+// the key bits over the row, and the row is emitted from that threshold.
+// ---------------------------------------------------------------------------------------
+constexpr int kWarpCand = 256;
+
+template <class T>
+__global__ void __launch_bounds__(256)
+select_topk_warp_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, int* __restrict__ idx_out,
+                        float* __restrict__ val_out, unsigned* __restrict__ fired_bits, long long rows, int B, int F,
+                        int k) {
+  __shared__ float cand_v[8][kWarpCand];
+  __shared__ int cand_i[8][kWarpCand];
+  const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long row = blockIdx.x * 8ll + wib;
+  if (row >= rows) return;
+  const int l = (int)(row / B);
+  const T* zr = z + (size_t)row * F;
+  const float* br = b_enc + (size_t)l * F;
+  int* io = idx_out + (size_t)row * k;
+  float* vo = val_out + (size_t)row * k;
+  const int words = (F + 31) / 32;
+  float* cv = cand_v[wib];
+  int* ci = cand_i[wib];
+
+  // sweep 1
+  float m = 0.f;
+  for (int i = 8 * lane; i < F; i += 256) {
+    float v[8];
+    RowReader<T>::load8(zr, br, i, v);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) m = fmaxf(m, v[q]);
+  }
+  int rank = 0;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    const float o = __shfl_sync(0xffffffffu, m, j);
+    rank += (o > m || (o == m && j < lane)) ? 1 : 0;
+  }
+  const unsigned who = __ballot_sync(0xffffffffu, rank == k - 1);
+  const float lo = __shfl_sync(0xffffffffu, m, __ffs(who) - 1);  // 0: fewer than k lanes saw a positive value
+
+  // sweep 2
+  int nc = 0;
+  for (int i = 8 * lane; i < F; i += 256) {
+    float v[8];
+    RowReader<T>::load8(zr, br, i, v);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const bool take = v[q] > 0.f && v[q] >= lo;
+      const unsigned bal = __ballot_sync(0xffffffffu, take);
+      if (take) {
+        const int c = nc + __popc(bal & ((1u << lane) - 1u));
+        if (c < kWarpCand) cv[c] = v[q], ci[c] = i + q;
+      }
+      nc += __popc(bal);
+    }
+  }
+  __syncwarp();
+  if (nc <= kWarpCand) {
+    for (int c = lane; c < nc; c += 32) {
+      const float v = cv[c];
+      const int fi = ci[c];
+      int r = 0;
+      for (int j = 0; j < nc; ++j) {
+        const float o = cv[j];
+        r += (o > v || (o == v && ci[j] < fi)) ? 1 : 0;
+      }
+      if (r < k) {
+        io[r] = fi;
+        vo[r] = v;
+        if (fired_bits != nullptr) atomicOr(fired_bits + (size_t)l * words + fi / 32, 1u << (fi & 31));
+      }
+    }
+    for (int s2 = nc + lane; s2 < k; s2 += 32) io[s2] = 0, vo[s2] = 0.f;
+    return;
+  }
+  // overflow: exact threshold by bisection on the key bits (largest T with count(key >= T) >= k)
+  unsigned Tk = 0u;
+  for (int bit = 30; bit >= 0; --bit) {
+    const unsigned trial = Tk | (1u << bit);
+    int c = 0;
+    for (int i = lane; i < F; i += 32) c += positive_key(ld_as_float<T>(zr, i) + __ldg(br + i)) >= trial ? 1 : 0;
+    c = __reduce_add_sync(0xffffffffu, c);
+    if (c >= k) Tk = trial;
+  }
+  int n_gt = 0;
+  for (int i = lane; i < F; i += 32) n_gt += positive_key(ld_as_float<T>(zr, i) + __ldg(br + i)) > Tk ? 1 : 0;
+  n_gt = __reduce_add_sync(0xffffffffu, n_gt);
+  int n_out = 0, ties_left = k - n_gt;  // Tk == 0 only if fewer than k positives: then every positive is above it
+  for (int i0 = 0; i0 < F; i0 += 32) {
+    const int i = i0 + lane;
+    const float v = i < F ? ld_as_float<T>(zr, i) + __ldg(br + i) : 0.f;
+    const unsigned key = positive_key(v);
+    const bool gt = key > Tk;
+    const bool tie = key != 0u && key == Tk;
+    const unsigned tb = __ballot_sync(0xffffffffu, tie);
+    const bool tie_take = tie && (__popc(tb & ((1u << lane) - 1u)) < ties_left);
+    const bool take = gt || tie_take;
+    const unsigned bal = __ballot_sync(0xffffffffu, take);
+    if (take) {
+      const int slot = n_out + __popc(bal & ((1u << lane) - 1u));
+      if (slot < k) {
+        io[slot] = i;
+        vo[slot] = v;
+        if (fired_bits != nullptr) atomicOr(fired_bits + (size_t)l * words + i / 32, 1u << (i & 31));
+      }
+    }
+    n_out += __popc(bal);
+    ties_left -= min(ties_left, __popc(tb));
+  }
+  for (int s2 = n_out + lane; s2 < k; s2 += 32) io[s2] = 0, vo[s2] = 0.f;
+}
+
+// ---------------------------------------------------------------------------------------
 // Dead-feature list per layer: dead_list[l, 0..n_dead[l]) = ascending indices with dead != 0.
 // One CTA per layer.
 // ---------------------------------------------------------------------------------------
@@ -383,6 +503,32 @@ select_aux_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, cons
 }
 
 // ---------------------------------------------------------------------------------------
+// cnt[row] = number of positive pre-activations among the dead features of the row.  Feature
+// shards sum these counts: a row whose total does not exceed k_aux keeps all of them, so no
+// candidate exchange is needed for it.  One warp per row.
+// ---------------------------------------------------------------------------------------
+template <class T>
+__global__ void aux_count_kernel(const T* __restrict__ z, const float* __restrict__ b_enc,
+                                 const int* __restrict__ dead_list, const int* __restrict__ n_dead,
+                                 int* __restrict__ cnt, long long rows, int B, int F) {
+  const long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int l = (int)(row / B);
+  const int nd = n_dead[l];
+  const T* zr = z + (size_t)row * F;
+  const float* br = b_enc + (size_t)l * F;
+  const int* dl = dead_list + (size_t)l * F;
+  int c = 0;
+  for (int j = lane; j < nd; j += 32) {
+    const int f = __ldg(dl + j);
+    c += (ld_as_float<T>(zr, f) + __ldg(br + f) > 0.f) ? 1 : 0;
+  }
+  c = __reduce_add_sync(0xffffffffu, c);
+  if (lane == 0) cnt[row] = c;
+}
+
+// ---------------------------------------------------------------------------------------
 // Exchange between feature shards: every rank contributes its k best values of a row;
 // thr[row] = the k-th largest positive value among all R * k of them (0 when there are fewer
 // than k positive ones, i.e. every positive value stays).  vals [R, rows, k].
@@ -395,24 +541,63 @@ topk_threshold_kernel(const float* __restrict__ vals, float* __restrict__ thr, l
   if (threadIdx.x == 0) thr[row] = __uint_as_float(sel.T);
 }
 
-// Keep the local candidates at or above the exchanged threshold (ties are all kept), clear the
-// others, mark the fired features.
-__global__ void topk_apply_threshold_kernel(const int* __restrict__ idx, float* __restrict__ val,
-                                            const float* __restrict__ thr, unsigned* __restrict__ fired_bits,
-                                            long long total, int B, int F, int k) {
-  const int words = (F + 31) / 32;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long row = i / k;
-    const float v = val[i];
-    if (v <= 0.f) continue;
-    if (positive_key(v) < positive_key(thr[row])) {
-      val[i] = 0.f;
-    } else if (fired_bits != nullptr) {
-      const int l = (int)(row / B), f = idx[i];
-      atomicOr(fired_bits + (size_t)l * words + f / 32, 1u << (f & 31));
-    }
+// Same threshold for short candidate lists (R * k <= 256): one warp per row holds all values in
+// registers and bisects on the key bits (31 steps of compare + popcount).
+__global__ void topk_threshold_warp_kernel(const float* __restrict__ vals, float* __restrict__ thr, long long rows, int R,
+                                           int k) {
+  const long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int n = R * k;
+  unsigned key[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const int i = lane + 32 * q;
+    key[q] = i < n ? positive_key(__ldg(vals + ((size_t)(i / k) * rows + row) * k + i % k)) : 0u;
   }
+  unsigned Tk = 0u;
+  for (int bit = 30; bit >= 0; --bit) {
+    const unsigned trial = Tk | (1u << bit);
+    int c = 0;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) c += key[q] >= trial ? 1 : 0;
+    c = __reduce_add_sync(0xffffffffu, c);
+    if (c >= k) Tk = trial;
+  }
+  if (lane == 0) thr[row] = __uint_as_float(Tk);
+}
+
+// Keep the local candidates at or above the exchanged threshold (ties are all kept), move them to
+// the front of the row's slots, clear the rest, mark the fired features.  One warp per row.
+__global__ void topk_apply_threshold_kernel(int* __restrict__ idx, float* __restrict__ val,
+                                            const float* __restrict__ thr, unsigned* __restrict__ fired_bits,
+                                            long long rows, int B, int F, int k) {
+  const long long row = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int words = (F + 31) / 32;
+  const int l = (int)(row / B);
+  const unsigned tk = positive_key(thr[row]);
+  int* ir = idx + (size_t)row * k;
+  float* vr = val + (size_t)row * k;
+  int n_out = 0;
+  for (int j0 = 0; j0 < k; j0 += 32) {
+    const int j = j0 + lane;
+    const float v = j < k ? vr[j] : 0.f;
+    const int f = j < k ? ir[j] : 0;
+    const bool keep = v > 0.f && positive_key(v) >= tk;
+    const unsigned bal = __ballot_sync(0xffffffffu, keep);
+    __syncwarp();
+    if (keep) {
+      const int slot = n_out + __popc(bal & ((1u << lane) - 1u));  // slot <= j: never overtakes the reads
+      vr[slot] = v;
+      ir[slot] = f;
+      if (fired_bits != nullptr) atomicOr(fired_bits + (size_t)l * words + f / 32, 1u << (f & 31));
+    }
+    n_out += __popc(bal);
+    __syncwarp();
+  }
+  for (int j = n_out + lane; j < k; j += 32) vr[j] = 0.f, ir[j] = 0;
 }
 
 }  // namespace
@@ -432,12 +617,23 @@ int clt_select_topk(const void* z, const float* b_enc, int* idx_out, float* val_
   const long long rows = (long long)L * B;
   CLT_CHECK_ARG(rows < (1ll << 31), "select_topk: too many rows");
   cudaStream_t s = (cudaStream_t)stream;
-  if (bf16)
-    select_topk_kernel<__nv_bfloat16><<<(unsigned)rows, kSelThreads, 0, s>>>((const __nv_bfloat16*)z, b_enc, idx_out,
-                                                                               val_out, fired_bits, B, F, k);
-  else
-    select_topk_kernel<float><<<(unsigned)rows, kSelThreads, 0, s>>>((const float*)z, b_enc, idx_out, val_out,
-                                                                      fired_bits, B, F, k);
+  const bool warp_rows = k <= 32 && F % 256 == 0 && F <= 8192;   // short rows: one warp each
+  const unsigned wblocks = (unsigned)((rows + 7) / 8);
+  if (bf16) {
+    if (warp_rows)
+      select_topk_warp_kernel<__nv_bfloat16><<<wblocks, 256, 0, s>>>((const __nv_bfloat16*)z, b_enc, idx_out, val_out,
+                                                                      fired_bits, rows, B, F, k);
+    else
+      select_topk_kernel<__nv_bfloat16><<<(unsigned)rows, kSelThreads, 0, s>>>((const __nv_bfloat16*)z, b_enc, idx_out,
+                                                                                 val_out, fired_bits, B, F, k);
+  } else {
+    if (warp_rows)
+      select_topk_warp_kernel<float><<<wblocks, 256, 0, s>>>((const float*)z, b_enc, idx_out, val_out, fired_bits, rows,
+                                                              B, F, k);
+    else
+      select_topk_kernel<float><<<(unsigned)rows, kSelThreads, 0, s>>>((const float*)z, b_enc, idx_out, val_out,
+                                                                        fired_bits, B, F, k);
+  }
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -478,22 +674,42 @@ int clt_select_aux(const void* z, const float* b_enc, const int* dead_list, cons
   return 0;
 }
 
-int clt_topk_threshold(const float* vals, float* thr, int64_t rows, int R, int k, clt_stream_t stream) {
-  CLT_CHECK_ARG(rows > 0 && R > 0 && k > 0 && rows < (1ll << 31), "topk_threshold: bad dims");
-  CLT_CHECK_ARG(vals && thr, "topk_threshold: null pointer");
-  topk_threshold_kernel<<<(unsigned)rows, kSelThreads, 0, (cudaStream_t)stream>>>(vals, thr, rows, R, k);
+int clt_aux_count(const void* z, const float* b_enc, const int* dead_list, const int* n_dead, int* cnt, int B, int L,
+                  int F, int bf16, clt_stream_t stream) {
+  CLT_CHECK_ARG(B > 0 && L > 0 && F > 0, "aux_count: bad dims");
+  CLT_CHECK_ARG(z && b_enc && dead_list && n_dead && cnt, "aux_count: null pointer");
+  const long long rows = (long long)L * B;
+  const unsigned blocks = (unsigned)((rows * 32 + 255) / 256);
+  if (bf16)
+    aux_count_kernel<__nv_bfloat16><<<blocks, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)z, b_enc, dead_list,
+                                                                              n_dead, cnt, rows, B, F);
+  else
+    aux_count_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>((const float*)z, b_enc, dead_list, n_dead, cnt,
+                                                                     rows, B, F);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
 
-int clt_topk_apply_threshold(const int* idx, float* val, const float* thr, uint32_t* fired_bits, int B, int L, int F,
-                             int k, clt_stream_t stream) {
+int clt_topk_threshold(const float* vals, float* thr, int64_t rows, int R, int k, clt_stream_t stream) {
+  CLT_CHECK_ARG(rows > 0 && R > 0 && k > 0 && rows < (1ll << 31), "topk_threshold: bad dims");
+  CLT_CHECK_ARG(vals && thr, "topk_threshold: null pointer");
+  if ((long long)R * k <= 256) {
+    const unsigned blocks = (unsigned)((rows * 32 + 255) / 256);
+    topk_threshold_warp_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(vals, thr, rows, R, k);
+  } else {
+    topk_threshold_kernel<<<(unsigned)rows, kSelThreads, 0, (cudaStream_t)stream>>>(vals, thr, rows, R, k);
+  }
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int clt_topk_apply_threshold(int* idx, float* val, const float* thr, uint32_t* fired_bits, int B, int L, int F, int k,
+                             clt_stream_t stream) {
   CLT_CHECK_ARG(B > 0 && L > 0 && F > 0 && k > 0, "topk_apply_threshold: bad dims");
   CLT_CHECK_ARG(idx && val && thr, "topk_apply_threshold: null pointer");
-  const long long total = (long long)L * B * k;
-  const long long want = (total + 255) / 256;
-  topk_apply_threshold_kernel<<<(unsigned)(want < 148 * 16 ? want : 148 * 16), 256, 0, (cudaStream_t)stream>>>(
-      idx, val, thr, fired_bits, total, B, F, k);
+  const long long rows = (long long)L * B;
+  const unsigned blocks = (unsigned)((rows * 32 + 255) / 256);
+  topk_apply_threshold_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(idx, val, thr, fired_bits, rows, B, F, k);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -89,27 +89,27 @@ sparse_dec_fwd_kernel(const int* __restrict__ idx, const float* __restrict__ val
 #pragma unroll
     for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
   const int s_lo = crosslayer ? 0 : t;
-  const int nrows = (t - s_lo + 1) * k;
-  for (int r = warp; r < nrows; r += 4) {
-    const int s = s_lo + r / k, j = r % k;
-    const size_t e = ((size_t)s * B + b) * k + j;
-    const float v = __ldg(val + e);
-    if (v == 0.f) continue;
-    const int f = __ldg(idx + e);
-    if (f < 0 || f >= F) {
-      report_status(status, kBadIndex);
-      continue;
-    }
+  for (int s = s_lo; s <= t; ++s) {
     const size_t p = crosslayer ? (size_t)pair_index(t, s) : (size_t)t;
-    const T* row = W + (p * F + f) * D;
+    const size_t e0 = ((size_t)s * B + b) * k;
+    for (int j = warp; j < k; j += 4) {
+      const float v = __ldg(val + e0 + j);
+      if (v == 0.f) break;  // valid slots come first
+      const int f = __ldg(idx + e0 + j);
+      if (f < 0 || f >= F) {
+        report_status(status, kBadIndex);
+        continue;
+      }
+      const T* row = W + (p * F + f) * D;
 #pragma unroll
-    for (int i = 0; i < VPL; ++i) {
-      const int c = lane + 32 * i;
-      if (c < nvec) {
-        float w[8];
-        Vec8<T>::load(row + 8 * c, w);
+      for (int i = 0; i < VPL; ++i) {
+        const int c = lane + 32 * i;
+        if (c < nvec) {
+          float w[8];
+          Vec8<T>::load(row + 8 * c, w);
 #pragma unroll
-        for (int q = 0; q < 8; ++q) acc[i][q] = fmaf(v, w[q], acc[i][q]);
+          for (int q = 0; q < 8; ++q) acc[i][q] = fmaf(v, w[q], acc[i][q]);
+        }
       }
     }
   }

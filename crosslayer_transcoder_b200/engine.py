@@ -407,11 +407,19 @@ class StepEngine:
             nd = int(n_dead.max())                      # host read: sizes the compacted contractions
             nd_pad = max(64, _round_up(nd, 64))
             a_aux = ws.get("a_aux", (L, B, nd_pad), T, dev)
+            exchange = False
             if world > 1:
+                # a row whose positive dead values, summed over the shards, do not exceed k_aux keeps all
+                # of them: the candidate exchange is needed only if some row has more
+                from .parallel import all_gather, all_reduce_sum
+
+                cnt = ws.get("aux_cnt", (L, B), torch.int32, dev)
+                self._call("clt_aux_count", z, enc.b.data, dead_list, n_dead, cnt, B, L, F, int(bf16), s)
+                all_reduce_sum(cnt, group)
+                exchange = int(cnt.max()) > k_aux           # host read (same value on every rank)
+            if exchange:
                 # offer this shard's k_aux best dead values per row; the gather runs while the main
                 # decoder works
-                from .parallel import all_gather
-
                 cand = ws.get("aux_cand", (L, B, k_aux), torch.float32, dev)
                 self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, None, cand, None, 1, B, L, F, k_aux,
                            nd_pad, int(bf16), s)
@@ -424,7 +432,7 @@ class StepEngine:
 
             pending.append(all_reduce_sum(rbuf[:n_rec], group, async_op=True))
         if k_aux > 0:
-            if world == 1:
+            if not exchange:
                 self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, a_aux, None, None, 0, B, L, F, k_aux,
                            nd_pad, int(bf16), s)
             else:

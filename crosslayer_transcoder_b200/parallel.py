@@ -51,3 +51,19 @@ def all_gather(out: torch.Tensor, part: torch.Tensor, group, async_op: bool = Fa
     if dist.get_backend(group) == "nccl":
         return dist.all_gather_into_tensor(out, part.contiguous(), group=group, async_op=async_op)
     return dist.all_gather(list(out.unbind(0)), part.contiguous(), group=group, async_op=async_op)
+
+
+def upload_batch(batch_host: torch.Tensor, staging: torch.Tensor, group) -> torch.Tensor:
+    """Bring a pinned host batch ``[B, ...]`` that every rank holds onto every GPU while crossing
+    PCIe only once per row: rank r copies rows ``[r c, (r+1) c)`` (c = ceil(B / R)) host-to-device
+    and the slices are all-gathered over NVLink.  ``staging`` is a device buffer ``[R c, ...]``;
+    returns its first B rows."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    B = batch_host.shape[0]
+    c = (B + world - 1) // world
+    lo, hi = min(rank * c, B), min((rank + 1) * c, B)
+    mine = staging[rank * c:(rank + 1) * c]
+    if hi > lo:
+        mine[: hi - lo].copy_(batch_host[lo:hi], non_blocking=True)
+    all_gather(staging.view(world, c, *staging.shape[1:]), mine, group)
+    return staging[:B]

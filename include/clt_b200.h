@@ -118,8 +118,8 @@ int clt_dead_update(int64_t* last_active, uint32_t* fired_bits, uint8_t* dead, i
 /* ---- TopK path --------------------------------------------------------------------------- */
 
 /* PerLayerTopK._training_forward (crosslayer_transcoder/model/topk.py:53-63) on pre = z + b_enc:
- * idx / val [L, B, k] hold the (at most k) largest positive pre-activations of every row, unused
- * slots idx 0 / val 0 (a kept value that is not positive is zero after the ReLU and gets no
+ * idx / val [L, B, k] hold the (at most k) largest positive pre-activations of every row, valid
+ * slots first, unused slots idx 0 / val 0 (a kept value that is not positive is zero after the ReLU and gets no
  * gradient, so it is not stored).  fired_bits as in clt_encoder_fwd_act; may be NULL. */
 int clt_select_topk(const void* z, const float* b_enc, int* idx_out, float* val_out, uint32_t* fired_bits,
                     int B, int L, int F, int k, int bf16, clt_stream_t stream);
@@ -138,13 +138,19 @@ int clt_select_aux(const void* z, const float* b_enc, const int* dead_list, cons
                    float* cand_out, const float* thr, int mode, int B, int L, int F, int k_aux, int nd_pad,
                    int bf16, clt_stream_t stream);
 
+/* cnt[l, b] = number of positive pre-activations among the dead features of the row (feature shards
+ * sum these to see whether any row needs the candidate exchange of the auxiliary selection). */
+int clt_aux_count(const void* z, const float* b_enc, const int* dead_list, const int* n_dead, int* cnt, int B,
+                  int L, int F, int bf16, clt_stream_t stream);
+
 /* Selection across feature shards (the reference has no counterpart: its tensor-parallel plan
  * rejects TopK, crosslayer_transcoder/model/parallel.py:269-274).  vals [R, rows, k] holds every
  * shard's k best values per row; thr[row] = the k-th largest positive one (0: keep all). */
 int clt_topk_threshold(const float* vals, float* thr, int64_t rows, int R, int k, clt_stream_t stream);
-/* Clear the local candidates below thr (ties stay), mark the fired features. */
-int clt_topk_apply_threshold(const int* idx, float* val, const float* thr, uint32_t* fired_bits, int B, int L,
-                             int F, int k, clt_stream_t stream);
+/* Keep the local candidates at or above thr (ties stay), moved to the front of the row's slots;
+ * clear the rest; mark the fired features. */
+int clt_topk_apply_threshold(int* idx, float* val, const float* thr, uint32_t* fired_bits, int B, int L, int F,
+                             int k, clt_stream_t stream);
 
 /* CrosslayerDecoder.forward / Decoder.forward (clt.py:334-343, 241-248) on the selected features:
  * recon[b,t,:] = b_dec[t] + sum_{s<=t} sum_j val[s,b,j] W_dec[pair(t,s), idx[s,b,j], :]. */

@@ -79,7 +79,8 @@ CASES = [
     ("clt_no_dead", 2, 64, 256, 129, True, 4, 8, 0.0),
     ("clt_few_dead", 3, 64, 512, 150, True, 16, 64, 0.05),      # fewer dead features than k_aux
     ("clt_no_aux", 2, 64, 256, 100, True, 4, 0, 0.0),
-    ("clt_wide", 2, 64, 4096, 130, True, 32, 64, 0.1),          # wide rows: the two-sweep selection path
+    ("clt_wide", 2, 64, 4096, 130, True, 32, 64, 0.1),          # one warp per row, k = 32
+    ("clt_wider", 2, 64, 16384, 70, True, 32, 64, 0.05),        # one CTA per row: the two-sweep selection path
 ]
 
 
@@ -116,7 +117,7 @@ def test_selection_edge_cases():
 
     dev = torch.device("cuda:0")
     lib().check_device()
-    for L, B, F, ks in ((2, 5, 96, (1, 7, 96)), (2, 5, 4096, (1, 32, 256, 300, 4096))):
+    for L, B, F, ks in ((2, 5, 96, (1, 7, 96)), (2, 5, 4096, (1, 32, 256, 300, 4096)), (2, 9, 16384, (1, 32, 256, 300))):
         _check_selection(dev, L, B, F, ks)
     spec = synthetic.WorkloadSpec("kbig", 2, 64, 64, 16, "topk", True, False, rank_u=8, n_outlier=1, k=65, k_aux=0)
     batch, w, la = spec_inputs(spec)
