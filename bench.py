@@ -36,7 +36,8 @@ DEFAULT_WORKLOAD = "c3_clt_topk_bf16"
 
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels from
 # the ncu captures summarised under profiles/; None where no capture has been taken.
-NCU_TRAFFIC = {}
+# Adam: 29.83 B/parameter (profiles/adam_kernel_c3_4layer.md), scaled by the parameter count at run time.
+NCU_TRAFFIC_PER_UNIT = {"clt_adam_step": 29.83}
 
 
 def load_peaks():
@@ -425,7 +426,7 @@ def main():
         roofline = {"kernel": top, "bound": tk["bound"], "achieved": tk["achieved"],
                     "peak": peaks["bf16_tflops"] if tk["bound"] == "tensor" else peaks["hbm_gbs"],
                     "unit": tk["unit"], "frac": tk["frac"], "peak_source": peaks["source"],
-                    "traffic": NCU_TRAFFIC.get((spec.name, top))}
+                    "traffic": (NCU_TRAFFIC_PER_UNIT[top] * eng.flat.numel if top in NCU_TRAFFIC_PER_UNIT else None)}
         line = {"metric": METRIC, "value": spec.batch * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
                 "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
