@@ -165,6 +165,8 @@ def algorithmic_work(spec, Fl: int, n_params: int, batch_bytes_per_elem: int, nd
     P = L * (L + 1) // 2 if spec.crosslayer else L
     e = 2 if spec.bf16 else 4
     Fd = nd_pad if spec.kind == "topk" else Fl        # width of the dense decoder-side contractions
+    if spec.kind == "batchtopk":
+        k = max(spec.k, 1)
     enc = 2.0 * B * L * D * Fl
     dec = 2.0 * B * P * Fd * D
     bld = float(B) * L * D
@@ -189,6 +191,8 @@ def algorithmic_work(spec, Fl: int, n_params: int, batch_bytes_per_elem: int, nd
         "clt_scatter_rows": ("hbm", float(P) * nd_pad * D * 4 * 3),
         "clt_scatter_cols": ("hbm", float(L) * nd_pad * D * 4 * 3),
         "clt_csc_build": ("hbm", float(L) * B * k * 8 * 2 + float(L) * Fl * 4 * 3),
+        "clt_batchtopk_hist": ("hbm", float(L) * B * Fl * e),
+        "clt_batchtopk_collect": ("hbm", float(L) * B * Fl * e + float(L) * B * k * 12),
     }
     return work
 

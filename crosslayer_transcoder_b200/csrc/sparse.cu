@@ -76,7 +76,8 @@ struct Vec8<float> {
 // =========================================================================================
 template <class T, int VPL>
 __global__ void __launch_bounds__(128)
-sparse_dec_fwd_kernel(const int* __restrict__ idx, const float* __restrict__ val, const T* __restrict__ W,
+sparse_dec_fwd_kernel(const int* __restrict__ idx, const float* __restrict__ val, const int* __restrict__ row_start,
+                      const int* __restrict__ row_cnt, long long npl, const T* __restrict__ W,
                       const float* __restrict__ b_dec, float* __restrict__ recon, int B, int L, int D, int F, int k,
                       int crosslayer, int* status) {
   extern __shared__ float red[];  // [4][D]
@@ -91,8 +92,14 @@ sparse_dec_fwd_kernel(const int* __restrict__ idx, const float* __restrict__ val
   const int s_lo = crosslayer ? 0 : t;
   for (int s = s_lo; s <= t; ++s) {
     const size_t p = crosslayer ? (size_t)pair_index(t, s) : (size_t)t;
-    const size_t e0 = ((size_t)s * B + b) * k;
-    for (int j = warp; j < k; j += 4) {
+    // the row's entries: k fixed slots (valid ones first), or a (start, count) segment of the layer's list
+    size_t e0 = ((size_t)s * B + b) * k;
+    int n = k;
+    if (row_start != nullptr) {
+      e0 = (size_t)s * npl + __ldg(row_start + (size_t)s * B + b);
+      n = __ldg(row_cnt + (size_t)s * B + b);
+    }
+    for (int j = warp; j < n; j += 4) {
       const float v = __ldg(val + e0 + j);
       if (v == 0.f) break;  // valid slots come first
       const int f = __ldg(idx + e0 + j);
@@ -214,8 +221,9 @@ __global__ void csc_fill_kernel(const int* __restrict__ idx, const float* __rest
 template <class T, int VPL>
 __global__ void __launch_bounds__(128)
 sparse_bwd_dec_kernel(const int* __restrict__ col_ptr, const int* __restrict__ ent, const float* __restrict__ val,
-                      const T* __restrict__ W, const T* __restrict__ drecon, float* __restrict__ dW,
-                      float* __restrict__ dval, int B, int L, int D, int F, int k, int crosslayer, long long n_rows) {
+                      const int* __restrict__ etok, long long npl_, const T* __restrict__ W,
+                      const T* __restrict__ drecon, float* __restrict__ dW, float* __restrict__ dval, int B, int L,
+                      int D, int F, int k, int crosslayer, long long n_rows) {
   const long long wid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (wid >= n_rows) return;
@@ -225,7 +233,7 @@ sparse_bwd_dec_kernel(const int* __restrict__ col_ptr, const int* __restrict__ e
   const int nvec = D / 8;
   const int* cp = col_ptr + (size_t)s * (F + 1);
   const int e0 = __ldg(cp + f), e1 = __ldg(cp + f + 1);
-  const size_t npl = (size_t)B * k;
+  const size_t npl = (size_t)npl_;
   const size_t roff = ((size_t)p * F + f) * D;
   using V = Vec8<T>;
   constexpr bool kTwo = VPL <= 4;  // two rows in flight while the register budget allows it
@@ -242,11 +250,12 @@ sparse_bwd_dec_kernel(const int* __restrict__ col_ptr, const int* __restrict__ e
   // (two at a time where possible, so that two independent row fetches are in flight per warp)
   for (int eb = e0; eb < e1; eb += 32) {
     const int n = min(32, e1 - eb);
-    int my_slot = 0;
+    int my_slot = 0, my_tok = 0;
     float my_val = 0.f;
     if (lane < n) {
       my_slot = __ldg(ent + (size_t)s * npl + eb + lane);
       my_val = __ldg(val + (size_t)s * npl + my_slot);
+      my_tok = etok != nullptr ? __ldg(etok + (size_t)s * npl + my_slot) : my_slot / k;
     }
     for (int j = 0; j < n; j += (kTwo ? 2 : 1)) {
       const bool two = kTwo && (j + 1 < n);
@@ -254,8 +263,10 @@ sparse_bwd_dec_kernel(const int* __restrict__ col_ptr, const int* __restrict__ e
       const int slot1 = __shfl_sync(0xffffffffu, my_slot, two ? j + 1 : j);
       const float v0 = __shfl_sync(0xffffffffu, my_val, j);
       const float v1 = two ? __shfl_sync(0xffffffffu, my_val, j + 1) : 0.f;
-      const T* dr0 = drecon + ((size_t)t * B + slot0 / k) * D;
-      const T* dr1 = drecon + ((size_t)t * B + slot1 / k) * D;
+      const int tok0 = __shfl_sync(0xffffffffu, my_tok, j);
+      const int tok1 = __shfl_sync(0xffffffffu, my_tok, two ? j + 1 : j);
+      const T* dr0 = drecon + ((size_t)t * B + tok0) * D;
+      const T* dr1 = drecon + ((size_t)t * B + tok1) * D;
       typename V::Raw x0[VPL], x1[kTwo ? VPL : 1];
 #pragma unroll
       for (int i = 0; i < VPL; ++i) {
@@ -315,11 +326,11 @@ constexpr int kEncFB = 8;
 template <class T>
 __global__ void __launch_bounds__(256)
 sparse_bwd_enc_kernel(const int* __restrict__ col_ptr, const int* __restrict__ ent, const float* __restrict__ dval,
-                      const T* __restrict__ xn, float* __restrict__ dW, float* __restrict__ db, int B, int D, int F,
-                      int k) {
+                      const int* __restrict__ etok, long long npl_, const T* __restrict__ xn, float* __restrict__ dW,
+                      float* __restrict__ db, int B, int D, int F, int k) {
   const int l = blockIdx.y, f0 = blockIdx.x * kEncFB, d0 = blockIdx.z * 768;
   const int* cp = col_ptr + (size_t)l * (F + 1);
-  const size_t npl = (size_t)B * k;
+  const size_t npl = (size_t)npl_;
   float acc[3][kEncFB];
 #pragma unroll
   for (int i = 0; i < 3; ++i)
@@ -335,7 +346,8 @@ sparse_bwd_enc_kernel(const int* __restrict__ col_ptr, const int* __restrict__ e
     for (int e = e0; e < e1; ++e) {
       const int slot = __ldg(ent + (size_t)l * npl + e);
       const float g = __ldg(dval + (size_t)l * npl + slot);
-      const T* x = xn + ((size_t)l * B + slot / k) * D;
+      const int tok = etok != nullptr ? __ldg(etok + (size_t)l * npl + slot) : slot / k;
+      const T* x = xn + ((size_t)l * B + tok) * D;
       bs += g;
 #pragma unroll
       for (int i = 0; i < 3; ++i) {
@@ -420,8 +432,9 @@ __global__ void scatter_cols_kernel(const float* __restrict__ src, const float* 
 }
 
 template <class T>
-int launch_dec_fwd(const int* idx, const float* val, const void* W, const float* b_dec, float* recon, int B, int L,
-                   int D, int F, int k, int crosslayer, int* status, cudaStream_t s) {
+int launch_dec_fwd(const int* idx, const float* val, const int* row_start, const int* row_cnt, long long npl,
+                   const void* W, const float* b_dec, float* recon, int B, int L, int D, int F, int k, int crosslayer,
+                   int* status, cudaStream_t s) {
   const int vpl = (D / 8 + 31) / 32;
   dim3 grid(B, L);
   const size_t smem = 4 * (size_t)D * sizeof(float);
@@ -429,8 +442,8 @@ int launch_dec_fwd(const int* idx, const float* val, const void* W, const float*
   case V:                                                                                                           \
     CLT_CHECK_CUDA(cudaFuncSetAttribute(sparse_dec_fwd_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                         (int)smem));                                                                \
-    sparse_dec_fwd_kernel<T, V><<<grid, 128, smem, s>>>(idx, val, (const T*)W, b_dec, recon, B, L, D, F, k,         \
-                                                        crosslayer, status);                                        \
+    sparse_dec_fwd_kernel<T, V><<<grid, 128, smem, s>>>(idx, val, row_start, row_cnt, npl, (const T*)W, b_dec,      \
+                                                        recon, B, L, D, F, k, crosslayer, status);                  \
     break;
   switch (vpl) {
     CLT_DEC_FWD(1) CLT_DEC_FWD(2) CLT_DEC_FWD(3) CLT_DEC_FWD(4) CLT_DEC_FWD(6) CLT_DEC_FWD(8) CLT_DEC_FWD(9)
@@ -445,8 +458,9 @@ int launch_dec_fwd(const int* idx, const float* val, const void* W, const float*
 }
 
 template <class T>
-int launch_bwd_dec(const int* col_ptr, const int* ent, const float* val, const void* W, const void* drecon, float* dW,
-                   float* dval, int B, int L, int D, int F, int k, int crosslayer, cudaStream_t s) {
+int launch_bwd_dec(const int* col_ptr, const int* ent, const float* val, const int* etok, long long npl, const void* W,
+                   const void* drecon, float* dW, float* dval, int B, int L, int D, int F, int k, int crosslayer,
+                   cudaStream_t s) {
   const int vpl = (D / 8 + 31) / 32;
   const int P = crosslayer ? L * (L + 1) / 2 : L;
   const long long rows = (long long)P * F;
@@ -455,8 +469,8 @@ int launch_bwd_dec(const int* col_ptr, const int* ent, const float* val, const v
   const unsigned grid = (unsigned)blocks;
 #define CLT_BWD_DEC(V)                                                                                            \
   case V:                                                                                                         \
-    sparse_bwd_dec_kernel<T, V><<<grid, 128, 0, s>>>(col_ptr, ent, val, (const T*)W, (const T*)drecon, dW, dval, \
-                                                     B, L, D, F, k, crosslayer, rows);                            \
+    sparse_bwd_dec_kernel<T, V><<<grid, 128, 0, s>>>(col_ptr, ent, val, etok, npl, (const T*)W, (const T*)drecon, \
+                                                     dW, dval, B, L, D, F, k, crosslayer, rows);                  \
     break;
   switch (vpl) {
     CLT_BWD_DEC(1) CLT_BWD_DEC(2) CLT_BWD_DEC(3) CLT_BWD_DEC(4) CLT_BWD_DEC(6) CLT_BWD_DEC(8) CLT_BWD_DEC(9)
@@ -477,26 +491,29 @@ using namespace clt;
 
 extern "C" {
 
-int clt_sparse_decoder_fwd(const int* idx, const float* val, const void* W_dec, const float* b_dec, float* recon, int B,
-                           int L, int D, int F, int k, int crosslayer, int bf16, int* status, clt_stream_t stream) {
+int clt_sparse_decoder_fwd(const int* idx, const float* val, const int* row_start, const int* row_cnt, int64_t npl,
+                           const void* W_dec, const float* b_dec, float* recon, int B, int L, int D, int F, int k,
+                           int crosslayer, int bf16, int* status, clt_stream_t stream) {
   CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && F > 0 && k > 0, "sparse_decoder_fwd: bad dims B=%d L=%d D=%d F=%d k=%d", B,
                 L, D, F, k);
   CLT_CHECK_ARG(D % 8 == 0, "sparse_decoder_fwd: d_acts=%d must be a multiple of 8", D);
   CLT_CHECK_ARG(idx && val && W_dec && recon, "sparse_decoder_fwd: null pointer");
+  CLT_CHECK_ARG((row_start == nullptr) == (row_cnt == nullptr), "sparse_decoder_fwd: row_start and row_cnt go together");
+  CLT_CHECK_ARG(row_start != nullptr || npl == (int64_t)B * k, "sparse_decoder_fwd: fixed slots need npl = B*k");
   CLT_CHECK_ARG(B <= 2147483647 && L <= 65535, "sparse_decoder_fwd: grid too large");
   if (bf16)
-    return launch_dec_fwd<__nv_bfloat16>(idx, val, W_dec, b_dec, recon, B, L, D, F, k, crosslayer, status,
-                                         (cudaStream_t)stream);
-  return launch_dec_fwd<float>(idx, val, W_dec, b_dec, recon, B, L, D, F, k, crosslayer, status, (cudaStream_t)stream);
+    return launch_dec_fwd<__nv_bfloat16>(idx, val, row_start, row_cnt, npl, W_dec, b_dec, recon, B, L, D, F, k,
+                                         crosslayer, status, (cudaStream_t)stream);
+  return launch_dec_fwd<float>(idx, val, row_start, row_cnt, npl, W_dec, b_dec, recon, B, L, D, F, k, crosslayer,
+                               status, (cudaStream_t)stream);
 }
 
-int clt_csc_build(const int* idx, const float* val, int* col_ptr, int* cursor, int* ent, int B, int L, int F, int k,
+int clt_csc_build(const int* idx, const float* val, int* col_ptr, int* cursor, int* ent, int64_t npl, int L, int F,
                   int* status, clt_stream_t stream) {
-  CLT_CHECK_ARG(B > 0 && L > 0 && F > 0 && k > 0, "csc_build: bad dims B=%d L=%d F=%d k=%d", B, L, F, k);
+  CLT_CHECK_ARG(npl > 0 && L > 0 && F > 0, "csc_build: bad dims npl=%lld L=%d F=%d", (long long)npl, L, F);
   CLT_CHECK_ARG(idx && val && col_ptr && cursor && ent, "csc_build: null pointer");
   cudaStream_t s = (cudaStream_t)stream;
-  const long long npl = (long long)B * k;
-  CLT_CHECK_ARG(npl < (1ll << 31), "csc_build: B*k too large");
+  CLT_CHECK_ARG(npl < (1ll << 31), "csc_build: too many entries per layer");
   CLT_CHECK_CUDA(cudaMemsetAsync(col_ptr, 0, sizeof(int) * (size_t)L * (F + 1), s));
   const long long total = npl * L;
   const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
@@ -533,9 +550,9 @@ static int* static_cursor_ptr(int* err) {
   return ptr[dev];
 }
 
-int clt_csc_build_static(const int* idx, const float* val, int* col_ptr, int* ent, int B, int L, int F, int k,
+int clt_csc_build_static(const int* idx, const float* val, int* col_ptr, int* ent, int64_t npl, int L, int F,
                          int* status, clt_stream_t stream) {
-  CLT_CHECK_ARG(B > 0 && L > 0 && F > 0 && k > 0, "csc_build_static: bad dims B=%d L=%d F=%d k=%d", B, L, F, k);
+  CLT_CHECK_ARG(npl > 0 && L > 0 && F > 0, "csc_build_static: bad dims npl=%lld L=%d F=%d", (long long)npl, L, F);
   CLT_CHECK_ARG(idx && val && col_ptr && ent, "csc_build_static: null pointer");
   CLT_CHECK_ARG((long long)L * F <= kStaticCursorCap,
                 "csc_build_static: L*F = %lld exceeds the built-in scratch of %lld entries; use clt_csc_build with a "
@@ -546,35 +563,36 @@ int clt_csc_build_static(const int* idx, const float* val, int* col_ptr, int* en
   if (cursor == nullptr) return err;
   // every cursor entry in [0, L*F) is rewritten by the scan before the fill reads it, so nothing left
   // in the array by an earlier call is ever observed
-  return clt_csc_build(idx, val, col_ptr, cursor, ent, B, L, F, k, status, stream);
+  return clt_csc_build(idx, val, col_ptr, cursor, ent, npl, L, F, status, stream);
 }
 
-int clt_sparse_bwd_dec(const int* col_ptr, const int* ent, const float* val, const void* W_dec, const void* drecon,
-                       float* dW, float* dval, int B, int L, int D, int F, int k, int crosslayer, int bf16,
-                       clt_stream_t stream) {
-  CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && F > 0 && k > 0, "sparse_bwd_dec: bad dims");
+int clt_sparse_bwd_dec(const int* col_ptr, const int* ent, const float* val, const int* etok, int64_t npl,
+                       const void* W_dec, const void* drecon, float* dW, float* dval, int B, int L, int D, int F, int k,
+                       int crosslayer, int bf16, clt_stream_t stream) {
+  CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && F > 0 && k > 0 && npl > 0, "sparse_bwd_dec: bad dims");
   CLT_CHECK_ARG(D % 8 == 0, "sparse_bwd_dec: d_acts=%d must be a multiple of 8", D);
   CLT_CHECK_ARG(col_ptr && ent && val && W_dec && drecon && dW && dval, "sparse_bwd_dec: null pointer");
-  CLT_CHECK_CUDA(cudaMemsetAsync(dval, 0, sizeof(float) * (size_t)L * B * k, (cudaStream_t)stream));
+  CLT_CHECK_CUDA(cudaMemsetAsync(dval, 0, sizeof(float) * (size_t)L * npl, (cudaStream_t)stream));
   if (bf16)
-    return launch_bwd_dec<__nv_bfloat16>(col_ptr, ent, val, W_dec, drecon, dW, dval, B, L, D, F, k, crosslayer,
-                                         (cudaStream_t)stream);
-  return launch_bwd_dec<float>(col_ptr, ent, val, W_dec, drecon, dW, dval, B, L, D, F, k, crosslayer,
+    return launch_bwd_dec<__nv_bfloat16>(col_ptr, ent, val, etok, npl, W_dec, drecon, dW, dval, B, L, D, F, k,
+                                         crosslayer, (cudaStream_t)stream);
+  return launch_bwd_dec<float>(col_ptr, ent, val, etok, npl, W_dec, drecon, dW, dval, B, L, D, F, k, crosslayer,
                                (cudaStream_t)stream);
 }
 
-int clt_sparse_bwd_enc(const int* col_ptr, const int* ent, const float* dval, const void* xn, float* dW_enc,
-                       float* db_enc, int B, int L, int D, int F, int k, int bf16, clt_stream_t stream) {
-  CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && F > 0 && k > 0, "sparse_bwd_enc: bad dims");
+int clt_sparse_bwd_enc(const int* col_ptr, const int* ent, const float* dval, const int* etok, int64_t npl,
+                       const void* xn, float* dW_enc, float* db_enc, int B, int L, int D, int F, int k, int bf16,
+                       clt_stream_t stream) {
+  CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && F > 0 && k > 0 && npl > 0, "sparse_bwd_enc: bad dims");
   CLT_CHECK_ARG(col_ptr && ent && dval && xn && dW_enc && db_enc, "sparse_bwd_enc: null pointer");
   dim3 grid((F + kEncFB - 1) / kEncFB, L, (D + 767) / 768);
   CLT_CHECK_ARG(grid.y <= 65535 && grid.z <= 65535, "sparse_bwd_enc: grid too large");
   if (bf16)
     sparse_bwd_enc_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>(
-        col_ptr, ent, dval, (const __nv_bfloat16*)xn, dW_enc, db_enc, B, D, F, k);
+        col_ptr, ent, dval, etok, npl, (const __nv_bfloat16*)xn, dW_enc, db_enc, B, D, F, k);
   else
-    sparse_bwd_enc_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(col_ptr, ent, dval, (const float*)xn, dW_enc,
-                                                                        db_enc, B, D, F, k);
+    sparse_bwd_enc_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(col_ptr, ent, dval, etok, npl,
+                                                                        (const float*)xn, dW_enc, db_enc, B, D, F, k);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -226,6 +226,8 @@ class StepEngine:
             ctx = self._forward_dense(batch, hyper, bf16)
         elif kind == "topk":
             ctx = self._forward_topk(batch, hyper, bf16)
+        elif kind == "batchtopk":
+            ctx = self._forward_batchtopk(batch, hyper, bf16)
         else:
             raise NotImplementedError(f"nonlinearity kind {kind!r}")
         self.last_terms = ctx["out"][1:5]          # mse, sparsity, pre-activation, auxiliary summands
@@ -286,7 +288,7 @@ class StepEngine:
     def backward(self, ctx: dict, gscale: torch.Tensor):
         if ctx["kind"] in ("jumprelu", "relu"):
             self._backward_dense(ctx, gscale)
-        elif ctx["kind"] == "topk":
+        elif ctx["kind"] in ("topk", "batchtopk"):
             self._backward_topk(ctx, gscale)
         else:
             raise NotImplementedError(ctx["kind"])
@@ -425,8 +427,8 @@ class StepEngine:
                            nd_pad, int(bf16), s)
                 cand_all = ws.get("aux_cand_all", (world, L, B, k_aux), torch.float32, dev)
                 h_gather = all_gather(cand_all, cand, group, async_op=True)
-        self._call("clt_sparse_decoder_fwd", idx, val, W_op, bias, recon, B, L, D, F, kk, crosslayer, int(bf16),
-                   self.status, s)
+        self._call("clt_sparse_decoder_fwd", idx, val, None, None, B * kk, W_op, bias, recon, B, L, D, F, kk, crosslayer,
+                   int(bf16), self.status, s)
         if world > 1:
             from .parallel import all_reduce_sum
 
@@ -458,6 +460,88 @@ class StepEngine:
         return dict(kind="topk", bf16=bf16, batch=batch, B=B, L=L, D=D, F=F, k=kk, crosslayer=crosslayer, out=out,
                     stats=(mu_i, sd_i, mu_o, sd_o), in_code=in_code, aux=aux, aux_scale=aux_scale, idx=idx, val=val)
 
+    # ------------------------------------------------------------------ BatchTopK path
+    def _forward_batchtopk(self, batch, h, bf16):
+        """BatchTopK step (reference topk.py:76-96 inside clt_lightning.py:290-312): one threshold for
+        the whole batch from a three-level histogram select, survivors collected into per-layer entry
+        lists, then the same sparse decoder and loss as the per-layer TopK path."""
+        mod = self.module
+        model = mod.model
+        enc, dec, nl = model.encoder, model.decoder, model.nonlinearity
+        B, L, D, F = batch.shape[0], enc.n_layers, enc.d_acts, enc.d_features
+        k = int(nl.k)
+        assert k <= F                                   # reference topk.py:80
+        if nl.e is None and k > 0:
+            raise TypeError("BatchTopK needs its EMA rate `e` for training (reference topk.py:95)")
+        dev = batch.device
+        T = torch.bfloat16 if bf16 else torch.float32
+        s = stream_ptr()
+        crosslayer = 1 if dec.crosslayer else 0
+        mu_i, sd_i, mu_o, sd_o = self._stats()
+        ws = self.ws
+        world, group = getattr(mod, "tp_world", 1), getattr(mod, "tp_group", None)
+        rank = getattr(mod, "tp_rank", 0)
+        bias = dec.b.data if rank == 0 else None
+        xn = ws.get("xn", (L, B, D), T, dev)
+        z = ws.get("z", (L, B, F), T, dev)
+        n_rec = B * L * D
+        rbuf = ws.get("recon2", (2 * n_rec + 8,), torch.float32, dev)
+        recon, acc = rbuf[:n_rec].view(B, L, D), rbuf[2 * n_rec:]
+        out = torch.empty(5, dtype=torch.float32, device=dev)
+        acc.zero_()
+        in_code = DTYPE_CODE[batch.dtype]
+        W_op, _, _ = self._dec_flat(bf16)
+        self._call("clt_prep_input", batch, in_code, mu_i, sd_i, xn, int(bf16), B, L, D, s)
+        self._call("clt_encoder_fwd_store", xn, self._operand(enc.W, bf16), z, B, L, D, F, int(bf16), self.status, s)
+        n_keep = k * B * L                              # the whole batch, all layers and all feature shards
+        npl = max(1, min(n_keep, B * F))                # entry slots per layer (worst case: all in one layer)
+        idx = ws.get("bt_idx", (L, npl), torch.int32, dev)
+        val = ws.get("bt_val", (L, npl), torch.float32, dev)
+        etok = ws.get("bt_tok", (L, npl), torch.int32, dev)
+        row_start = ws.get("bt_row_start", (L, B), torch.int32, dev)
+        row_cnt = ws.get("bt_row_cnt", (L, B), torch.int32, dev)
+        if n_keep > 0:
+            state = ws.get("bt_state", (8,), torch.int64, dev, zero=True)
+            hist_l = ws.get("bt_hist_local", (2048,), torch.int64, dev)
+            hist = ws.get("bt_hist", (2048,), torch.int64, dev) if world > 1 else hist_l
+            for level in range(3):
+                self._call("clt_batchtopk_hist", z, enc.b.data, state, hist_l, level, B, L, F, int(bf16), s)
+                if world > 1:
+                    from .parallel import all_reduce_sum
+
+                    hist.copy_(hist_l)
+                    all_reduce_sum(hist, group)
+                self._call("clt_batchtopk_pick", hist, hist_l if world > 1 else None, state, level, n_keep, s)
+            quota = None
+            if world > 1:
+                # elements equal to the threshold are kept in rank order until the global count is reached
+                from .parallel import all_gather
+
+                ties = torch.empty(world, 1, dtype=torch.int64, device=dev)
+                all_gather(ties, state[5:6], group)
+                before = ties[:rank].sum()
+                quota = (state[3] - before).clamp(min=0).minimum(state[5]).reshape(1).contiguous()
+            fill = ws.get("bt_fill", (L,), torch.int32, dev)
+            self._call("clt_batchtopk_collect", z, enc.b.data, state, quota, idx, val, etok, row_start, row_cnt, fill,
+                       self.fired, B, L, F, npl, int(bf16), self.status, s)
+            self._call("clt_batchtopk_threshold_update", state, nl.threshold, float(nl.e), s)
+        else:
+            val.zero_()
+            row_start.zero_()
+            row_cnt.zero_()
+        self._call("clt_dead_update", mod.last_active, self.fired, None, B, int(mod.tokens_till_dead), L, F, s)
+        self._call("clt_sparse_decoder_fwd", idx, val, row_start, row_cnt, npl, W_op, bias, recon, B, L, D, F, 1,
+                   crosslayer, int(bf16), self.status, s)
+        if world > 1:
+            from .parallel import all_reduce_sum
+
+            all_reduce_sum(rbuf[:n_rec], group)
+        self._call("clt_loss_fwd", recon, None, batch, in_code, mu_o, sd_o, acc[2:4], B, L, D, s)
+        self._call("clt_finalize_loss", acc[2:4], None, out[0:1], out[1:5], 1.0 / (B * L * D), 0.0, 0.0, 0.0, s)
+        return dict(kind="batchtopk", bf16=bf16, batch=batch, B=B, L=L, D=D, F=F, k=1, crosslayer=crosslayer, out=out,
+                    stats=(mu_i, sd_i, mu_o, sd_o), in_code=in_code, aux=None, aux_scale=0.0, idx=idx, val=val,
+                    npl=npl, etok=etok)
+
     def _backward_topk(self, c, gscale):
         model = self.module.model
         enc, dec = model.encoder, model.decoder
@@ -484,14 +568,16 @@ class StepEngine:
                    B, L, D, s)
         W_op, _, dW_dec = self._dec_flat(bf16)
         idx, val = c["idx"], c["val"]
+        npl, etok = c.get("npl", B * k), c.get("etok")       # entry slots per layer, token of each entry
         col_ptr = ws.get("col_ptr", (L, F + 1), torch.int32, dev)
         cursor = ws.get("cursor", (L, F), torch.int32, dev)
-        ent = ws.get("ent", (L, B * k), torch.int32, dev)
-        dval = ws.get("dval", (L, B, k), torch.float32, dev)
-        self._call("clt_csc_build", idx, val, col_ptr, cursor, ent, B, L, F, k, self.status, s)
-        self._call("clt_sparse_bwd_dec", col_ptr, ent, val, W_op, drecon, dW_dec, dval, B, L, D, F, k, cross,
+        ent = ws.get("ent", (L, npl), torch.int32, dev)
+        dval = ws.get("dval", (L, npl), torch.float32, dev)
+        self._call("clt_csc_build", idx, val, col_ptr, cursor, ent, npl, L, F, self.status, s)
+        self._call("clt_sparse_bwd_dec", col_ptr, ent, val, etok, npl, W_op, drecon, dW_dec, dval, B, L, D, F, k, cross,
                    int(bf16), s)
-        self._call("clt_sparse_bwd_enc", col_ptr, ent, dval, xn, gview(enc.W), gview(enc.b), B, L, D, F, k, int(bf16), s)
+        self._call("clt_sparse_bwd_enc", col_ptr, ent, dval, etok, npl, xn, gview(enc.W), gview(enc.b), B, L, D, F, k,
+                   int(bf16), s)
         if aux is not None:
             nd_pad, a_aux, w_c = aux["nd_pad"], aux["a_aux"], aux["w_c"]
             dl, n_dead = aux["dead_list"], aux["n_dead"]

@@ -152,16 +152,22 @@ int clt_topk_threshold(const float* vals, float* thr, int64_t rows, int R, int k
 int clt_topk_apply_threshold(int* idx, float* val, const float* thr, uint32_t* fired_bits, int B, int L, int F,
                              int k, clt_stream_t stream);
 
-/* CrosslayerDecoder.forward / Decoder.forward (clt.py:334-343, 241-248) on the selected features:
- * recon[b,t,:] = b_dec[t] + sum_{s<=t} sum_j val[s,b,j] W_dec[pair(t,s), idx[s,b,j], :]. */
-int clt_sparse_decoder_fwd(const int* idx, const float* val, const void* W_dec, const float* b_dec, float* recon,
-                           int B, int L, int D, int F, int k, int crosslayer, int bf16, int* status,
-                           clt_stream_t stream);
+/* Sparse feature lists.  Every layer owns `npl` entry slots: idx / val [L, npl] (val 0 = unused).
+ * PerLayerTopK uses npl = B k with the k slots of token b at b k .. b k + k - 1 (valid ones first);
+ * BatchTopK uses one list per layer in which the entries of token b occupy the segment
+ * row_start[l, b] .. + row_cnt[l, b], with etok [L, npl] naming the token of every entry.
+ *
+ * CrosslayerDecoder.forward / Decoder.forward (clt.py:334-343, 241-248) on the selected features:
+ * recon[b,t,:] = b_dec[t] + sum_{s<=t} sum_{entries e of (s,b)} val[e] W_dec[pair(t,s), idx[e], :].
+ * row_start / row_cnt NULL = fixed k slots per token. */
+int clt_sparse_decoder_fwd(const int* idx, const float* val, const int* row_start, const int* row_cnt,
+                           int64_t npl, const void* W_dec, const float* b_dec, float* recon, int B, int L, int D,
+                           int F, int k, int crosslayer, int bf16, int* status, clt_stream_t stream);
 
-/* Feature-major copy of the selection: col_ptr [L, F+1], ent [L, B*k] (entry = b*k + j, grouped by
+/* Feature-major copy of the selection: col_ptr [L, F+1], ent [L, npl] (entry slots grouped by
  * feature).  cursor [L, F] is scratch. */
-int clt_csc_build(const int* idx, const float* val, int* col_ptr, int* cursor, int* ent, int B, int L, int F,
-                  int k, int* status, clt_stream_t stream);
+int clt_csc_build(const int* idx, const float* val, int* col_ptr, int* cursor, int* ent, int64_t npl, int L,
+                  int F, int* status, clt_stream_t stream);
 
 /* Same result as clt_csc_build, for hosts that must not allocate device memory on behalf of this
  * library.  (No counterpart in the reference: it exists only for this library's callers.)
@@ -178,21 +184,23 @@ int clt_csc_build(const int* idx, const float* val, int* col_ptr, int* cursor, i
  * - All calls on a device share the one array, which keeps whatever the previous call left in
  *   it.  Every entry the call reads is rewritten by the call first, so no clearing is needed,
  *   but two calls that overlap on the GPU (different streams, no ordering) race on it. */
-int clt_csc_build_static(const int* idx, const float* val, int* col_ptr, int* ent, int B, int L, int F, int k,
+int clt_csc_build_static(const int* idx, const float* val, int* col_ptr, int* ent, int64_t npl, int L, int F,
                          int* status, clt_stream_t stream);
 
 /* Backward of the decoder on the selected features (autograd of clt.py:334-343 restricted to the
- * non-zero features): dval[s,b,j] = sum_{t>=s} drecon[t,b,:] . W_dec[pair(t,s), idx, :] and
- * dW_dec[pair(t,s), f, :] = sum_{(b,j): idx = f} val drecon[t,b,:]; every row of dW is written. */
-int clt_sparse_bwd_dec(const int* col_ptr, const int* ent, const float* val, const void* W_dec,
-                       const void* drecon, float* dW, float* dval, int B, int L, int D, int F, int k,
-                       int crosslayer, int bf16, clt_stream_t stream);
+ * non-zero features): dval[e] = sum_{t>=s} drecon[t,b(e),:] . W_dec[pair(t,s), idx[e], :] and
+ * dW_dec[pair(t,s), f, :] = sum_{e: idx[e] = f} val[e] drecon[t,b(e),:]; every row of dW is written.
+ * etok NULL: token of slot e is e / k. */
+int clt_sparse_bwd_dec(const int* col_ptr, const int* ent, const float* val, const int* etok, int64_t npl,
+                       const void* W_dec, const void* drecon, float* dW, float* dval, int B, int L, int D, int F,
+                       int k, int crosslayer, int bf16, clt_stream_t stream);
 
 /* Backward of the encoder on the selected features (autograd of clt.py:157-165 through the TopK
- * scatter): dW_enc[l,:,f] = sum_{(b,j): idx = f} dval xn[l,b,:], db_enc[l,f] = sum dval; every
+ * scatter): dW_enc[l,:,f] = sum_{e: idx[e] = f} dval[e] xn[l,b(e),:], db_enc[l,f] = sum dval[e]; every
  * element of both is written. */
-int clt_sparse_bwd_enc(const int* col_ptr, const int* ent, const float* dval, const void* xn, float* dW_enc,
-                       float* db_enc, int B, int L, int D, int F, int k, int bf16, clt_stream_t stream);
+int clt_sparse_bwd_enc(const int* col_ptr, const int* ent, const float* dval, const int* etok, int64_t npl,
+                       const void* xn, float* dW_enc, float* db_enc, int B, int L, int D, int F, int k, int bf16,
+                       clt_stream_t stream);
 
 /* Compaction helpers of the auxiliary dead-feature path (clt_lightning.py:544-549 run as dense
  * contractions over the dead features only):
@@ -205,6 +213,30 @@ int clt_scatter_rows(const float* src, const int* dead_list, const int* n_dead, 
                      int D, int nd_pad, int crosslayer, clt_stream_t stream);
 int clt_scatter_cols(const float* src, const float* db_src, const int* dead_list, const int* n_dead,
                      float* dW_enc, float* db_enc, int L, int D, int F, int nd_pad, clt_stream_t stream);
+
+/* ---- BatchTopK path ---------------------------------------------------------------------- */
+
+/* BatchTopK._training_forward (crosslayer_transcoder/model/topk.py:76-96): the k B L largest of all
+ * pre-activations of the batch.  The threshold is found by a three-level radix select; per level:
+ * clt_batchtopk_hist fills hist [2048] (64-bit counters) with the digit histogram of the elements
+ * inside the bucket chosen so far, feature shards sum their histograms, clt_batchtopk_pick chooses
+ * the next bucket.  state: 8 64-bit words of device memory, zero before the first step
+ * ([2] threshold key after level 2, [3] kept elements equal to it, [5] this rank's count of them).
+ * hist_local (may be NULL) is this rank's own histogram when hist holds the sum over shards. */
+int clt_batchtopk_hist(const void* z, const float* b_enc, const uint64_t* state, uint64_t* hist, int level, int B,
+                       int L, int F, int bf16, clt_stream_t stream);
+int clt_batchtopk_pick(const uint64_t* hist, const uint64_t* hist_local, uint64_t* state, int level,
+                       int64_t n_keep, clt_stream_t stream);
+/* Collect the survivors into per-layer entry lists idx / val / etok [L, npl] with the segment of
+ * token b at row_start[l,b] .. + row_cnt[l,b]; layer_fill [L] receives the list lengths.  tie_quota
+ * (device int64, may be NULL = all kept ties are this rank's) bounds the elements equal to the
+ * threshold this rank keeps.  Sets fired_bits (may be NULL); reports list overflow in status. */
+int clt_batchtopk_collect(const void* z, const float* b_enc, uint64_t* state, const int64_t* tie_quota, int* idx,
+                          float* val, int* etok, int* row_start, int* row_cnt, int* layer_fill,
+                          uint32_t* fired_bits, int B, int L, int F, int64_t npl, int bf16, int* status,
+                          clt_stream_t stream);
+/* threshold <- (1 - e) threshold + e * smallest kept value (topk.py:94-95). */
+int clt_batchtopk_threshold_update(const uint64_t* state, float* threshold, float e, clt_stream_t stream);
 
 /* torch.optim.Adam / AdamW step (clt_lightning.py:339-352) over one flat fp32 buffer; `step`
  * counts from 1.  shadow_bf16 (may be NULL) receives the bf16 copy of the new parameters. */

@@ -28,7 +28,7 @@ def load_golden(name):
 
 def rel_err(a, b):
     """max |a-b| over max |b|: the relative error measure of the parity bar."""
-    a, b = a.double(), b.double()
+    a, b = a.detach().double(), b.detach().double()
     den = b.abs().max().clamp_min(1e-30)
     return float((a - b).abs().max() / den)
 

@@ -35,6 +35,9 @@ def main():
     if kind == "jumprelu":
         spec = synthetic.WorkloadSpec("mp_jr", 3, 128, 512, 200, "jumprelu", True, bf16, rank_u=16, n_outlier=2,
                                       lambda_sparsity=4e-4, pre_actv_loss=3e-6, lr=1e-3)
+    elif kind == "batchtopk":
+        spec = synthetic.WorkloadSpec("mp_btk", 3, 128, 1024, 200, "batchtopk", True, bf16, rank_u=16, n_outlier=2, k=4,
+                                      e=0.05, lr=1e-3)
     else:
         spec = synthetic.WorkloadSpec("mp_topk", 3, 128, 1024, 200, "topk", True, bf16, rank_u=16, n_outlier=2, k=8,
                                       k_aux=32, aux_loss_scale=1 / 32, tokens_till_dead=1000, dead_fraction=0.2,
@@ -70,6 +73,10 @@ def main():
         bad = {k: v for k, v in errs.items() if not v < tol}
         if kind == "topk" and not torch.equal(la_out, ref.last_active):
             bad["last_active"] = 1.0
+        if kind == "batchtopk":
+            errs["threshold"] = rel_err(mod.model.nonlinearity.threshold.cpu(), ref.threshold)
+            if not errs["threshold"] < tol:
+                bad["threshold"] = errs["threshold"]
         print("errors", errs)
         ok = not bad
         if bad:

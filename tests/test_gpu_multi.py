@@ -12,7 +12,7 @@ ROOT = Path(__file__).resolve().parents[1]
 
 
 @pytest.mark.parametrize("prec", ["fp32", "bf16"])
-@pytest.mark.parametrize("kind", ["jumprelu", "topk"])
+@pytest.mark.parametrize("kind", ["jumprelu", "topk", "batchtopk"])
 def test_two_shards_match_unsharded_oracle(kind, prec):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")

@@ -48,8 +48,8 @@ def test_static_scratch_matches_caller_scratch_twice():
         ent_a = torch.full((L, B * k), -1, dtype=torch.int32, device=dev)
         ent_b = torch.full_like(ent_a, -1)
         cursor = torch.empty(L, F, dtype=torch.int32, device=dev)
-        L_.call("clt_csc_build", idx, val, cp_a, cursor, ent_a, B, L, F, k, status, stream_ptr())
-        L_.call("clt_csc_build_static", idx, val, cp_b, ent_b, B, L, F, k, status, stream_ptr())
+        L_.call("clt_csc_build", idx, val, cp_a, cursor, ent_a, B * k, L, F, status, stream_ptr())
+        L_.call("clt_csc_build_static", idx, val, cp_b, ent_b, B * k, L, F, status, stream_ptr())
         torch.cuda.synchronize()
         assert int(status) == 0
         assert torch.equal(cp_a, cp_b)
@@ -66,4 +66,4 @@ def test_static_scratch_rejects_oversize():
     L_.check_device()
     t = torch.zeros(8, dtype=torch.int32, device=dev)
     with pytest.raises(CltError, match="exceeds the built-in scratch"):
-        L_.call("clt_csc_build_static", t, t.float(), t, t, 1, 2, (1 << 20), 1, None, stream_ptr())
+        L_.call("clt_csc_build_static", t, t.float(), t, t, 1, 2, (1 << 20), None, stream_ptr())
