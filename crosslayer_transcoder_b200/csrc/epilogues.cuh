@@ -16,7 +16,8 @@
 //     static void init(State&);
 //     template <int CS>                   // CS = stride between staged arrays (columns per tile)
 //     static void apply(const Params&, State&, int z, int row, bool row_ok, int n0, int M, int N,
-//                       float (&v)[32], const float* colp);   // colp[arr * CS + i], i = 0..31
+//                       float (&v)[32], const float* colp,    // colp[arr * CS + i], i = 0..31
+//                       unsigned char* stage);                // per-warp staging buffer (kStageBytes)
 //     static void finish(const Params&, State&);   // once per thread, warp-converged
 //   };
 #pragma once
@@ -111,6 +112,79 @@ __device__ __forceinline__ bool can_vec(int n0, int N) {
   return (n0 + 32 <= N) && (N % (16 / (int)sizeof(T)) == 0);
 }
 
+// ---- coalesced store of a warp's 32 x 32 sub-tile ------------------------------------------------
+// Each lane holds one row (32 consecutive columns).  Writing that straight to global memory makes
+// every store instruction touch 32 different rows, 16 bytes each.  Instead the sub-tile goes through
+// a per-warp shared-memory buffer (kStageBytes, rows padded to 80 bytes: conflict-free 16-byte
+// accesses) and is written out with 4 lanes per row segment, so an instruction covers 8 rows x 64
+// contiguous bytes (full 32-byte sectors).  fp32 tiles go in two halves of 16 columns.
+// `base` points at (first row of the warp, column n0); `rows_valid` rows of the 32 exist.
+constexpr int kStageRow = 80;
+constexpr int kStageBytes = 32 * kStageRow;
+
+template <class T>
+__device__ __forceinline__ void store_rows32(unsigned char* stage, T* base, size_t ld, int rows_valid,
+                                             const float (&v)[32]);
+
+template <>
+__device__ __forceinline__ void store_rows32<__nv_bfloat16>(unsigned char* stage, __nv_bfloat16* base, size_t ld,
+                                                            int rows_valid, const float (&v)[32]) {
+  const int lane = threadIdx.x & 31;
+  uint4* mine = reinterpret_cast<uint4*>(stage + lane * kStageRow);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 t;
+    t.x = pack_bf16x2(v[8 * i], v[8 * i + 1]);
+    t.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+    t.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+    t.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+    mine[i] = t;
+  }
+  __syncwarp();
+  const int piece = lane & 3;
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int r = it * 8 + (lane >> 2);
+    const uint4 t = *reinterpret_cast<const uint4*>(stage + r * kStageRow + piece * 16);
+    if (r < rows_valid) *reinterpret_cast<uint4*>(base + (size_t)r * ld + piece * 8) = t;
+  }
+  __syncwarp();
+}
+
+template <>
+__device__ __forceinline__ void store_rows32<float>(unsigned char* stage, float* base, size_t ld, int rows_valid,
+                                                    const float (&v)[32]) {
+  const int lane = threadIdx.x & 31;
+  float4* mine = reinterpret_cast<float4*>(stage + lane * kStageRow);
+  const int piece = lane & 3;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      mine[i] = make_float4(v[16 * h + 4 * i], v[16 * h + 4 * i + 1], v[16 * h + 4 * i + 2], v[16 * h + 4 * i + 3]);
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int r = it * 8 + (lane >> 2);
+      const float4 t = *reinterpret_cast<const float4*>(stage + r * kStageRow + piece * 16);
+      if (r < rows_valid) *reinterpret_cast<float4*>(base + (size_t)r * ld + 16 * h + piece * 4) = t;
+    }
+    __syncwarp();
+  }
+}
+
+// Store a warp's sub-tile: coalesced through `stage` when the 32 columns are all inside the matrix
+// and rows are 16-byte aligned, else lane by lane with guards.  `row0` is the warp's first row.
+template <class T>
+__device__ __forceinline__ void store_tile(unsigned char* stage, T* mat, size_t ld, int row0, int row, bool row_ok,
+                                           int M, int n0, int N, bool aligned, const float (&v)[32]) {
+  if (aligned && n0 + 32 <= N) {
+    store_rows32<T>(stage, mat + (size_t)row0 * ld + n0, ld, M - row0, v);
+  } else if (row_ok) {
+    store32<T>(mat + (size_t)row * ld + n0, N - n0, false, v);
+  }
+}
+
 // lane j adds its column total to dst[n0 + j]
 __device__ __forceinline__ void col_atomic_add(float* dst, int n0, int N, float colsum) {
   const int lane = threadIdx.x & 31;
@@ -132,10 +206,10 @@ struct StoreZ {
   __device__ static void init(State&) {}
   template <int CS>
   __device__ static void apply(const Params& p, State&, int z, int row, bool row_ok, int n0, int M, int N,
-                               float (&v)[32], const float*) {
-    if (!row_ok) return;
-    T* dst = p.out + ((size_t)z * M + row) * N + n0;
-    store32<T>(dst, N - n0, can_vec<T>(n0, N), v);
+                               float (&v)[32], const float*, unsigned char* stage) {
+    const int row0 = row - (threadIdx.x & 31);
+    store_tile<T>(stage, p.out + (size_t)z * M * N, (size_t)N, row0, row, row_ok, M, n0, N,
+                  N % (16 / (int)sizeof(T)) == 0, v);
   }
   __device__ static void finish(const Params&, State&) {}
 };
@@ -155,13 +229,12 @@ struct DecOut {
   __device__ static void init(State&) {}
   template <int CS>
   __device__ static void apply(const Params& p, State&, int z, int row, bool row_ok, int n0, int M, int N,
-                               float (&v)[32], const float* colp) {
-    if (!row_ok) return;
+                               float (&v)[32], const float* colp, unsigned char* stage) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] += colp[i];
-    float* dst = p.out + (size_t)row * p.ld + (size_t)z * p.zstride + n0;
-    const bool vec = (n0 + 32 <= N) && (p.ld % 4 == 0) && (p.zstride % 4 == 0);
-    store32<float>(dst, N - n0, vec, v);
+    const int row0 = row - (threadIdx.x & 31);
+    store_tile<float>(stage, p.out + (size_t)z * p.zstride, (size_t)p.ld, row0, row, row_ok, M, n0, N,
+                      (p.ld % 4 == 0) && (p.zstride % 4 == 0), v);
   }
   __device__ static void finish(const Params&, State&) {}
 };
@@ -182,11 +255,10 @@ struct GradOut {
   __device__ static void init(State&) {}
   template <int CS>
   __device__ static void apply(const Params& p, State&, int z, int row, bool row_ok, int n0, int M, int N,
-                               float (&v)[32], const float*) {
-    if (!row_ok) return;
-    const size_t off = ((size_t)z * M + row) * N + n0;
+                               float (&v)[32], const float*, unsigned char* stage) {
+    const size_t off = ((size_t)z * M + (row_ok ? row : 0)) * N + n0;
     const bool vec = can_vec<float>(n0, N);
-    if (p.rowcoef != nullptr) {
+    if (p.rowcoef != nullptr && row_ok) {
       int zc = z;
       if (p.coef_by_source) {
         int t;
@@ -198,7 +270,8 @@ struct GradOut {
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = fmaf(c, w[i], v[i]);
     }
-    store32<float>(p.out + off, N - n0, vec, v);
+    const int row0 = row - (threadIdx.x & 31);
+    store_tile<float>(stage, p.out + (size_t)z * M * N, (size_t)N, row0, row, row_ok, M, n0, N, N % 4 == 0, v);
   }
   __device__ static void finish(const Params&, State&) {}
 };
@@ -239,7 +312,7 @@ struct EncJumpReLU {
   __device__ static void init(State& s) { s.s_pre = 0.f, s.s_sp = 0.f; }
   template <int CS>
   __device__ static void apply(const Params& p, State& st, int z, int row, bool row_ok, int n0, int M, int N,
-                               float (&v)[32], const float* colp) {
+                               float (&v)[32], const float* colp, unsigned char* stage) {
     const bool full = n0 + 32 <= N;
     const bool sp = p.dec_norm != nullptr;
     float feat[32];
@@ -271,11 +344,10 @@ struct EncJumpReLU {
       mask = __reduce_or_sync(0xffffffffu, mask);
       if ((threadIdx.x & 31) == 0 && mask != 0u) atomicOr(p.fired_bits + (size_t)z * ((N + 31) / 32) + n0 / 32, mask);
     }
-    if (!row_ok) return;
-    const size_t off = ((size_t)z * M + row) * N + n0;
-    const bool vec = can_vec<T>(n0, N);
-    store32<T>(p.z_out + off, N - n0, vec, v);
-    store32<T>(p.feat_out + off, N - n0, vec, feat);
+    const int row0 = row - (threadIdx.x & 31);
+    const bool al = N % (16 / (int)sizeof(T)) == 0;
+    store_tile<T>(stage, p.z_out + (size_t)z * M * N, (size_t)N, row0, row, row_ok, M, n0, N, al, v);
+    store_tile<T>(stage, p.feat_out + (size_t)z * M * N, (size_t)N, row0, row, row_ok, M, n0, N, al, feat);
   }
   __device__ static void finish(const Params& p, State& st) {
     const float a = warp_sum(st.s_pre), b = warp_sum(st.s_sp);
@@ -329,7 +401,7 @@ struct DFeatJumpReLU {
   __device__ static void init(State&) {}
   template <int CS>
   __device__ static void apply(const Params& p, State&, int z, int row, bool row_ok, int n0, int M, int N,
-                               float (&v)[32], const float* colp) {
+                               float (&v)[32], const float* colp, unsigned char* stage) {
     const size_t off = ((size_t)z * M + (row_ok ? row : 0)) * N + n0;
     const bool full = n0 + 32 <= N;
     const bool vec = can_vec<T>(n0, N);
@@ -368,7 +440,11 @@ struct DFeatJumpReLU {
       dth[i] = (ok && rect) ? colp[3 * CS + i] * gs : 0.f;
       dnr[i] = ok ? dn : 0.f;
     }
-    if (row_ok) store32<T>(p.dpre_out + off, N - n0, vec, v);
+    {
+      const int row0 = row - (threadIdx.x & 31);
+      store_tile<T>(stage, p.dpre_out + (size_t)z * M * N, (size_t)N, row0, row, row_ok, M, n0, N,
+                    N % (16 / (int)sizeof(T)) == 0, v);
+    }
     col_atomic_add(p.dbenc + (size_t)z * N, n0, N, warp_colsum32(v));
     if (p.dtheta != nullptr) col_atomic_add(p.dtheta + (size_t)z * N, n0, N, warp_colsum32(dth));
     if (p.dnorm != nullptr) col_atomic_add(p.dnorm + (size_t)z * N, n0, N, warp_colsum32(dnr));

@@ -92,6 +92,7 @@ __global__ void __launch_bounds__(128) gemm_simt_kernel(GemmGeom g, SimtOperands
     }
     __syncthreads();
   }
+  __shared__ __align__(16) unsigned char stage[4][epi::kStageBytes];
   typename Epi::State st;
   Epi::init(st);
 #pragma unroll
@@ -100,7 +101,8 @@ __global__ void __launch_bounds__(128) gemm_simt_kernel(GemmGeom g, SimtOperands
       float v[32];
 #pragma unroll
       for (int i = 0; i < 32; ++i) v[i] = acc[32 * c + i];
-      Epi::template apply<kSimtBN>(ep, st, z, row, row_ok, n0 + 32 * c, g.M, g.N, v, &colp[0][32 * c]);
+      Epi::template apply<kSimtBN>(ep, st, z, row, row_ok, n0 + 32 * c, g.M, g.N, v, &colp[0][32 * c],
+                                   stage[tid >> 5]);
     }
   }
   Epi::finish(ep, st);

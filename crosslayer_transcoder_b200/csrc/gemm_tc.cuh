@@ -46,7 +46,9 @@ constexpr int kThreads = 64 + kEpiThreads;
 constexpr int kTmemCols = 512;
 constexpr int kMaxColArrays = 4;
 constexpr int kColBytes = 2 * kMaxColArrays * kBN * 4;  // staged per-column parameters, double-buffered
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kColBytes;
+constexpr int kEpiStageBytes = kEpiWarps * epi::kStageBytes;  // per-warp staging of coalesced stores
+constexpr int kSmemBytes =
+    kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + kColBytes + kEpiStageBytes;
 constexpr long long kWaitCycles = 4000000000ll;  // about two seconds
 
 // ---- PTX wrappers ---------------------------------------------------------------
@@ -305,6 +307,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     // ------------------------------ epilogue ----------------------------------
     static_assert(Epi::kColArrays <= kMaxColArrays, "too many per-column parameter arrays");
     float* colp_base = reinterpret_cast<float*>(smem + kStages * kStageBytes + 256);
+    unsigned char* stage = smem + kStages * kStageBytes + 256 + kColBytes + (warp - 2) * epi::kStageBytes;
     const int et = threadIdx.x - 64;          // 0..255 among the epilogue threads
     const int quarter = warp & 3;             // tensor-memory lanes 32*quarter .. +31
     const int half = (warp - 2) >> 2;         // which 128 columns of the tile
@@ -349,7 +352,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         if (n >= g.N) break;
         float v[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kBN + 32 * c), v);
-        Epi::template apply<kBN>(ep, st, z, row, row_ok, n, g.M, g.N, v, colp + 32 * c);
+        Epi::template apply<kBN>(ep, st, z, row, row_ok, n, g.M, g.N, v, colp + 32 * c, stage);
       }
       tc_fence_before();
       __syncwarp();

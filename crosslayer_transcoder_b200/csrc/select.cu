@@ -285,9 +285,9 @@ select_topk_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, int
 // Main selection for short rows (a feature shard's slice): one WARP per row, 8 rows per CTA,
 // so that the per-row launch and synchronisation overhead does not dominate when F is a few
 // thousand.  Same scheme as above with 32 lanes instead of 256 threads (k <= 32):
-//   sweep 1  lane maxima; T_lo = k-th largest of the 32 maxima
-//   sweep 2  elements >= T_lo appended to the warp's shared-memory list (ballot offsets)
-//   finish   rank by counting, slot = rank
+//   sweep 1  the two largest values per lane; T_lo = k-th largest of those 64 (bisection on bits)
+//   sweep 2  elements >= T_lo appended to the warp's shared-memory list
+//   finish   exact k-th largest of the list by bisection on the key bits, then emit
 // If the list overflows (masses of equal values) the exact k-th value is found by bisection on
 // the key bits over the row, and the row is emitted from that threshold.
 // ---------------------------------------------------------------------------------------
@@ -300,6 +300,7 @@ select_topk_warp_kernel(const T* __restrict__ z, const float* __restrict__ b_enc
                         int k) {
   __shared__ float cand_v[8][kWarpCand];
   __shared__ int cand_i[8][kWarpCand];
+  __shared__ int cand_n[8];
   const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long row = blockIdx.x * 8ll + wib;
   if (row >= rows) return;
@@ -312,56 +313,86 @@ select_topk_warp_kernel(const T* __restrict__ z, const float* __restrict__ b_enc
   float* cv = cand_v[wib];
   int* ci = cand_i[wib];
 
-  // sweep 1
-  float m = 0.f;
-  for (int i = 8 * lane; i < F; i += 256) {
-    float v[8];
-    RowReader<T>::load8(zr, br, i, v);
-#pragma unroll
-    for (int q = 0; q < 8; ++q) m = fmaxf(m, v[q]);
-  }
-  int rank = 0;
-#pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    const float o = __shfl_sync(0xffffffffu, m, j);
-    rank += (o > m || (o == m && j < lane)) ? 1 : 0;
-  }
-  const unsigned who = __ballot_sync(0xffffffffu, rank == k - 1);
-  const float lo = __shfl_sync(0xffffffffu, m, __ffs(who) - 1);  // 0: fewer than k lanes saw a positive value
-
-  // sweep 2
-  int nc = 0;
+  // sweep 1: the two largest values of every lane's share -> 64 distinct elements of the row
+  float m1 = 0.f, m2 = 0.f;
   for (int i = 8 * lane; i < F; i += 256) {
     float v[8];
     RowReader<T>::load8(zr, br, i, v);
 #pragma unroll
     for (int q = 0; q < 8; ++q) {
-      const bool take = v[q] > 0.f && v[q] >= lo;
-      const unsigned bal = __ballot_sync(0xffffffffu, take);
-      if (take) {
-        const int c = nc + __popc(bal & ((1u << lane) - 1u));
+      const float x = v[q];
+      m2 = fmaxf(m2, fminf(m1, x));
+      m1 = fmaxf(m1, x);
+    }
+  }
+  // T_lo = k-th largest of the 64 values (lower bound of the row's k-th largest): bisection on the bits
+  const unsigned k1 = positive_key(m1), k2 = positive_key(m2);
+  unsigned lo_key = 0u;
+  for (int bit = 30; bit >= 0; --bit) {
+    const unsigned trial = lo_key | (1u << bit);
+    const int c = __popc(__ballot_sync(0xffffffffu, k1 >= trial)) + __popc(__ballot_sync(0xffffffffu, k2 >= trial));
+    if (c >= k) lo_key = trial;
+  }
+  if (lane == 0) cand_n[wib] = 0;
+  __syncwarp();
+  // sweep 2: candidates (>= T_lo; every positive value when fewer than k of the 64 are positive)
+  for (int i = 8 * lane; i < F; i += 256) {
+    float v[8];
+    RowReader<T>::load8(zr, br, i, v);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const unsigned key = positive_key(v[q]);
+      if (key != 0u && key >= lo_key) {
+        const int c = atomicAdd(&cand_n[wib], 1);
         if (c < kWarpCand) cv[c] = v[q], ci[c] = i + q;
       }
-      nc += __popc(bal);
     }
   }
   __syncwarp();
+  const int nc = cand_n[wib];
   if (nc <= kWarpCand) {
-    for (int c = lane; c < nc; c += 32) {
-      const float v = cv[c];
-      const int fi = ci[c];
-      int r = 0;
-      for (int j = 0; j < nc; ++j) {
-        const float o = cv[j];
-        r += (o > v || (o == v && ci[j] < fi)) ? 1 : 0;
-      }
-      if (r < k) {
-        io[r] = fi;
-        vo[r] = v;
-        if (fired_bits != nullptr) atomicOr(fired_bits + (size_t)l * words + fi / 32, 1u << (fi & 31));
+    // exact k-th largest key among the candidates by bisection, then emit (> T, then ties in list order)
+    unsigned ck[kWarpCand / 32];
+#pragma unroll
+    for (int q = 0; q < kWarpCand / 32; ++q) ck[q] = (lane + 32 * q) < nc ? positive_key(cv[lane + 32 * q]) : 0u;
+    unsigned Tk = 0u;
+    if (nc > k) {
+      for (int bit = 30; bit >= 0; --bit) {
+        const unsigned trial = Tk | (1u << bit);
+        int c = 0;
+#pragma unroll
+        for (int q = 0; q < kWarpCand / 32; ++q) c += ck[q] >= trial ? 1 : 0;
+        c = __reduce_add_sync(0xffffffffu, c);
+        if (c >= k) Tk = trial;
       }
     }
-    for (int s2 = nc + lane; s2 < k; s2 += 32) io[s2] = 0, vo[s2] = 0.f;
+    int n_gt = 0;
+#pragma unroll
+    for (int q = 0; q < kWarpCand / 32; ++q) n_gt += ck[q] > Tk ? 1 : 0;
+    n_gt = __reduce_add_sync(0xffffffffu, n_gt);
+    int n_out = 0, ties_left = (nc > k) ? k - n_gt : 0x7fffffff;
+#pragma unroll
+    for (int q = 0; q < kWarpCand / 32; ++q) {
+      const unsigned key = ck[q];
+      const bool gt = key > Tk;
+      const bool tie = key != 0u && key == Tk;
+      const unsigned tb = __ballot_sync(0xffffffffu, tie);
+      const bool take = gt || (tie && __popc(tb & ((1u << lane) - 1u)) < ties_left);
+      const unsigned bal = __ballot_sync(0xffffffffu, take);
+      if (take) {
+        const int slot = n_out + __popc(bal & ((1u << lane) - 1u));
+        const int c = lane + 32 * q;
+        if (slot < k) {
+          const int fi = ci[c];
+          io[slot] = fi;
+          vo[slot] = cv[c];
+          if (fired_bits != nullptr) atomicOr(fired_bits + (size_t)l * words + fi / 32, 1u << (fi & 31));
+        }
+      }
+      n_out += __popc(bal);
+      ties_left -= min(ties_left, __popc(tb));
+    }
+    for (int s2 = n_out + lane; s2 < k; s2 += 32) io[s2] = 0, vo[s2] = 0.f;
     return;
   }
   // overflow: exact threshold by bisection on the key bits (largest T with count(key >= T) >= k)
@@ -617,7 +648,7 @@ int clt_select_topk(const void* z, const float* b_enc, int* idx_out, float* val_
   const long long rows = (long long)L * B;
   CLT_CHECK_ARG(rows < (1ll << 31), "select_topk: too many rows");
   cudaStream_t s = (cudaStream_t)stream;
-  const bool warp_rows = k <= 32 && F % 256 == 0 && F <= 8192;   // short rows: one warp each
+  const bool warp_rows = k <= 64 && F % 8 == 0 && F >= 512 && F <= 8192;   // short rows: one warp each
   const unsigned wblocks = (unsigned)((rows + 7) / 8);
   if (bf16) {
     if (warp_rows)

@@ -137,6 +137,89 @@ sparse_dec_fwd_kernel(const int* __restrict__ idx, const float* __restrict__ val
   }
 }
 
+// Same computation with one WARP per (token, target layer) and no shared-memory reduction: for
+// short entry lists (a feature shard keeps only a few of a row's k slots) the per-CTA overhead of
+// the kernel above dominates.  Entries are fetched 32 at a time, rows two at a time.
+template <class T, int VPL>
+__global__ void __launch_bounds__(128)
+sparse_dec_fwd_warp_kernel(const int* __restrict__ idx, const float* __restrict__ val,
+                           const int* __restrict__ row_start, const int* __restrict__ row_cnt, long long npl,
+                           const T* __restrict__ W, const float* __restrict__ b_dec, float* __restrict__ recon, int B,
+                           int L, int D, int F, int k, int crosslayer, int* status) {
+  const long long pair = blockIdx.x * 4ll + (threadIdx.x >> 5);
+  if (pair >= (long long)B * L) return;
+  const int b = (int)(pair % B), t = (int)(pair / B);
+  const int lane = threadIdx.x & 31;
+  const int nvec = D / 8;
+  using V = Vec8<T>;
+  float acc[VPL][8];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+  const int s_lo = crosslayer ? 0 : t;
+  for (int s = s_lo; s <= t; ++s) {
+    const size_t p = crosslayer ? (size_t)pair_index(t, s) : (size_t)t;
+    size_t e0 = ((size_t)s * B + b) * k;
+    int n = k;
+    if (row_start != nullptr) {
+      e0 = (size_t)s * npl + __ldg(row_start + (size_t)s * B + b);
+      n = __ldg(row_cnt + (size_t)s * B + b);
+    }
+    for (int j0 = 0; j0 < n; j0 += 32) {
+      const int m = min(32, n - j0);
+      float my_v = 0.f;
+      int my_f = 0;
+      if (lane < m) {
+        my_v = __ldg(val + e0 + j0 + lane);
+        my_f = __ldg(idx + e0 + j0 + lane);
+        if (my_f < 0 || my_f >= F) {
+          report_status(status, kBadIndex);
+          my_v = 0.f, my_f = 0;
+        }
+      }
+      const int valid = __popc(__ballot_sync(0xffffffffu, my_v != 0.f));  // valid slots come first
+      for (int j = 0; j < valid; j += 2) {
+        const bool two = j + 1 < valid;
+        const float v0 = __shfl_sync(0xffffffffu, my_v, j);
+        const float v1 = two ? __shfl_sync(0xffffffffu, my_v, j + 1) : 0.f;
+        const T* r0 = W + (p * F + __shfl_sync(0xffffffffu, my_f, j)) * D;
+        const T* r1 = W + (p * F + __shfl_sync(0xffffffffu, my_f, two ? j + 1 : j)) * D;
+        typename V::Raw x0[VPL], x1[VPL];
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+          const int c = lane + 32 * i;
+          x0[i] = c < nvec ? V::load_raw(r0 + 8 * c) : V::zero();
+          x1[i] = (two && c < nvec) ? V::load_raw(r1 + 8 * c) : V::zero();
+        }
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+          float w[8];
+          V::unpack(x0[i], w);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) acc[i][q] = fmaf(v0, w[q], acc[i][q]);
+          V::unpack(x1[i], w);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) acc[i][q] = fmaf(v1, w[q], acc[i][q]);
+        }
+      }
+      if (valid < m) break;
+    }
+  }
+  float* out = recon + ((size_t)b * L + t) * D;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = lane + 32 * i;
+    if (c < nvec) {
+      float bb[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (b_dec != nullptr) Vec8<float>::load(b_dec + (size_t)t * D + 8 * c, bb);
+      float4* o = reinterpret_cast<float4*>(out + 8 * c);
+      o[0] = make_float4(acc[i][0] + bb[0], acc[i][1] + bb[1], acc[i][2] + bb[2], acc[i][3] + bb[3]);
+      o[1] = make_float4(acc[i][4] + bb[4], acc[i][5] + bb[5], acc[i][6] + bb[6], acc[i][7] + bb[7]);
+    }
+  }
+}
+
 // =========================================================================================
 // Feature-major copy of the selection (counting sort per layer).
 // =========================================================================================
@@ -434,12 +517,18 @@ __global__ void scatter_cols_kernel(const float* __restrict__ src, const float* 
 template <class T>
 int launch_dec_fwd(const int* idx, const float* val, const int* row_start, const int* row_cnt, long long npl,
                    const void* W, const float* b_dec, float* recon, int B, int L, int D, int F, int k, int crosslayer,
-                   int* status, cudaStream_t s) {
+                   int short_rows, int* status, cudaStream_t s) {
   const int vpl = (D / 8 + 31) / 32;
   dim3 grid(B, L);
   const size_t smem = 4 * (size_t)D * sizeof(float);
+  const unsigned wgrid = (unsigned)(((long long)B * L + 3) / 4);
 #define CLT_DEC_FWD(V)                                                                                              \
   case V:                                                                                                           \
+    if (short_rows) {                                                                                               \
+      sparse_dec_fwd_warp_kernel<T, V><<<wgrid, 128, 0, s>>>(idx, val, row_start, row_cnt, npl, (const T*)W, b_dec, \
+                                                             recon, B, L, D, F, k, crosslayer, status);             \
+      break;                                                                                                        \
+    }                                                                                                               \
     CLT_CHECK_CUDA(cudaFuncSetAttribute(sparse_dec_fwd_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                         (int)smem));                                                                \
     sparse_dec_fwd_kernel<T, V><<<grid, 128, smem, s>>>(idx, val, row_start, row_cnt, npl, (const T*)W, b_dec,      \
@@ -493,7 +582,7 @@ extern "C" {
 
 int clt_sparse_decoder_fwd(const int* idx, const float* val, const int* row_start, const int* row_cnt, int64_t npl,
                            const void* W_dec, const float* b_dec, float* recon, int B, int L, int D, int F, int k,
-                           int crosslayer, int bf16, int* status, clt_stream_t stream) {
+                           int crosslayer, int short_rows, int bf16, int* status, clt_stream_t stream) {
   CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && F > 0 && k > 0, "sparse_decoder_fwd: bad dims B=%d L=%d D=%d F=%d k=%d", B,
                 L, D, F, k);
   CLT_CHECK_ARG(D % 8 == 0, "sparse_decoder_fwd: d_acts=%d must be a multiple of 8", D);
@@ -503,9 +592,9 @@ int clt_sparse_decoder_fwd(const int* idx, const float* val, const int* row_star
   CLT_CHECK_ARG(B <= 2147483647 && L <= 65535, "sparse_decoder_fwd: grid too large");
   if (bf16)
     return launch_dec_fwd<__nv_bfloat16>(idx, val, row_start, row_cnt, npl, W_dec, b_dec, recon, B, L, D, F, k,
-                                         crosslayer, status, (cudaStream_t)stream);
+                                         crosslayer, short_rows, status, (cudaStream_t)stream);
   return launch_dec_fwd<float>(idx, val, row_start, row_cnt, npl, W_dec, b_dec, recon, B, L, D, F, k, crosslayer,
-                               status, (cudaStream_t)stream);
+                               short_rows, status, (cudaStream_t)stream);
 }
 
 int clt_csc_build(const int* idx, const float* val, int* col_ptr, int* cursor, int* ent, int64_t npl, int L, int F,

@@ -428,7 +428,7 @@ class StepEngine:
                 cand_all = ws.get("aux_cand_all", (world, L, B, k_aux), torch.float32, dev)
                 h_gather = all_gather(cand_all, cand, group, async_op=True)
         self._call("clt_sparse_decoder_fwd", idx, val, None, None, B * kk, W_op, bias, recon, B, L, D, F, kk, crosslayer,
-                   int(bf16), self.status, s)
+                   int(kk <= 8 * world), int(bf16), self.status, s)
         if world > 1:
             from .parallel import all_reduce_sum
 
@@ -531,7 +531,7 @@ class StepEngine:
             row_cnt.zero_()
         self._call("clt_dead_update", mod.last_active, self.fired, None, B, int(mod.tokens_till_dead), L, F, s)
         self._call("clt_sparse_decoder_fwd", idx, val, row_start, row_cnt, npl, W_op, bias, recon, B, L, D, F, 1,
-                   crosslayer, int(bf16), self.status, s)
+                   crosslayer, int(k <= 8 * world), int(bf16), self.status, s)
         if world > 1:
             from .parallel import all_reduce_sum
 

@@ -159,10 +159,12 @@ int clt_topk_apply_threshold(int* idx, float* val, const float* thr, uint32_t* f
  *
  * CrosslayerDecoder.forward / Decoder.forward (clt.py:334-343, 241-248) on the selected features:
  * recon[b,t,:] = b_dec[t] + sum_{s<=t} sum_{entries e of (s,b)} val[e] W_dec[pair(t,s), idx[e], :].
- * row_start / row_cnt NULL = fixed k slots per token. */
+ * row_start / row_cnt NULL = fixed k slots per token.  short_rows != 0 selects the variant with one
+ * warp per (token, target) for lists of a few entries per row (feature shards); same result. */
 int clt_sparse_decoder_fwd(const int* idx, const float* val, const int* row_start, const int* row_cnt,
                            int64_t npl, const void* W_dec, const float* b_dec, float* recon, int B, int L, int D,
-                           int F, int k, int crosslayer, int bf16, int* status, clt_stream_t stream);
+                           int F, int k, int crosslayer, int short_rows, int bf16, int* status,
+                           clt_stream_t stream);
 
 /* Feature-major copy of the selection: col_ptr [L, F+1], ent [L, npl] (entry slots grouped by
  * feature).  cursor [L, F] is scratch. */
