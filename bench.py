@@ -177,6 +177,8 @@ def algorithmic_work(spec, Fl: int, n_params: int, batch_bytes_per_elem: int, nd
         "clt_encoder_dense_bwd_dw": ("tensor", 2.0 * B * L * D * Fd if spec.kind == "topk" else enc),
         "clt_decoder_dense_fwd": ("tensor", dec),
         "clt_decoder_dense_bwd_dfeat": ("tensor", dec), "clt_decoder_dense_bwd_dw": ("tensor", dec),
+        "clt_decoder_dense_bwd_dfeat_raw": ("tensor", dec),
+        "clt_act_fwd": ("hbm", float(B) * L * Fl * e * 2), "clt_act_bwd": ("hbm", float(B) * L * Fl * e * 3),
         "clt_adam_step": ("hbm", n_params * (28.0 + (2 if spec.bf16 else 0))),
         "clt_prep_input": ("hbm", bld * (batch_bytes_per_elem + e)),
         "clt_loss_fwd": ("hbm", bld * (4 + batch_bytes_per_elem + (4 if spec.k_aux else 0))),

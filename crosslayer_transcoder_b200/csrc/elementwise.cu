@@ -403,6 +403,185 @@ int loss_bwd(const float* recon, const float* aux, const void* batch, int in_dty
 }
 
 // ---------------------------------------------------------------------------------
+// (Jump)ReLU forward / backward as streaming kernels over z [L, B, F].
+// When the contraction length is short (d_acts of a few hundred) the tensor-core main loop of a
+// tile is shorter than a fused activation epilogue, so the encoder contraction only stores z and
+// these kernels do the rest at HBM speed; for long contractions the fused epilogues are used.
+// A thread owns 8 consecutive features: their bias / threshold / norm live in registers, the
+// per-feature sums accumulate in registers over the CTA's rows and leave with one atomic each.
+//
+// forward : feat = pre [pre > theta, pre > 0], pre = z + b;  loss_acc[0] += sum relu(-pre),
+//           loss_acc[1] += sum tanh(feat n c) (or the product);  fired bits
+// backward: dpre, dtheta, db_enc, d dec_norm from g = dL/dfeat exactly as csrc/epilogues.cuh states
+// ---------------------------------------------------------------------------------
+template <class T>
+__global__ void __launch_bounds__(128)
+act_fwd_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, const float* __restrict__ theta,
+               const float* __restrict__ dec_norm, T* __restrict__ feat, unsigned* __restrict__ fired_bits,
+               float* __restrict__ loss_acc, float c_sparsity, int use_tanh, int want_pre, int B, int F,
+               int rows_per_cta) {
+  const int l = blockIdx.z;
+  const int f0 = (blockIdx.x * 128 + threadIdx.x) * 8;
+  const int r0 = blockIdx.y * rows_per_cta, r1 = min(B, r0 + rows_per_cta);
+  float s_pre = 0.f, s_sp = 0.f;
+  if (f0 < F) {
+    float bb[8], tt[8], nn[8];
+    load8<float>(b_enc + (size_t)l * F + f0, bb);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) tt[q] = 0.f, nn[q] = 0.f;
+    if (theta != nullptr) load8<float>(theta + (size_t)l * F + f0, tt);
+    const bool sp = dec_norm != nullptr;
+    if (sp) {
+      load8<float>(dec_norm + (size_t)l * F + f0, nn);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) nn[q] *= c_sparsity;
+    }
+    unsigned mask = 0u;
+    for (int r = r0; r < r1; ++r) {
+      const size_t o = ((size_t)l * B + r) * F + f0;
+      float zv[8], fv[8];
+      load8<T>(z + o, zv);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float pre = zv[q] + bb[q];
+        const float f = (pre > tt[q] && pre > 0.f) ? pre : 0.f;
+        fv[q] = f;
+        mask |= (f > 0.f) ? (1u << q) : 0u;
+        if (want_pre) s_pre += fmaxf(-pre, 0.f);
+        if (sp) {
+          const float w = f * nn[q];
+          s_sp += use_tanh ? tanhf(w) : w;
+        }
+      }
+      store8<T>(feat + o, fv);
+    }
+    if (fired_bits != nullptr && mask != 0u)
+      atomicOr(fired_bits + (size_t)l * ((F + 31) / 32) + f0 / 32, mask << (f0 & 31));
+  }
+  s_pre = warp_sum(s_pre);
+  s_sp = warp_sum(s_sp);
+  if ((threadIdx.x & 31) == 0) {
+    if (s_pre != 0.f) atomicAdd(loss_acc + 0, s_pre);
+    if (s_sp != 0.f) atomicAdd(loss_acc + 1, s_sp);
+  }
+}
+
+template <class T>
+__global__ void __launch_bounds__(128)
+act_bwd_kernel(const T* __restrict__ g, const T* __restrict__ z, const float* __restrict__ b_enc,
+               const float* __restrict__ theta, const float* __restrict__ dec_norm, T* __restrict__ dpre,
+               float* __restrict__ dtheta, float* __restrict__ dbenc, float* __restrict__ dnorm, float bandwidth,
+               float lam_, float c_sparsity, float pal_, int use_tanh, const float* __restrict__ gscale, int B, int F,
+               int rows_per_cta) {
+  const int l = blockIdx.z;
+  const int f0 = (blockIdx.x * 128 + threadIdx.x) * 8;
+  if (f0 >= F) return;
+  const int r0 = blockIdx.y * rows_per_cta, r1 = min(B, r0 + rows_per_cta);
+  const float gsc = gscale != nullptr ? __ldg(gscale) : 1.f;
+  const float lam = lam_ * gsc, pal = pal_ * gsc;
+  const float hb = 0.5f * bandwidth;
+  const bool relu = theta == nullptr;
+  const bool sp = dec_norm != nullptr;
+  const float pass_lim = relu ? 0.f : -1.0e-45f;   // JumpReLU passes pre >= 0, ReLU pre > 0
+  float bb[8], tt[8], nn[8], cc[8];
+  load8<float>(b_enc + (size_t)l * F + f0, bb);
+#pragma unroll
+  for (int q = 0; q < 8; ++q) tt[q] = 0.f, nn[q] = 0.f, cc[q] = 0.f;
+  if (!relu) {
+    load8<float>(theta + (size_t)l * F + f0, tt);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) cc[q] = -tt[q] / bandwidth;
+  }
+  if (sp) {
+    load8<float>(dec_norm + (size_t)l * F + f0, nn);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) nn[q] *= c_sparsity;
+  }
+  float sb[8], st[8], sn[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) sb[q] = 0.f, st[q] = 0.f, sn[q] = 0.f;
+  for (int r = r0; r < r1; ++r) {
+    const size_t o = ((size_t)l * B + r) * F + f0;
+    float gv[8], zv[8], dp[8];
+    load8<T>(g + o, gv);
+    load8<T>(z + o, zv);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float th = tt[q];
+      const float pre = zv[q] + bb[q];
+      float gs = gv[q];
+      if (sp) {
+        const float f = (pre > th && pre > 0.f) ? pre : 0.f;
+        float d1 = 1.f;
+        if (use_tanh) {
+          const float tw = tanhf(f * nn[q]);
+          d1 = 1.f - tw * tw;
+        }
+        gs = fmaf(lam * d1, nn[q], gs);
+        sn[q] = fmaf(lam * d1 * c_sparsity, f, sn[q]);
+      }
+      const float d = pre - th;
+      const bool rect = (d > -hb) && !(d > hb);
+      float x = (pre > pass_lim) ? gs : 0.f;
+      x = (pre < 0.f) ? x - pal : x;
+      dp[q] = x;
+      sb[q] += x;
+      st[q] += rect ? cc[q] * gs : 0.f;
+    }
+    store8<T>(dpre + o, dp);
+  }
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const size_t i = (size_t)l * F + f0 + q;
+    if (sb[q] != 0.f) atomicAdd(dbenc + i, sb[q]);
+    if (dtheta != nullptr && st[q] != 0.f) atomicAdd(dtheta + i, st[q]);
+    if (dnorm != nullptr && sn[q] != 0.f) atomicAdd(dnorm + i, sn[q]);
+  }
+}
+
+static int act_rows_per_cta(int B) { return B >= 2048 ? 250 : (B >= 256 ? 64 : 16); }
+
+int act_fwd(const void* z, const float* b_enc, const float* theta, const float* dec_norm, void* feat,
+            unsigned* fired_bits, float* loss_acc, float c_sparsity, int use_tanh, int want_pre, int B, int L, int F,
+            int bf16, cudaStream_t s) {
+  if (B <= 0) return 0;
+  CLT_CHECK_ARG(F % 8 == 0, "act_fwd: d_features=%d must be a multiple of 8", F);
+  const int rpc = act_rows_per_cta(B);
+  dim3 grid((F / 8 + 127) / 128, (B + rpc - 1) / rpc, L);
+  CLT_CHECK_ARG(grid.y <= 65535 && grid.z <= 65535, "act_fwd: grid too large");
+  if (bf16)
+    act_fwd_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>((const __nv_bfloat16*)z, b_enc, theta, dec_norm,
+                                                       (__nv_bfloat16*)feat, fired_bits, loss_acc, c_sparsity, use_tanh,
+                                                       want_pre, B, F, rpc);
+  else
+    act_fwd_kernel<float><<<grid, 128, 0, s>>>((const float*)z, b_enc, theta, dec_norm, (float*)feat, fired_bits,
+                                               loss_acc, c_sparsity, use_tanh, want_pre, B, F, rpc);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int act_bwd(const void* g, const void* z, const float* b_enc, const float* theta, const float* dec_norm, void* dpre,
+            float* dtheta, float* dbenc, float* dnorm, float bandwidth, float lam, float c_sparsity, float pal,
+            int use_tanh, const float* gscale, int B, int L, int F, int bf16, cudaStream_t s) {
+  if (B <= 0) return 0;
+  CLT_CHECK_ARG(F % 8 == 0, "act_bwd: d_features=%d must be a multiple of 8", F);
+  CLT_CHECK_ARG(bandwidth > 0.f, "act_bwd: bandwidth must be positive");
+  const int rpc = act_rows_per_cta(B);
+  dim3 grid((F / 8 + 127) / 128, (B + rpc - 1) / rpc, L);
+  CLT_CHECK_ARG(grid.y <= 65535 && grid.z <= 65535, "act_bwd: grid too large");
+  if (bf16)
+    act_bwd_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)z, b_enc, theta,
+                                                       dec_norm, (__nv_bfloat16*)dpre, dtheta, dbenc, dnorm, bandwidth,
+                                                       lam, c_sparsity, pal, use_tanh, gscale, B, F, rpc);
+  else
+    act_bwd_kernel<float><<<grid, 128, 0, s>>>((const float*)g, (const float*)z, b_enc, theta, dec_norm, (float*)dpre,
+                                               dtheta, dbenc, dnorm, bandwidth, lam, c_sparsity, pal, use_tanh, gscale,
+                                               B, F, rpc);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
 // Decoder row norms  n[s, f] = sqrt( sum over blocks (t, s) of |W[pair(t,s), f, :]|^2 ).
 // crosslayer = 0: one block per layer (per-layer decoder), n[l, f] = |W[l, f, :]|.
 // One warp per (s, f).

@@ -12,6 +12,7 @@
 //     struct Params;                      // pointers and scalars, passed by value
 //     struct State;                       // per-thread registers living for the whole kernel
 //     static constexpr int kColArrays;    // per-column parameter arrays to stage
+//     static constexpr bool kPrefetch;    // registers allow reading the next accumulator chunk early
 //     static float col_value(const Params&, int arr, int z, int n, int N);   // array arr at column n < N
 //     static void init(State&);
 //     template <int CS>                   // CS = stride between staged arrays (columns per tile)
@@ -185,6 +186,65 @@ __device__ __forceinline__ void store_tile(unsigned char* stage, T* mat, size_t 
   }
 }
 
+// Coalesced load of a warp's 32 x 32 sub-tile (the mirror image of store_rows32): 4 lanes fetch one
+// row's 64-byte segment, the tile is parked in the staging buffer, every lane then reads its own row.
+// Rows beyond rows_valid read as 0.
+template <class T>
+__device__ __forceinline__ void load_rows32(unsigned char* stage, const T* base, size_t ld, int rows_valid,
+                                            float (&o)[32]);
+
+template <>
+__device__ __forceinline__ void load_rows32<__nv_bfloat16>(unsigned char* stage, const __nv_bfloat16* base, size_t ld,
+                                                           int rows_valid, float (&o)[32]) {
+  const int lane = threadIdx.x & 31;
+  const int piece = lane & 3;
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int r = it * 8 + (lane >> 2);
+    uint4 t = make_uint4(0, 0, 0, 0);
+    if (r < rows_valid) t = *reinterpret_cast<const uint4*>(base + (size_t)r * ld + piece * 8);
+    *reinterpret_cast<uint4*>(stage + r * kStageRow + piece * 16) = t;
+  }
+  __syncwarp();
+  const uint4* mine = reinterpret_cast<const uint4*>(stage + lane * kStageRow);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 t = mine[i];
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      o[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+      o[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+    }
+  }
+  __syncwarp();
+}
+
+template <>
+__device__ __forceinline__ void load_rows32<float>(unsigned char* stage, const float* base, size_t ld, int rows_valid,
+                                                   float (&o)[32]) {
+  const int lane = threadIdx.x & 31;
+  const int piece = lane & 3;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int r = it * 8 + (lane >> 2);
+      float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < rows_valid) t = *reinterpret_cast<const float4*>(base + (size_t)r * ld + 16 * h + piece * 4);
+      *reinterpret_cast<float4*>(stage + r * kStageRow + piece * 16) = t;
+    }
+    __syncwarp();
+    const float4* mine = reinterpret_cast<const float4*>(stage + lane * kStageRow);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 t = mine[i];
+      o[16 * h + 4 * i] = t.x, o[16 * h + 4 * i + 1] = t.y, o[16 * h + 4 * i + 2] = t.z, o[16 * h + 4 * i + 3] = t.w;
+    }
+    __syncwarp();
+  }
+}
+
 // lane j adds its column total to dst[n0 + j]
 __device__ __forceinline__ void col_atomic_add(float* dst, int n0, int N, float colsum) {
   const int lane = threadIdx.x & 31;
@@ -202,6 +262,7 @@ struct StoreZ {
   };
   struct State {};
   static constexpr int kColArrays = 0;
+  static constexpr bool kPrefetch = true;
   __device__ static float col_value(const Params&, int, int, int, int) { return 0.f; }
   __device__ static void init(State&) {}
   template <int CS>
@@ -223,6 +284,7 @@ struct DecOut {
   };
   struct State {};
   static constexpr int kColArrays = 1;
+  static constexpr bool kPrefetch = true;
   __device__ static float col_value(const Params& p, int, int z, int n, int N) {
     return p.bias != nullptr ? __ldg(p.bias + (size_t)z * N + n) : 0.f;
   }
@@ -251,6 +313,7 @@ struct GradOut {
   };
   struct State {};
   static constexpr int kColArrays = 0;
+  static constexpr bool kPrefetch = true;
   __device__ static float col_value(const Params&, int, int, int, int) { return 0.f; }
   __device__ static void init(State&) {}
   template <int CS>
@@ -303,6 +366,7 @@ struct EncJumpReLU {
     float s_pre, s_sp;
   };
   static constexpr int kColArrays = 3;
+  static constexpr bool kPrefetch = false;
   __device__ static float col_value(const Params& p, int arr, int z, int n, int N) {
     const size_t i = (size_t)z * N + n;
     if (arr == 0) return __ldg(p.b_enc + i);
@@ -310,36 +374,61 @@ struct EncJumpReLU {
     return p.dec_norm != nullptr ? __ldg(p.dec_norm + i) * p.c_sparsity : 0.f;
   }
   __device__ static void init(State& s) { s.s_pre = 0.f, s.s_sp = 0.f; }
+  // The element loop, specialised on the launch-constant options so that it carries no branches:
+  // kPre (pre-activation sum wanted), kSp (sparsity sum wanted), kEdge (tile edge: per-element guards).
+  template <int CS, bool kPre, bool kSp, bool kEdge>
+  __device__ static __forceinline__ void body(const Params& p, State& st, bool row_ok, int n0, int N, float (&v)[32],
+                                              float (&feat)[32], unsigned& mask, const float* colp) {
+    float s_pre = 0.f, s_sp = 0.f;
+#pragma unroll
+    for (int i4 = 0; i4 < 8; ++i4) {
+      const float4 b4 = *reinterpret_cast<const float4*>(colp + 4 * i4);
+      const float4 t4 = *reinterpret_cast<const float4*>(colp + CS + 4 * i4);
+      const float bb[4] = {b4.x, b4.y, b4.z, b4.w}, tt[4] = {t4.x, t4.y, t4.z, t4.w};
+      float nn[4] = {0.f, 0.f, 0.f, 0.f};
+      if (kSp) {
+        const float4 n4 = *reinterpret_cast<const float4*>(colp + 2 * CS + 4 * i4);
+        nn[0] = n4.x, nn[1] = n4.y, nn[2] = n4.z, nn[3] = n4.w;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = 4 * i4 + j;
+        const float zr = round_to<T>(v[i]);
+        const float pre = zr + bb[j];
+        float f = (pre > tt[j] && pre > 0.f) ? pre : 0.f;
+        bool ok = true;
+        if (kEdge) {
+          ok = row_ok && (n0 + i < N);
+          f = ok ? f : 0.f;
+        }
+        v[i] = zr;
+        feat[i] = f;
+        mask |= (f > 0.f) ? (1u << i) : 0u;
+        if (kPre) s_pre += ok ? fmaxf(-pre, 0.f) : 0.f;
+        if (kSp) {
+          const float w = f * nn[j];
+          s_sp += p.use_tanh ? tanhf(w) : w;
+        }
+      }
+    }
+    st.s_pre += s_pre, st.s_sp += s_sp;
+  }
+
   template <int CS>
   __device__ static void apply(const Params& p, State& st, int z, int row, bool row_ok, int n0, int M, int N,
                                float (&v)[32], const float* colp, unsigned char* stage) {
-    const bool full = n0 + 32 <= N;
+    const bool edge = (n0 + 32 > N) || __any_sync(0xffffffffu, !row_ok);
     const bool sp = p.dec_norm != nullptr;
     float feat[32];
     unsigned mask = 0u;
-    float s_pre = 0.f, s_sp = 0.f;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const float zr = round_to<T>(v[i]);
-      const float pre = zr + colp[i];
-      float f = (pre > colp[CS + i] && pre > 0.f) ? pre : 0.f;
-      if (!(row_ok && (full || n0 + i < N))) f = 0.f;
-      v[i] = zr;
-      feat[i] = f;
-      mask |= (f > 0.f) ? (1u << i) : 0u;
-      if (p.want_pre) s_pre += fmaxf(-pre, 0.f);
-      if (sp) {
-        const float w = f * colp[2 * CS + i];
-        s_sp += p.use_tanh ? tanhf(w) : w;
-      }
+    const int sel = (p.want_pre ? 1 : 0) | (sp ? 2 : 0) | (edge ? 4 : 0);
+    switch (sel) {
+      case 0: body<CS, false, false, false>(p, st, row_ok, n0, N, v, feat, mask, colp); break;
+      case 1: body<CS, true, false, false>(p, st, row_ok, n0, N, v, feat, mask, colp); break;
+      case 2: body<CS, false, true, false>(p, st, row_ok, n0, N, v, feat, mask, colp); break;
+      case 3: body<CS, true, true, false>(p, st, row_ok, n0, N, v, feat, mask, colp); break;
+      default: body<CS, true, true, true>(p, st, row_ok, n0, N, v, feat, mask, colp); break;
     }
-    if (p.want_pre && !full) {  // ragged edge: redo the sum with the column guard
-      s_pre = 0.f;
-#pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (n0 + i < N) s_pre += fmaxf(-(v[i] + colp[i]), 0.f);
-    }
-    if (row_ok) st.s_pre += s_pre, st.s_sp += s_sp;
     if (p.fired_bits != nullptr) {
       mask = __reduce_or_sync(0xffffffffu, mask);
       if ((threadIdx.x & 31) == 0 && mask != 0u) atomicOr(p.fired_bits + (size_t)z * ((N + 31) / 32) + n0 / 32, mask);
@@ -391,6 +480,7 @@ struct DFeatJumpReLU {
   };
   struct State {};
   static constexpr int kColArrays = 4;
+  static constexpr bool kPrefetch = false;
   __device__ static float col_value(const Params& p, int arr, int z, int n, int N) {
     const size_t i = (size_t)z * N + n;
     if (arr == 0) return __ldg(p.b_enc + i);
@@ -402,52 +492,88 @@ struct DFeatJumpReLU {
   template <int CS>
   __device__ static void apply(const Params& p, State&, int z, int row, bool row_ok, int n0, int M, int N,
                                float (&v)[32], const float* colp, unsigned char* stage) {
-    const size_t off = ((size_t)z * M + (row_ok ? row : 0)) * N + n0;
-    const bool full = n0 + 32 <= N;
-    const bool vec = can_vec<T>(n0, N);
+    const bool edge = (n0 + 32 > N) || __any_sync(0xffffffffu, !row_ok);
+    const bool al = N % (16 / (int)sizeof(T)) == 0;
+    const int row0 = row - (threadIdx.x & 31);
     float zv[32];
-    load32<T>(p.z_in + off, row_ok ? N - n0 : 0, vec && row_ok, zv);
+    if (al && n0 + 32 <= N) {
+      load_rows32<T>(stage, p.z_in + ((size_t)z * M + row0) * N + n0, (size_t)N, M - row0, zv);
+    } else {
+      const size_t off = ((size_t)z * M + (row_ok ? row : 0)) * N + n0;
+      load32<T>(p.z_in + off, row_ok ? N - n0 : 0, false, zv);
+    }
     float dth[32], dnr[32];
-    const bool relu = p.theta == nullptr;
     const bool sp = p.dec_norm != nullptr;
+    if (sp) {
+      if (edge) body<CS, true, true>(p, row_ok, n0, N, v, zv, dth, dnr, colp);
+      else body<CS, true, false>(p, row_ok, n0, N, v, zv, dth, dnr, colp);
+    } else {
+      if (edge) body<CS, false, true>(p, row_ok, n0, N, v, zv, dth, dnr, colp);
+      else body<CS, false, false>(p, row_ok, n0, N, v, zv, dth, dnr, colp);
+    }
+    store_tile<T>(stage, p.dpre_out + (size_t)z * M * N, (size_t)N, row0, row, row_ok, M, n0, N, al, v);
+    col_atomic_add(p.dbenc + (size_t)z * N, n0, N, warp_colsum32(v));
+    if (p.dtheta != nullptr) col_atomic_add(p.dtheta + (size_t)z * N, n0, N, warp_colsum32(dth));
+    if (sp && p.dnorm != nullptr) col_atomic_add(p.dnorm + (size_t)z * N, n0, N, warp_colsum32(dnr));
+  }
+
+  // The element loop, specialised on kSp (sparsity gradient present) and kEdge (tile edge guards).
+  template <int CS, bool kSp, bool kEdge>
+  __device__ static __forceinline__ void body(const Params& p, bool row_ok, int n0, int N, float (&v)[32],
+                                              const float (&zv)[32], float (&dth)[32], float (&dnr)[32],
+                                              const float* colp) {
+    const bool relu = p.theta == nullptr;
     const float gsc = p.gscale != nullptr ? __ldg(p.gscale) : 1.f;
     const float lam = p.lam * gsc, pal = p.pal * gsc;
     const float hb = 0.5f * p.bandwidth;
+    // JumpReLU passes the gradient for pre >= 0, plain ReLU for pre > 0
+    const float pass_lim = relu ? 0.f : -1.0e-45f;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const bool ok = row_ok && (full || n0 + i < N);
-      const float th = colp[CS + i];
-      const float pre = zv[i] + colp[i];
-      float gs = v[i];
-      float dn = 0.f;
-      if (sp) {
-        const float f = (pre > th && pre > 0.f) ? pre : 0.f;
-        const float nc = colp[2 * CS + i];
-        float d1 = 1.f;
-        if (p.use_tanh) {
-          const float tw = tanhf(f * nc);
-          d1 = 1.f - tw * tw;
-        }
-        gs = fmaf(lam * d1, nc, gs);
-        dn = lam * d1 * f * p.c_sparsity;
+    for (int i4 = 0; i4 < 8; ++i4) {
+      const float4 b4 = *reinterpret_cast<const float4*>(colp + 4 * i4);
+      const float4 t4 = *reinterpret_cast<const float4*>(colp + CS + 4 * i4);
+      const float4 c4 = *reinterpret_cast<const float4*>(colp + 3 * CS + 4 * i4);
+      const float bb[4] = {b4.x, b4.y, b4.z, b4.w}, tt[4] = {t4.x, t4.y, t4.z, t4.w};
+      const float cc[4] = {c4.x, c4.y, c4.z, c4.w};
+      float nn[4] = {0.f, 0.f, 0.f, 0.f};
+      if (kSp) {
+        const float4 n4 = *reinterpret_cast<const float4*>(colp + 2 * CS + 4 * i4);
+        nn[0] = n4.x, nn[1] = n4.y, nn[2] = n4.z, nn[3] = n4.w;
       }
-      const float d = pre - th;
-      const bool rect = (d > -hb) && !(d > hb);
-      const bool pass = relu ? (pre > 0.f) : !(pre < 0.f);
-      float dp = pass ? gs : 0.f;
-      if (pre < 0.f) dp -= pal;
-      v[i] = ok ? dp : 0.f;
-      dth[i] = (ok && rect) ? colp[3 * CS + i] * gs : 0.f;
-      dnr[i] = ok ? dn : 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = 4 * i4 + j;
+        const float th = tt[j];
+        const float pre = zv[i] + bb[j];
+        float gs = v[i];
+        float dn = 0.f;
+        if (kSp) {
+          const float f = (pre > th && pre > 0.f) ? pre : 0.f;
+          const float nc = nn[j];
+          float d1 = 1.f;
+          if (p.use_tanh) {
+            const float tw = tanhf(f * nc);
+            d1 = 1.f - tw * tw;
+          }
+          gs = fmaf(lam * d1, nc, gs);
+          dn = lam * d1 * f * p.c_sparsity;
+        }
+        const float d = pre - th;
+        const bool rect = (d > -hb) && !(d > hb);
+        float dp = (pre > pass_lim) ? gs : 0.f;
+        dp = (pre < 0.f) ? dp - pal : dp;
+        float dt = rect ? cc[j] * gs : 0.f;
+        if (kEdge) {
+          const bool ok = row_ok && (n0 + i < N);
+          dp = ok ? dp : 0.f;
+          dt = ok ? dt : 0.f;
+          dn = ok ? dn : 0.f;
+        }
+        v[i] = dp;
+        dth[i] = dt;
+        if (kSp) dnr[i] = dn;
+      }
     }
-    {
-      const int row0 = row - (threadIdx.x & 31);
-      store_tile<T>(stage, p.dpre_out + (size_t)z * M * N, (size_t)N, row0, row, row_ok, M, n0, N,
-                    N % (16 / (int)sizeof(T)) == 0, v);
-    }
-    col_atomic_add(p.dbenc + (size_t)z * N, n0, N, warp_colsum32(v));
-    if (p.dtheta != nullptr) col_atomic_add(p.dtheta + (size_t)z * N, n0, N, warp_colsum32(dth));
-    if (p.dnorm != nullptr) col_atomic_add(p.dnorm + (size_t)z * N, n0, N, warp_colsum32(dnr));
   }
   __device__ static void finish(const Params&, State&) {}
 };

@@ -120,6 +120,18 @@ int clt_decoder_dense_bwd_dfeat(const void* drecon, const void* W_dec, const voi
                                                                           (cudaStream_t)stream);
 }
 
+int clt_decoder_dense_bwd_dfeat_raw(const void* drecon, const void* W_dec, void* g_out, int B, int L, int D, int F,
+                                    int crosslayer, int bf16, int* status, clt_stream_t stream) {
+  CLT_CHECK_ARG(dims_ok(B, L, D, F), "decoder_dense_bwd_dfeat_raw: bad dims B=%d L=%d D=%d F=%d", B, L, D, F);
+  CLT_CHECK_ARG(drecon && W_dec && g_out, "decoder_dense_bwd_dfeat_raw: null pointer");
+  const int P = crosslayer ? L * (L + 1) / 2 : L;
+  GemmGeom g{crosslayer ? kDecDFeat : kBatched, B, F, D, L, L};
+  Operand a{drecon, 1, B, D, L}, b{W_dec, 1, F, D, P};
+  epi::StoreZ<float>::Params p32{(float*)g_out};
+  epi::StoreZ<bf16_t>::Params p16{(bf16_t*)g_out};
+  return run_gemm<epi::StoreZ<float>, epi::StoreZ<bf16_t>>(g, a, b, p32, p16, bf16, status, (cudaStream_t)stream);
+}
+
 int clt_decoder_dense_bwd_dw(const void* feat, const void* drecon, float* dW, const float* rowcoef,
                              const float* W_master, int B, int L, int D, int F, int crosslayer, int bf16, int* status,
                              clt_stream_t stream) {

@@ -84,7 +84,7 @@ __global__ void __launch_bounds__(128) gemm_simt_kernel(GemmGeom g, SimtOperands
 
   // per-column parameters of this tile, staged once and read as broadcasts
   constexpr int kCols = Epi::kColArrays > 0 ? Epi::kColArrays : 1;
-  __shared__ float colp[kCols][kSimtBN];
+  __shared__ __align__(16) float colp[kCols][kSimtBN];
   if (Epi::kColArrays > 0) {
     for (int e = tid; e < Epi::kColArrays * kSimtBN; e += 128) {
       const int arr = e / kSimtBN, j = e % kSimtBN;

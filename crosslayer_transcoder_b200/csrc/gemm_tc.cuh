@@ -126,8 +126,9 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
+// Asynchronous read of 32 accumulator columns of this warp's 32 lanes; the registers are valid only
+// after tmem_ld_wait().
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -138,10 +139,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
       : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor, 128-byte swizzle.
 //   bits  0-13 start address >> 4      bits 16-29 leading byte offset >> 4
@@ -345,14 +344,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < g.M;
-#pragma unroll 1
-      for (int cc = 0; cc < kBN / 64; ++cc) {
-        const int c = half * (kBN / 64) + cc;
-        const int n = n0 + 32 * c;
+      // the warp's 4 chunks of 32 columns; the read of chunk c+1 is in flight while chunk c is processed
+      constexpr int kChunks = kBN / 64;
+      const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kBN + 32 * half * kChunks);
+      const int nbase = n0 + 32 * half * kChunks;
+      uint32_t ra[32], rb[32];
+      if (nbase < g.N) tmem_ld32_issue(taddr0, ra);
+#pragma unroll
+      for (int cc = 0; cc < kChunks; ++cc) {
+        const int n = nbase + 32 * cc;
         if (n >= g.N) break;
+        if (!Epi::kPrefetch && cc > 0) tmem_ld32_issue(taddr0 + 32 * cc, ra);
+        tmem_ld_wait();
+        uint32_t(&cur)[32] = (Epi::kPrefetch && (cc & 1)) ? rb : ra;
+        uint32_t(&nxt)[32] = (cc & 1) ? ra : rb;
+        if (Epi::kPrefetch && cc + 1 < kChunks && n + 32 < g.N) tmem_ld32_issue(taddr0 + 32 * (cc + 1), nxt);
         float v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kBN + 32 * c), v);
-        Epi::template apply<kBN>(ep, st, z, row, row_ok, n, g.M, g.N, v, colp + 32 * c, stage);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(cur[i]);
+        Epi::template apply<kBN>(ep, st, z, row, row_ok, n, g.M, g.N, v, colp + 32 * (half * kChunks + cc), stage);
       }
       tc_fence_before();
       __syncwarp();

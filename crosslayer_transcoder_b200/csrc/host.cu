@@ -117,6 +117,22 @@ int clt_loss_bwd(const float* recon, const float* aux, const void* batch, int in
                   (cudaStream_t)stream);
 }
 
+int clt_act_fwd(const void* z, const float* b_enc, const float* theta, const float* dec_norm, void* feat_out,
+                uint32_t* fired_bits, float* loss_acc, float c_sparsity, int use_tanh, int want_pre, int B, int L, int F,
+                int bf16, clt_stream_t stream) {
+  CLT_CHECK_ARG(z && b_enc && feat_out && loss_acc, "act_fwd: null pointer");
+  return act_fwd(z, b_enc, theta, dec_norm, feat_out, fired_bits, loss_acc, c_sparsity, use_tanh, want_pre, B, L, F,
+                 bf16, (cudaStream_t)stream);
+}
+
+int clt_act_bwd(const void* g, const void* z, const float* b_enc, const float* theta, const float* dec_norm,
+                void* dpre_out, float* dtheta, float* dbenc, float* dnorm, float bandwidth, float lam, float c_sparsity,
+                float pal, int use_tanh, const float* gscale, int B, int L, int F, int bf16, clt_stream_t stream) {
+  CLT_CHECK_ARG(g && z && b_enc && dpre_out && dbenc, "act_bwd: null pointer");
+  return act_bwd(g, z, b_enc, theta, dec_norm, dpre_out, dtheta, dbenc, dnorm, bandwidth, lam, c_sparsity, pal,
+                 use_tanh, gscale, B, L, F, bf16, (cudaStream_t)stream);
+}
+
 int clt_dec_norms(const float* W_dec, float* out, int L, int F, int D, int crosslayer, clt_stream_t stream) {
   return dec_norms(W_dec, out, L, F, D, crosslayer, (cudaStream_t)stream);
 }

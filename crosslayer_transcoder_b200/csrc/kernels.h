@@ -14,6 +14,12 @@ int loss_fwd(const float* recon, const float* aux, const void* batch, int in_dty
 int loss_bwd(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu, const float* sd,
              const float* gscale, float aux_scale, void* drecon, void* daux, int out_bf16, float* db_dec, int B, int L,
              int D, cudaStream_t s);
+int act_fwd(const void* z, const float* b_enc, const float* theta, const float* dec_norm, void* feat,
+            unsigned* fired_bits, float* loss_acc, float c_sparsity, int use_tanh, int want_pre, int B, int L, int F,
+            int bf16, cudaStream_t s);
+int act_bwd(const void* g, const void* z, const float* b_enc, const float* theta, const float* dec_norm, void* dpre,
+            float* dtheta, float* dbenc, float* dnorm, float bandwidth, float lam, float c_sparsity, float pal,
+            int use_tanh, const float* gscale, int B, int L, int F, int bf16, cudaStream_t s);
 int dec_norms(const float* W, float* out, int L, int F, int D, int crosslayer, cudaStream_t s);
 int norm_coef(const float* dnorm, const float* n, float* out, int count, cudaStream_t s);
 int dead_update(long long* last_active, unsigned* fired_bits, unsigned char* dead, long long B, long long limit, int L,

@@ -204,6 +204,17 @@ class StepEngine:
         f = lambda t: t.detach().float().contiguous()
         return f(ins.mean), f(ins.std), f(outs.mean), f(outs.std)
 
+    def _fuse_activation(self, D: int, F: int, bf16: bool) -> bool:
+        """Fuse the (Jump)ReLU into the contraction epilogues?  ``module.fuse_activation`` forces it
+        (True / False); "auto" fuses when the contraction is long enough to hide the epilogue behind
+        the tensor-core main loop of a tile (d_acts >= 1536), and always on the fp32 CUDA-core path."""
+        mode = getattr(self.module, "fuse_activation", "auto")
+        if F % 8 != 0:
+            return True
+        if mode == "auto":
+            return (not bf16) or D >= 1536
+        return bool(mode)
+
     def _bandwidth(self, nl) -> float:
         """JumpReLU bandwidth as a host number, read from the device buffer once."""
         if getattr(self, "_bw_cache", None) is None:
@@ -265,9 +276,16 @@ class StepEngine:
         if lam != 0.0:
             norm = ws.get("dec_norm", (L, F), torch.float32, dev)
             self._call("clt_dec_norms", W_master, norm, L, F, D, crosslayer, s)
-        self._call("clt_encoder_fwd_act", xn, self._operand(enc.W, bf16), enc.b.data, theta, norm, z, feat,
-                   self.fired, acc[0:2], float(h.get("c_sparsity", 1.0)), int(h.get("use_tanh", True)),
-                   int(float(h.get("pre_actv_loss", 0.0)) != 0.0), B, L, D, F, int(bf16), self.status, s)
+        c_sp, use_tanh = float(h.get("c_sparsity", 1.0)), int(h.get("use_tanh", True))
+        want_pre = int(float(h.get("pre_actv_loss", 0.0)) != 0.0)
+        fused = self._fuse_activation(D, F, bf16)
+        if fused:
+            self._call("clt_encoder_fwd_act", xn, self._operand(enc.W, bf16), enc.b.data, theta, norm, z, feat,
+                       self.fired, acc[0:2], c_sp, use_tanh, want_pre, B, L, D, F, int(bf16), self.status, s)
+        else:
+            self._call("clt_encoder_fwd_store", xn, self._operand(enc.W, bf16), z, B, L, D, F, int(bf16), self.status, s)
+            self._call("clt_act_fwd", z, enc.b.data, theta, norm, feat, self.fired, acc[0:2], c_sp, use_tanh, want_pre,
+                       B, L, F, int(bf16), s)
         self._call("clt_decoder_dense_fwd", feat, W_op, dec.b.data if first_rank else None, recon, B, L, D, F,
                    crosslayer, int(bf16), self.status, s)
         if world > 1:
@@ -282,7 +300,7 @@ class StepEngine:
         return dict(kind=h["kind"], bf16=bf16, batch=batch, B=B, L=L, D=D, F=F, crosslayer=crosslayer, lam=lam,
                     pal=pal, c=float(h.get("c_sparsity", 1.0)), use_tanh=int(h.get("use_tanh", True)),
                     bandwidth=self._bandwidth(nl) if h["kind"] == "jumprelu" else 1.0, out=out,
-                    stats=(mu_i, sd_i, mu_o, sd_o), norm=norm, in_code=in_code)
+                    stats=(mu_i, sd_i, mu_o, sd_o), norm=norm, in_code=in_code, fused=fused)
 
     # ------------------------------------------------------------------ backward
     def backward(self, ctx: dict, gscale: torch.Tensor):
@@ -329,9 +347,15 @@ class StepEngine:
         if norm is not None:
             dnorm = ws.get("dnorm", (L, F), torch.float32, dev)
             dnorm.zero_()
-        self._call("clt_decoder_dense_bwd_dfeat", drecon, W_op, z, enc.b.data, theta, norm, dpre, dtheta,
-                   gview(enc.b), dnorm, c["bandwidth"], c["lam"] / B, c["c"], c["pal"] / (B * L), c["use_tanh"], gs,
-                   B, L, D, F, c["crosslayer"], int(bf16), self.status, s)
+        if c["fused"]:
+            self._call("clt_decoder_dense_bwd_dfeat", drecon, W_op, z, enc.b.data, theta, norm, dpre, dtheta,
+                       gview(enc.b), dnorm, c["bandwidth"], c["lam"] / B, c["c"], c["pal"] / (B * L), c["use_tanh"], gs,
+                       B, L, D, F, c["crosslayer"], int(bf16), self.status, s)
+        else:
+            self._call("clt_decoder_dense_bwd_dfeat_raw", drecon, W_op, dpre, B, L, D, F, c["crosslayer"], int(bf16),
+                       self.status, s)
+            self._call("clt_act_bwd", dpre, z, enc.b.data, theta, norm, dpre, dtheta, gview(enc.b), dnorm,
+                       c["bandwidth"], c["lam"] / B, c["c"], c["pal"] / (B * L), c["use_tanh"], gs, B, L, F, int(bf16), s)
         rowcoef = None
         if norm is not None:
             rowcoef = ws.get("rowcoef", (L, F), torch.float32, dev)

@@ -65,6 +65,8 @@ class CrossLayerTranscoderModule(_Base):
                              torch.zeros(model.encoder.n_layers, model.encoder.d_features, dtype=torch.long))
         #: "auto" follows torch.autocast (bf16-mixed -> tensor cores); "bf16" / "fp32" force a path
         self.precision = "auto"
+        #: fuse the (Jump)ReLU into the contraction epilogues: "auto" (by d_acts), True or False
+        self.fuse_activation = "auto"
         self._engine = StepEngine(self)
 
     # ---- nonlinearity -> step kind -----------------------------------------------------

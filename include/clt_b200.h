@@ -94,6 +94,21 @@ int clt_decoder_dense_bwd_dfeat(const void* drecon, const void* W_dec, const voi
                                 float pal, int use_tanh, const float* gscale, int B, int L, int D, int F,
                                 int crosslayer, int bf16, int* status, clt_stream_t stream);
 
+/* The same two fused operations split in two, for short contractions (small d_acts) where a fused
+ * activation epilogue would outlast the tensor-core main loop of a tile:
+ * clt_encoder_fwd_store + clt_act_fwd  ==  clt_encoder_fwd_act,
+ * clt_decoder_dense_bwd_dfeat_raw (g = dfeat rounded to T) + clt_act_bwd  ==  clt_decoder_dense_bwd_dfeat.
+ * dpre_out may alias g. */
+int clt_act_fwd(const void* z, const float* b_enc, const float* theta, const float* dec_norm, void* feat_out,
+                uint32_t* fired_bits, float* loss_acc, float c_sparsity, int use_tanh, int want_pre, int B, int L,
+                int F, int bf16, clt_stream_t stream);
+int clt_decoder_dense_bwd_dfeat_raw(const void* drecon, const void* W_dec, void* g_out, int B, int L, int D, int F,
+                                    int crosslayer, int bf16, int* status, clt_stream_t stream);
+int clt_act_bwd(const void* g, const void* z, const float* b_enc, const float* theta, const float* dec_norm,
+                void* dpre_out, float* dtheta, float* dbenc, float* dnorm, float bandwidth, float lam,
+                float c_sparsity, float pal, int use_tanh, const float* gscale, int B, int L, int F, int bf16,
+                clt_stream_t stream);
+
 /* Decoder weight gradient: dW_dec[pair(t,s)] = feat[s]^T drecon[t] (+ rowcoef[s,f] W_dec[p,f,:],
  * the gradient through the decoder norms of clt_lightning.py:438-448); fp32 output [P,F,D]. */
 int clt_decoder_dense_bwd_dw(const void* feat, const void* drecon, float* dW, const float* rowcoef,

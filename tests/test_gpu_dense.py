@@ -27,6 +27,7 @@ def test_golden_step(case, prec):
     spec = synthetic.WorkloadSpec(**g["spec"])
     dev = torch.device("cuda:0")
     mod = build_module(spec, g["weights"], dev)
+    mod.fuse_activation = True
     batch = g["batch"].to(dev)
     mod.model.initialize_standardizers(batch)
     for name, ref in (("mean", g["stats"]["mu_in"]), ("std", g["stats"]["sd_in"])):
@@ -59,9 +60,10 @@ SPECS = [
 ]
 
 
+@pytest.mark.parametrize("fuse", [True, False], ids=["fused_epilogue", "split_activation"])
 @pytest.mark.parametrize("prec", ["fp32", "bf16"])
 @pytest.mark.parametrize("name,L,D,F,B,cross,lam,pal", SPECS)
-def test_oracle_step(name, L, D, F, B, cross, lam, pal, prec):
+def test_oracle_step(name, L, D, F, B, cross, lam, pal, prec, fuse):
     spec = synthetic.WorkloadSpec(name, L, D, F, B, "jumprelu", cross, prec == "bf16", rank_u=16, n_outlier=2,
                                   lambda_sparsity=lam, pre_actv_loss=pal, lr=1e-3)
     batch, w, la = spec_inputs(spec)
@@ -69,6 +71,7 @@ def test_oracle_step(name, L, D, F, B, cross, lam, pal, prec):
     ref, ref_grads = O.step_with_grads(P, batch, stats, H, **kw)
     dev = torch.device("cuda:0")
     mod = build_module(spec, w, dev)
+    mod.fuse_activation = fuse                          # both forms of the (Jump)ReLU: in the epilogues or streamed
     loss = run_step(mod, batch.to(dev), idx=0)          # idx 0: the step initialises the standardizers itself
     tol = TOL[prec]
     assert rel_err(loss.cpu(), ref.loss) < tol
