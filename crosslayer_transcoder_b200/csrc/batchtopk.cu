@@ -12,7 +12,11 @@
 // A last pass walks the rows: one CTA per (layer, token) counts the row's survivors, reserves a
 // segment of the layer's entry list with one atomic and writes (feature, value, token).
 //
-// State block (device memory, 8 x 64-bit words):
+// PerLayerBatchTopK (topk.py:99-133) is the same selection run independently per layer: the kernels
+// take a number of groups (1 = whole batch, L = one per layer), with one state block and one
+// histogram per group.
+//
+// State block (device memory, 8 x 64-bit words per group):
 //   [0] prefix (bits fixed so far)   [1] want (rank of the threshold inside the current bucket)
 //   [2] threshold key T (valid after level 2; 0 = keep every positive)
 //   [3] ties: number of elements equal to T that are kept (all ranks together)
@@ -54,13 +58,17 @@ __device__ __forceinline__ bool digit_of(unsigned key, int level, unsigned prefi
 // One streaming pass over z [L, B, F]: histogram of the level's digit.
 template <class T>
 __global__ void __launch_bounds__(256)
-bt_hist_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, const u64* __restrict__ state,
-               u64* __restrict__ hist, int level, long long rows, int B, int F) {
+bt_hist_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, const u64* __restrict__ state_all,
+               u64* __restrict__ hist_all, int level, long long rows_per_group, int B, int F) {
   __shared__ unsigned sh[kBins];
   for (int i = threadIdx.x; i < kBins; i += blockDim.x) sh[i] = 0u;
   __syncthreads();
+  const int grp = blockIdx.y;
+  const u64* state = state_all + 8 * grp;
+  u64* hist = hist_all + (size_t)kBins * grp;
   const unsigned prefix = (unsigned)state[0];
-  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+  const long long row_lo = grp * rows_per_group, rows = row_lo + rows_per_group;
+  for (long long row = row_lo + blockIdx.x; row < rows; row += gridDim.x) {
     const int l = (int)(row / B);
     const T* zr = z + (size_t)row * F;
     const float* br = b_enc + (size_t)l * F;
@@ -76,8 +84,11 @@ bt_hist_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, const u
 }
 
 // Pick the bucket of the current level from the (summed) histogram; one CTA of 256 threads.
-__global__ void bt_pick_kernel(const u64* __restrict__ hist, const u64* __restrict__ hist_local, u64* __restrict__ state,
-                               int level, u64 n_keep) {
+__global__ void bt_pick_kernel(const u64* __restrict__ hist_all, const u64* __restrict__ hist_local_all,
+                               u64* __restrict__ state_all, int level, u64 n_keep) {
+  const u64* hist = hist_all + (size_t)kBins * blockIdx.x;
+  const u64* hist_local = hist_local_all != nullptr ? hist_local_all + (size_t)kBins * blockIdx.x : nullptr;
+  u64* state = state_all + 8 * blockIdx.x;
   __shared__ u64 tot[256];
   __shared__ int sh_digit;
   __shared__ u64 sh_above;
@@ -137,13 +148,15 @@ __global__ void bt_pick_kernel(const u64* __restrict__ hist, const u64* __restri
 //   layer's fill counter reserves the row's segment, sweep 2 writes (feature, value, token).
 template <class T>
 __global__ void __launch_bounds__(256)
-bt_collect_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, u64* __restrict__ state,
-                  const long long* __restrict__ tie_quota, int* __restrict__ idx, float* __restrict__ val,
+bt_collect_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, u64* __restrict__ state_all,
+                  const long long* __restrict__ tie_quota_all, int* __restrict__ idx, float* __restrict__ val,
                   int* __restrict__ etok, int* __restrict__ row_start, int* __restrict__ row_cnt,
                   int* __restrict__ layer_fill, unsigned* __restrict__ fired_bits, int B, int F, long long npl,
-                  int* status) {
+                  int groups, int* status) {
   const long long row = blockIdx.x;
   const int l = (int)(row / B), b = (int)(row % B);
+  u64* state = state_all + 8 * (groups > 1 ? l : 0);
+  const long long* tie_quota = tie_quota_all != nullptr ? tie_quota_all + (groups > 1 ? l : 0) : nullptr;
   const T* zr = z + (size_t)row * F;
   const float* br = b_enc + (size_t)l * F;
   const unsigned Tk = (unsigned)state[2];
@@ -214,9 +227,12 @@ bt_collect_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, u64*
 }
 
 // threshold <- (1 - e) threshold + e * (smallest kept value)   (topk.py:94-95)
-__global__ void bt_threshold_update_kernel(const u64* __restrict__ state, float* __restrict__ threshold, float e) {
-  const float tmin = __uint_as_float((unsigned)state[2]);  // the threshold value; 0 if nothing was cut
-  threshold[0] = (1.f - e) * threshold[0] + e * tmin;
+__global__ void bt_threshold_update_kernel(const u64* __restrict__ state, float* __restrict__ threshold, float e,
+                                           int groups) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= groups) return;
+  const float tmin = __uint_as_float((unsigned)state[8 * g + 2]);  // the threshold value; 0 if nothing was cut
+  threshold[g] = (1.f - e) * threshold[g] + e * tmin;
 }
 
 }  // namespace
@@ -226,36 +242,40 @@ using namespace clt;
 
 extern "C" {
 
-int clt_batchtopk_hist(const void* z, const float* b_enc, const uint64_t* state, uint64_t* hist, int level, int B, int L,
-                       int F, int bf16, clt_stream_t stream) {
+int clt_batchtopk_hist(const void* z, const float* b_enc, const uint64_t* state, uint64_t* hist, int level, int groups,
+                       int B, int L, int F, int bf16, clt_stream_t stream) {
   CLT_CHECK_ARG(B > 0 && L > 0 && F > 0 && level >= 0 && level <= 2, "batchtopk_hist: bad arguments");
+  CLT_CHECK_ARG(groups == 1 || groups == L, "batchtopk_hist: groups must be 1 (whole batch) or L (per layer)");
   CLT_CHECK_ARG(z && b_enc && state && hist, "batchtopk_hist: null pointer");
   cudaStream_t s = (cudaStream_t)stream;
-  CLT_CHECK_CUDA(cudaMemsetAsync(hist, 0, sizeof(u64) * kBins, s));
-  const long long rows = (long long)L * B;
-  const int grid = (int)(rows < device_sm_count() * 8 ? rows : device_sm_count() * 8);
+  CLT_CHECK_CUDA(cudaMemsetAsync(hist, 0, sizeof(u64) * kBins * groups, s));
+  const long long rows_per_group = (long long)L * B / groups;
+  const long long want = (long long)device_sm_count() * 8 / groups + 1;
+  dim3 grid((unsigned)(rows_per_group < want ? rows_per_group : want), groups);
   if (bf16)
     bt_hist_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)z, b_enc, (const u64*)state, (u64*)hist,
-                                                       level, rows, B, F);
+                                                       level, rows_per_group, B, F);
   else
-    bt_hist_kernel<float><<<grid, 256, 0, s>>>((const float*)z, b_enc, (const u64*)state, (u64*)hist, level, rows, B, F);
+    bt_hist_kernel<float><<<grid, 256, 0, s>>>((const float*)z, b_enc, (const u64*)state, (u64*)hist, level,
+                                               rows_per_group, B, F);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
 
-int clt_batchtopk_pick(const uint64_t* hist, const uint64_t* hist_local, uint64_t* state, int level, int64_t n_keep,
-                       clt_stream_t stream) {
-  CLT_CHECK_ARG(hist && state && level >= 0 && level <= 2 && n_keep > 0, "batchtopk_pick: bad arguments");
-  bt_pick_kernel<<<1, 256, 0, (cudaStream_t)stream>>>((const u64*)hist, (const u64*)hist_local, (u64*)state, level,
-                                                      (u64)n_keep);
+int clt_batchtopk_pick(const uint64_t* hist, const uint64_t* hist_local, uint64_t* state, int level, int groups,
+                       int64_t n_keep, clt_stream_t stream) {
+  CLT_CHECK_ARG(hist && state && level >= 0 && level <= 2 && n_keep > 0 && groups > 0, "batchtopk_pick: bad arguments");
+  bt_pick_kernel<<<groups, 256, 0, (cudaStream_t)stream>>>((const u64*)hist, (const u64*)hist_local, (u64*)state, level,
+                                                           (u64)n_keep);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
 
 int clt_batchtopk_collect(const void* z, const float* b_enc, uint64_t* state, const int64_t* tie_quota, int* idx,
                           float* val, int* etok, int* row_start, int* row_cnt, int* layer_fill, uint32_t* fired_bits,
-                          int B, int L, int F, int64_t npl, int bf16, int* status, clt_stream_t stream) {
+                          int groups, int B, int L, int F, int64_t npl, int bf16, int* status, clt_stream_t stream) {
   CLT_CHECK_ARG(B > 0 && L > 0 && F > 0 && npl > 0 && npl < (1ll << 31), "batchtopk_collect: bad dims");
+  CLT_CHECK_ARG(groups == 1 || groups == L, "batchtopk_collect: groups must be 1 or L");
   CLT_CHECK_ARG(z && b_enc && state && idx && val && etok && row_start && row_cnt && layer_fill,
                 "batchtopk_collect: null pointer");
   cudaStream_t s = (cudaStream_t)stream;
@@ -266,18 +286,19 @@ int clt_batchtopk_collect(const void* z, const float* b_enc, uint64_t* state, co
   if (bf16)
     bt_collect_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, s>>>(
         (const __nv_bfloat16*)z, b_enc, (u64*)state, (const long long*)tie_quota, idx, val, etok, row_start, row_cnt,
-        layer_fill, fired_bits, B, F, npl, status);
+        layer_fill, fired_bits, B, F, npl, groups, status);
   else
     bt_collect_kernel<float><<<(unsigned)rows, 256, 0, s>>>((const float*)z, b_enc, (u64*)state,
                                                             (const long long*)tie_quota, idx, val, etok, row_start,
-                                                            row_cnt, layer_fill, fired_bits, B, F, npl, status);
+                                                            row_cnt, layer_fill, fired_bits, B, F, npl, groups, status);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
 
-int clt_batchtopk_threshold_update(const uint64_t* state, float* threshold, float e, clt_stream_t stream) {
-  CLT_CHECK_ARG(state && threshold, "batchtopk_threshold_update: null pointer");
-  bt_threshold_update_kernel<<<1, 1, 0, (cudaStream_t)stream>>>((const u64*)state, threshold, e);
+int clt_batchtopk_threshold_update(const uint64_t* state, float* threshold, float e, int groups, clt_stream_t stream) {
+  CLT_CHECK_ARG(state && threshold && groups > 0, "batchtopk_threshold_update: bad arguments");
+  bt_threshold_update_kernel<<<(groups + 63) / 64, 64, 0, (cudaStream_t)stream>>>((const u64*)state, threshold, e,
+                                                                                 groups);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

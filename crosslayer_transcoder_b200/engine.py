@@ -237,7 +237,7 @@ class StepEngine:
             ctx = self._forward_dense(batch, hyper, bf16)
         elif kind == "topk":
             ctx = self._forward_topk(batch, hyper, bf16)
-        elif kind == "batchtopk":
+        elif kind in ("batchtopk", "perlayer_batchtopk"):
             ctx = self._forward_batchtopk(batch, hyper, bf16)
         else:
             raise NotImplementedError(f"nonlinearity kind {kind!r}")
@@ -517,7 +517,10 @@ class StepEngine:
         W_op, _, _ = self._dec_flat(bf16)
         self._call("clt_prep_input", batch, in_code, mu_i, sd_i, xn, int(bf16), B, L, D, s)
         self._call("clt_encoder_fwd_store", xn, self._operand(enc.W, bf16), z, B, L, D, F, int(bf16), self.status, s)
-        n_keep = k * B * L                              # the whole batch, all layers and all feature shards
+        # BatchTopK: one selection over the whole batch (all layers, all feature shards);
+        # PerLayerBatchTopK: one per layer
+        groups = L if h["kind"] == "perlayer_batchtopk" else 1
+        n_keep = k * B * L // groups
         npl = max(1, min(n_keep, B * F))                # entry slots per layer (worst case: all in one layer)
         idx = ws.get("bt_idx", (L, npl), torch.int32, dev)
         val = ws.get("bt_val", (L, npl), torch.float32, dev)
@@ -525,30 +528,30 @@ class StepEngine:
         row_start = ws.get("bt_row_start", (L, B), torch.int32, dev)
         row_cnt = ws.get("bt_row_cnt", (L, B), torch.int32, dev)
         if n_keep > 0:
-            state = ws.get("bt_state", (8,), torch.int64, dev, zero=True)
-            hist_l = ws.get("bt_hist_local", (2048,), torch.int64, dev)
-            hist = ws.get("bt_hist", (2048,), torch.int64, dev) if world > 1 else hist_l
+            state = ws.get("bt_state", (groups, 8), torch.int64, dev, zero=True)
+            hist_l = ws.get("bt_hist_local", (groups, 2048), torch.int64, dev)
+            hist = ws.get("bt_hist", (groups, 2048), torch.int64, dev) if world > 1 else hist_l
             for level in range(3):
-                self._call("clt_batchtopk_hist", z, enc.b.data, state, hist_l, level, B, L, F, int(bf16), s)
+                self._call("clt_batchtopk_hist", z, enc.b.data, state, hist_l, level, groups, B, L, F, int(bf16), s)
                 if world > 1:
                     from .parallel import all_reduce_sum
 
                     hist.copy_(hist_l)
                     all_reduce_sum(hist, group)
-                self._call("clt_batchtopk_pick", hist, hist_l if world > 1 else None, state, level, n_keep, s)
+                self._call("clt_batchtopk_pick", hist, hist_l if world > 1 else None, state, level, groups, n_keep, s)
             quota = None
             if world > 1:
                 # elements equal to the threshold are kept in rank order until the global count is reached
                 from .parallel import all_gather
 
-                ties = torch.empty(world, 1, dtype=torch.int64, device=dev)
-                all_gather(ties, state[5:6], group)
-                before = ties[:rank].sum()
-                quota = (state[3] - before).clamp(min=0).minimum(state[5]).reshape(1).contiguous()
+                ties = torch.empty(world, groups, dtype=torch.int64, device=dev)
+                all_gather(ties, state[:, 5].contiguous(), group)
+                before = ties[:rank].sum(dim=0)
+                quota = (state[:, 3] - before).clamp(min=0).minimum(state[:, 5]).contiguous()
             fill = ws.get("bt_fill", (L,), torch.int32, dev)
             self._call("clt_batchtopk_collect", z, enc.b.data, state, quota, idx, val, etok, row_start, row_cnt, fill,
-                       self.fired, B, L, F, npl, int(bf16), self.status, s)
-            self._call("clt_batchtopk_threshold_update", state, nl.threshold, float(nl.e), s)
+                       self.fired, groups, B, L, F, npl, int(bf16), self.status, s)
+            self._call("clt_batchtopk_threshold_update", state, nl.threshold, float(nl.e), groups, s)
         else:
             val.zero_()
             row_start.zero_()

@@ -123,6 +123,23 @@ def batch_topk(pre: Tensor, k: int, threshold: Tensor, e: float) -> Tuple[Tensor
     return out.reshape(B, L, F), new_thr
 
 
+def per_layer_batch_topk(pre: Tensor, k: int, threshold: Tensor, e: float) -> Tuple[Tensor, Tensor]:
+    """Per layer, the k*B largest of that layer's [B*F] values, relu, scatter; one running threshold
+    per layer (topk.py:109-133).  Returns (features, new_threshold [L])."""
+    B, L, F = pre.shape
+    assert k <= F
+    n = k * B
+    flat = pre.permute(1, 0, 2).reshape(L, B * F)
+    out = torch.zeros_like(flat)
+    if n == 0:
+        return out.reshape(L, B, F).permute(1, 0, 2).contiguous(), threshold
+    vals, idx = torch.topk(flat, n, dim=-1, sorted=False)
+    vals = torch.relu(vals)
+    out.scatter_(dim=-1, index=idx, src=vals)
+    new_thr = (1 - e) * threshold + e * vals.detach().min(dim=-1).values
+    return out.reshape(L, B, F).permute(1, 0, 2).contiguous(), new_thr
+
+
 # --------------------------------------------------------------------------- #
 # parameters / hyper-parameters containers
 # --------------------------------------------------------------------------- #
@@ -163,7 +180,7 @@ class Params:
 
 @dataclass
 class Hyper:
-    kind: str = "jumprelu"          # jumprelu | relu | topk | batchtopk
+    kind: str = "jumprelu"          # jumprelu | relu | topk | batchtopk | perlayer_batchtopk
     bf16: bool = False
     # JumpReLU module (clt_lightning.py:396-409)
     bandwidth: float = 1.0
@@ -278,6 +295,8 @@ def training_step(P: Params, batch: Tensor, stats, H: Hyper,
             feat = per_layer_topk(pre, H.k)
         elif H.kind == "batchtopk":
             feat, out.threshold = batch_topk(pre, H.k, threshold, H.e)
+        elif H.kind == "perlayer_batchtopk":
+            feat, out.threshold = per_layer_batch_topk(pre, H.k, threshold, H.e)
         else:
             raise ValueError(H.kind)
         recons_norm = decoder_fwd(feat, P, H.bf16)

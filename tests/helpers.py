@@ -83,6 +83,8 @@ def build_module(spec, weights, device, last_active=None, precision=None):
         nl = M.ReLU()
     elif spec.kind == "topk":
         nl = M.PerLayerTopK(k=spec.k)
+    elif spec.kind == "perlayer_batchtopk":
+        nl = M.PerLayerBatchTopK(k=spec.k, e=spec.e, n_layers=L)
     else:
         nl = M.BatchTopK(k=spec.k, e=spec.e)
     model = M.CrossLayerTranscoder(nl, enc, dec, M.DimensionwiseInputStandardizer(L, D),
@@ -149,4 +151,6 @@ def oracle_for_spec(spec, batch, w, la):
         kw["last_active"] = la
     if spec.kind == "batchtopk":
         kw["threshold"] = torch.zeros(1)
+    if spec.kind == "perlayer_batchtopk":
+        kw["threshold"] = torch.zeros(spec.n_layers)
     return P, H, stats, kw

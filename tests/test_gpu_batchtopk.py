@@ -120,3 +120,30 @@ def test_batchtopk_edge_cases():
     assert float(mod.model.nonlinearity.threshold) == 0.0
     for a, b in zip(module_grad_list(mod), ref_grads):
         assert rel_err(a.cpu(), b) < 1e-4
+
+
+@pytest.mark.parametrize("prec", ["fp32", "bf16"])
+def test_oracle_perlayer_batchtopk_step(prec):
+    """PerLayerBatchTopK (reference topk.py:99-133): the same selection, one threshold per layer."""
+    L, B, F, k = 4, 150, 1024, 3
+    spec = synthetic.WorkloadSpec("plbtk", L, 128, F, B, "perlayer_batchtopk", True, prec == "bf16", rank_u=16,
+                                  n_outlier=2, k=k, e=0.05, lr=1e-3)
+    batch, w, la = spec_inputs(spec)
+    P, H, stats, kw = oracle_for_spec(spec, batch, w, la)
+    ref, ref_grads = O.step_with_grads(P, batch, stats, H, **kw)
+    dev = torch.device("cuda:0")
+    mod = build_module(spec, w, dev)
+    loss = run_step(mod, batch.to(dev), idx=0)
+    tol = TOL[prec]
+    feat = dense_from_lists(mod, B)
+    if prec == "fp32":
+        assert torch.equal(feat > 0, ref.feat > 0)
+        for l in range(L):
+            assert int((feat[:, l] != 0).sum()) == k * B            # k B survivors in every layer
+    else:
+        ref_sel, _ = O.per_layer_batch_topk(engine_pre(mod), k, torch.zeros(L), spec.e)
+        assert torch.equal(feat > 0, ref_sel > 0)
+    assert rel_err(mod.model.nonlinearity.threshold.cpu(), ref.threshold) < tol
+    assert rel_err(loss.cpu(), ref.loss) < tol
+    for a, b in zip(module_grad_list(mod), ref_grads):
+        assert rel_err(a.cpu(), b) < tol

@@ -22,6 +22,9 @@ def test_selections_match(ref):
     r = ref.topk.BatchTopK(k=4, e=0.2)
     out, thr = O.batch_topk(x, 4, torch.zeros(1), 0.2)
     assert torch.equal(out, r(x)) and torch.allclose(thr, r.threshold)
+    r = ref.topk.PerLayerBatchTopK(k=4, e=0.2, n_layers=3)
+    out, thr = O.per_layer_batch_topk(x, 4, torch.zeros(3), 0.2)
+    assert torch.equal(out, r(x)) and torch.allclose(thr, r.threshold)
 
 
 def test_jumprelu_forward_backward_match(ref):
