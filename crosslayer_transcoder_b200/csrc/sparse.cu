@@ -396,6 +396,148 @@ sparse_bwd_dec_kernel(const int* __restrict__ col_ptr, const int* __restrict__ e
   }
 }
 
+// Same computation with one warp per GROUP of 8 consecutive features of a block (needs F % 8 == 0).
+// The features' entries are contiguous in the feature-major list, so the group needs one read of 9
+// column pointers and coalesced reads of the entries' slots / values / tokens (32 at a time); the
+// decoder row of the next non-empty feature is fetched while the current one is processed; rows of
+// features nobody selected are zero-filled without touching W.  This removes most of the dependent
+// round trips (pointer -> entry -> token -> row) that bound the one-row-per-warp kernel above.
+template <class T, int VPL>
+__global__ void __launch_bounds__(128)
+sparse_bwd_dec_group_kernel(const int* __restrict__ col_ptr, const int* __restrict__ ent,
+                            const float* __restrict__ val, const int* __restrict__ etok, long long npl_,
+                            const T* __restrict__ W, const T* __restrict__ drecon, float* __restrict__ dW,
+                            float* __restrict__ dval, int B, int L, int D, int F, int k, int crosslayer,
+                            long long n_groups) {
+  const long long gid = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gid >= n_groups) return;
+  const int gpf = F / 8;
+  const int p = (int)(gid / gpf), f0 = (int)(gid % gpf) * 8;
+  int s = p, t = p;
+  if (crosslayer) pair_split(p, t, s);
+  const int nvec = D / 8;
+  const size_t npl = (size_t)npl_;
+  using V = Vec8<T>;
+  const int cpv = lane < 9 ? __ldg(col_ptr + (size_t)s * (F + 1) + f0 + lane) : 0;
+  const int cpn = __shfl_down_sync(0xffffffffu, cpv, 1);
+  unsigned mask = __ballot_sync(0xffffffffu, lane < 8 && cpn > cpv) & 0xffu;   // features with entries
+  const size_t row0 = ((size_t)p * F + f0) * D;
+  // rows of features without entries are zero
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    if (!((mask >> j) & 1u)) {
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int c = lane + 32 * i;
+        if (c < nvec) {
+          float4* o = reinterpret_cast<float4*>(dW + row0 + (size_t)j * D + 8 * c);
+          __stcs(o, make_float4(0.f, 0.f, 0.f, 0.f));
+          __stcs(o + 1, make_float4(0.f, 0.f, 0.f, 0.f));
+        }
+      }
+    }
+  }
+  if (mask == 0u) return;
+  // entry metadata, 32 entries at a time
+  int base = __shfl_sync(0xffffffffu, cpv, 0);
+  const int e_end = __shfl_sync(0xffffffffu, cpv, 8);
+  int my_slot = 0, my_tok = 0;
+  float my_val = 0.f;
+  auto load_chunk = [&](int b0) {
+    my_slot = 0, my_tok = 0, my_val = 0.f;
+    if (b0 + lane < e_end) {
+      my_slot = __ldg(ent + (size_t)s * npl + b0 + lane);
+      my_val = __ldg(val + (size_t)s * npl + my_slot);
+      my_tok = etok != nullptr ? __ldg(etok + (size_t)s * npl + my_slot) : my_slot / k;
+    }
+  };
+  load_chunk(base);
+  int fi = __ffs(mask) - 1;
+  typename V::Raw w_cur[VPL], w_next[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = lane + 32 * i;
+    w_cur[i] = c < nvec ? V::load_raw(W + row0 + (size_t)fi * D + 8 * c) : V::zero();
+    w_next[i] = V::zero();
+  }
+  for (;;) {
+    const unsigned rest = mask >> (fi + 1);
+    const bool has_next = rest != 0u;
+    const int fn = fi + __ffs(rest);   // index of the next feature with entries (valid when has_next)
+    if (has_next) {
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int c = lane + 32 * i;
+        if (c < nvec) w_next[i] = V::load_raw(W + row0 + (size_t)fn * D + 8 * c);
+      }
+    }
+    float g[VPL][8];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i)
+#pragma unroll
+      for (int q = 0; q < 8; ++q) g[i][q] = 0.f;
+    const int eb = __shfl_sync(0xffffffffu, cpv, fi), ee = __shfl_sync(0xffffffffu, cpv, fi + 1);
+    for (int e = eb; e < ee; e += 2) {
+      const bool two = e + 1 < ee;
+      if (e + 1 - base >= 32) {   // both entries of the pair must lie inside the loaded chunk
+        base = e;
+        load_chunk(base);
+      }
+      const int j0 = e - base, j1 = two ? j0 + 1 : j0;
+      const int slot0 = __shfl_sync(0xffffffffu, my_slot, j0), slot1 = __shfl_sync(0xffffffffu, my_slot, j1);
+      const float v0 = __shfl_sync(0xffffffffu, my_val, j0);
+      const float v1 = two ? __shfl_sync(0xffffffffu, my_val, j1) : 0.f;
+      const T* dr0 = drecon + ((size_t)t * B + __shfl_sync(0xffffffffu, my_tok, j0)) * D;
+      const T* dr1 = drecon + ((size_t)t * B + __shfl_sync(0xffffffffu, my_tok, j1)) * D;
+      typename V::Raw x0[VPL], x1[VPL];
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int c = lane + 32 * i;
+        x0[i] = c < nvec ? V::load_raw(dr0 + 8 * c) : V::zero();
+        x1[i] = (two && c < nvec) ? V::load_raw(dr1 + 8 * c) : V::zero();
+      }
+      float dot0 = 0.f, dot1 = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        float wf[8], xf[8];
+        V::unpack(w_cur[i], wf);
+        V::unpack(x0[i], xf);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          dot0 = fmaf(wf[q], xf[q], dot0);
+          g[i][q] = fmaf(v0, xf[q], g[i][q]);
+        }
+        V::unpack(x1[i], xf);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          dot1 = fmaf(wf[q], xf[q], dot1);
+          g[i][q] = fmaf(v1, xf[q], g[i][q]);
+        }
+      }
+      dot0 = warp_sum(dot0);
+      dot1 = warp_sum(dot1);
+      if (lane == 0) {
+        atomicAdd(dval + (size_t)s * npl + slot0, dot0);
+        if (two) atomicAdd(dval + (size_t)s * npl + slot1, dot1);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nvec) {
+        float4* o = reinterpret_cast<float4*>(dW + row0 + (size_t)fi * D + 8 * c);
+        __stcs(o, make_float4(g[i][0], g[i][1], g[i][2], g[i][3]));
+        __stcs(o + 1, make_float4(g[i][4], g[i][5], g[i][6], g[i][7]));
+      }
+    }
+    if (!has_next) break;
+    fi = fn;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) w_cur[i] = w_next[i];
+  }
+}
+
 // =========================================================================================
 // Encoder backward, feature-major.  One CTA per (layer l, 8 features, 768 input dims):
 //   dW_enc[l, d, f] = sum over tokens b that selected f of dval[l,b,j] * xn[l,b,d]
@@ -556,10 +698,19 @@ int launch_bwd_dec(const int* col_ptr, const int* ent, const float* val, const i
   const long long blocks = (rows + 3) / 4;
   CLT_CHECK_ARG(blocks < (1ll << 31), "sparse decoder backward: too many rows");
   const unsigned grid = (unsigned)blocks;
+  const bool grouped = F % 8 == 0 && vpl <= 4;          // one warp per 8 features (see the kernel's comment)
+  const long long n_groups = rows / 8;
+  const unsigned ggrid = (unsigned)((n_groups + 3) / 4);
 #define CLT_BWD_DEC(V)                                                                                            \
   case V:                                                                                                         \
-    sparse_bwd_dec_kernel<T, V><<<grid, 128, 0, s>>>(col_ptr, ent, val, etok, npl, (const T*)W, (const T*)drecon, \
-                                                     dW, dval, B, L, D, F, k, crosslayer, rows);                  \
+    if (grouped && V <= 4)                                                                                        \
+      sparse_bwd_dec_group_kernel<T, (V <= 4 ? V : 1)><<<ggrid, 128, 0, s>>>(                                     \
+          col_ptr, ent, val, etok, npl, (const T*)W, (const T*)drecon, dW, dval, B, L, D, F, k, crosslayer,       \
+          n_groups);                                                                                              \
+    else                                                                                                          \
+      sparse_bwd_dec_kernel<T, V><<<grid, 128, 0, s>>>(col_ptr, ent, val, etok, npl, (const T*)W,                 \
+                                                       (const T*)drecon, dW, dval, B, L, D, F, k, crosslayer,     \
+                                                       rows);                                                     \
     break;
   switch (vpl) {
     CLT_BWD_DEC(1) CLT_BWD_DEC(2) CLT_BWD_DEC(3) CLT_BWD_DEC(4) CLT_BWD_DEC(6) CLT_BWD_DEC(8) CLT_BWD_DEC(9)

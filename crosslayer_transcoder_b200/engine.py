@@ -430,9 +430,6 @@ class StepEngine:
             dead_list = ws.get("dead_list", (L, F), torch.int32, dev)
             n_dead = ws.get("n_dead", (L,), torch.int32, dev)
             self._call("clt_dead_compact", dead, dead_list, n_dead, L, F, s)
-            nd = int(n_dead.max())                      # host read: sizes the compacted contractions
-            nd_pad = max(64, _round_up(nd, 64))
-            a_aux = ws.get("a_aux", (L, B, nd_pad), T, dev)
             exchange = False
             if world > 1:
                 # a row whose positive dead values, summed over the shards, do not exceed k_aux keeps all
@@ -442,7 +439,12 @@ class StepEngine:
                 cnt = ws.get("aux_cnt", (L, B), torch.int32, dev)
                 self._call("clt_aux_count", z, enc.b.data, dead_list, n_dead, cnt, B, L, F, int(bf16), s)
                 all_reduce_sum(cnt, group)
-                exchange = int(cnt.max()) > k_aux           # host read (same value on every rank)
+                both = torch.stack([n_dead.max(), cnt.max()]).tolist()   # ONE host read for both sizes
+                nd, exchange = int(both[0]), int(both[1]) > k_aux          # (same values on every rank for cnt)
+            else:
+                nd = int(n_dead.max())                  # host read: sizes the compacted contractions
+            nd_pad = max(64, _round_up(nd, 64))
+            a_aux = ws.get("a_aux", (L, B, nd_pad), T, dev)
             if exchange:
                 # offer this shard's k_aux best dead values per row; the gather runs while the main
                 # decoder works
