@@ -21,6 +21,12 @@
 //   [2] threshold key T (valid after level 2; 0 = keep every positive)
 //   [3] ties: number of elements equal to T that are kept (all ranks together)
 //   [4] ties_taken (atomic counter of the collecting pass)   [5] local count of elements equal to T
+//   [6] 0 = threshold found, 1 = fewer positives than wanted (keep all), 2 = the guessed floor was too high (retry)
+//   [7] guessed floor for the next step's first level: half of this step's threshold (as a key).
+//       The first level then histograms only the elements above the floor, which turns it into a pure
+//       streaming pass (hardly any shared-memory atomics); if fewer than n_keep elements lie above it,
+//       the pick kernel asks for a retry without the floor, which the host has already enqueued
+//       (the retry kernels return immediately when no retry is pending).
 #include "../../include/clt_b200.h"
 #include "common.cuh"
 #include "kernels.h"
@@ -42,6 +48,26 @@ __device__ __forceinline__ float ld_f<__nv_bfloat16>(const __nv_bfloat16* p, siz
 
 __device__ __forceinline__ unsigned pos_key(float v) { return v > 0.f ? __float_as_uint(v) : 0u; }
 
+// 8 consecutive pre-activations (z + b) starting at a multiple of 8
+template <class T>
+__device__ __forceinline__ void pre8(const T* z, const float* b, int i, float (&o)[8]);
+template <>
+__device__ __forceinline__ void pre8<__nv_bfloat16>(const __nv_bfloat16* z, const float* b, int i, float (&o)[8]) {
+  const uint4 t = __ldg(reinterpret_cast<const uint4*>(z + i));
+  const float4 b0 = __ldg(reinterpret_cast<const float4*>(b + i)), b1 = __ldg(reinterpret_cast<const float4*>(b + i) + 1);
+  o[0] = __uint_as_float(t.x << 16) + b0.x, o[1] = __uint_as_float(t.x & 0xffff0000u) + b0.y;
+  o[2] = __uint_as_float(t.y << 16) + b0.z, o[3] = __uint_as_float(t.y & 0xffff0000u) + b0.w;
+  o[4] = __uint_as_float(t.z << 16) + b1.x, o[5] = __uint_as_float(t.z & 0xffff0000u) + b1.y;
+  o[6] = __uint_as_float(t.w << 16) + b1.z, o[7] = __uint_as_float(t.w & 0xffff0000u) + b1.w;
+}
+template <>
+__device__ __forceinline__ void pre8<float>(const float* z, const float* b, int i, float (&o)[8]) {
+  const float4 z0 = __ldg(reinterpret_cast<const float4*>(z + i)), z1 = __ldg(reinterpret_cast<const float4*>(z + i) + 1);
+  const float4 b0 = __ldg(reinterpret_cast<const float4*>(b + i)), b1 = __ldg(reinterpret_cast<const float4*>(b + i) + 1);
+  o[0] = z0.x + b0.x, o[1] = z0.y + b0.y, o[2] = z0.z + b0.z, o[3] = z0.w + b0.w;
+  o[4] = z1.x + b1.x, o[5] = z1.y + b1.y, o[6] = z1.z + b1.z, o[7] = z1.w + b1.w;
+}
+
 __device__ __forceinline__ bool digit_of(unsigned key, int level, unsigned prefix, unsigned& d) {
   if (level == 0) {
     d = key >> 20;
@@ -59,23 +85,40 @@ __device__ __forceinline__ bool digit_of(unsigned key, int level, unsigned prefi
 template <class T>
 __global__ void __launch_bounds__(256)
 bt_hist_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, const u64* __restrict__ state_all,
-               u64* __restrict__ hist_all, int level, long long rows_per_group, int B, int F) {
+               u64* __restrict__ hist_all, int level, int retry, long long rows_per_group, int B, int F) {
   __shared__ unsigned sh[kBins];
-  for (int i = threadIdx.x; i < kBins; i += blockDim.x) sh[i] = 0u;
-  __syncthreads();
   const int grp = blockIdx.y;
   const u64* state = state_all + 8 * grp;
+  // nothing to do: a retry that is not pending, or finer levels after "keep all"
+  if (retry ? state[6] != 2 : (level > 0 && state[6] == 1)) return;
+  for (int i = threadIdx.x; i < kBins; i += blockDim.x) sh[i] = 0u;
+  __syncthreads();
   u64* hist = hist_all + (size_t)kBins * grp;
   const unsigned prefix = (unsigned)state[0];
+  const unsigned floor_key = (level == 0 && !retry) ? (unsigned)state[7] : 0u;
   const long long row_lo = grp * rows_per_group, rows = row_lo + rows_per_group;
+  const bool vec = F % 8 == 0;
   for (long long row = row_lo + blockIdx.x; row < rows; row += gridDim.x) {
     const int l = (int)(row / B);
     const T* zr = z + (size_t)row * F;
     const float* br = b_enc + (size_t)l * F;
-    for (int f = threadIdx.x; f < F; f += blockDim.x) {
-      const unsigned key = pos_key(ld_f<T>(zr, f) + __ldg(br + f));
-      unsigned d;
-      if (key != 0u && digit_of(key, level, prefix, d)) atomicAdd(&sh[d], 1u);
+    if (vec) {
+      for (int f = 8 * threadIdx.x; f < F; f += 8 * blockDim.x) {
+        float v[8];
+        pre8<T>(zr, br, f, v);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const unsigned key = pos_key(v[q]);
+          unsigned d;
+          if (key != 0u && key >= floor_key && digit_of(key, level, prefix, d)) atomicAdd(&sh[d], 1u);
+        }
+      }
+    } else {
+      for (int f = threadIdx.x; f < F; f += blockDim.x) {
+        const unsigned key = pos_key(ld_f<T>(zr, f) + __ldg(br + f));
+        unsigned d;
+        if (key != 0u && key >= floor_key && digit_of(key, level, prefix, d)) atomicAdd(&sh[d], 1u);
+      }
     }
   }
   __syncthreads();
@@ -85,7 +128,8 @@ bt_hist_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, const u
 
 // Pick the bucket of the current level from the (summed) histogram; one CTA of 256 threads.
 __global__ void bt_pick_kernel(const u64* __restrict__ hist_all, const u64* __restrict__ hist_local_all,
-                               u64* __restrict__ state_all, int level, u64 n_keep) {
+                               u64* __restrict__ state_all, int level, int retry, u64 n_keep) {
+  if (retry ? state_all[8 * blockIdx.x + 6] != 2 : (level > 0 && state_all[8 * blockIdx.x + 6] == 1)) return;
   const u64* hist = hist_all + (size_t)kBins * blockIdx.x;
   const u64* hist_local = hist_local_all != nullptr ? hist_local_all + (size_t)kBins * blockIdx.x : nullptr;
   u64* state = state_all + 8 * blockIdx.x;
@@ -107,13 +151,16 @@ __global__ void bt_pick_kernel(const u64* __restrict__ hist_all, const u64* __re
   __syncthreads();
   u64 above = 0;
   for (int j = t + 1; j < 256; ++j) above += tot[j];
-  if (level == 0 && t == 0 && above + s < want) sh_none = 1;  // fewer positives than n_keep: keep them all
+  if (level == 0 && t == 0 && above + s < want) sh_none = 1;  // fewer elements than n_keep above the floor
   __syncthreads();
   if (sh_none) {
-    if (t == 0) state[0] = 0, state[1] = 0, state[2] = 0, state[3] = 0, state[4] = 0, state[5] = 0, state[6] = 1;
+    if (t == 0) {
+      const bool floored = !retry && state[7] != 0;
+      state[0] = 0, state[1] = 0, state[2] = 0, state[3] = 0, state[4] = 0, state[5] = 0;
+      state[6] = floored ? 2 : 1;   // retry without the floor, or (no floor) fewer positives than wanted: keep all
+    }
     return;
   }
-  if (level > 0 && state[6] != 0) return;  // "keep all" was decided at level 0
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const u64 gt = above + (i < 7 ? local[i + 1] : 0);
@@ -165,24 +212,32 @@ bt_collect_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, u64*
   __shared__ int n_row, base, cursor;
   if (threadIdx.x == 0) n_row = 0, cursor = 0;
   __syncthreads();
-  // sweep 1: elements above the threshold; ties claim their quota here (and remember it in a flag bit)
-  int mine = 0;
-  for (int f = threadIdx.x; f < F; f += blockDim.x) {
-    const unsigned key = pos_key(ld_f<T>(zr, f) + __ldg(br + f));
-    if (key > Tk) ++mine;
-  }
-  if (mine) atomicAdd(&n_row, mine);
-  __syncthreads();
-  // ties are rare: claim them one by one in a second look at the row, by a single warp-uniform pass
+  // sweep 1: count the row's elements above the threshold and those equal to it
+  const bool vec = F % 8 == 0;
   __shared__ int n_tie;
   if (threadIdx.x == 0) n_tie = 0;
   __syncthreads();
-  if (Tk != 0u && quota > 0) {
+  int mine = 0, mine_tie = 0;
+  if (vec) {
+    for (int f = 8 * threadIdx.x; f < F; f += 8 * blockDim.x) {
+      float v[8];
+      pre8<T>(zr, br, f, v);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const unsigned key = pos_key(v[q]);
+        mine += key > Tk ? 1 : 0;
+        mine_tie += (key != 0u && key == Tk) ? 1 : 0;
+      }
+    }
+  } else {
     for (int f = threadIdx.x; f < F; f += blockDim.x) {
       const unsigned key = pos_key(ld_f<T>(zr, f) + __ldg(br + f));
-      if (key == Tk) atomicAdd(&n_tie, 1);
+      mine += key > Tk ? 1 : 0;
+      mine_tie += (key != 0u && key == Tk) ? 1 : 0;
     }
   }
+  if (mine) atomicAdd(&n_row, mine);
+  if (mine_tie && Tk != 0u && quota > 0) atomicAdd(&n_tie, mine_tie);
   __syncthreads();
   __shared__ int tie_take;
   if (threadIdx.x == 0) {
@@ -211,8 +266,7 @@ bt_collect_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, u64*
   if (base < 0 || n_row + tie_take == 0) return;
   // sweep 2: write
   const size_t o = (size_t)l * npl + base;
-  for (int f = threadIdx.x; f < F; f += blockDim.x) {
-    const float v = ld_f<T>(zr, f) + __ldg(br + f);
+  auto emit = [&](int f, float v) {
     const unsigned key = pos_key(v);
     bool take = key > Tk;
     if (!take && key != 0u && key == Tk && tie_take > 0) take = atomicAdd(&n_tie, 1) < tie_take;
@@ -223,16 +277,27 @@ bt_collect_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, u64*
       etok[o + c] = b;
       if (fired_bits != nullptr) atomicOr(fired_bits + (size_t)l * words + f / 32, 1u << (f & 31));
     }
+  };
+  if (vec) {
+    for (int f = 8 * threadIdx.x; f < F; f += 8 * blockDim.x) {
+      float v[8];
+      pre8<T>(zr, br, f, v);
+#pragma unroll
+      for (int q = 0; q < 8; ++q) emit(f + q, v[q]);
+    }
+  } else {
+    for (int f = threadIdx.x; f < F; f += blockDim.x) emit(f, ld_f<T>(zr, f) + __ldg(br + f));
   }
 }
 
 // threshold <- (1 - e) threshold + e * (smallest kept value)   (topk.py:94-95)
-__global__ void bt_threshold_update_kernel(const u64* __restrict__ state, float* __restrict__ threshold, float e,
+__global__ void bt_threshold_update_kernel(u64* __restrict__ state, float* __restrict__ threshold, float e,
                                            int groups) {
   const int g = blockIdx.x * blockDim.x + threadIdx.x;
   if (g >= groups) return;
   const float tmin = __uint_as_float((unsigned)state[8 * g + 2]);  // the threshold value; 0 if nothing was cut
   threshold[g] = (1.f - e) * threshold[g] + e * tmin;
+  state[8 * g + 7] = (u64)pos_key(0.5f * tmin);                   // floor of the next step's first pass
 }
 
 }  // namespace
@@ -242,11 +307,12 @@ using namespace clt;
 
 extern "C" {
 
-int clt_batchtopk_hist(const void* z, const float* b_enc, const uint64_t* state, uint64_t* hist, int level, int groups,
-                       int B, int L, int F, int bf16, clt_stream_t stream) {
+int clt_batchtopk_hist(const void* z, const float* b_enc, const uint64_t* state, uint64_t* hist, int level, int retry,
+                       int groups, int B, int L, int F, int bf16, clt_stream_t stream) {
   CLT_CHECK_ARG(B > 0 && L > 0 && F > 0 && level >= 0 && level <= 2, "batchtopk_hist: bad arguments");
   CLT_CHECK_ARG(groups == 1 || groups == L, "batchtopk_hist: groups must be 1 (whole batch) or L (per layer)");
   CLT_CHECK_ARG(z && b_enc && state && hist, "batchtopk_hist: null pointer");
+  CLT_CHECK_ARG(!retry || level == 0, "batchtopk_hist: only the first level is retried");
   cudaStream_t s = (cudaStream_t)stream;
   CLT_CHECK_CUDA(cudaMemsetAsync(hist, 0, sizeof(u64) * kBins * groups, s));
   const long long rows_per_group = (long long)L * B / groups;
@@ -254,19 +320,19 @@ int clt_batchtopk_hist(const void* z, const float* b_enc, const uint64_t* state,
   dim3 grid((unsigned)(rows_per_group < want ? rows_per_group : want), groups);
   if (bf16)
     bt_hist_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)z, b_enc, (const u64*)state, (u64*)hist,
-                                                       level, rows_per_group, B, F);
+                                                       level, retry, rows_per_group, B, F);
   else
-    bt_hist_kernel<float><<<grid, 256, 0, s>>>((const float*)z, b_enc, (const u64*)state, (u64*)hist, level,
+    bt_hist_kernel<float><<<grid, 256, 0, s>>>((const float*)z, b_enc, (const u64*)state, (u64*)hist, level, retry,
                                                rows_per_group, B, F);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
 
-int clt_batchtopk_pick(const uint64_t* hist, const uint64_t* hist_local, uint64_t* state, int level, int groups,
-                       int64_t n_keep, clt_stream_t stream) {
+int clt_batchtopk_pick(const uint64_t* hist, const uint64_t* hist_local, uint64_t* state, int level, int retry,
+                       int groups, int64_t n_keep, clt_stream_t stream) {
   CLT_CHECK_ARG(hist && state && level >= 0 && level <= 2 && n_keep > 0 && groups > 0, "batchtopk_pick: bad arguments");
   bt_pick_kernel<<<groups, 256, 0, (cudaStream_t)stream>>>((const u64*)hist, (const u64*)hist_local, (u64*)state, level,
-                                                           (u64)n_keep);
+                                                           retry, (u64)n_keep);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -295,10 +361,9 @@ int clt_batchtopk_collect(const void* z, const float* b_enc, uint64_t* state, co
   return 0;
 }
 
-int clt_batchtopk_threshold_update(const uint64_t* state, float* threshold, float e, int groups, clt_stream_t stream) {
+int clt_batchtopk_threshold_update(uint64_t* state, float* threshold, float e, int groups, clt_stream_t stream) {
   CLT_CHECK_ARG(state && threshold && groups > 0, "batchtopk_threshold_update: bad arguments");
-  bt_threshold_update_kernel<<<(groups + 63) / 64, 64, 0, (cudaStream_t)stream>>>((const u64*)state, threshold, e,
-                                                                                 groups);
+  bt_threshold_update_kernel<<<(groups + 63) / 64, 64, 0, (cudaStream_t)stream>>>((u64*)state, threshold, e, groups);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -556,31 +556,62 @@ sparse_bwd_enc_kernel(const int* __restrict__ col_ptr, const int* __restrict__ e
   const int l = blockIdx.y, f0 = blockIdx.x * kEncFB, d0 = blockIdx.z * 768;
   const int* cp = col_ptr + (size_t)l * (F + 1);
   const size_t npl = (size_t)npl_;
+  // the block's entries (all 8 features' lists are contiguous): gradient and token, staged once
+  constexpr int kCap = 512;
+  __shared__ float s_g[kCap];
+  __shared__ int s_tok[kCap];
+  __shared__ int s_cp[kEncFB + 1];
+  if (threadIdx.x <= kEncFB) s_cp[threadIdx.x] = __ldg(cp + min(f0 + (int)threadIdx.x, F));
+  __syncthreads();
+  const int e_begin = s_cp[0], e_end = s_cp[kEncFB];
   float acc[3][kEncFB];
 #pragma unroll
   for (int i = 0; i < 3; ++i)
 #pragma unroll
     for (int q = 0; q < kEncFB; ++q) acc[i][q] = 0.f;
   float bsum = 0.f;
-#pragma unroll
-  for (int q = 0; q < kEncFB; ++q) {
-    const int f = f0 + q;
-    if (f >= F) break;
-    const int e0 = __ldg(cp + f), e1 = __ldg(cp + f + 1);
-    float bs = 0.f;
-    for (int e = e0; e < e1; ++e) {
+  const T* xl = xn + (size_t)l * B * D;
+  for (int c0 = e_begin; c0 < e_end; c0 += kCap) {
+    const int c1 = min(e_end, c0 + kCap);
+    __syncthreads();
+    for (int e = c0 + threadIdx.x; e < c1; e += 256) {
       const int slot = __ldg(ent + (size_t)l * npl + e);
-      const float g = __ldg(dval + (size_t)l * npl + slot);
-      const int tok = etok != nullptr ? __ldg(etok + (size_t)l * npl + slot) : slot / k;
-      const T* x = xn + ((size_t)l * B + tok) * D;
-      bs += g;
-#pragma unroll
-      for (int i = 0; i < 3; ++i) {
-        const int d = d0 + threadIdx.x + 256 * i;
-        if (d < D) acc[i][q] = fmaf(g, ToFloat<T>::get(x[d]), acc[i][q]);
-      }
+      s_g[e - c0] = __ldg(dval + (size_t)l * npl + slot);
+      s_tok[e - c0] = etok != nullptr ? __ldg(etok + (size_t)l * npl + slot) : slot / k;
     }
-    if ((int)threadIdx.x == q) bsum = bs;
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < kEncFB; ++q) {
+      const int eb = max(s_cp[q], c0), ee = min(s_cp[q + 1], c1);
+      float bs = 0.f;
+      int e = eb;
+      for (; e + 1 < ee; e += 2) {  // two rows of x in flight
+        const float g0 = s_g[e - c0], g1 = s_g[e + 1 - c0];
+        const T* x0 = xl + (size_t)s_tok[e - c0] * D;
+        const T* x1 = xl + (size_t)s_tok[e + 1 - c0] * D;
+        float a0[3], a1[3];
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+          const int d = d0 + threadIdx.x + 256 * i;
+          a0[i] = d < D ? ToFloat<T>::get(x0[d]) : 0.f;
+          a1[i] = d < D ? ToFloat<T>::get(x1[d]) : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 3; ++i) acc[i][q] = fmaf(g1, a1[i], fmaf(g0, a0[i], acc[i][q]));
+        bs += g0 + g1;
+      }
+      if (e < ee) {
+        const float g0 = s_g[e - c0];
+        const T* x0 = xl + (size_t)s_tok[e - c0] * D;
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+          const int d = d0 + threadIdx.x + 256 * i;
+          if (d < D) acc[i][q] = fmaf(g0, ToFloat<T>::get(x0[d]), acc[i][q]);
+        }
+        bs += g0;
+      }
+      if ((int)threadIdx.x == q) bsum += bs;
+    }
   }
   const bool vec = (F % 4 == 0) && (f0 + kEncFB <= F);
 #pragma unroll

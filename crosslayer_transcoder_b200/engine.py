@@ -533,14 +533,17 @@ class StepEngine:
             state = ws.get("bt_state", (groups, 8), torch.int64, dev, zero=True)
             hist_l = ws.get("bt_hist_local", (groups, 2048), torch.int64, dev)
             hist = ws.get("bt_hist", (groups, 2048), torch.int64, dev) if world > 1 else hist_l
-            for level in range(3):
-                self._call("clt_batchtopk_hist", z, enc.b.data, state, hist_l, level, groups, B, L, F, int(bf16), s)
+            # level 0, its retry without the guessed floor (returns at once unless requested), levels 1, 2
+            for level, retry in ((0, 0), (0, 1), (1, 0), (2, 0)):
+                self._call("clt_batchtopk_hist", z, enc.b.data, state, hist_l, level, retry, groups, B, L, F,
+                           int(bf16), s)
                 if world > 1:
                     from .parallel import all_reduce_sum
 
                     hist.copy_(hist_l)
                     all_reduce_sum(hist, group)
-                self._call("clt_batchtopk_pick", hist, hist_l if world > 1 else None, state, level, groups, n_keep, s)
+                self._call("clt_batchtopk_pick", hist, hist_l if world > 1 else None, state, level, retry, groups,
+                           n_keep, s)
             quota = None
             if world > 1:
                 # elements equal to the threshold are kept in rank order until the global count is reached

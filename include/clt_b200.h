@@ -240,12 +240,15 @@ int clt_scatter_cols(const float* src, const float* db_src, const int* dead_list
  * histogram of the elements inside the bucket chosen so far, feature shards sum their histograms,
  * clt_batchtopk_pick chooses the next bucket (n_keep = elements kept per group).
  * state: [groups, 8] 64-bit words of device memory, zero before the first step ([2] threshold key
- * after level 2, [3] kept elements equal to it, [5] this rank's count of them).  hist_local (may be
- * NULL) is this rank's own histogram when hist holds the sum over shards. */
+ * after level 2, [3] kept elements equal to it, [5] this rank's count of them, [7] half of the last
+ * threshold: the first level only looks at elements above it).  If that floor turns out too high
+ * the pick kernel requests a retry: always enqueue the level-0 pair a second time with retry = 1
+ * before levels 1 and 2; it returns at once when no retry is pending.  hist_local (may be NULL) is
+ * this rank's own histogram when hist holds the sum over shards. */
 int clt_batchtopk_hist(const void* z, const float* b_enc, const uint64_t* state, uint64_t* hist, int level,
-                       int groups, int B, int L, int F, int bf16, clt_stream_t stream);
-int clt_batchtopk_pick(const uint64_t* hist, const uint64_t* hist_local, uint64_t* state, int level, int groups,
-                       int64_t n_keep, clt_stream_t stream);
+                       int retry, int groups, int B, int L, int F, int bf16, clt_stream_t stream);
+int clt_batchtopk_pick(const uint64_t* hist, const uint64_t* hist_local, uint64_t* state, int level, int retry,
+                       int groups, int64_t n_keep, clt_stream_t stream);
 /* Collect the survivors into per-layer entry lists idx / val / etok [L, npl] with the segment of
  * token b at row_start[l,b] .. + row_cnt[l,b]; layer_fill [L] receives the list lengths.  tie_quota
  * (device int64 per group, may be NULL = all kept ties are this rank's) bounds the elements equal to
@@ -255,8 +258,7 @@ int clt_batchtopk_collect(const void* z, const float* b_enc, uint64_t* state, co
                           uint32_t* fired_bits, int groups, int B, int L, int F, int64_t npl, int bf16,
                           int* status, clt_stream_t stream);
 /* threshold[g] <- (1 - e) threshold[g] + e * smallest kept value of group g (topk.py:94-95, 131-132). */
-int clt_batchtopk_threshold_update(const uint64_t* state, float* threshold, float e, int groups,
-                                   clt_stream_t stream);
+int clt_batchtopk_threshold_update(uint64_t* state, float* threshold, float e, int groups, clt_stream_t stream);
 
 /* torch.optim.Adam / AdamW step (clt_lightning.py:339-352) over one flat fp32 buffer; `step`
  * counts from 1.  shadow_bf16 (may be NULL) receives the bf16 copy of the new parameters. */

@@ -93,10 +93,19 @@ def test_oracle_batchtopk_step(name, L, D, F, B, cross, k, prec):
     assert rel_err(loss.cpu(), ref.loss) < tol
     for a, b in zip(module_grad_list(mod), ref_grads):
         assert rel_err(a.cpu(), b) < tol
-    # a second step moves the threshold's running average on
+    # a second step moves the threshold's running average on; its first histogram pass starts from half of
+    # the previous threshold
     thr1 = float(mod.model.nonlinearity.threshold)
     run_step(mod, batch.to(dev), idx=1)
     assert float(mod.model.nonlinearity.threshold) > thr1
+    sel, _ = O.batch_topk(engine_pre(mod), k, torch.zeros(1), spec.e)
+    assert torch.equal(dense_from_lists(mod, B) > 0, sel > 0)
+    # a much quieter batch: the guessed floor is now too high and the selection must fall back to the full range
+    run_step(mod, (0.2 * batch).to(dev), idx=2)
+    sel, _ = O.batch_topk(engine_pre(mod), k, torch.zeros(1), spec.e)
+    got = dense_from_lists(mod, B)
+    assert int((got != 0).sum()) == k * B * L
+    assert torch.equal(got > 0, sel > 0)
 
 
 def test_batchtopk_edge_cases():
