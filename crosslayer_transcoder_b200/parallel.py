@@ -67,3 +67,54 @@ def upload_batch(batch_host: torch.Tensor, staging: torch.Tensor, group) -> torc
         mine[: hi - lo].copy_(batch_host[lo:hi], non_blocking=True)
     all_gather(staging.view(world, c, *staging.shape[1:]), mine, group)
     return staging[:B]
+
+
+# --------------------------------------------------------------------------------------------------
+# checkpoints of feature-sharded modules in the reference's (unsharded) layout
+# --------------------------------------------------------------------------------------------------
+def _feature_axis(key: str, ndim: int):
+    """Axis of the feature dimension for a state-dict key of the transcoder, or None if replicated.
+    encoder.W [L,D,F] -> 2, encoder.b [L,F] -> 1, decoder.W_t [(t+1),F,D] / decoder.W [L,F,D] -> 1,
+    nonlinearity.theta [1,L,F] -> 2, last_active [L,F] -> 1; decoder.b, standardizers, thresholds: replicated."""
+    leaf = key.split(".")[-1]
+    owner = key.split(".")[-2] if "." in key else ""
+    if owner == "encoder":
+        return {"W": 2, "b": 1}.get(leaf)
+    if owner == "decoder":
+        return 1 if leaf.startswith("W") else None
+    if leaf == "theta":
+        return 2
+    if leaf == "last_active":
+        return 1
+    return None
+
+
+def gather_state_dict(module: torch.nn.Module, group=None) -> dict:
+    """State dict of a feature-sharded module with every sharded tensor concatenated over the ranks, i.e.
+    the keys and shapes of the reference's unsharded module (what ``save_pretrained`` / ``load_state_dict``
+    of the reference expect).  Every rank gets the full dict."""
+    group = group if group is not None else dist.group.WORLD
+    world = dist.get_world_size(group)
+    out = {}
+    for key, t in module.state_dict().items():
+        ax = _feature_axis(key, t.dim())
+        if ax is None or world == 1:
+            out[key] = t.detach().clone()
+            continue
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t.detach().contiguous(), group=group)
+        out[key] = torch.cat(parts, dim=ax)
+    return out
+
+
+def shard_state_dict(full: dict, rank: int, world: int) -> dict:
+    """The slice of an unsharded (reference-layout) state dict that ``rank`` of ``world`` holds."""
+    out = {}
+    for key, t in full.items():
+        ax = _feature_axis(key, t.dim())
+        if ax is None or world == 1:
+            out[key] = t
+        else:
+            lo, hi = feature_shard(t.shape[ax], rank, world)
+            out[key] = t.narrow(ax, lo, hi - lo).contiguous()
+    return out

@@ -74,3 +74,47 @@ def test_feature_shard_bounds():
     assert parallel.feature_shard(32768, 3, 8) == (12288, 16384)
     with pytest.raises(ValueError):
         parallel.feature_shard(100, 0, 8)
+
+
+def _ckpt_worker(rank, world, port, q):
+    sys.path.insert(0, str(ROOT))
+    import crosslayer_transcoder_b200.model as M
+    from crosslayer_transcoder_b200 import parallel
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        L, D, F = 3, 8, 16
+        torch.manual_seed(7)
+        full = M.JumpReLUCrossLayerTranscoderModule(model=M.CrossLayerTranscoder(
+            M.JumpReLU(0.03, 1.0, L, F), M.Encoder(D, F, L), M.CrosslayerDecoder(D, F, L),
+            M.DimensionwiseInputStandardizer(L, D), M.DimensionwiseOutputStandardizer(L, D)))
+        full.last_active.copy_(torch.arange(L * F).reshape(L, F))
+        ref_sd = {k: v.clone() for k, v in full.state_dict().items()}
+        lo, hi = parallel.feature_shard(F, rank, world)
+        shard = M.JumpReLUCrossLayerTranscoderModule(model=M.CrossLayerTranscoder(
+            M.JumpReLU(0.03, 1.0, L, hi - lo), M.Encoder(D, hi - lo, L), M.CrosslayerDecoder(D, hi - lo, L),
+            M.DimensionwiseInputStandardizer(L, D), M.DimensionwiseOutputStandardizer(L, D)))
+        shard.load_state_dict(parallel.shard_state_dict(ref_sd, rank, world))      # reference layout -> this rank's slice
+        assert shard.model.encoder.W.shape == (L, D, hi - lo)
+        back = parallel.gather_state_dict(shard)                                   # and back
+        assert list(back) == list(ref_sd)
+        for k in ref_sd:
+            assert back[k].shape == ref_sd[k].shape and torch.equal(back[k], ref_sd[k]), k
+        q.put((rank, "ok"))
+    except Exception as e:  # pragma: no cover
+        q.put((rank, repr(e)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_checkpoint_round_trip_in_reference_layout():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_ckpt_worker, args=(r, 2, 29613, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=30)
+    assert all(v == "ok" for _, v in res), res
