@@ -362,6 +362,8 @@ def main():
     if world > 1:
         from crosslayer_transcoder_b200 import parallel
 
+        # its own communicator: batch uploads must not queue behind (or ahead of) the step's collectives
+        upload_group = dist.new_group(ranks=list(range(world)))
         chunk = (spec.batch + world - 1) // world
         shape = (world * chunk, *batch_dev.shape[1:])
         bufs = [torch.empty(shape, dtype=batch_dev.dtype, device=dev) for _ in range(2)]
@@ -377,7 +379,7 @@ def main():
             if world > 1:
                 # every rank holds the batch on the host; each uploads 1/R of the rows and the rest
                 # arrives over NVLink
-                views[slot] = parallel.upload_batch(batch_host, bufs[slot], mod.tp_group)
+                views[slot] = parallel.upload_batch(batch_host, bufs[slot], upload_group)
             else:
                 bufs[slot].copy_(batch_host, non_blocking=True)
                 views[slot] = bufs[slot]
@@ -390,6 +392,10 @@ def main():
     t1 = torch.cuda.Event(enable_timing=True)
     t0.record()
     upload(0)
+    # the loss of every step is copied to pinned host memory inside the timed region; the host looks at a
+    # step's value one step later, so that reading it does not drain the launch queue
+    loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
+    loss_ready = [torch.cuda.Event(), torch.cuda.Event()]
     last = 0.0
     for i in range(args.steps):
         slot = i & 1
@@ -398,7 +404,13 @@ def main():
         torch.cuda.current_stream().wait_event(ready[slot])
         loss = step(views[slot], 200 + i)
         freed[slot].record()
-        last = float(loss.detach())             # device -> host read of the step's result
+        loss_host[slot:slot + 1].copy_(loss.detach().reshape(1), non_blocking=True)   # device -> host, every step
+        loss_ready[slot].record()
+        if i > 0:
+            loss_ready[slot ^ 1].synchronize()
+            last = float(loss_host[slot ^ 1])
+    loss_ready[(args.steps - 1) & 1].synchronize()
+    last = float(loss_host[(args.steps - 1) & 1])
     t1.record()
     barrier()
     e2e_ms = t0.elapsed_time(t1)
