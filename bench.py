@@ -318,8 +318,11 @@ def main():
     mod = build_on_device(spec, dev, rank, world)
     opt = mod.configure_optimizers()
     eng = mod._engine
-    batch_host = synthetic.make_batch(spec, seed=0).half().pin_memory()      # fp16, the reference's activation dtype
-    batch_dev = batch_host.to(dev, non_blocking=True)
+    # fp16 activations (the reference's storage dtype), drawn on the device (same on every rank), with a pinned
+    # host copy for the end-to-end arm
+    batch_dev = synthetic.make_batch(spec, seed=0, dtype=torch.float16, device=dev)
+    batch_host = torch.empty(batch_dev.shape, dtype=batch_dev.dtype).pin_memory()
+    batch_host.copy_(batch_dev)
     torch.cuda.synchronize()
 
     def step(b, idx):
@@ -387,6 +390,10 @@ def main():
 
     for f in freed:
         f.record()
+    # untimed: one upload per slot, so that the upload communicator exists and the pinned pages are mapped
+    upload(0)
+    upload(1)
+    torch.cuda.synchronize()
     barrier()
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)

@@ -3,9 +3,9 @@ distributions of the benchmark configurations.
 
 They stand in for the GPT-2 / OpenWebText MLP activations the reference trains
 on (config/default.yaml:114-118 of the reference), which cannot be downloaded
-where the benchmark runs.  Everything is drawn on the CPU from one
+where the benchmark runs.  By default everything is drawn on the CPU from one
 ``torch.Generator`` so that the same tensors reach the CUDA path and the CPU
-checker.
+checker; the benchmark draws its (much larger) batch on the device instead.
 """
 from __future__ import annotations
 
@@ -72,29 +72,35 @@ def scaled(spec: WorkloadSpec, **over) -> WorkloadSpec:
     return WorkloadSpec(**d)
 
 
-def make_batch(spec: WorkloadSpec, seed: int = 0, dtype=torch.float32) -> torch.Tensor:
+def make_batch(spec: WorkloadSpec, seed: int = 0, dtype=torch.float32, device="cpu") -> torch.Tensor:
     """``[B, 2, L, D]`` batch: ``[:,0]`` residual-stream input, ``[:,1]`` MLP output.
 
     x_l = (0.5 u B_l + 0.87 eps_l) * s,  u ~ N(0, I_r) shared over layers,
     B_l ~ N(0, 1/r), eps_l ~ N(0, I), s = per-dimension lognormal(0, 0.5) with a
     few outlier dimensions scaled up; y_l = x_l M_l + 0.1 N(0, I), M_l ~ N(0, 1/D).
+
+    ``device`` selects where the draws and products happen: the CPU generator gives the tensors
+    the tests and golden vectors use; a CUDA device gives the same distribution (other values)
+    quickly for the large benchmark shapes.
     """
-    g = torch.Generator().manual_seed(seed)
+    dev = torch.device(device)
+    g = torch.Generator(device=dev).manual_seed(seed)
     B, L, D, r = spec.batch, spec.n_layers, spec.d_acts, spec.rank_u
-    u = torch.randn(B, r, generator=g)
-    s = torch.exp(0.5 * torch.randn(D, generator=g))
-    out_idx = torch.randperm(D, generator=g)[: spec.n_outlier]
+    kw = dict(generator=g, device=dev)
+    u = torch.randn(B, r, **kw)
+    s = torch.exp(0.5 * torch.randn(D, **kw))
+    out_idx = torch.randperm(D, **kw)[: spec.n_outlier]
     s[out_idx] *= spec.outlier_scale
-    batch = torch.empty(B, 2, L, D, dtype=torch.float32)
+    batch = torch.empty(B, 2, L, D, dtype=dtype, device=dev)
     for l in range(L):
-        Bl = torch.randn(r, D, generator=g) / math.sqrt(r)
-        eps = torch.randn(B, D, generator=g)
+        Bl = torch.randn(r, D, **kw) / math.sqrt(r)
+        eps = torch.randn(B, D, **kw)
         x = (0.5 * (u @ Bl) + 0.87 * eps) * s
-        M = torch.randn(D, D, generator=g) / math.sqrt(D)
-        y = x @ M + 0.1 * torch.randn(B, D, generator=g)
-        batch[:, 0, l] = x
-        batch[:, 1, l] = y
-    return batch.to(dtype)
+        M = torch.randn(D, D, **kw) / math.sqrt(D)
+        y = x @ M + 0.1 * torch.randn(B, D, **kw)
+        batch[:, 0, l] = x.to(dtype)
+        batch[:, 1, l] = y.to(dtype)
+    return batch
 
 
 def make_weights(spec: WorkloadSpec, seed: int = 1, f_lo: int = 0, f_hi: Optional[int] = None) -> Dict[str, object]:
