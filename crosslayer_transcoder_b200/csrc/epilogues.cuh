@@ -108,6 +108,18 @@ __device__ __forceinline__ float round_to<float>(float x) { return x; }
 template <>
 __device__ __forceinline__ float round_to<__nv_bfloat16>(float x) { return bf16_round(x); }
 
+// tanh at the accuracy the activation type needs: the exact routine beside fp32 activations, the
+// hardware approximation (relative error about 2^-11, below the 2^-9 rounding step of bf16) beside bf16
+// ones, where the routine's instruction count would otherwise outweigh the rest of the epilogue.
+template <class T>
+__device__ __forceinline__ float tanh_as(float x) { return tanhf(x); }
+template <>
+__device__ __forceinline__ float tanh_as<__nv_bfloat16>(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <class T>
 __device__ __forceinline__ bool can_vec(int n0, int N) {
   return (n0 + 32 <= N) && (N % (16 / (int)sizeof(T)) == 0);
@@ -407,7 +419,7 @@ struct EncJumpReLU {
         if (kPre) s_pre += ok ? fmaxf(-pre, 0.f) : 0.f;
         if (kSp) {
           const float w = f * nn[j];
-          s_sp += p.use_tanh ? tanhf(w) : w;
+          s_sp += p.use_tanh ? tanh_as<T>(w) : w;
         }
       }
     }
@@ -458,7 +470,7 @@ struct EncJumpReLU {
 //   dnorm  += lam * (1 - tanh^2(w)) * feat * c
 //   db_enc += dpre
 // dpre is stored rounded to T (the operand type of the encoder weight-gradient contraction).
-// Staged columns: 0 = b, 1 = theta (0 for ReLU), 2 = dec_norm * c, 3 = -theta / bw.
+// Staged columns: 0 = b, 1 = theta (0 for ReLU), 2 = dec_norm * c.
 // rect is evaluated as -bw/2 < pre - theta <= bw/2, the same set without the division.
 template <class T>
 struct DFeatJumpReLU {
@@ -479,14 +491,13 @@ struct DFeatJumpReLU {
     const float* gscale;  // device scalar: gradient of the loss w.r.t. itself (null = 1)
   };
   struct State {};
-  static constexpr int kColArrays = 4;
+  static constexpr int kColArrays = 3;
   static constexpr bool kPrefetch = false;
   __device__ static float col_value(const Params& p, int arr, int z, int n, int N) {
     const size_t i = (size_t)z * N + n;
     if (arr == 0) return __ldg(p.b_enc + i);
     if (arr == 1) return p.theta != nullptr ? __ldg(p.theta + i) : 0.f;
-    if (arr == 2) return p.dec_norm != nullptr ? __ldg(p.dec_norm + i) * p.c_sparsity : 0.f;
-    return p.theta != nullptr ? -__ldg(p.theta + i) / p.bandwidth : 0.f;
+    return p.dec_norm != nullptr ? __ldg(p.dec_norm + i) * p.c_sparsity : 0.f;
   }
   __device__ static void init(State&) {}
   template <int CS>
@@ -525,16 +536,14 @@ struct DFeatJumpReLU {
     const bool relu = p.theta == nullptr;
     const float gsc = p.gscale != nullptr ? __ldg(p.gscale) : 1.f;
     const float lam = p.lam * gsc, pal = p.pal * gsc;
-    const float hb = 0.5f * p.bandwidth;
+    const float hb = 0.5f * p.bandwidth, ninv_bw = -1.f / p.bandwidth;
     // JumpReLU passes the gradient for pre >= 0, plain ReLU for pre > 0
     const float pass_lim = relu ? 0.f : -1.0e-45f;
 #pragma unroll
     for (int i4 = 0; i4 < 8; ++i4) {
       const float4 b4 = *reinterpret_cast<const float4*>(colp + 4 * i4);
       const float4 t4 = *reinterpret_cast<const float4*>(colp + CS + 4 * i4);
-      const float4 c4 = *reinterpret_cast<const float4*>(colp + 3 * CS + 4 * i4);
       const float bb[4] = {b4.x, b4.y, b4.z, b4.w}, tt[4] = {t4.x, t4.y, t4.z, t4.w};
-      const float cc[4] = {c4.x, c4.y, c4.z, c4.w};
       float nn[4] = {0.f, 0.f, 0.f, 0.f};
       if (kSp) {
         const float4 n4 = *reinterpret_cast<const float4*>(colp + 2 * CS + 4 * i4);
@@ -552,7 +561,7 @@ struct DFeatJumpReLU {
           const float nc = nn[j];
           float d1 = 1.f;
           if (p.use_tanh) {
-            const float tw = tanhf(f * nc);
+            const float tw = tanh_as<T>(f * nc);
             d1 = 1.f - tw * tw;
           }
           gs = fmaf(lam * d1, nc, gs);
@@ -562,7 +571,7 @@ struct DFeatJumpReLU {
         const bool rect = (d > -hb) && !(d > hb);
         float dp = (pre > pass_lim) ? gs : 0.f;
         dp = (pre < 0.f) ? dp - pal : dp;
-        float dt = rect ? cc[j] * gs : 0.f;
+        float dt = rect ? (th * ninv_bw) * gs : 0.f;
         if (kEdge) {
           const bool ok = row_ok && (n0 + i < N);
           dp = ok ? dp : 0.f;

@@ -1,11 +1,17 @@
 // bf16 contraction on the 5th-generation tensor cores (tcgen05), fp32 accumulators
 // in tensor memory, operands staged in shared memory by TMA.
 //
-// One persistent CTA per SM, 320 threads:
-//   warp 0      TMA producer (one elected lane)
-//   warp 1      tensor-memory allocation, MMA issue (one elected lane)
-//   warps 2..9  epilogue: warp w reads the 32 tensor-memory lanes of quarter w % 4;
-//               warps 2..5 take columns 0..127 of the tile, warps 6..9 columns 128..255
+// One persistent CTA per SM, 384 threads in three warpgroups:
+//   warp 0       TMA producer (one elected lane)
+//   warp 1       tensor-memory allocation, MMA issue (one elected lane)
+//   warps 2..3   no role (they fill the first warpgroup)
+//   warps 4..11  epilogue: warp w reads the 32 tensor-memory lanes of quarter w % 4;
+//                warps 4..7 take columns 0..127 of the tile, warps 8..11 columns 128..255
+// The kernel starts with 168 registers per thread (three warps per scheduler share its 16K
+// registers); after set-up the first warpgroup hands registers back (setmaxnreg.dec to 72) and the
+// two epilogue warpgroups take them (setmaxnreg.inc to 216: 128*72 + 256*216 = 384*168), so that the
+// fused epilogues keep a 32-column chunk, its second operand and their results in registers while the
+// next chunk's tensor-memory read is in flight.
 // A CTA walks output tiles of 128 x 256 (tile index = blockIdx.x + i * gridDim.x).
 // Four 48 KB stages (A 128x64, B 256x64 bf16) are handed from the producer to the
 // MMA lane through full/empty mbarriers; two 256-column accumulators in tensor
@@ -42,7 +48,9 @@ constexpr int kBBytes = kBN * kBK * 2;  // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kEpiWarps = 8;
 constexpr int kEpiThreads = kEpiWarps * 32;
-constexpr int kThreads = 64 + kEpiThreads;
+constexpr int kFirstEpiWarp = 4;
+constexpr int kThreads = kFirstEpiWarp * 32 + kEpiThreads;
+constexpr int kRegsLean = 72, kRegsEpi = 216;  // per-thread register budgets after set-up
 constexpr int kTmemCols = 512;
 constexpr int kMaxColArrays = 4;
 constexpr int kColBytes = 2 * kMaxColArrays * kBN * 4;  // staged per-column parameters, double-buffered
@@ -214,102 +222,108 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = bars->tmem_base;
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool alive = true;
-      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-        const int z = slab_of_rank(g, tile / tiles_per_slab);
-        const int r = tile % tiles_per_slab;
-        const int m0 = (r % m_tiles) * kBM;
-        const int n0 = (r / m_tiles) * kBN;
-        const int nseg = seg_count(g, z);
-        for (int j = 0; j < nseg && alive; ++j) {
-          int za, zb;
-          seg_index(g, z, j, za, zb);
-          for (int kb = 0; kb < kb_per_seg; ++kb) {
-            if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, status, kTimeoutEmpty)) {
+  // Register hand-over between the warpgroups: all four warps of a warpgroup execute one and the same
+  // instruction, and the roles branch below it so that each branch is compiled for its own budget.
+  if (warp < kFirstEpiWarp) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsLean));
+    if (warp == 0) {
+      // ------------------------------ TMA producer ------------------------------
+      if (lane == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool alive = true;
+        for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+          const int z = slab_of_rank(g, tile / tiles_per_slab);
+          const int r = tile % tiles_per_slab;
+          const int m0 = (r % m_tiles) * kBM;
+          const int n0 = (r / m_tiles) * kBN;
+          const int nseg = seg_count(g, z);
+          for (int j = 0; j < nseg && alive; ++j) {
+            int za, zb;
+            seg_index(g, z, j, za, zb);
+            for (int kb = 0; kb < kb_per_seg; ++kb) {
+              if (!mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, status, kTimeoutEmpty)) {
+                alive = false;
+                break;
+              }
+              const uint32_t full = smem_u32(&bars->full[stage]);
+              mbar_expect_tx(full, kStageBytes);
+              const uint32_t sa = smem_u32(smem + stage * kStageBytes);
+              const uint32_t sb = sa + kABytes;
+              const int k0 = kb * kBK;
+              if (A_MN) {
+  #pragma unroll
+                for (int i = 0; i < kBM / 64; ++i) tma_load_3d(sa + i * 8192, &mapA, full, m0 + 64 * i, k0, za);
+              } else {
+                tma_load_3d(sa, &mapA, full, k0, m0, za);
+              }
+              if (B_MN) {
+  #pragma unroll
+                for (int i = 0; i < kBN / 64; ++i) tma_load_3d(sb + i * 8192, &mapB, full, n0 + 64 * i, k0, zb);
+              } else {
+                tma_load_3d(sb, &mapB, full, k0, n0, zb);
+              }
+              if (++stage == kStages) stage = 0, phase ^= 1;
+            }
+          }
+        }
+        if (!alive) {
+          // let copies that are still in flight land before the CTA's shared memory goes away
+          const long long t0 = clock64();
+          while (clock64() - t0 < 2000000ll) {
+          }
+        }
+      }
+      __syncwarp();
+    } else if (warp == 1) {
+      // ------------------------------ MMA issuer --------------------------------
+      if (lane == 0) {
+        constexpr uint32_t idesc = instr_desc(A_MN, B_MN);
+        int stage = 0;
+        uint32_t phase = 0;
+        uint32_t acc_phase[2] = {0, 0};
+        int it = 0;
+        bool alive = true;
+        for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++it) {
+          const int buf = it & 1;
+          const int z = slab_of_rank(g, tile / tiles_per_slab);
+          const int nkb = seg_count(g, z) * kb_per_seg;
+          if (!mbar_wait(smem_u32(&bars->tmem_empty[buf]), acc_phase[buf] ^ 1, abort_flag, status, kTimeoutTmemEmpty))
+            break;
+          acc_phase[buf] ^= 1;
+          tc_fence_after();
+          const uint32_t tmem_d = tmem_base + buf * kBN;
+          for (int kb = 0; kb < nkb; ++kb) {
+            if (!mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag, status, kTimeoutFull)) {
               alive = false;
               break;
             }
-            const uint32_t full = smem_u32(&bars->full[stage]);
-            mbar_expect_tx(full, kStageBytes);
+            tc_fence_after();
             const uint32_t sa = smem_u32(smem + stage * kStageBytes);
             const uint32_t sb = sa + kABytes;
-            const int k0 = kb * kBK;
-            if (A_MN) {
-#pragma unroll
-              for (int i = 0; i < kBM / 64; ++i) tma_load_3d(sa + i * 8192, &mapA, full, m0 + 64 * i, k0, za);
-            } else {
-              tma_load_3d(sa, &mapA, full, k0, m0, za);
+  #pragma unroll
+            for (int k = 0; k < kBK / 16; ++k) {
+              const uint64_t da = A_MN ? smem_desc(sa + k * 2048, 8192, 1024) : smem_desc(sa + k * 32, 16, 1024);
+              const uint64_t db = B_MN ? smem_desc(sb + k * 2048, 8192, 1024) : smem_desc(sb + k * 32, 16, 1024);
+              umma_bf16(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
             }
-            if (B_MN) {
-#pragma unroll
-              for (int i = 0; i < kBN / 64; ++i) tma_load_3d(sb + i * 8192, &mapB, full, n0 + 64 * i, k0, zb);
-            } else {
-              tma_load_3d(sb, &mapB, full, k0, n0, zb);
-            }
+            umma_commit(smem_u32(&bars->empty[stage]));  // frees the stage once these MMAs have read it
             if (++stage == kStages) stage = 0, phase ^= 1;
           }
+          if (alive) umma_commit(smem_u32(&bars->tmem_full[buf]));
         }
       }
-      if (!alive) {
-        // let copies that are still in flight land before the CTA's shared memory goes away
-        const long long t0 = clock64();
-        while (clock64() - t0 < 2000000ll) {
-        }
-      }
+      __syncwarp();
     }
-    __syncwarp();
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = instr_desc(A_MN, B_MN);
-      int stage = 0;
-      uint32_t phase = 0;
-      uint32_t acc_phase[2] = {0, 0};
-      int it = 0;
-      bool alive = true;
-      for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++it) {
-        const int buf = it & 1;
-        const int z = slab_of_rank(g, tile / tiles_per_slab);
-        const int nkb = seg_count(g, z) * kb_per_seg;
-        if (!mbar_wait(smem_u32(&bars->tmem_empty[buf]), acc_phase[buf] ^ 1, abort_flag, status, kTimeoutTmemEmpty))
-          break;
-        acc_phase[buf] ^= 1;
-        tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * kBN;
-        for (int kb = 0; kb < nkb; ++kb) {
-          if (!mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag, status, kTimeoutFull)) {
-            alive = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * kStageBytes);
-          const uint32_t sb = sa + kABytes;
-#pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) {
-            const uint64_t da = A_MN ? smem_desc(sa + k * 2048, 8192, 1024) : smem_desc(sa + k * 32, 16, 1024);
-            const uint64_t db = B_MN ? smem_desc(sb + k * 2048, 8192, 1024) : smem_desc(sb + k * 32, 16, 1024);
-            umma_bf16(tmem_d, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          }
-          umma_commit(smem_u32(&bars->empty[stage]));  // frees the stage once these MMAs have read it
-          if (++stage == kStages) stage = 0, phase ^= 1;
-        }
-        if (alive) umma_commit(smem_u32(&bars->tmem_full[buf]));
-      }
-    }
-    __syncwarp();
   } else {
     // ------------------------------ epilogue ----------------------------------
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsEpi));
     static_assert(Epi::kColArrays <= kMaxColArrays, "too many per-column parameter arrays");
     float* colp_base = reinterpret_cast<float*>(smem + kStages * kStageBytes + 256);
-    unsigned char* stage = smem + kStages * kStageBytes + 256 + kColBytes + (warp - 2) * epi::kStageBytes;
-    const int et = threadIdx.x - 64;          // 0..255 among the epilogue threads
-    const int quarter = warp & 3;             // tensor-memory lanes 32*quarter .. +31
-    const int half = (warp - 2) >> 2;         // which 128 columns of the tile
+    unsigned char* stage = smem + kStages * kStageBytes + 256 + kColBytes + (warp - kFirstEpiWarp) * epi::kStageBytes;
+    const int et = threadIdx.x - kFirstEpiWarp * 32;  // 0..255 among the epilogue threads
+    const int quarter = warp & 3;                     // tensor-memory lanes 32*quarter .. +31
+    const int half = (warp - kFirstEpiWarp) >> 2;     // which 128 columns of the tile
     typename Epi::State st;
     Epi::init(st);
     uint32_t acc_phase[2] = {0, 0};
@@ -344,25 +358,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const bool row_ok = row < g.M;
-      // the warp's 4 chunks of 32 columns; the read of chunk c+1 is in flight while chunk c is processed
+      // the warp's 4 chunks of 32 columns
       constexpr int kChunks = kBN / 64;
       const uint32_t taddr0 = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * kBN + 32 * half * kChunks);
       const int nbase = n0 + 32 * half * kChunks;
-      uint32_t ra[32], rb[32];
-      if (nbase < g.N) tmem_ld32_issue(taddr0, ra);
+      // Neither loop below is unrolled further: an epilogue body is several thousand instructions, and
+      // four copies of it per tile overflow the instruction cache.
+      if constexpr (Epi::kPrefetch) {
+        // two chunks per iteration; the read of the next chunk is in flight while one is processed
+        static_assert(kChunks % 2 == 0, "chunks are taken in pairs");
+        uint32_t ra[32], rb[32];
+        if (nbase < g.N) tmem_ld32_issue(taddr0, ra);
+#pragma unroll 1
+        for (int cc = 0; cc < kChunks; cc += 2) {
+          const int n = nbase + 32 * cc;
+          if (n >= g.N) break;
+          tmem_ld_wait();
+          const bool second = n + 32 < g.N;
+          if (second) tmem_ld32_issue(taddr0 + 32 * (cc + 1), rb);
+          float v[32];
 #pragma unroll
-      for (int cc = 0; cc < kChunks; ++cc) {
-        const int n = nbase + 32 * cc;
-        if (n >= g.N) break;
-        if (!Epi::kPrefetch && cc > 0) tmem_ld32_issue(taddr0 + 32 * cc, ra);
-        tmem_ld_wait();
-        uint32_t(&cur)[32] = (Epi::kPrefetch && (cc & 1)) ? rb : ra;
-        uint32_t(&nxt)[32] = (cc & 1) ? ra : rb;
-        if (Epi::kPrefetch && cc + 1 < kChunks && n + 32 < g.N) tmem_ld32_issue(taddr0 + 32 * (cc + 1), nxt);
-        float v[32];
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(ra[i]);
+          Epi::template apply<kBN>(ep, st, z, row, row_ok, n, g.M, g.N, v, colp + 32 * (half * kChunks + cc), stage);
+          if (!second) break;
+          tmem_ld_wait();
+          if (cc + 2 < kChunks && n + 64 < g.N) tmem_ld32_issue(taddr0 + 32 * (cc + 2), ra);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(cur[i]);
-        Epi::template apply<kBN>(ep, st, z, row, row_ok, n, g.M, g.N, v, colp + 32 * (half * kChunks + cc), stage);
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(rb[i]);
+          Epi::template apply<kBN>(ep, st, z, row, row_ok, n + 32, g.M, g.N, v, colp + 32 * (half * kChunks + cc + 1),
+                                   stage);
+        }
+      } else {
+#pragma unroll 1
+        for (int cc = 0; cc < kChunks; ++cc) {
+          const int n = nbase + 32 * cc;
+          if (n >= g.N) break;
+          uint32_t ra[32];
+          tmem_ld32_issue(taddr0 + 32 * cc, ra);
+          tmem_ld_wait();
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(ra[i]);
+          Epi::template apply<kBN>(ep, st, z, row, row_ok, n, g.M, g.N, v, colp + 32 * (half * kChunks + cc), stage);
+        }
       }
       tc_fence_before();
       __syncwarp();
