@@ -181,6 +181,20 @@ struct Barriers {
   int abort_flag;
 };
 
+// Order of the tiles of one slab.  CTAs work on consecutive tiles at the same time, so the faster axis
+// is the one along which tiles share the LARGER operand: with more rows than columns (A is the big
+// operand) the column tiles of one row block are neighbours and A's row block is fetched from HBM
+// once and found in L2 by the others; with more columns than rows it is the other way round.
+__device__ __forceinline__ void tile_origin(int r, int m_tiles, int n_tiles, int& m0, int& n0) {
+  if (m_tiles > n_tiles) {
+    m0 = (r / n_tiles) * kBM;
+    n0 = (r % n_tiles) * kBN;
+  } else {
+    m0 = (r % m_tiles) * kBM;
+    n0 = (r / m_tiles) * kBN;
+  }
+}
+
 template <class Epi, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, GemmGeom g,
@@ -235,8 +249,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         for (int tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
           const int z = slab_of_rank(g, tile / tiles_per_slab);
           const int r = tile % tiles_per_slab;
-          const int m0 = (r % m_tiles) * kBM;
-          const int n0 = (r / m_tiles) * kBN;
+          int m0, n0;
+          tile_origin(r, m_tiles, n_tiles, m0, n0);
           const int nseg = seg_count(g, z);
           for (int j = 0; j < nseg && alive; ++j) {
             int za, zb;
@@ -332,8 +346,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       const int buf = it & 1;
       const int z = slab_of_rank(g, tile / tiles_per_slab);
       const int r = tile % tiles_per_slab;
-      const int m0 = (r % m_tiles) * kBM;
-      const int n0 = (r / m_tiles) * kBN;
+      int m0, n0;
+      tile_origin(r, m_tiles, n_tiles, m0, n0);
       float* colp = colp_base + buf * (kMaxColArrays * kBN);
       // stage this tile's per-column parameters while its main loop is still running
 #pragma unroll
