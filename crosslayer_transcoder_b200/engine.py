@@ -302,6 +302,52 @@ class StepEngine:
                     bandwidth=self._bandwidth(nl) if h["kind"] == "jumprelu" else 1.0, out=out,
                     stats=(mu_i, sd_i, mu_o, sd_o), norm=norm, in_code=in_code, fused=fused)
 
+    # ------------------------------------------------------------------ inference forward
+    @torch.no_grad()
+    def infer(self, acts: torch.Tensor):
+        """``(pre_actvs [B,L,F], features [B,L,F], recons_norm [B,L,D], recons [B,L,D])`` of
+        ``CrossLayerTranscoder.forward`` (reference crosslayer_transcoder/model/clt.py:403-425) with the two
+        contractions on this library's kernels: the encoder product through ``clt_encoder_fwd_store``, the
+        (crosslayer) decoder sum through ``clt_decoder_dense_fwd``.  Standardizers and the nonlinearity are
+        the module's own element-wise PyTorch code.  No autograd graph is built.  On feature shards the
+        partial reconstructions are summed over the ranks; the returned features are the rank's slice, and
+        nonlinearities that rank across the whole feature axis (TopK, BatchTopK) are refused there."""
+        if not acts.is_cuda:
+            raise CltError("the kernel forward runs on CUDA tensors only (no CPU fallback)")
+        if acts.dim() != 3:
+            raise CltError(f"expected acts [batch, n_layers, d_acts], got {tuple(acts.shape)}")
+        mod, model = self.module, self.module.model
+        enc, dec = model.encoder, model.decoder
+        B, L, D, F = acts.shape[0], enc.n_layers, enc.d_acts, enc.d_features
+        if acts.shape[1] != L or acts.shape[2] != D:
+            raise CltError(f"acts {tuple(acts.shape)} do not match n_layers={L}, d_acts={D}")
+        bf16 = self._precision(acts)
+        dev = acts.device
+        self.prepare(dev, bf16)
+        world, group = getattr(mod, "tp_world", 1), getattr(mod, "tp_group", None)
+        if world > 1 and mod._kind() not in ("jumprelu", "relu"):
+            raise NotImplementedError("the kernel forward on feature shards supports element-wise nonlinearities only")
+        T = torch.bfloat16 if bf16 else torch.float32
+        s = stream_ptr()
+        x = model.input_standardizer(acts.float()) if model.input_standardizer is not None else acts.float()
+        xn = x.permute(1, 0, 2).to(T).contiguous()
+        z = torch.empty(L, B, F, dtype=T, device=dev)
+        self._call("clt_encoder_fwd_store", xn, self._operand(enc.W, bf16), z, B, L, D, F, int(bf16), self.status, s)
+        pre_actvs = z.permute(1, 0, 2).float() + enc.b.data
+        features = model.nonlinearity(pre_actvs)
+        feat = features.permute(1, 0, 2).to(T).contiguous()
+        W_op, _, _ = self._dec_flat(bf16)
+        recon = torch.empty(B, L, D, dtype=torch.float32, device=dev)
+        first_rank = getattr(mod, "tp_rank", 0) == 0
+        self._call("clt_decoder_dense_fwd", feat, W_op, dec.b.data if first_rank else None, recon, B, L, D, F,
+                   1 if dec.crosslayer else 0, int(bf16), self.status, s)
+        if world > 1:
+            from .parallel import all_reduce_sum
+
+            all_reduce_sum(recon, group)
+        recons = model.output_standardizer(recon) if model.output_standardizer is not None else recon
+        return pre_actvs, features, recon, recons
+
     # ------------------------------------------------------------------ backward
     def backward(self, ctx: dict, gscale: torch.Tensor):
         if ctx["kind"] in ("jumprelu", "relu"):

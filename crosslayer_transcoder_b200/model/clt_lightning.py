@@ -88,6 +88,11 @@ class CrossLayerTranscoderModule(_Base):
         return {"kind": self._kind()}
 
     def forward(self, acts_norm):
+        """``(pre_actvs, features, recons_norm, recons)`` (reference clt_lightning.py:121-129).  On CUDA
+        tensors with gradients disabled (validation, metrics) the two contractions run on this library's
+        kernels (``StepEngine.infer``); otherwise this is the model's differentiable PyTorch forward."""
+        if acts_norm.is_cuda and not torch.is_grad_enabled():
+            return self._engine.infer(acts_norm)
         return self.model(acts_norm)
 
     def configure_model(self):

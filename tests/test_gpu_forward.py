@@ -1,0 +1,64 @@
+"""The inference forward (``module.forward`` without gradients) on the contraction kernels against the
+model's own PyTorch forward, which follows the reference's ``CrossLayerTranscoder.forward``
+(crosslayer_transcoder/model/clt.py:403-425)."""
+import pytest
+import torch
+
+from crosslayer_transcoder_b200 import synthetic
+
+from helpers import build_module, rel_err, spec_inputs
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # name, L, D, F, B, crosslayer, kind, k
+    ("clt_jumprelu", 3, 64, 192, 136, True, "jumprelu", 0),
+    ("plt_jumprelu", 2, 96, 256, 77, False, "jumprelu", 0),
+    ("clt_topk", 3, 64, 128, 50, True, "topk", 8),
+    ("clt_batchtopk", 2, 64, 128, 64, True, "batchtopk", 4),
+]
+
+
+@pytest.mark.parametrize("prec", ["fp32", "bf16"])
+@pytest.mark.parametrize("name,L,D,F,B,cross,kind,k", CASES)
+def test_kernel_forward_matches_model_forward(name, L, D, F, B, cross, kind, k, prec):
+    bf16 = prec == "bf16"
+    if bf16 and kind != "jumprelu":
+        pytest.skip("selection sets of a bf16 run depend on the accumulation order; covered in fp32")
+    dev = torch.device("cuda:0")
+    spec = synthetic.WorkloadSpec(name, L, D, F, B, kind, cross, bf16, rank_u=8, n_outlier=1, k=k, k_aux=0)
+    batch, w, la = spec_inputs(spec)
+    mod = build_module(spec, w, dev, last_active=la)
+    mod.model.initialize_standardizers(batch.to(dev))
+    acts = batch[:, 0].to(dev)
+    tol = 2e-2 if bf16 else 1e-4
+    with torch.no_grad():
+        got = mod(acts)
+        if bf16:
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                want = mod.model(acts)
+        else:
+            want = mod.model(acts)
+    mod._engine.check_status("kernel forward")
+    assert mod._engine.launches >= 2
+    names = ("pre_actvs", "features", "recons_norm", "recons")
+    for n, a, b in zip(names, got, want):
+        assert a.shape == b.shape, n
+        if n == "features" and bf16:
+            # a pre-activation within rounding distance of its threshold may land on either side
+            frac = float(((a > 0) != (b > 0)).float().mean())
+            assert frac < 2e-3, (n, frac)
+            continue
+        assert rel_err(a.float(), b.float()) < tol, (n, rel_err(a.float(), b.float()))
+
+
+def test_kernel_forward_needs_cuda_without_grad():
+    """With gradients enabled, or on CPU tensors, forward is the model's differentiable PyTorch code."""
+    dev = torch.device("cuda:0")
+    spec = synthetic.WorkloadSpec("g", 2, 32, 64, 16, "jumprelu", True, False, rank_u=8, n_outlier=1)
+    batch, w, la = spec_inputs(spec)
+    mod = build_module(spec, w, dev, last_active=la)
+    mod.model.initialize_standardizers(batch.to(dev))
+    n0 = mod._engine.launches
+    out = mod(batch[:, 0].to(dev))
+    assert mod._engine.launches == n0 and out[3].requires_grad
