@@ -106,7 +106,7 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------
 # workload construction
 # --------------------------------------------------------------------------------------
-def build_on_device(spec: synthetic.WorkloadSpec, dev, rank: int, world: int):
+def build_on_device(spec: synthetic.WorkloadSpec, dev, rank: int, world: int, exchange: str = "nccl"):
     """The package's training module for this rank's feature shard, weights drawn on the device."""
     import crosslayer_transcoder_b200.model as M
     from crosslayer_transcoder_b200 import parallel
@@ -153,7 +153,7 @@ def build_on_device(spec: synthetic.WorkloadSpec, dev, rank: int, world: int):
     mod = mod.to(dev)
     mod.precision = "bf16" if spec.bf16 else "fp32"
     if world > 1:
-        parallel.attach(mod)
+        parallel.attach(mod, fused={"nccl": False, "fused": True, "auto": "auto"}[exchange])
     return mod
 
 
@@ -268,6 +268,9 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(synthetic.WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", choices=["nccl", "fused", "auto"], default="nccl",
+                    help="feature shards: sum the partial reconstructions with NCCL, or fused into the kernels "
+                         "over peer memory (TopK step)")
     ap.add_argument("--override", default="", help="comma-separated field=value changes to the workload "
                     "(reduced shapes for profiler captures; the result is then not a benchmark value)")
     args = ap.parse_args()
@@ -315,7 +318,9 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    mod = build_on_device(spec, dev, rank, world)
+    mod = build_on_device(spec, dev, rank, world, args.exchange)
+    if world > 1:
+        config["exchange"] = "fused into the kernels over peer memory" if getattr(mod, "tp_fused", False) else "nccl"
     opt = mod.configure_optimizers()
     eng = mod._engine
     # fp16 activations (the reference's storage dtype), drawn on the device (same on every rank), with a pinned

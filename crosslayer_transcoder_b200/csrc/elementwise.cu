@@ -373,6 +373,122 @@ __global__ void loss_bwd_vec_kernel(const float* __restrict__ recon, const float
   }
 }
 
+// Loss backward for the token rows this rank owns, with the all-gather fused in: the rank holds the
+// summed reconstructions of rows [b_lo, b_lo + b_cnt) as [b_cnt, L, D]; the gradient rows it derives
+// are written straight into every rank's [L, B, D] gradient buffer (16/8-byte stores over NVLink for
+// the peers), so no collective has to move them afterwards.  db_dec receives this rank's partial
+// column sums.  Same arithmetic as loss_bwd_vec_kernel; needs D % 4 == 0.
+constexpr int kMaxPushRanks = 16;
+struct PushPtrs {
+  unsigned long long drecon[kMaxPushRanks];
+  unsigned long long daux[kMaxPushRanks];
+  int n;
+};
+
+template <class TIn, class TOut>
+__global__ void loss_bwd_push_kernel(const float* __restrict__ recon, const float* __restrict__ aux,
+                                     const TIn* __restrict__ batch, const float* __restrict__ mu,
+                                     const float* __restrict__ sd, const float* __restrict__ gscale, float aux_scale,
+                                     PushPtrs dst, float* __restrict__ db_dec, int B, int b_lo, int b_cnt, int L,
+                                     int D, int rows_per_cta) {
+  const int LD = L * D;
+  const int c = (blockIdx.x * 32 + threadIdx.x) * 4;
+  const int r0 = blockIdx.y * rows_per_cta;
+  const int r1 = min(b_cnt, r0 + rows_per_cta);
+  const float gs = (gscale != nullptr ? *gscale : 1.f) / ((float)B * (float)L * (float)D);
+  float cs[4] = {0.f, 0.f, 0.f, 0.f};
+  if (c < LD) {
+    const int l = c / D, d = c % D;
+    const float4 m = *reinterpret_cast<const float4*>(mu + c), sv = *reinterpret_cast<const float4*>(sd + c);
+    const float mm[4] = {m.x, m.y, m.z, m.w}, ss[4] = {sv.x, sv.y, sv.z, sv.w};
+    for (int r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
+      const int b = b_lo + r;
+      const long long i = (long long)r * LD + c;
+      const TIn* yp = batch + ((long long)b * 2 + 1) * LD + c;
+      const float4 r4 = *reinterpret_cast<const float4*>(recon + i);
+      const float rr[4] = {r4.x, r4.y, r4.z, r4.w};
+      float aa[4] = {0.f, 0.f, 0.f, 0.f};
+      if (aux != nullptr) {
+        const float4 a4 = *reinterpret_cast<const float4*>(aux + i);
+        aa[0] = a4.x, aa[1] = a4.y, aa[2] = a4.z, aa[3] = a4.w;
+      }
+      float g[4], ga[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float y = (to_float<TIn>(yp[q]) - mm[q]) / ss[q];
+        const float diff = rr[q] - y;
+        g[q] = 2.f * diff * gs;
+        ga[q] = 0.f;
+        if (aux != nullptr) {
+          const float ad = aa[q] + diff;
+          ga[q] = (ad * ad == ad * ad) ? 2.f * ad * aux_scale * gs : 0.f;
+          g[q] += ga[q];
+          cs[q] += ga[q];
+        }
+        cs[q] += g[q];
+      }
+      const long long o = ((long long)l * B + b) * D + d;
+      TOut gq[4], gaq[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) gq[q] = from_float<TOut>(g[q]), gaq[q] = from_float<TOut>(ga[q]);
+      for (int k = 0; k < dst.n; ++k) {
+        TOut* dr = reinterpret_cast<TOut*>(dst.drecon[k]) + o;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) dr[q] = gq[q];
+        if (aux != nullptr) {
+          TOut* da = reinterpret_cast<TOut*>(dst.daux[k]) + o;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) da[q] = gaq[q];
+        }
+      }
+    }
+  }
+  __shared__ float sh[8][32][4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) sh[threadIdx.y][threadIdx.x][q] = cs[q];
+  __syncthreads();
+  if (threadIdx.y == 0 && c < LD) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      float t = 0.f;
+      for (int j = 0; j < (int)blockDim.y; ++j) t += sh[j][threadIdx.x][q];
+      if (t != 0.f) atomicAdd(db_dec + c + q, t);
+    }
+  }
+}
+
+int loss_bwd_push(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu,
+                  const float* sd, const float* gscale, float aux_scale, const unsigned long long* drecon_ptrs,
+                  const unsigned long long* daux_ptrs, int n_ranks, int out_bf16, float* db_dec, int B, int b_lo,
+                  int b_cnt, int L, int D, cudaStream_t s) {
+  if (b_cnt <= 0) return 0;
+  if (n_ranks > kMaxPushRanks) {
+    set_error("loss_bwd_push: %d ranks, at most %d", n_ranks, kMaxPushRanks);
+    return 1;
+  }
+  PushPtrs dst;
+  dst.n = n_ranks;
+  for (int k = 0; k < n_ranks; ++k) dst.drecon[k] = drecon_ptrs[k], dst.daux[k] = daux_ptrs ? daux_ptrs[k] : 0ull;
+  const int LD = L * D;
+  const int rows_per_cta = 64;
+  dim3 grid((LD / 4 + 31) / 32, (b_cnt + rows_per_cta - 1) / rows_per_cta), block(32, 8);
+#define CLT_LBP(TI, TO)                                                                                            \
+  loss_bwd_push_kernel<TI, TO><<<grid, block, 0, s>>>(recon, aux, (const TI*)batch, mu, sd, gscale, aux_scale, dst, \
+                                                      db_dec, B, b_lo, b_cnt, L, D, rows_per_cta)
+  switch (in_dtype * 2 + (out_bf16 ? 1 : 0)) {
+    case 0: CLT_LBP(float, float); break;
+    case 1: CLT_LBP(float, __nv_bfloat16); break;
+    case 2: CLT_LBP(__half, float); break;
+    case 3: CLT_LBP(__half, __nv_bfloat16); break;
+    case 4: CLT_LBP(__nv_bfloat16, float); break;
+    case 5: CLT_LBP(__nv_bfloat16, __nv_bfloat16); break;
+    default: set_error("loss_bwd_push: unknown input dtype %d", in_dtype); return 1;
+  }
+#undef CLT_LBP
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
 int loss_bwd(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu, const float* sd,
              const float* gscale, float aux_scale, void* drecon, void* daux, int out_bf16, float* db_dec, int B, int L,
              int D, cudaStream_t s) {

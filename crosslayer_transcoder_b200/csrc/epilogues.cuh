@@ -313,6 +313,65 @@ struct DecOut {
   __device__ static void finish(const Params&, State&) {}
 };
 
+// Decoder forward with the reduce-scatter over feature-shard ranks fused in.  The token axis is split
+// over the ranks (rank o owns rows [o * rows_per_rank, (o+1) * rows_per_rank) and holds them as
+// [rows_per_rank, nz, N] fp32 in a buffer every rank has mapped); acc + bias is ADDED to the owner's
+// buffer with 16-byte red.global.add (over NVLink for the peers' buffers), tile by tile while the main
+// loop of the next tile runs.  Sub-tiles go through the staging buffer so that an instruction covers
+// 8 rows x 64 contiguous bytes.
+constexpr int kMaxPushRanks = 16;
+struct DecOutPush {
+  struct Params {
+    unsigned long long bases[kMaxPushRanks];  // address of each rank's buffer
+    const float* bias;                        // [nz, N] or null
+    int rows_per_rank;
+    long long ld, zstride;                    // row and slab strides inside a rank's buffer
+  };
+  struct State {};
+  static constexpr int kColArrays = 1;
+  static constexpr bool kPrefetch = true;
+  __device__ static float col_value(const Params& p, int, int z, int n, int N) {
+    return p.bias != nullptr ? __ldg(p.bias + (size_t)z * N + n) : 0.f;
+  }
+  __device__ static void init(State&) {}
+  __device__ static __forceinline__ float* row_ptr(const Params& p, int row, int z) {
+    const int o = row / p.rows_per_rank;
+    return reinterpret_cast<float*>(p.bases[o]) + (size_t)(row - o * p.rows_per_rank) * p.ld + (size_t)z * p.zstride;
+  }
+  template <int CS>
+  __device__ static void apply(const Params& p, State&, int z, int row, bool row_ok, int n0, int M, int N,
+                               float (&v)[32], const float* colp, unsigned char* stage) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] += colp[i];
+    const int lane = threadIdx.x & 31;
+    const int row0 = row - lane;
+    if (n0 + 32 <= N && p.ld % 4 == 0 && p.zstride % 4 == 0 && N % 4 == 0) {
+      float4* mine = reinterpret_cast<float4*>(stage + lane * kStageRow);
+      const int piece = lane & 3;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          mine[i] = make_float4(v[16 * h + 4 * i], v[16 * h + 4 * i + 1], v[16 * h + 4 * i + 2], v[16 * h + 4 * i + 3]);
+        __syncwarp();
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int r = it * 8 + (lane >> 2);
+          const float4 t = *reinterpret_cast<const float4*>(stage + r * kStageRow + piece * 16);
+          if (row0 + r < M) atomicAdd(reinterpret_cast<float4*>(row_ptr(p, row0 + r, z) + n0 + 16 * h + piece * 4), t);
+        }
+        __syncwarp();
+      }
+    } else if (row_ok) {
+      float* o = row_ptr(p, row, z) + n0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (n0 + i < N) atomicAdd(o + i, v[i]);
+    }
+  }
+  __device__ static void finish(const Params&, State&) {}
+};
+
 // Weight gradient: out[z, row, n] = acc (+ rowcoef[zc, row] * w[z, row, n]).
 // The optional second term is the gradient of the decoder-norm factor of the
 // sparsity penalty: d|W[s,f,:]| / dW = W / |W|, scaled per feature row.

@@ -100,6 +100,27 @@ int clt_decoder_dense_fwd(const void* feat, const void* W_dec, const float* b_de
   return run_gemm<epi::DecOut, epi::DecOut>(g, a, b, p, p, bf16, status, (cudaStream_t)stream);
 }
 
+int clt_decoder_dense_fwd_push(const void* feat, const void* W_dec, const float* b_dec, const uint64_t* rank_bases,
+                               int rows_per_rank, int n_ranks, int B, int L, int D, int F, int crosslayer, int bf16,
+                               int* status, clt_stream_t stream) {
+  CLT_CHECK_ARG(dims_ok(B, L, D, F), "decoder_dense_fwd_push: bad dims B=%d L=%d D=%d F=%d", B, L, D, F);
+  CLT_CHECK_ARG(feat && W_dec && rank_bases, "decoder_dense_fwd_push: null pointer");
+  CLT_CHECK_ARG(n_ranks > 0 && n_ranks <= epi::kMaxPushRanks && rows_per_rank > 0 &&
+                    (long long)rows_per_rank * n_ranks >= B,
+                "decoder_dense_fwd_push: %d ranks x %d rows do not cover B=%d (at most %d ranks)", n_ranks,
+                rows_per_rank, B, epi::kMaxPushRanks);
+  const int P = crosslayer ? L * (L + 1) / 2 : L;
+  GemmGeom g{crosslayer ? kDecFwd : kBatched, B, D, F, L, L};
+  Operand a{feat, 1, B, F, L}, b{W_dec, 0, D, F, P};
+  epi::DecOutPush::Params p;
+  for (int r = 0; r < epi::kMaxPushRanks; ++r) p.bases[r] = r < n_ranks ? (unsigned long long)rank_bases[r] : 0ull;
+  p.bias = b_dec;
+  p.rows_per_rank = rows_per_rank;
+  p.ld = (long long)L * D;
+  p.zstride = (long long)D;
+  return run_gemm<epi::DecOutPush, epi::DecOutPush>(g, a, b, p, p, bf16, status, (cudaStream_t)stream);
+}
+
 int clt_decoder_dense_bwd_dfeat(const void* drecon, const void* W_dec, const void* z_in, const float* b_enc,
                                 const float* theta, const float* dec_norm, void* dpre_out, float* dtheta, float* dbenc,
                                 float* dnorm, float bandwidth, float lam, float c_sparsity, float pal, int use_tanh,

@@ -117,6 +117,22 @@ int clt_loss_bwd(const float* recon, const float* aux, const void* batch, int in
                   (cudaStream_t)stream);
 }
 
+int clt_loss_bwd_push(const float* recon_own, const float* aux_own, const void* batch, int in_dtype,
+                      const float* mu_out, const float* sd_out, const float* gscale, float aux_scale,
+                      const uint64_t* drecon_bases, const uint64_t* daux_bases, int n_ranks, int bf16, float* db_dec,
+                      int B, int b_lo, int b_cnt, int L, int D, clt_stream_t stream) {
+  CLT_CHECK_ARG(recon_own && batch && mu_out && sd_out && drecon_bases && db_dec, "loss_bwd_push: null pointer");
+  CLT_CHECK_ARG((aux_own == nullptr) == (daux_bases == nullptr), "loss_bwd_push: aux_own and daux_bases go together");
+  CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && D % 4 == 0, "loss_bwd_push: bad dims B=%d L=%d D=%d (D %% 4 == 0)", B, L, D);
+  CLT_CHECK_ARG(b_lo >= 0 && b_cnt >= 0 && b_lo + b_cnt <= B, "loss_bwd_push: rows [%d, %d) outside [0, %d)", b_lo,
+                b_lo + b_cnt, B);
+  CLT_CHECK_ARG(n_ranks > 0, "loss_bwd_push: n_ranks=%d", n_ranks);
+  return loss_bwd_push(recon_own, aux_own, batch, in_dtype, mu_out, sd_out, gscale, aux_scale,
+                       reinterpret_cast<const unsigned long long*>(drecon_bases),
+                       reinterpret_cast<const unsigned long long*>(daux_bases), n_ranks, bf16, db_dec, B, b_lo, b_cnt,
+                       L, D, (cudaStream_t)stream);
+}
+
 int clt_act_fwd(const void* z, const float* b_enc, const float* theta, const float* dec_norm, void* feat_out,
                 uint32_t* fired_bits, float* loss_acc, float c_sparsity, int use_tanh, int want_pre, int B, int L, int F,
                 int bf16, clt_stream_t stream) {

@@ -69,6 +69,24 @@ struct Vec8<float> {
   __device__ static __forceinline__ void load(const float* p, float (&o)[8]) { unpack(load_raw(p), o); }
 };
 
+// Where a reconstruction row goes.  On one GPU, or when the partial reconstructions are summed by a
+// library collective afterwards, the row is stored to `recon` [B, L, D].  With the reduction fused
+// into this kernel the token axis is split over the ranks: rank o owns tokens
+// [o * rows_per_rank, (o+1) * rows_per_rank), holds them as [rows_per_rank, L, D] in a buffer that
+// every rank has mapped, and every rank ADDS its partial row there (16-byte red.global.add over
+// NVLink for the peers' buffers), so that the transfer overlaps the gather row by row.
+constexpr int kMaxPushRanks = 16;
+struct PushDst {
+  unsigned long long bases[kMaxPushRanks];  // address of each rank's buffer
+  int rows_per_rank;                        // 0 = plain store to `recon`
+};
+
+__device__ __forceinline__ float* push_row(const PushDst& p, float* recon, int b, int t, int L, int D) {
+  if (p.rows_per_rank == 0) return recon + ((size_t)b * L + t) * D;
+  const int o = b / p.rows_per_rank;
+  return reinterpret_cast<float*>(p.bases[o]) + ((size_t)(b - o * p.rows_per_rank) * L + t) * D;
+}
+
 // =========================================================================================
 // Decoder forward, token-major gather.  One CTA per (token b, target layer t):
 //   recon[b, t, :] = b_dec[t] + sum_{s <= t} sum_j val[s,b,j] * W[pair(t,s), idx[s,b,j], :]
@@ -79,7 +97,7 @@ __global__ void __launch_bounds__(128)
 sparse_dec_fwd_kernel(const int* __restrict__ idx, const float* __restrict__ val, const int* __restrict__ row_start,
                       const int* __restrict__ row_cnt, long long npl, const T* __restrict__ W,
                       const float* __restrict__ b_dec, float* __restrict__ recon, int B, int L, int D, int F, int k,
-                      int crosslayer, int* status) {
+                      int crosslayer, int* status, PushDst push) {
   extern __shared__ float red[];  // [4][D]
   const int b = blockIdx.x, t = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -129,7 +147,22 @@ sparse_dec_fwd_kernel(const int* __restrict__ idx, const float* __restrict__ val
     }
   }
   __syncthreads();
-  float* out = recon + ((size_t)b * L + t) * D;
+  float* out = push_row(push, recon, b, t, L, D);
+  if (push.rows_per_rank != 0) {  // D % 8 == 0 here
+    for (int d = 4 * threadIdx.x; d < D; d += 4 * 128) {
+      float4 sum;
+      sum.x = red[d] + red[D + d] + red[2 * D + d] + red[3 * D + d];
+      sum.y = red[d + 1] + red[D + d + 1] + red[2 * D + d + 1] + red[3 * D + d + 1];
+      sum.z = red[d + 2] + red[D + d + 2] + red[2 * D + d + 2] + red[3 * D + d + 2];
+      sum.w = red[d + 3] + red[D + d + 3] + red[2 * D + d + 3] + red[3 * D + d + 3];
+      if (b_dec != nullptr) {
+        const float4 bb = __ldg(reinterpret_cast<const float4*>(b_dec + (size_t)t * D + d));
+        sum.x += bb.x, sum.y += bb.y, sum.z += bb.z, sum.w += bb.w;
+      }
+      atomicAdd(reinterpret_cast<float4*>(out + d), sum);
+    }
+    return;
+  }
   for (int d = threadIdx.x; d < D; d += 128) {
     float sum = red[d] + red[D + d] + red[2 * D + d] + red[3 * D + d];
     if (b_dec != nullptr) sum += __ldg(b_dec + (size_t)t * D + d);
@@ -145,7 +178,7 @@ __global__ void __launch_bounds__(128)
 sparse_dec_fwd_warp_kernel(const int* __restrict__ idx, const float* __restrict__ val,
                            const int* __restrict__ row_start, const int* __restrict__ row_cnt, long long npl,
                            const T* __restrict__ W, const float* __restrict__ b_dec, float* __restrict__ recon, int B,
-                           int L, int D, int F, int k, int crosslayer, int* status) {
+                           int L, int D, int F, int k, int crosslayer, int* status, PushDst push) {
   const long long pair = blockIdx.x * 4ll + (threadIdx.x >> 5);
   if (pair >= (long long)B * L) return;
   const int b = (int)(pair % B), t = (int)(pair / B);
@@ -206,7 +239,7 @@ sparse_dec_fwd_warp_kernel(const int* __restrict__ idx, const float* __restrict_
       if (valid < m) break;
     }
   }
-  float* out = recon + ((size_t)b * L + t) * D;
+  float* out = push_row(push, recon, b, t, L, D);
 #pragma unroll
   for (int i = 0; i < VPL; ++i) {
     const int c = lane + 32 * i;
@@ -214,8 +247,15 @@ sparse_dec_fwd_warp_kernel(const int* __restrict__ idx, const float* __restrict_
       float bb[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       if (b_dec != nullptr) Vec8<float>::load(b_dec + (size_t)t * D + 8 * c, bb);
       float4* o = reinterpret_cast<float4*>(out + 8 * c);
-      o[0] = make_float4(acc[i][0] + bb[0], acc[i][1] + bb[1], acc[i][2] + bb[2], acc[i][3] + bb[3]);
-      o[1] = make_float4(acc[i][4] + bb[4], acc[i][5] + bb[5], acc[i][6] + bb[6], acc[i][7] + bb[7]);
+      const float4 lo = make_float4(acc[i][0] + bb[0], acc[i][1] + bb[1], acc[i][2] + bb[2], acc[i][3] + bb[3]);
+      const float4 hi = make_float4(acc[i][4] + bb[4], acc[i][5] + bb[5], acc[i][6] + bb[6], acc[i][7] + bb[7]);
+      if (push.rows_per_rank != 0) {
+        atomicAdd(o, lo);
+        atomicAdd(o + 1, hi);
+      } else {
+        o[0] = lo;
+        o[1] = hi;
+      }
     }
   }
 }
@@ -403,7 +443,7 @@ sparse_bwd_dec_kernel(const int* __restrict__ col_ptr, const int* __restrict__ e
 // features nobody selected are zero-filled without touching W.  This removes most of the dependent
 // round trips (pointer -> entry -> token -> row) that bound the one-row-per-warp kernel above.
 template <class T, int VPL>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 5)
 sparse_bwd_dec_group_kernel(const int* __restrict__ col_ptr, const int* __restrict__ ent,
                             const float* __restrict__ val, const int* __restrict__ etok, long long npl_,
                             const T* __restrict__ W, const T* __restrict__ drecon, float* __restrict__ dW,
@@ -515,12 +555,13 @@ sparse_bwd_dec_group_kernel(const int* __restrict__ col_ptr, const int* __restri
           g[i][q] = fmaf(v1, xf[q], g[i][q]);
         }
       }
-      dot0 = warp_sum(dot0);
-      dot1 = warp_sum(dot1);
-      if (lane == 0) {
-        atomicAdd(dval + (size_t)s * npl + slot0, dot0);
-        if (two) atomicAdd(dval + (size_t)s * npl + slot1, dot1);
-      }
+      // both dot products in one butterfly: the lower half-warp ends with dot0, the upper with dot1
+      const bool lower = lane < 16;
+      float r = (lower ? dot0 : dot1) + __shfl_xor_sync(0xffffffffu, lower ? dot1 : dot0, 16);
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+      if (lane == 0) atomicAdd(dval + (size_t)s * npl + slot0, r);
+      if (lane == 16 && two) atomicAdd(dval + (size_t)s * npl + slot1, r);
     }
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
@@ -690,7 +731,7 @@ __global__ void scatter_cols_kernel(const float* __restrict__ src, const float* 
 template <class T>
 int launch_dec_fwd(const int* idx, const float* val, const int* row_start, const int* row_cnt, long long npl,
                    const void* W, const float* b_dec, float* recon, int B, int L, int D, int F, int k, int crosslayer,
-                   int short_rows, int* status, cudaStream_t s) {
+                   int short_rows, int* status, cudaStream_t s, PushDst push = PushDst{{0ull}, 0}) {
   const int vpl = (D / 8 + 31) / 32;
   dim3 grid(B, L);
   const size_t smem = 4 * (size_t)D * sizeof(float);
@@ -699,13 +740,13 @@ int launch_dec_fwd(const int* idx, const float* val, const int* row_start, const
   case V:                                                                                                           \
     if (short_rows) {                                                                                               \
       sparse_dec_fwd_warp_kernel<T, V><<<wgrid, 128, 0, s>>>(idx, val, row_start, row_cnt, npl, (const T*)W, b_dec, \
-                                                             recon, B, L, D, F, k, crosslayer, status);             \
+                                                             recon, B, L, D, F, k, crosslayer, status, push);       \
       break;                                                                                                        \
     }                                                                                                               \
     CLT_CHECK_CUDA(cudaFuncSetAttribute(sparse_dec_fwd_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                         (int)smem));                                                                \
     sparse_dec_fwd_kernel<T, V><<<grid, 128, smem, s>>>(idx, val, row_start, row_cnt, npl, (const T*)W, b_dec,      \
-                                                        recon, B, L, D, F, k, crosslayer, status);                  \
+                                                        recon, B, L, D, F, k, crosslayer, status, push);            \
     break;
   switch (vpl) {
     CLT_DEC_FWD(1) CLT_DEC_FWD(2) CLT_DEC_FWD(3) CLT_DEC_FWD(4) CLT_DEC_FWD(6) CLT_DEC_FWD(8) CLT_DEC_FWD(9)
@@ -777,6 +818,32 @@ int clt_sparse_decoder_fwd(const int* idx, const float* val, const int* row_star
                                          crosslayer, short_rows, status, (cudaStream_t)stream);
   return launch_dec_fwd<float>(idx, val, row_start, row_cnt, npl, W_dec, b_dec, recon, B, L, D, F, k, crosslayer,
                                short_rows, status, (cudaStream_t)stream);
+}
+
+int clt_sparse_decoder_fwd_push(const int* idx, const float* val, const int* row_start, const int* row_cnt, int64_t npl,
+                                const void* W_dec, const float* b_dec, const uint64_t* rank_bases, int rows_per_rank,
+                                int n_ranks, int B, int L, int D, int F, int k, int crosslayer, int short_rows,
+                                int bf16, int* status, clt_stream_t stream) {
+  CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && F > 0 && k > 0, "sparse_decoder_fwd_push: bad dims B=%d L=%d D=%d F=%d k=%d",
+                B, L, D, F, k);
+  CLT_CHECK_ARG(D % 8 == 0, "sparse_decoder_fwd_push: d_acts=%d must be a multiple of 8", D);
+  CLT_CHECK_ARG(idx && val && W_dec && rank_bases, "sparse_decoder_fwd_push: null pointer");
+  CLT_CHECK_ARG((row_start == nullptr) == (row_cnt == nullptr),
+                "sparse_decoder_fwd_push: row_start and row_cnt go together");
+  CLT_CHECK_ARG(row_start != nullptr || npl == (int64_t)B * k, "sparse_decoder_fwd_push: fixed slots need npl = B*k");
+  CLT_CHECK_ARG(B <= 2147483647 && L <= 65535, "sparse_decoder_fwd_push: grid too large");
+  CLT_CHECK_ARG(n_ranks > 0 && n_ranks <= kMaxPushRanks && rows_per_rank > 0 &&
+                    (long long)rows_per_rank * n_ranks >= B,
+                "sparse_decoder_fwd_push: %d ranks x %d rows do not cover B=%d (at most %d ranks)", n_ranks,
+                rows_per_rank, B, kMaxPushRanks);
+  PushDst push;
+  for (int r = 0; r < kMaxPushRanks; ++r) push.bases[r] = r < n_ranks ? (unsigned long long)rank_bases[r] : 0ull;
+  push.rows_per_rank = rows_per_rank;
+  if (bf16)
+    return launch_dec_fwd<__nv_bfloat16>(idx, val, row_start, row_cnt, npl, W_dec, b_dec, nullptr, B, L, D, F, k,
+                                         crosslayer, short_rows, status, (cudaStream_t)stream, push);
+  return launch_dec_fwd<float>(idx, val, row_start, row_cnt, npl, W_dec, b_dec, nullptr, B, L, D, F, k, crosslayer,
+                               short_rows, status, (cudaStream_t)stream, push);
 }
 
 int clt_csc_build(const int* idx, const float* val, int* col_ptr, int* cursor, int* ent, int64_t npl, int L, int F,

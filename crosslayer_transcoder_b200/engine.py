@@ -221,6 +221,42 @@ class StepEngine:
             self._bw_cache = float(nl.bandwidth)
         return self._bw_cache
 
+    # ------------------------------------------------------------------ fused exchange over peer memory
+    def _peer_exchange(self, B: int, L: int, D: int, T, dev):
+        """Buffers of the exchange that is fused into the kernels (feature shards on one node), created
+        once per shape, collectively over the group.  The token axis is split over the ranks: this rank
+        owns rows ``[b_lo, b_lo + b_cnt)``.  ``recon_own`` / ``aux_own`` [rows_per_rank, L, D] fp32 receive
+        every rank's partial (auxiliary) reconstruction rows for the owned tokens (the decoder kernels
+        add into them);
+        ``drecon`` / ``daux`` [L, B, D] receive every owner's gradient rows (the loss backward writes
+        them into all ranks' copies)."""
+        key = (B, L, D, T, dev)
+        px = getattr(self, "_px", None)
+        if px is not None and px["key"] == key:
+            return px
+        from .parallel import PeerBuffer
+
+        mod = self.module
+        world, rank, group = mod.tp_world, mod.tp_rank, mod.tp_group
+        rpr = (B + world - 1) // world
+        b_lo = min(B, rank * rpr)
+        b_cnt = max(0, min(B, b_lo + rpr) - b_lo)
+        own = PeerBuffer((2, rpr, L, D), torch.float32, dev, group)      # [0] main, [1] auxiliary reconstruction
+        drecon = PeerBuffer((L, B, D), T, dev, group)
+        daux = PeerBuffer((L, B, D), T, dev, group)
+        self._px = dict(key=key, rpr=rpr, b_lo=b_lo, b_cnt=b_cnt, own=own, recon_own=own.local[0],
+                        aux_own=own.local[1], recon_bases=own.bases, aux_bases=own.bases + rpr * L * D * 4,
+                        drecon=drecon, daux=daux, token=torch.zeros(1, dtype=torch.float32, device=dev))
+        return self._px
+
+    def _rank_barrier(self, px):
+        """Order the ranks on the compute stream: a one-element all-reduce.  After it, every kernel that
+        any rank enqueued before its own call has finished, so rows pushed into this rank's buffers
+        have landed."""
+        from .parallel import all_reduce_sum
+
+        all_reduce_sum(px["token"], self.module.tp_group)
+
     # ------------------------------------------------------------------ forward
     def forward(self, batch: torch.Tensor, hyper: dict) -> torch.Tensor:
         """Run the forward half of the step on ``batch`` ``[B, 2, L, D]`` and return the scalar
@@ -444,6 +480,12 @@ class StepEngine:
         bias = dec.b.data if getattr(mod, "tp_rank", 0) == 0 else None      # added once, not per shard
         in_code = DTYPE_CODE[batch.dtype]
         W_op, _, _ = self._dec_flat(bf16)
+        # exchange fused into the kernels: the main decoder adds its rows into the owning rank's buffer,
+        # the loss runs on the owned rows only (see _peer_exchange)
+        px = None
+        if world > 1 and getattr(mod, "tp_fused", False) and k > 0 and D % 8 == 0:
+            px = self._peer_exchange(B, L, D, T, dev)
+            px["own"].local.zero_()                     # ordered before any rank's adds by the collectives below
         self._call("clt_prep_input", batch, in_code, mu_i, sd_i, xn, int(bf16), B, L, D, s)
         self._call("clt_encoder_fwd_store", xn, self._operand(enc.W, bf16), z, B, L, D, F, int(bf16), self.status, s)
         kk = max(k, 1)
@@ -499,12 +541,21 @@ class StepEngine:
                            nd_pad, int(bf16), s)
                 cand_all = ws.get("aux_cand_all", (world, L, B, k_aux), torch.float32, dev)
                 h_gather = all_gather(cand_all, cand, group, async_op=True)
-        self._call("clt_sparse_decoder_fwd", idx, val, None, None, B * kk, W_op, bias, recon, B, L, D, F, kk, crosslayer,
-                   int(kk <= 8 * world), int(bf16), self.status, s)
-        if world > 1:
-            from .parallel import all_reduce_sum
+        def main_decoder():
+            if px is not None:
+                self._call("clt_sparse_decoder_fwd_push", idx, val, None, None, B * kk, W_op, bias,
+                           px["recon_bases"], px["rpr"], world, B, L, D, F, kk, crosslayer, int(kk <= 8 * world),
+                           int(bf16), self.status, s)
+                return
+            self._call("clt_sparse_decoder_fwd", idx, val, None, None, B * kk, W_op, bias, recon, B, L, D, F, kk,
+                       crosslayer, int(kk <= 8 * world), int(bf16), self.status, s)
+            if world > 1:
+                from .parallel import all_reduce_sum
 
-            pending.append(all_reduce_sum(rbuf[:n_rec], group, async_op=True))
+                pending.append(all_reduce_sum(rbuf[:n_rec], group, async_op=True))
+
+        if px is None:
+            main_decoder()          # its all-reduce runs while the auxiliary path computes
         if k_aux > 0:
             if not exchange:
                 self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, a_aux, None, None, 0, B, L, F, k_aux,
@@ -519,18 +570,37 @@ class StepEngine:
             w_c = ws.get("w_c", (P, nd_pad, D), T, dev)
             self._call("clt_gather_rows", W_op, dead_list, n_dead, w_c, L, F, D, nd_pad, crosslayer, int(bf16), s)
             aux_recon = aux_recon_buf
-            self._call("clt_decoder_dense_fwd", a_aux, w_c, bias, aux_recon, B, L, D, nd_pad, crosslayer,
-                       int(bf16), self.status, s)
+            if px is not None:
+                # the contraction's epilogue adds each tile to the owning ranks' buffers
+                self._call("clt_decoder_dense_fwd_push", a_aux, w_c, bias, px["aux_bases"], px["rpr"], world, B, L, D,
+                           nd_pad, crosslayer, int(bf16), self.status, s)
+            else:
+                self._call("clt_decoder_dense_fwd", a_aux, w_c, bias, aux_recon, B, L, D, nd_pad, crosslayer,
+                           int(bf16), self.status, s)
             aux = dict(dead_list=dead_list, n_dead=n_dead, nd_pad=nd_pad, a_aux=a_aux, w_c=w_c)
-            if world > 1:
+            if world > 1 and px is None:
                 pending.append(all_reduce_sum(rbuf[n_rec:2 * n_rec], group, async_op=True))
-        for h_ in pending:
-            h_.wait()
-        self._call("clt_loss_fwd", recon, aux_recon, batch, in_code, mu_o, sd_o, acc[2:4], B, L, D, s)
+        if px is not None:
+            from .parallel import all_reduce_sum
+
+            main_decoder()
+            self._rank_barrier(px)                      # every rank's rows have been added
+            for h_ in pending:
+                h_.wait()
+            b_lo, b_cnt = px["b_lo"], px["b_cnt"]
+            if b_cnt > 0:
+                self._call("clt_loss_fwd", px["recon_own"], px["aux_own"] if aux is not None else None,
+                           batch[b_lo:b_lo + b_cnt], in_code, mu_o, sd_o, acc[2:4], b_cnt, L, D, s)
+            all_reduce_sum(acc[2:4], group)             # loss sums of all owners
+        else:
+            for h_ in pending:
+                h_.wait()
+            self._call("clt_loss_fwd", recon, aux_recon, batch, in_code, mu_o, sd_o, acc[2:4], B, L, D, s)
         self._call("clt_finalize_loss", acc[2:4], None, out[0:1], out[1:5], 1.0 / (B * L * D), 0.0, 0.0,
                    aux_scale if aux is not None else 0.0, s)
         return dict(kind="topk", bf16=bf16, batch=batch, B=B, L=L, D=D, F=F, k=kk, crosslayer=crosslayer, out=out,
-                    stats=(mu_i, sd_i, mu_o, sd_o), in_code=in_code, aux=aux, aux_scale=aux_scale, idx=idx, val=val)
+                    stats=(mu_i, sd_i, mu_o, sd_o), in_code=in_code, aux=aux, aux_scale=aux_scale, idx=idx, val=val,
+                    px=px)
 
     # ------------------------------------------------------------------ BatchTopK path
     def _forward_batchtopk(self, batch, h, bf16):
@@ -641,9 +711,25 @@ class StepEngine:
         gview = lambda p: self.flat.view_of(p, g)
         gview(dec.b).zero_()
         gs = gscale.detach().to(torch.float32).reshape(1).contiguous()
-        self._call("clt_loss_bwd", recon, aux_recon if aux is not None else None, c["batch"], c["in_code"],
-                   mu_o, sd_o, gs, c["aux_scale"] if aux is not None else 0.0, drecon, daux, int(bf16), gview(dec.b),
-                   B, L, D, s)
+        px = c.get("px")
+        if px is not None:
+            # owned rows only; the gradient rows go straight into every rank's buffers, and the all-reduce
+            # of the bias gradient's partial sums also orders the ranks before those buffers are read
+            from .parallel import all_reduce_sum
+
+            b_lo, b_cnt = px["b_lo"], px["b_cnt"]
+            drecon, daux = px["drecon"].local, (px["daux"].local if aux is not None else None)
+            if b_cnt > 0:
+                self._call("clt_loss_bwd_push", px["recon_own"], px["aux_own"] if aux is not None else None,
+                           c["batch"], c["in_code"], mu_o,
+                           sd_o, gs, c["aux_scale"] if aux is not None else 0.0, px["drecon"].bases,
+                           px["daux"].bases if aux is not None else None, self.module.tp_world, int(bf16),
+                           gview(dec.b), B, b_lo, b_cnt, L, D, s)
+            all_reduce_sum(gview(dec.b), self.module.tp_group)
+        else:
+            self._call("clt_loss_bwd", recon, aux_recon if aux is not None else None, c["batch"], c["in_code"],
+                       mu_o, sd_o, gs, c["aux_scale"] if aux is not None else 0.0, drecon, daux, int(bf16),
+                       gview(dec.b), B, L, D, s)
         W_op, _, dW_dec = self._dec_flat(bf16)
         idx, val = c["idx"], c["val"]
         npl, etok = c.get("npl", B * k), c.get("etok")       # entry slots per layer, token of each entry

@@ -30,14 +30,55 @@ def feature_shard(d_features: int, rank: int, world: int) -> Tuple[int, int]:
     return rank * per, (rank + 1) * per
 
 
-def attach(module, group: Optional[dist.ProcessGroup] = None) -> None:
+def attach(module, group: Optional[dist.ProcessGroup] = None, fused="auto") -> None:
     """Mark ``module`` (built with this rank's feature slice) as one shard of a group.  With no
-    group the default process group is used."""
+    group the default process group is used.
+
+    ``fused`` asks for the exchange that is fused into the kernels over peer memory (the TopK step's
+    decoder adds its partial rows straight into the owning rank's buffer, the loss backward writes its
+    rows into every rank's buffer): "auto" uses it on an NCCL group when the ranks can map each other's
+    memory, ``False`` keeps the NCCL all-reduce, ``True`` raises if peer mapping is not available."""
     if not dist.is_initialized():
         raise RuntimeError("torch.distributed is not initialised")
     module.tp_group = group if group is not None else dist.group.WORLD
     module.tp_rank = dist.get_rank(module.tp_group)
     module.tp_world = dist.get_world_size(module.tp_group)
+    module.tp_fused = False
+    if fused and module.tp_world > 1 and dist.get_backend(module.tp_group) == "nccl":
+        try:
+            _symm()
+            module.tp_fused = True
+        except Exception:
+            if fused is True:
+                raise
+
+
+def _symm():
+    """torch's symmetric-memory module, set up for plain peer pointers (no NVLink multicast binding:
+    the kernels here use peer loads / stores / reductions only)."""
+    import os
+
+    os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+    import torch.distributed._symmetric_memory as symm_mem
+
+    return symm_mem
+
+
+class PeerBuffer:
+    """A tensor of the same shape on every rank of ``group``, each rank's copy mapped into every other
+    rank's address space.  ``local`` is this rank's tensor; ``bases`` is a CPU int64 tensor with the
+    device address of every rank's copy (this rank's own at index ``rank``), in the form the C ABI's
+    ``*_push`` entry points take.  Construction is collective over the group."""
+
+    def __init__(self, shape, dtype, device, group):
+        symm_mem = _symm()
+        self.local = symm_mem.empty(*shape, dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.local, group)
+        rank = dist.get_rank(group)
+        off = self.local.data_ptr() - int(self.handle.buffer_ptrs[rank])
+        if off < 0 or off + self.local.numel() * self.local.element_size() > int(self.handle.buffer_size):
+            raise RuntimeError("symmetric-memory tensor lies outside its registered buffer")
+        self.bases = torch.tensor([int(p) + off for p in self.handle.buffer_ptrs], dtype=torch.int64)
 
 
 def all_reduce_sum(buf: torch.Tensor, group, async_op: bool = False):

@@ -66,6 +66,17 @@ int clt_encoder_fwd_store(const void* xn, const void* W_enc, void* z_out, int B,
 int clt_decoder_dense_fwd(const void* feat, const void* W_dec, const float* b_dec, float* recon, int B, int L,
                           int D, int F, int crosslayer, int bf16, int* status, clt_stream_t stream);
 
+/* clt_decoder_dense_fwd fused with the reduce-scatter of the partial reconstructions over the
+ * feature-shard ranks of one node (same buffer convention as clt_sparse_decoder_fwd_push: rank o owns
+ * tokens [o rows_per_rank, (o+1) rows_per_rank) as [rows_per_rank, L, D] fp32, zero before the first
+ * rank starts; rank_bases is a host array of n_ranks device addresses).  The contraction's epilogue
+ * adds each finished tile to the owners' buffers (16-byte red.global.add, over NVLink for the peers)
+ * while the tensor cores work on the next tile.  Replaces the DTensor all-reduce after the decoder
+ * (crosslayer_transcoder/model/parallel.py:157-339). */
+int clt_decoder_dense_fwd_push(const void* feat, const void* W_dec, const float* b_dec, const uint64_t* rank_bases,
+                               int rows_per_rank, int n_ranks, int B, int L, int D, int F, int crosslayer, int bf16,
+                               int* status, clt_stream_t stream);
+
 /* Reconstruction MSE (clt_lightning.py:303-304) and, with aux != NULL, the TopK auxiliary
  * loss (clt_lightning.py:548-551).  acc[0] += sum diff^2, acc[1] += sum (aux + diff)^2. */
 int clt_loss_fwd(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu_out,
@@ -82,6 +93,20 @@ int clt_finalize_loss(const float* mse_acc, const float* enc_acc, float* loss, f
 int clt_loss_bwd(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu_out,
                  const float* sd_out, const float* gscale, float aux_scale, void* drecon, void* daux, int bf16,
                  float* db_dec, int B, int L, int D, clt_stream_t stream);
+
+/* clt_loss_bwd for the token rows [b_lo, b_lo + b_cnt) that this rank owns, fused with the all-gather of
+ * the result over the feature-shard ranks of one node.  recon_own / aux_own hold the owned rows'
+ * summed reconstructions as [b_cnt, L, D]; batch is the whole [B, 2, L, D] batch; the gradient rows are
+ * written to row b of EVERY rank's [L, B, D] buffer (drecon_bases / daux_bases: host arrays of n_ranks
+ * device addresses, this rank's own buffer included; the peers' buffers must be mapped into this
+ * process, e.g. CUDA IPC or symmetric memory).  db_dec receives this rank's partial column sums.  The
+ * caller orders the ranks (any stream-ordered collective after this call) before the buffers are read.
+ * The reference has no counterpart: its tensor-parallel plan replicates the loss on every rank
+ * (crosslayer_transcoder/model/clt_lightning.py:100-119). */
+int clt_loss_bwd_push(const float* recon_own, const float* aux_own, const void* batch, int in_dtype,
+                      const float* mu_out, const float* sd_out, const float* gscale, float aux_scale,
+                      const uint64_t* drecon_bases, const uint64_t* daux_bases, int n_ranks, int bf16, float* db_dec,
+                      int B, int b_lo, int b_cnt, int L, int D, clt_stream_t stream);
 
 /* Backward of the decoder w.r.t. the features fused with the JumpReLU / ReLU backward
  * (jumprelu.py:41-48), the sparsity-penalty and pre-activation-loss gradients
@@ -180,6 +205,19 @@ int clt_sparse_decoder_fwd(const int* idx, const float* val, const int* row_star
                            int64_t npl, const void* W_dec, const float* b_dec, float* recon, int B, int L, int D,
                            int F, int k, int crosslayer, int short_rows, int bf16, int* status,
                            clt_stream_t stream);
+
+/* clt_sparse_decoder_fwd fused with the reduce-scatter of the partial reconstructions over the
+ * feature-shard ranks of one node: rank o owns tokens [o rows_per_rank, (o+1) rows_per_rank) and holds
+ * their reconstructions as [rows_per_rank, L, D] fp32 in a buffer mapped into every rank's process
+ * (rank_bases: host array of n_ranks device addresses, this rank's own included).  Every rank ADDS its
+ * partial rows there (16-byte red.global.add, over NVLink for the peers), so the buffers must be zero
+ * before the first rank starts and are complete once every rank's call has finished (the caller orders
+ * the ranks with any stream-ordered collective).  The reference sums the partial decoder outputs with a
+ * DTensor all-reduce after the decoder (crosslayer_transcoder/model/parallel.py:157-339). */
+int clt_sparse_decoder_fwd_push(const int* idx, const float* val, const int* row_start, const int* row_cnt,
+                                int64_t npl, const void* W_dec, const float* b_dec, const uint64_t* rank_bases,
+                                int rows_per_rank, int n_ranks, int B, int L, int D, int F, int k, int crosslayer,
+                                int short_rows, int bf16, int* status, clt_stream_t stream);
 
 /* Feature-major copy of the selection: col_ptr [L, F+1], ent [L, npl] (entry slots grouped by
  * feature).  cursor [L, F] is scratch. */

@@ -26,6 +26,7 @@ def shard_weights(w, lo, hi, crosslayer):
 
 def main():
     kind, prec = sys.argv[1], sys.argv[2]
+    mode = sys.argv[3] if len(sys.argv) > 3 else "nccl"     # "fused": exchange fused into the kernels over peer memory
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -45,11 +46,25 @@ def main():
     batch, w, la = spec_inputs(spec)
     lo, hi = parallel.feature_shard(spec.d_features, rank, world)
     mod = build_module(spec, shard_weights(w, lo, hi, spec.crosslayer), dev, last_active=la[:, lo:hi].contiguous())
-    parallel.attach(mod)
+    parallel.attach(mod, fused=(mode == "fused"))
+    assert mod.tp_fused == (mode == "fused")
     loss = mod.training_step(batch.to(dev), 0)
     loss.backward()
     mod._engine.check_status("multi-GPU step")
     m = mod.model
+    if mode == "fused":
+        # a second step on the same weights reuses the peer buffers: it must reproduce the first one
+        first = [p.grad.clone() for p in mod.parameters() if p.grad is not None]
+        la_first = mod.last_active.clone()
+        mod.last_active.copy_(la[:, lo:hi].to(dev))
+        for p in mod.parameters():
+            p.grad = None
+        loss2 = mod.training_step(batch.to(dev), 1)
+        loss2.backward()
+        second = [p.grad for p in mod.parameters() if p.grad is not None]
+        same = abs(float(loss2) - float(loss)) <= 1e-6 * abs(float(loss)) and all(
+            rel_err(a, b) < 1e-5 for a, b in zip(second, first)) and torch.equal(mod.last_active, la_first)
+        assert same, "the second step on the same weights differs from the first"
     # gather the feature-sharded gradients on every rank
     def gather(t, dim):
         parts = [torch.empty_like(t) for _ in range(world)]

@@ -11,13 +11,16 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parents[1]
 
 
-@pytest.mark.parametrize("prec", ["fp32", "bf16"])
-@pytest.mark.parametrize("kind", ["jumprelu", "topk", "batchtopk"])
-def test_two_shards_match_unsharded_oracle(kind, prec):
+CASES = [(k, p, "nccl") for k in ("jumprelu", "topk", "batchtopk") for p in ("fp32", "bf16")]
+CASES += [("topk", "fp32", "fused"), ("topk", "bf16", "fused")]   # exchange fused into the kernels over peer memory
+
+
+@pytest.mark.parametrize("kind,prec,mode", CASES)
+def test_two_shards_match_unsharded_oracle(kind, prec, mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29533", str(ROOT / "tests" / "mp_worker.py"), kind, prec]
+           "127.0.0.1", "--master-port", "29533", str(ROOT / "tests" / "mp_worker.py"), kind, prec, mode]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
