@@ -377,7 +377,7 @@ __global__ void loss_bwd_vec_kernel(const float* __restrict__ recon, const float
 // summed reconstructions of rows [b_lo, b_lo + b_cnt) as [b_cnt, L, D]; the gradient rows it derives
 // are written straight into every rank's [L, B, D] gradient buffer (16/8-byte stores over NVLink for
 // the peers), so no collective has to move them afterwards.  db_dec receives this rank's partial
-// column sums.  Same arithmetic as loss_bwd_vec_kernel; needs D % 4 == 0.
+// column sums.  Same arithmetic as loss_bwd_vec_kernel.
 constexpr int kMaxPushRanks = 16;
 struct PushPtrs {
   unsigned long long drecon[kMaxPushRanks];
@@ -385,6 +385,25 @@ struct PushPtrs {
   int n;
 };
 
+template <class TOut>
+__device__ __forceinline__ void store8_as(TOut* p, const float (&v)[8]);
+template <>
+__device__ __forceinline__ void store8_as<float>(float* p, const float (&v)[8]) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void store8_as<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
+  uint4 t;
+  t.x = *reinterpret_cast<unsigned*>(&a), t.y = *reinterpret_cast<unsigned*>(&b);
+  t.z = *reinterpret_cast<unsigned*>(&c), t.w = *reinterpret_cast<unsigned*>(&d);
+  *reinterpret_cast<uint4*>(p) = t;
+}
+
+// 8 consecutive columns per thread (blockDim (32, 8) covers 256 columns): the gradient rows leave as
+// 16-byte stores, which is what the NVLink path to the peers' buffers wants.  Needs D % 8 == 0.
 template <class TIn, class TOut>
 __global__ void loss_bwd_push_kernel(const float* __restrict__ recon, const float* __restrict__ aux,
                                      const TIn* __restrict__ batch, const float* __restrict__ mu,
@@ -392,31 +411,27 @@ __global__ void loss_bwd_push_kernel(const float* __restrict__ recon, const floa
                                      PushPtrs dst, float* __restrict__ db_dec, int B, int b_lo, int b_cnt, int L,
                                      int D, int rows_per_cta) {
   const int LD = L * D;
-  const int c = (blockIdx.x * 32 + threadIdx.x) * 4;
+  const int c = (blockIdx.x * 32 + threadIdx.x) * 8;
   const int r0 = blockIdx.y * rows_per_cta;
   const int r1 = min(b_cnt, r0 + rows_per_cta);
   const float gs = (gscale != nullptr ? *gscale : 1.f) / ((float)B * (float)L * (float)D);
-  float cs[4] = {0.f, 0.f, 0.f, 0.f};
+  float cs[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   if (c < LD) {
     const int l = c / D, d = c % D;
-    const float4 m = *reinterpret_cast<const float4*>(mu + c), sv = *reinterpret_cast<const float4*>(sd + c);
-    const float mm[4] = {m.x, m.y, m.z, m.w}, ss[4] = {sv.x, sv.y, sv.z, sv.w};
+    float mm[8], ss[8];
+    load8<float>(mu + c, mm);
+    load8<float>(sd + c, ss);
     for (int r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
       const int b = b_lo + r;
       const long long i = (long long)r * LD + c;
-      const TIn* yp = batch + ((long long)b * 2 + 1) * LD + c;
-      const float4 r4 = *reinterpret_cast<const float4*>(recon + i);
-      const float rr[4] = {r4.x, r4.y, r4.z, r4.w};
-      float aa[4] = {0.f, 0.f, 0.f, 0.f};
-      if (aux != nullptr) {
-        const float4 a4 = *reinterpret_cast<const float4*>(aux + i);
-        aa[0] = a4.x, aa[1] = a4.y, aa[2] = a4.z, aa[3] = a4.w;
-      }
-      float g[4], ga[4];
+      float y[8], rr[8], aa[8];
+      load8<TIn>(batch + ((long long)b * 2 + 1) * LD + c, y);
+      load8<float>(recon + i, rr);
+      if (aux != nullptr) load8<float>(aux + i, aa);
+      float g[8], ga[8];
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float y = (to_float<TIn>(yp[q]) - mm[q]) / ss[q];
-        const float diff = rr[q] - y;
+      for (int q = 0; q < 8; ++q) {
+        const float diff = rr[q] - (y[q] - mm[q]) / ss[q];
         g[q] = 2.f * diff * gs;
         ga[q] = 0.f;
         if (aux != nullptr) {
@@ -428,28 +443,19 @@ __global__ void loss_bwd_push_kernel(const float* __restrict__ recon, const floa
         cs[q] += g[q];
       }
       const long long o = ((long long)l * B + b) * D + d;
-      TOut gq[4], gaq[4];
-#pragma unroll
-      for (int q = 0; q < 4; ++q) gq[q] = from_float<TOut>(g[q]), gaq[q] = from_float<TOut>(ga[q]);
       for (int k = 0; k < dst.n; ++k) {
-        TOut* dr = reinterpret_cast<TOut*>(dst.drecon[k]) + o;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) dr[q] = gq[q];
-        if (aux != nullptr) {
-          TOut* da = reinterpret_cast<TOut*>(dst.daux[k]) + o;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) da[q] = gaq[q];
-        }
+        store8_as<TOut>(reinterpret_cast<TOut*>(dst.drecon[k]) + o, g);
+        if (aux != nullptr) store8_as<TOut>(reinterpret_cast<TOut*>(dst.daux[k]) + o, ga);
       }
     }
   }
-  __shared__ float sh[8][32][4];
+  __shared__ float sh[8][32][9];
 #pragma unroll
-  for (int q = 0; q < 4; ++q) sh[threadIdx.y][threadIdx.x][q] = cs[q];
+  for (int q = 0; q < 8; ++q) sh[threadIdx.y][threadIdx.x][q] = cs[q];
   __syncthreads();
   if (threadIdx.y == 0 && c < LD) {
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
+    for (int q = 0; q < 8; ++q) {
       float t = 0.f;
       for (int j = 0; j < (int)blockDim.y; ++j) t += sh[j][threadIdx.x][q];
       if (t != 0.f) atomicAdd(db_dec + c + q, t);
@@ -471,7 +477,7 @@ int loss_bwd_push(const float* recon, const float* aux, const void* batch, int i
   for (int k = 0; k < n_ranks; ++k) dst.drecon[k] = drecon_ptrs[k], dst.daux[k] = daux_ptrs ? daux_ptrs[k] : 0ull;
   const int LD = L * D;
   const int rows_per_cta = 64;
-  dim3 grid((LD / 4 + 31) / 32, (b_cnt + rows_per_cta - 1) / rows_per_cta), block(32, 8);
+  dim3 grid((LD / 8 + 31) / 32, (b_cnt + rows_per_cta - 1) / rows_per_cta), block(32, 8);
 #define CLT_LBP(TI, TO)                                                                                            \
   loss_bwd_push_kernel<TI, TO><<<grid, block, 0, s>>>(recon, aux, (const TI*)batch, mu, sd, gscale, aux_scale, dst, \
                                                       db_dec, B, b_lo, b_cnt, L, D, rows_per_cta)

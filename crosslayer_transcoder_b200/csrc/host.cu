@@ -123,7 +123,7 @@ int clt_loss_bwd_push(const float* recon_own, const float* aux_own, const void* 
                       int B, int b_lo, int b_cnt, int L, int D, clt_stream_t stream) {
   CLT_CHECK_ARG(recon_own && batch && mu_out && sd_out && drecon_bases && db_dec, "loss_bwd_push: null pointer");
   CLT_CHECK_ARG((aux_own == nullptr) == (daux_bases == nullptr), "loss_bwd_push: aux_own and daux_bases go together");
-  CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && D % 4 == 0, "loss_bwd_push: bad dims B=%d L=%d D=%d (D %% 4 == 0)", B, L, D);
+  CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && D % 8 == 0, "loss_bwd_push: bad dims B=%d L=%d D=%d (D %% 8 == 0)", B, L, D);
   CLT_CHECK_ARG(b_lo >= 0 && b_cnt >= 0 && b_lo + b_cnt <= B, "loss_bwd_push: rows [%d, %d) outside [0, %d)", b_lo,
                 b_lo + b_cnt, B);
   CLT_CHECK_ARG(n_ranks > 0, "loss_bwd_push: n_ranks=%d", n_ranks);
