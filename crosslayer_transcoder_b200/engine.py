@@ -322,13 +322,31 @@ class StepEngine:
             self._call("clt_encoder_fwd_store", xn, self._operand(enc.W, bf16), z, B, L, D, F, int(bf16), self.status, s)
             self._call("clt_act_fwd", z, enc.b.data, theta, norm, feat, self.fired, acc[0:2], c_sp, use_tanh, want_pre,
                        B, L, F, int(bf16), s)
-        self._call("clt_decoder_dense_fwd", feat, W_op, dec.b.data if first_rank else None, recon, B, L, D, F,
-                   crosslayer, int(bf16), self.status, s)
-        if world > 1:
+        px = None
+        if world > 1 and getattr(mod, "tp_fused", False) and D % 8 == 0:
+            # exchange fused into the kernels (see _peer_exchange): the contraction's epilogue adds each tile
+            # to the owning rank's buffer, the loss runs on the owned rows
             from .parallel import all_reduce_sum
 
-            all_reduce_sum(rbuf[: B * L * D + 2], group)      # partial reconstructions + encoder-side sums
-        self._call("clt_loss_fwd", recon, None, batch, in_code, mu_o, sd_o, acc[2:4], B, L, D, s)
+            px = self._peer_exchange(B, L, D, T, dev)
+            px["own"].local[0].zero_()
+            self._rank_barrier(px)                      # every buffer is zero before any rank adds
+            self._call("clt_decoder_dense_fwd_push", feat, W_op, dec.b.data if first_rank else None,
+                       px["recon_bases"], px["rpr"], world, B, L, D, F, crosslayer, int(bf16), self.status, s)
+            self._rank_barrier(px)                      # every rank's tiles have been added
+            b_lo, b_cnt = px["b_lo"], px["b_cnt"]
+            if b_cnt > 0:
+                self._call("clt_loss_fwd", px["recon_own"], None, batch[b_lo:b_lo + b_cnt], in_code, mu_o, sd_o,
+                           acc[2:4], b_cnt, L, D, s)
+            all_reduce_sum(acc[0:4], group)             # encoder-side sums of all shards, loss sums of all owners
+        else:
+            self._call("clt_decoder_dense_fwd", feat, W_op, dec.b.data if first_rank else None, recon, B, L, D, F,
+                       crosslayer, int(bf16), self.status, s)
+            if world > 1:
+                from .parallel import all_reduce_sum
+
+                all_reduce_sum(rbuf[: B * L * D + 2], group)      # partial reconstructions + encoder-side sums
+            self._call("clt_loss_fwd", recon, None, batch, in_code, mu_o, sd_o, acc[2:4], B, L, D, s)
         pal = float(h.get("pre_actv_loss", 0.0))
         self._call("clt_finalize_loss", acc[2:4], acc[0:2], out[0:1], out[1:5], 1.0 / (B * L * D), lam / B,
                    pal / (B * L), 0.0, s)
@@ -336,7 +354,7 @@ class StepEngine:
         return dict(kind=h["kind"], bf16=bf16, batch=batch, B=B, L=L, D=D, F=F, crosslayer=crosslayer, lam=lam,
                     pal=pal, c=float(h.get("c_sparsity", 1.0)), use_tanh=int(h.get("use_tanh", True)),
                     bandwidth=self._bandwidth(nl) if h["kind"] == "jumprelu" else 1.0, out=out,
-                    stats=(mu_i, sd_i, mu_o, sd_o), norm=norm, in_code=in_code, fused=fused)
+                    stats=(mu_i, sd_i, mu_o, sd_o), norm=norm, in_code=in_code, fused=fused, px=px)
 
     # ------------------------------------------------------------------ inference forward
     @torch.no_grad()
@@ -419,8 +437,19 @@ class StepEngine:
         gview = lambda p: self.flat.view_of(p, g)
         self._zero_small_grads()
         gs = gscale.detach().to(torch.float32).reshape(1).contiguous()
-        self._call("clt_loss_bwd", recon, None, c["batch"], c["in_code"], mu_o, sd_o, gs, 0.0, drecon, None,
-                   int(bf16), gview(dec.b), B, L, D, s)
+        px = c.get("px")
+        if px is not None:
+            from .parallel import all_reduce_sum
+
+            drecon = px["drecon"].local
+            if px["b_cnt"] > 0:
+                self._call("clt_loss_bwd_push", px["recon_own"], None, c["batch"], c["in_code"], mu_o, sd_o, gs, 0.0,
+                           px["drecon"].bases, None, self.module.tp_world, int(bf16), gview(dec.b), B, px["b_lo"],
+                           px["b_cnt"], L, D, s)
+            all_reduce_sum(gview(dec.b), self.module.tp_group)   # partial bias gradients; orders the ranks
+        else:
+            self._call("clt_loss_bwd", recon, None, c["batch"], c["in_code"], mu_o, sd_o, gs, 0.0, drecon, None,
+                       int(bf16), gview(dec.b), B, L, D, s)
         W_op, W_master, dW_dec = self._dec_flat(bf16)
         theta = nl.theta.data if c["kind"] == "jumprelu" else None
         dtheta = gview(nl.theta) if c["kind"] == "jumprelu" else None

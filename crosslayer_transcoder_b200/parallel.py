@@ -34,9 +34,9 @@ def attach(module, group: Optional[dist.ProcessGroup] = None, fused="auto") -> N
     """Mark ``module`` (built with this rank's feature slice) as one shard of a group.  With no
     group the default process group is used.
 
-    ``fused`` asks for the exchange that is fused into the kernels over peer memory (the TopK step's
-    decoder adds its partial rows straight into the owning rank's buffer, the loss backward writes its
-    rows into every rank's buffer): "auto" uses it on an NCCL group when the ranks can map each other's
+    ``fused`` asks for the exchange that is fused into the kernels over peer memory (the decoder of the
+    JumpReLU / TopK step adds its partial rows straight into the owning rank's buffer, the loss backward
+    writes its rows into every rank's buffer): "auto" uses it on an NCCL group when the ranks can map each other's
     memory, ``False`` keeps the NCCL all-reduce, ``True`` raises if peer mapping is not available."""
     if not dist.is_initialized():
         raise RuntimeError("torch.distributed is not initialised")

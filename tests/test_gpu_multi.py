@@ -12,7 +12,8 @@ ROOT = Path(__file__).resolve().parents[1]
 
 
 CASES = [(k, p, "nccl") for k in ("jumprelu", "topk", "batchtopk") for p in ("fp32", "bf16")]
-CASES += [("topk", "fp32", "fused"), ("topk", "bf16", "fused")]   # exchange fused into the kernels over peer memory
+# exchange fused into the kernels over peer memory
+CASES += [(k, p, "fused") for k in ("jumprelu", "topk") for p in ("fp32", "bf16")]
 
 
 @pytest.mark.parametrize("kind,prec,mode", CASES)
