@@ -378,6 +378,29 @@ __global__ void loss_bwd_vec_kernel(const float* __restrict__ recon, const float
 // are written straight into every rank's [L, B, D] gradient buffer (16/8-byte stores over NVLink for
 // the peers), so no collective has to move them afterwards.  db_dec receives this rank's partial
 // column sums.  Same arithmetic as loss_bwd_vec_kernel.
+// out[i] = sum over slots of slots[s * n + i]: the owner's local reduction of the partial rows that the
+// ranks stored into its slots.  n % 4 == 0.
+__global__ void sum_slots_kernel(const float4* __restrict__ slots, float4* __restrict__ out, int n_slots, long long n4) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 a = __ldcs(slots + i);
+    for (int s = 1; s < n_slots; ++s) {
+      const float4 b = __ldcs(slots + (long long)s * n4 + i);
+      a.x += b.x, a.y += b.y, a.z += b.z, a.w += b.w;
+    }
+    out[i] = a;
+  }
+}
+
+int sum_slots(const float* slots, float* out, int n_slots, long long n, cudaStream_t s) {
+  if (n <= 0) return 0;
+  const long long n4 = n / 4;
+  const int blocks = (int)min((n4 + 255) / 256, (long long)148 * 16);
+  sum_slots_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const float4*>(slots), reinterpret_cast<float4*>(out),
+                                          n_slots, n4);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
 constexpr int kMaxPushRanks = 16;
 struct PushPtrs {
   unsigned long long drecon[kMaxPushRanks];

@@ -313,19 +313,20 @@ struct DecOut {
   __device__ static void finish(const Params&, State&) {}
 };
 
-// Decoder forward with the reduce-scatter over feature-shard ranks fused in.  The token axis is split
-// over the ranks (rank o owns rows [o * rows_per_rank, (o+1) * rows_per_rank) and holds them as
-// [rows_per_rank, nz, N] fp32 in a buffer every rank has mapped); acc + bias is ADDED to the owner's
-// buffer with 16-byte red.global.add (over NVLink for the peers' buffers), tile by tile while the main
-// loop of the next tile runs.  Sub-tiles go through the staging buffer so that an instruction covers
-// 8 rows x 64 contiguous bytes.
+// Decoder forward with the exchange over feature-shard ranks fused in.  The token axis is split over
+// the ranks (rank o owns rows [o * rows_per_rank, (o+1) * rows_per_rank) and holds, in a buffer every
+// rank has mapped, one slot per source rank: [n_ranks, rows_per_rank, nz, N] fp32); acc + bias is STORED
+// into this rank's slot of the owner's buffer (16-byte stores, over NVLink for the peers' buffers),
+// tile by tile while the main loop of the next tile runs; the owner adds the slots afterwards.
+// Sub-tiles go through the staging buffer so that an instruction covers 8 rows x 64 contiguous bytes.
 constexpr int kMaxPushRanks = 16;
 struct DecOutPush {
   struct Params {
     unsigned long long bases[kMaxPushRanks];  // address of each rank's buffer
     const float* bias;                        // [nz, N] or null
     int rows_per_rank;
-    long long ld, zstride;                    // row and slab strides inside a rank's buffer
+    long long ld, zstride;                    // row and slab strides inside a slot
+    long long slot_offset;                    // this rank's slot, in elements
   };
   struct State {};
   static constexpr int kColArrays = 1;
@@ -336,7 +337,8 @@ struct DecOutPush {
   __device__ static void init(State&) {}
   __device__ static __forceinline__ float* row_ptr(const Params& p, int row, int z) {
     const int o = row / p.rows_per_rank;
-    return reinterpret_cast<float*>(p.bases[o]) + (size_t)(row - o * p.rows_per_rank) * p.ld + (size_t)z * p.zstride;
+    return reinterpret_cast<float*>(p.bases[o]) + p.slot_offset + (size_t)(row - o * p.rows_per_rank) * p.ld +
+           (size_t)z * p.zstride;
   }
   template <int CS>
   __device__ static void apply(const Params& p, State&, int z, int row, bool row_ok, int n0, int M, int N,
@@ -358,7 +360,7 @@ struct DecOutPush {
         for (int it = 0; it < 4; ++it) {
           const int r = it * 8 + (lane >> 2);
           const float4 t = *reinterpret_cast<const float4*>(stage + r * kStageRow + piece * 16);
-          if (row0 + r < M) atomicAdd(reinterpret_cast<float4*>(row_ptr(p, row0 + r, z) + n0 + 16 * h + piece * 4), t);
+          if (row0 + r < M) *reinterpret_cast<float4*>(row_ptr(p, row0 + r, z) + n0 + 16 * h + piece * 4) = t;
         }
         __syncwarp();
       }
@@ -366,7 +368,7 @@ struct DecOutPush {
       float* o = row_ptr(p, row, z) + n0;
 #pragma unroll
       for (int i = 0; i < 32; ++i)
-        if (n0 + i < N) atomicAdd(o + i, v[i]);
+        if (n0 + i < N) o[i] = v[i];
     }
   }
   __device__ static void finish(const Params&, State&) {}

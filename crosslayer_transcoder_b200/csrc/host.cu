@@ -117,6 +117,11 @@ int clt_loss_bwd(const float* recon, const float* aux, const void* batch, int in
                   (cudaStream_t)stream);
 }
 
+int clt_sum_slots(const float* slots, float* out, int n_slots, int64_t n, clt_stream_t stream) {
+  CLT_CHECK_ARG(slots && out && n_slots > 0 && n >= 0 && n % 4 == 0, "sum_slots: bad arguments (n %% 4 == 0)");
+  return sum_slots(slots, out, n_slots, (long long)n, (cudaStream_t)stream);
+}
+
 int clt_loss_bwd_push(const float* recon_own, const float* aux_own, const void* batch, int in_dtype,
                       const float* mu_out, const float* sd_out, const float* gscale, float aux_scale,
                       const uint64_t* drecon_bases, const uint64_t* daux_bases, int n_ranks, int bf16, float* db_dec,

@@ -70,21 +70,25 @@ struct Vec8<float> {
 };
 
 // Where a reconstruction row goes.  On one GPU, or when the partial reconstructions are summed by a
-// library collective afterwards, the row is stored to `recon` [B, L, D].  With the reduction fused
+// library collective afterwards, the row is stored to `recon` [B, L, D].  With the exchange fused
 // into this kernel the token axis is split over the ranks: rank o owns tokens
-// [o * rows_per_rank, (o+1) * rows_per_rank), holds them as [rows_per_rank, L, D] in a buffer that
-// every rank has mapped, and every rank ADDS its partial row there (16-byte red.global.add over
-// NVLink for the peers' buffers), so that the transfer overlaps the gather row by row.
+// [o * rows_per_rank, (o+1) * rows_per_rank) and holds, in a buffer that every rank has mapped, one
+// slot per source rank: [n_ranks, rows_per_rank, L, D].  Every rank STORES its partial row into its
+// own slot of the owner's buffer (16-byte stores, over NVLink for the peers' buffers), so that the
+// transfer overlaps the gather row by row; the owner adds the slots from its local memory afterwards
+// (clt_sum_slots).  Plain stores, because 16-byte reductions over NVLink ran at a third of the
+// stores' rate.
 constexpr int kMaxPushRanks = 16;
 struct PushDst {
   unsigned long long bases[kMaxPushRanks];  // address of each rank's buffer
   int rows_per_rank;                        // 0 = plain store to `recon`
+  long long slot_offset;                    // this rank's slot: slot * rows_per_rank * L * D elements
 };
 
 __device__ __forceinline__ float* push_row(const PushDst& p, float* recon, int b, int t, int L, int D) {
   if (p.rows_per_rank == 0) return recon + ((size_t)b * L + t) * D;
   const int o = b / p.rows_per_rank;
-  return reinterpret_cast<float*>(p.bases[o]) + ((size_t)(b - o * p.rows_per_rank) * L + t) * D;
+  return reinterpret_cast<float*>(p.bases[o]) + p.slot_offset + ((size_t)(b - o * p.rows_per_rank) * L + t) * D;
 }
 
 // =========================================================================================
@@ -148,7 +152,7 @@ sparse_dec_fwd_kernel(const int* __restrict__ idx, const float* __restrict__ val
   }
   __syncthreads();
   float* out = push_row(push, recon, b, t, L, D);
-  if (push.rows_per_rank != 0) {  // D % 8 == 0 here
+  if (D % 4 == 0) {  // 16-byte stores (always the case for pushed rows: D % 8 == 0 there)
     for (int d = 4 * threadIdx.x; d < D; d += 4 * 128) {
       float4 sum;
       sum.x = red[d] + red[D + d] + red[2 * D + d] + red[3 * D + d];
@@ -159,7 +163,7 @@ sparse_dec_fwd_kernel(const int* __restrict__ idx, const float* __restrict__ val
         const float4 bb = __ldg(reinterpret_cast<const float4*>(b_dec + (size_t)t * D + d));
         sum.x += bb.x, sum.y += bb.y, sum.z += bb.z, sum.w += bb.w;
       }
-      atomicAdd(reinterpret_cast<float4*>(out + d), sum);
+      *reinterpret_cast<float4*>(out + d) = sum;
     }
     return;
   }
@@ -249,13 +253,8 @@ sparse_dec_fwd_warp_kernel(const int* __restrict__ idx, const float* __restrict_
       float4* o = reinterpret_cast<float4*>(out + 8 * c);
       const float4 lo = make_float4(acc[i][0] + bb[0], acc[i][1] + bb[1], acc[i][2] + bb[2], acc[i][3] + bb[3]);
       const float4 hi = make_float4(acc[i][4] + bb[4], acc[i][5] + bb[5], acc[i][6] + bb[6], acc[i][7] + bb[7]);
-      if (push.rows_per_rank != 0) {
-        atomicAdd(o, lo);
-        atomicAdd(o + 1, hi);
-      } else {
-        o[0] = lo;
-        o[1] = hi;
-      }
+      o[0] = lo;
+      o[1] = hi;
     }
   }
 }
@@ -731,7 +730,7 @@ __global__ void scatter_cols_kernel(const float* __restrict__ src, const float* 
 template <class T>
 int launch_dec_fwd(const int* idx, const float* val, const int* row_start, const int* row_cnt, long long npl,
                    const void* W, const float* b_dec, float* recon, int B, int L, int D, int F, int k, int crosslayer,
-                   int short_rows, int* status, cudaStream_t s, PushDst push = PushDst{{0ull}, 0}) {
+                   int short_rows, int* status, cudaStream_t s, PushDst push = PushDst{{0ull}, 0, 0}) {
   const int vpl = (D / 8 + 31) / 32;
   dim3 grid(B, L);
   const size_t smem = 4 * (size_t)D * sizeof(float);
@@ -822,8 +821,8 @@ int clt_sparse_decoder_fwd(const int* idx, const float* val, const int* row_star
 
 int clt_sparse_decoder_fwd_push(const int* idx, const float* val, const int* row_start, const int* row_cnt, int64_t npl,
                                 const void* W_dec, const float* b_dec, const uint64_t* rank_bases, int rows_per_rank,
-                                int n_ranks, int B, int L, int D, int F, int k, int crosslayer, int short_rows,
-                                int bf16, int* status, clt_stream_t stream) {
+                                int n_ranks, int my_slot, int B, int L, int D, int F, int k, int crosslayer,
+                                int short_rows, int bf16, int* status, clt_stream_t stream) {
   CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && F > 0 && k > 0, "sparse_decoder_fwd_push: bad dims B=%d L=%d D=%d F=%d k=%d",
                 B, L, D, F, k);
   CLT_CHECK_ARG(D % 8 == 0, "sparse_decoder_fwd_push: d_acts=%d must be a multiple of 8", D);
@@ -838,7 +837,9 @@ int clt_sparse_decoder_fwd_push(const int* idx, const float* val, const int* row
                 rows_per_rank, B, kMaxPushRanks);
   PushDst push;
   for (int r = 0; r < kMaxPushRanks; ++r) push.bases[r] = r < n_ranks ? (unsigned long long)rank_bases[r] : 0ull;
+  CLT_CHECK_ARG(my_slot >= 0 && my_slot < n_ranks, "sparse_decoder_fwd_push: slot %d of %d", my_slot, n_ranks);
   push.rows_per_rank = rows_per_rank;
+  push.slot_offset = (long long)my_slot * rows_per_rank * L * D;
   if (bf16)
     return launch_dec_fwd<__nv_bfloat16>(idx, val, row_start, row_cnt, npl, W_dec, b_dec, nullptr, B, L, D, F, k,
                                          crosslayer, short_rows, status, (cudaStream_t)stream, push);

@@ -225,9 +225,9 @@ class StepEngine:
     def _peer_exchange(self, B: int, L: int, D: int, T, dev):
         """Buffers of the exchange that is fused into the kernels (feature shards on one node), created
         once per shape, collectively over the group.  The token axis is split over the ranks: this rank
-        owns rows ``[b_lo, b_lo + b_cnt)``.  ``recon_own`` / ``aux_own`` [rows_per_rank, L, D] fp32 receive
-        every rank's partial (auxiliary) reconstruction rows for the owned tokens (the decoder kernels
-        add into them);
+        owns rows ``[b_lo, b_lo + b_cnt)``.  ``slots`` [2, R, rows_per_rank, L, D] fp32 receives every rank's
+        partial (auxiliary) reconstruction rows for the owned tokens, one slot per source rank (the
+        decoder kernels store into them); ``recon_own`` / ``aux_own`` are their sums (``_sum_slots``);
         ``drecon`` / ``daux`` [L, B, D] receive every owner's gradient rows (the loss backward writes
         them into all ranks' copies)."""
         key = (B, L, D, T, dev)
@@ -241,13 +241,21 @@ class StepEngine:
         rpr = (B + world - 1) // world
         b_lo = min(B, rank * rpr)
         b_cnt = max(0, min(B, b_lo + rpr) - b_lo)
-        own = PeerBuffer((2, rpr, L, D), torch.float32, dev, group)      # [0] main, [1] auxiliary reconstruction
+        # [0] main, [1] auxiliary reconstruction; one slot per source rank
+        slots = PeerBuffer((2, world, rpr, L, D), torch.float32, dev, group)
+        own = torch.empty(2, rpr, L, D, dtype=torch.float32, device=dev)
         drecon = PeerBuffer((L, B, D), T, dev, group)
         daux = PeerBuffer((L, B, D), T, dev, group)
-        self._px = dict(key=key, rpr=rpr, b_lo=b_lo, b_cnt=b_cnt, own=own, recon_own=own.local[0],
-                        aux_own=own.local[1], recon_bases=own.bases, aux_bases=own.bases + rpr * L * D * 4,
+        self._px = dict(key=key, rpr=rpr, b_lo=b_lo, b_cnt=b_cnt, slots=slots, recon_own=own[0], aux_own=own[1],
+                        recon_bases=slots.bases, aux_bases=slots.bases + world * rpr * L * D * 4,
                         drecon=drecon, daux=daux, token=torch.zeros(1, dtype=torch.float32, device=dev))
         return self._px
+
+    def _sum_slots(self, px, which: int):
+        """Add the per-source slots of the owned rows (0: main, 1: auxiliary reconstruction)."""
+        n = px["recon_own"].numel()
+        self._call("clt_sum_slots", px["slots"].local[which], px["recon_own"] if which == 0 else px["aux_own"],
+                   self.module.tp_world, n, stream_ptr())
 
     def _rank_barrier(self, px):
         """Order the ranks on the compute stream: a one-element all-reduce.  After it, every kernel that
@@ -329,11 +337,11 @@ class StepEngine:
             from .parallel import all_reduce_sum
 
             px = self._peer_exchange(B, L, D, T, dev)
-            px["own"].local[0].zero_()
-            self._rank_barrier(px)                      # every buffer is zero before any rank adds
             self._call("clt_decoder_dense_fwd_push", feat, W_op, dec.b.data if first_rank else None,
-                       px["recon_bases"], px["rpr"], world, B, L, D, F, crosslayer, int(bf16), self.status, s)
-            self._rank_barrier(px)                      # every rank's tiles have been added
+                       px["recon_bases"], px["rpr"], world, mod.tp_rank, B, L, D, F, crosslayer, int(bf16),
+                       self.status, s)
+            self._rank_barrier(px)                      # every rank's tiles have landed in the owners' slots
+            self._sum_slots(px, 0)
             b_lo, b_cnt = px["b_lo"], px["b_cnt"]
             if b_cnt > 0:
                 self._call("clt_loss_fwd", px["recon_own"], None, batch[b_lo:b_lo + b_cnt], in_code, mu_o, sd_o,
@@ -514,7 +522,6 @@ class StepEngine:
         px = None
         if world > 1 and getattr(mod, "tp_fused", False) and k > 0 and D % 8 == 0:
             px = self._peer_exchange(B, L, D, T, dev)
-            px["own"].local.zero_()                     # ordered before any rank's adds by the collectives below
         self._call("clt_prep_input", batch, in_code, mu_i, sd_i, xn, int(bf16), B, L, D, s)
         self._call("clt_encoder_fwd_store", xn, self._operand(enc.W, bf16), z, B, L, D, F, int(bf16), self.status, s)
         kk = max(k, 1)
@@ -573,8 +580,8 @@ class StepEngine:
         def main_decoder():
             if px is not None:
                 self._call("clt_sparse_decoder_fwd_push", idx, val, None, None, B * kk, W_op, bias,
-                           px["recon_bases"], px["rpr"], world, B, L, D, F, kk, crosslayer, int(kk <= 8 * world),
-                           int(bf16), self.status, s)
+                           px["recon_bases"], px["rpr"], world, mod.tp_rank, B, L, D, F, kk, crosslayer,
+                           int(kk <= 8 * world), int(bf16), self.status, s)
                 return
             self._call("clt_sparse_decoder_fwd", idx, val, None, None, B * kk, W_op, bias, recon, B, L, D, F, kk,
                        crosslayer, int(kk <= 8 * world), int(bf16), self.status, s)
@@ -601,8 +608,8 @@ class StepEngine:
             aux_recon = aux_recon_buf
             if px is not None:
                 # the contraction's epilogue adds each tile to the owning ranks' buffers
-                self._call("clt_decoder_dense_fwd_push", a_aux, w_c, bias, px["aux_bases"], px["rpr"], world, B, L, D,
-                           nd_pad, crosslayer, int(bf16), self.status, s)
+                self._call("clt_decoder_dense_fwd_push", a_aux, w_c, bias, px["aux_bases"], px["rpr"], world,
+                           mod.tp_rank, B, L, D, nd_pad, crosslayer, int(bf16), self.status, s)
             else:
                 self._call("clt_decoder_dense_fwd", a_aux, w_c, bias, aux_recon, B, L, D, nd_pad, crosslayer,
                            int(bf16), self.status, s)
@@ -613,9 +620,12 @@ class StepEngine:
             from .parallel import all_reduce_sum
 
             main_decoder()
-            self._rank_barrier(px)                      # every rank's rows have been added
+            self._rank_barrier(px)                      # every rank's rows have landed in the owners' slots
             for h_ in pending:
                 h_.wait()
+            self._sum_slots(px, 0)
+            if aux is not None:
+                self._sum_slots(px, 1)
             b_lo, b_cnt = px["b_lo"], px["b_cnt"]
             if b_cnt > 0:
                 self._call("clt_loss_fwd", px["recon_own"], px["aux_own"] if aux is not None else None,

@@ -66,16 +66,15 @@ int clt_encoder_fwd_store(const void* xn, const void* W_enc, void* z_out, int B,
 int clt_decoder_dense_fwd(const void* feat, const void* W_dec, const float* b_dec, float* recon, int B, int L,
                           int D, int F, int crosslayer, int bf16, int* status, clt_stream_t stream);
 
-/* clt_decoder_dense_fwd fused with the reduce-scatter of the partial reconstructions over the
- * feature-shard ranks of one node (same buffer convention as clt_sparse_decoder_fwd_push: rank o owns
- * tokens [o rows_per_rank, (o+1) rows_per_rank) as [rows_per_rank, L, D] fp32, zero before the first
- * rank starts; rank_bases is a host array of n_ranks device addresses).  The contraction's epilogue
- * adds each finished tile to the owners' buffers (16-byte red.global.add, over NVLink for the peers)
- * while the tensor cores work on the next tile.  Replaces the DTensor all-reduce after the decoder
- * (crosslayer_transcoder/model/parallel.py:157-339). */
+/* clt_decoder_dense_fwd fused with the exchange of the partial reconstructions over the feature-shard
+ * ranks of one node (same buffer convention as clt_sparse_decoder_fwd_push: per-source slots
+ * [n_ranks, rows_per_rank, L, D] fp32 on the owner; rank_bases is a host array of n_ranks device
+ * addresses).  The contraction's epilogue stores each finished tile into slot my_slot of the owners'
+ * buffers (16-byte stores, over NVLink for the peers) while the tensor cores work on the next tile.
+ * Replaces the DTensor all-reduce after the decoder (crosslayer_transcoder/model/parallel.py:157-339). */
 int clt_decoder_dense_fwd_push(const void* feat, const void* W_dec, const float* b_dec, const uint64_t* rank_bases,
-                               int rows_per_rank, int n_ranks, int B, int L, int D, int F, int crosslayer, int bf16,
-                               int* status, clt_stream_t stream);
+                               int rows_per_rank, int n_ranks, int my_slot, int B, int L, int D, int F, int crosslayer,
+                               int bf16, int* status, clt_stream_t stream);
 
 /* Reconstruction MSE (clt_lightning.py:303-304) and, with aux != NULL, the TopK auxiliary
  * loss (clt_lightning.py:548-551).  acc[0] += sum diff^2, acc[1] += sum (aux + diff)^2. */
@@ -206,18 +205,22 @@ int clt_sparse_decoder_fwd(const int* idx, const float* val, const int* row_star
                            int F, int k, int crosslayer, int short_rows, int bf16, int* status,
                            clt_stream_t stream);
 
-/* clt_sparse_decoder_fwd fused with the reduce-scatter of the partial reconstructions over the
- * feature-shard ranks of one node: rank o owns tokens [o rows_per_rank, (o+1) rows_per_rank) and holds
- * their reconstructions as [rows_per_rank, L, D] fp32 in a buffer mapped into every rank's process
- * (rank_bases: host array of n_ranks device addresses, this rank's own included).  Every rank ADDS its
- * partial rows there (16-byte red.global.add, over NVLink for the peers), so the buffers must be zero
- * before the first rank starts and are complete once every rank's call has finished (the caller orders
- * the ranks with any stream-ordered collective).  The reference sums the partial decoder outputs with a
+/* clt_sparse_decoder_fwd fused with the exchange of the partial reconstructions over the feature-shard
+ * ranks of one node: rank o owns tokens [o rows_per_rank, (o+1) rows_per_rank) and holds, in a buffer
+ * mapped into every rank's process, one slot per source rank: [n_ranks, rows_per_rank, L, D] fp32
+ * (rank_bases: host array of n_ranks device addresses, this rank's own included).  This rank STORES its
+ * partial rows into slot my_slot of the owners' buffers (16-byte stores, over NVLink for the peers); once
+ * every rank's call has finished (the caller orders the ranks with any stream-ordered collective) the
+ * owner adds its slots with clt_sum_slots.  The reference sums the partial decoder outputs with a
  * DTensor all-reduce after the decoder (crosslayer_transcoder/model/parallel.py:157-339). */
 int clt_sparse_decoder_fwd_push(const int* idx, const float* val, const int* row_start, const int* row_cnt,
                                 int64_t npl, const void* W_dec, const float* b_dec, const uint64_t* rank_bases,
-                                int rows_per_rank, int n_ranks, int B, int L, int D, int F, int k, int crosslayer,
-                                int short_rows, int bf16, int* status, clt_stream_t stream);
+                                int rows_per_rank, int n_ranks, int my_slot, int B, int L, int D, int F, int k,
+                                int crosslayer, int short_rows, int bf16, int* status, clt_stream_t stream);
+
+/* out[i] = sum_s slots[s n + i], i < n (n % 4 == 0): the owner's local reduction of the slots the ranks
+ * filled with the *_push entry points.  No reference counterpart (part of the fused exchange). */
+int clt_sum_slots(const float* slots, float* out, int n_slots, int64_t n, clt_stream_t stream);
 
 /* Feature-major copy of the selection: col_ptr [L, F+1], ent [L, npl] (entry slots grouped by
  * feature).  cursor [L, F] is scratch. */

@@ -1,5 +1,5 @@
-"""The entry points of the exchange that is fused into the kernels (`*_push`), on ONE GPU: the "ranks" are
-several buffers on the same device, so the ownership arithmetic, the 16-byte reductions and the multi-
+"""The entry points of the exchange that is fused into the kernels (`*_push`, `clt_sum_slots`), on ONE GPU:
+the "ranks" are several buffers on the same device, so the ownership and slot arithmetic and the multi-
 destination stores are checked against the plain entry points without needing peers.  The 2-GPU run of
 the same kernels over NVLink is tests/test_gpu_multi.py."""
 import pytest
@@ -33,19 +33,23 @@ def test_sparse_decoder_push_matches_plain(bf16, short_rows):
     lib().call("clt_sparse_decoder_fwd", idx, val, None, None, B * k, W, bias, recon, B, L, D, F, k, 1, short_rows,
                bf16, status, stream_ptr())
     rpr = (B + R - 1) // R
-    bufs = [torch.zeros(rpr, L, D, device=dev) for _ in range(R)]
-    lib().call("clt_sparse_decoder_fwd_push", idx, val, None, None, B * k, W, bias, _bases(bufs), rpr, R, B, L, D, F, k,
-               1, short_rows, bf16, status, stream_ptr())
+    bufs = [torch.zeros(R, rpr, L, D, device=dev) for _ in range(R)]      # owner buffers: one slot per source
+    lib().call("clt_sparse_decoder_fwd_push", idx, val, None, None, B * k, W, bias, _bases(bufs), rpr, R, 1, B, L, D, F,
+               k, 1, short_rows, bf16, status, stream_ptr())
     torch.cuda.synchronize()
-    got = torch.cat(bufs, 0)
     assert int(status) == 0
-    assert torch.equal(got[:B], recon)                          # one add per element onto zero: exact
+    got = torch.cat([b[1] for b in bufs], 0)                    # slot 1 of every owner
+    assert torch.equal(got[:B], recon)
     assert float(got[B:].abs().sum()) == 0.0                    # rows past B stay untouched
-    # a second contribution accumulates
-    lib().call("clt_sparse_decoder_fwd_push", idx, val, None, None, B * k, W, None, _bases(bufs), rpr, R, B, L, D, F, k,
-               1, short_rows, bf16, status, stream_ptr())
+    assert all(float(b[0].abs().sum()) == 0.0 and float(b[2].abs().sum()) == 0.0 for b in bufs)   # other slots too
+    # a second source fills another slot; the owner's sum of its slots is the reduced reconstruction
+    lib().call("clt_sparse_decoder_fwd_push", idx, val, None, None, B * k, W, None, _bases(bufs), rpr, R, 2, B, L, D, F,
+               k, 1, short_rows, bf16, status, stream_ptr())
+    own = [torch.empty(rpr, L, D, device=dev) for _ in range(R)]
+    for b, o in zip(bufs, own):
+        lib().call("clt_sum_slots", b, o, R, rpr * L * D, stream_ptr())
     torch.cuda.synchronize()
-    assert torch.allclose(torch.cat(bufs, 0)[:B], 2 * recon - bias, rtol=1e-6, atol=1e-6)
+    assert torch.allclose(torch.cat(own, 0)[:B], 2 * recon - bias, rtol=1e-6, atol=1e-6)
 
 
 @pytest.mark.parametrize("bf16", [0, 1])
@@ -65,14 +69,15 @@ def test_dense_decoder_push_matches_plain(bf16):
     recon = torch.empty(B, L, D, device=dev)
     lib().call("clt_decoder_dense_fwd", feat, W, bias, recon, B, L, D, F, 1, bf16, status, stream_ptr())
     rpr = (B + R - 1) // R
-    bufs = [torch.zeros(rpr, L, D, device=dev) for _ in range(R)]
-    lib().call("clt_decoder_dense_fwd_push", feat, W, bias, _bases(bufs), rpr, R, B, L, D, F, 1, bf16, status,
+    bufs = [torch.zeros(R, rpr, L, D, device=dev) for _ in range(R)]
+    lib().call("clt_decoder_dense_fwd_push", feat, W, bias, _bases(bufs), rpr, R, 2, B, L, D, F, 1, bf16, status,
                stream_ptr())
     torch.cuda.synchronize()
     assert int(status) == 0
-    got = torch.cat(bufs, 0)
+    got = torch.cat([b[2] for b in bufs], 0)
     assert torch.equal(got[:B], recon)
     assert float(got[B:].abs().sum()) == 0.0
+    assert all(float(b[0].abs().sum()) == 0.0 and float(b[1].abs().sum()) == 0.0 for b in bufs)
 
 
 @pytest.mark.parametrize("with_aux", [False, True])
