@@ -106,7 +106,7 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------
 # workload construction
 # --------------------------------------------------------------------------------------
-def build_on_device(spec: synthetic.WorkloadSpec, dev, rank: int, world: int, exchange: str = "nccl"):
+def build_on_device(spec: synthetic.WorkloadSpec, dev, rank: int, world: int, exchange: str = "auto"):
     """The package's training module for this rank's feature shard, weights drawn on the device."""
     import crosslayer_transcoder_b200.model as M
     from crosslayer_transcoder_b200 import parallel
@@ -268,7 +268,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(synthetic.WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--exchange", choices=["nccl", "fused", "auto"], default="nccl",
+    ap.add_argument("--exchange", choices=["nccl", "fused", "auto"], default="auto",
                     help="feature shards: sum the partial reconstructions with NCCL, or fused into the kernels "
                          "over peer memory (TopK step)")
     ap.add_argument("--override", default="", help="comma-separated field=value changes to the workload "
