@@ -270,7 +270,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", choices=["nccl", "fused", "auto"], default="auto",
                     help="feature shards: sum the partial reconstructions with NCCL, or fused into the kernels "
-                         "over peer memory (TopK step)")
+                         "over peer memory (JumpReLU and TopK steps); auto = fused where available")
     ap.add_argument("--override", default="", help="comma-separated field=value changes to the workload "
                     "(reduced shapes for profiler captures; the result is then not a benchmark value)")
     args = ap.parse_args()
