@@ -111,6 +111,12 @@ class StepEngine:
         self.launches = 0                         # kernels launched by this engine (for reporting)
         self.last_terms: Optional[torch.Tensor] = None
         self.profile: Optional[dict] = None
+        # the device status word is copied to pinned host memory after every backward and looked at,
+        # without waiting, when the next steps begin
+        self._status_host: Optional[torch.Tensor] = None
+        self._status_evt = [None, None]
+        self._status_pending = [False, False]
+        self._status_slot = 0
 
     # ------------------------------------------------------------------ setup
     def _call(self, name, *args):
@@ -167,8 +173,40 @@ class StepEngine:
             self.fired = torch.zeros(enc.n_layers, (enc.d_features + 31) // 32, dtype=torch.int32, device=device)
 
     def check_status(self, where=""):
+        """Blocking check: synchronises with the device, raises ``CltError`` if any kernel since the last
+        check gave up on a bounded wait, met an out-of-range index or overflowed a list."""
         if self.status is not None:
+            self._status_pending = [False, False]
             _lib.check_status(self.status, where)
+
+    def post_status(self):
+        """Enqueue a copy of the status word to pinned host memory (no synchronisation).  Called at the
+        end of every backward; ``poll_status`` reads the copies that have arrived."""
+        if self.status is None:
+            return
+        if self._status_host is None:
+            self._status_host = torch.zeros(2, dtype=torch.int32).pin_memory()
+            self._status_evt = [torch.cuda.Event(), torch.cuda.Event()]
+        slot = self._status_slot
+        self._status_slot ^= 1
+        self._status_host[slot:slot + 1].copy_(self.status, non_blocking=True)
+        self._status_evt[slot].record()
+        self._status_pending[slot] = True
+
+    def poll_status(self, where="(reported by an earlier step)"):
+        """Non-blocking check on the training path: looks at the status copies whose transfer has
+        finished (normally the one of the step before last) and raises ``CltError`` on a failure code, so
+        that a run never trains on for long with partial results.  The word is sticky on the device
+        until it is reported."""
+        for slot in (0, 1):
+            if self._status_pending[slot] and self._status_evt[slot].query():
+                self._status_pending[slot] = False
+                code = int(self._status_host[slot])
+                if code != 0:
+                    self._status_pending = [False, False]
+                    self.status.zero_()
+                    raise CltError(f"device status {code:#x} {where}: "
+                                   f"{_lib.STATUS_NAMES.get(code, 'unknown code')}")
 
     # ------------------------------------------------------------------ helpers
     def _operand(self, p: torch.nn.Parameter, bf16: bool) -> torch.Tensor:
@@ -214,6 +252,71 @@ class StepEngine:
         if mode == "auto":
             return (not bf16) or D >= 1536
         return bool(mode)
+
+    def _dead_count(self, dev) -> torch.Tensor:
+        """One device int that ``clt_dead_update`` fills with the number of dead features of this rank."""
+        t = getattr(self, "_dead_cnt", None)
+        if t is None or t.device != dev:
+            t = self._dead_cnt = torch.zeros(1, dtype=torch.int32, device=dev)
+        return t
+
+    def dead_fraction(self) -> torch.Tensor:
+        """``idxs_dead.float().mean()`` of the last step (reference clt_lightning.py:286-287) as a device
+        scalar; on feature shards the mean over all shards."""
+        enc = self.module.model.encoder
+        cnt = self._dead_cnt.to(torch.float32)
+        world = getattr(self.module, "tp_world", 1)
+        if world > 1:
+            from .parallel import all_reduce_sum
+
+            all_reduce_sum(cnt, self.module.tp_group)
+        return (cnt / float(enc.n_layers * enc.d_features * world)).reshape(())
+
+    @torch.no_grad()
+    def training_metrics(self) -> Dict[str, torch.Tensor]:
+        """The scalar metrics of the reference's ``log_training_metrics`` (clt_lightning.py:131-199) for the
+        step that just ran, as device scalars under the reference's names: fraction of variance unexplained
+        (overall and per layer), MSE (overall, per layer, rescaled), the standard deviation of the
+        normalised reconstruction and L0 (overall and per layer).  Two kernels reduce buffers the step
+        already holds (``clt_recon_stats``, ``clt_count_active``); nothing is copied to the host.  On feature
+        shards every rank gets the figures of the whole model."""
+        c = getattr(self, "_last_ctx", None)
+        if c is None:
+            raise CltError("training_metrics() needs a training step to have run")
+        B, L, D, F = c["B"], c["L"], c["D"], c["F"]
+        dev = c["batch"].device
+        s = stream_ptr()
+        _, _, mu_o, sd_o = c["stats"]
+        world = getattr(self.module, "tp_world", 1)
+        group = getattr(self.module, "tp_group", None)
+        rows, b_lo, n = c["recon_rows"]
+        st = torch.zeros(L, D, 6, dtype=torch.float32, device=dev)
+        if n > 0:
+            self._call("clt_recon_stats", rows, c["batch"], c["in_code"], mu_o, sd_o, st, b_lo, n, L, D, s)
+        cnt = torch.zeros(L, dtype=torch.int64, device=dev)
+        src, code, npl = c["l0_src"]
+        self._call("clt_count_active", src, code, npl, L, cnt, s)
+        if world > 1:
+            from .parallel import all_reduce_sum
+
+            if c.get("px") is not None:
+                all_reduce_sum(st, group)           # every rank reduced its own tokens
+            all_reduce_sum(cnt, group)              # every rank counted its own features
+        yn, yn2, err, err_raw, r, r2 = st.unbind(-1)
+        ss_tot = yn2 - yn * yn / B
+        fvu = err / ss_tot
+        n_el = float(B) * L * D
+        out = {"metrics/fraction_of_variance_unexplained": fvu.mean(),
+               "metrics/train_mse": err.sum() / n_el,
+               "metrics/train_mse_rescaled": err_raw.sum() / n_el,
+               "metrics/recons_standardized_std": ((r2.sum() - r.sum() ** 2 / n_el) / (n_el - 1)).clamp_min(0).sqrt(),
+               "metrics/L0_avg_per_layer": cnt.sum().float() / (float(B) * L)}
+        fvu_l, mse_l, l0_l = fvu.mean(dim=-1), err.sum(dim=-1) / (float(B) * D), cnt.float() / float(B)
+        for l in range(L):
+            out[f"layers/fraction_of_variance_unexplained/layer_{l}"] = fvu_l[l]
+            out[f"layers/train_mse/layer_{l}"] = mse_l[l]
+            out[f"layers/L0/layer_{l}"] = l0_l[l]
+        return out
 
     def _bandwidth(self, nl) -> float:
         """JumpReLU bandwidth as a host number, read from the device buffer once."""
@@ -276,6 +379,7 @@ class StepEngine:
         batch = batch.contiguous()
         bf16 = self._precision(batch)
         self.prepare(batch.device, bf16)
+        self.poll_status()
         kind = hyper["kind"]
         if kind in ("jumprelu", "relu"):
             ctx = self._forward_dense(batch, hyper, bf16)
@@ -286,6 +390,7 @@ class StepEngine:
         else:
             raise NotImplementedError(f"nonlinearity kind {kind!r}")
         self.last_terms = ctx["out"][1:5]          # mse, sparsity, pre-activation, auxiliary summands
+        self._last_ctx = ctx
         params = self.flat.params
         return _StepFunction.apply(self, ctx, *params)
 
@@ -358,11 +463,14 @@ class StepEngine:
         pal = float(h.get("pre_actv_loss", 0.0))
         self._call("clt_finalize_loss", acc[2:4], acc[0:2], out[0:1], out[1:5], 1.0 / (B * L * D), lam / B,
                    pal / (B * L), 0.0, s)
-        self._call("clt_dead_update", mod.last_active, self.fired, None, B, int(mod.tokens_till_dead), L, F, s)
+        self._call("clt_dead_update", mod.last_active, self.fired, None, B, int(mod.tokens_till_dead), L, F,
+                   self._dead_count(dev), s)
         return dict(kind=h["kind"], bf16=bf16, batch=batch, B=B, L=L, D=D, F=F, crosslayer=crosslayer, lam=lam,
                     pal=pal, c=float(h.get("c_sparsity", 1.0)), use_tanh=int(h.get("use_tanh", True)),
                     bandwidth=self._bandwidth(nl) if h["kind"] == "jumprelu" else 1.0, out=out,
-                    stats=(mu_i, sd_i, mu_o, sd_o), norm=norm, in_code=in_code, fused=fused, px=px)
+                    stats=(mu_i, sd_i, mu_o, sd_o), norm=norm, in_code=in_code, fused=fused, px=px,
+                    recon_rows=(px["recon_own"], px["b_lo"], px["b_cnt"]) if px is not None else (recon, 0, B),
+                    l0_src=(feat, 2 if bf16 else 0, B * F))
 
     # ------------------------------------------------------------------ inference forward
     @torch.no_grad()
@@ -418,6 +526,7 @@ class StepEngine:
             self._backward_topk(ctx, gscale)
         else:
             raise NotImplementedError(ctx["kind"])
+        self.post_status()
 
     def _zero_small_grads(self):
         """Gradients accumulated with atomics start from zero; contraction outputs are overwritten."""
@@ -544,7 +653,8 @@ class StepEngine:
             idx.zero_()
             val.zero_()
         dead = ws.get("dead", (L, F), torch.uint8, dev)
-        self._call("clt_dead_update", mod.last_active, self.fired, dead, B, int(mod.tokens_till_dead), L, F, s)
+        self._call("clt_dead_update", mod.last_active, self.fired, dead, B, int(mod.tokens_till_dead), L, F,
+                   self._dead_count(dev), s)
         aux = None
         aux_recon = None
         aux_scale = float(h.get("aux_loss_scale", 0.0))
@@ -639,7 +749,9 @@ class StepEngine:
                    aux_scale if aux is not None else 0.0, s)
         return dict(kind="topk", bf16=bf16, batch=batch, B=B, L=L, D=D, F=F, k=kk, crosslayer=crosslayer, out=out,
                     stats=(mu_i, sd_i, mu_o, sd_o), in_code=in_code, aux=aux, aux_scale=aux_scale, idx=idx, val=val,
-                    px=px)
+                    px=px,
+                    recon_rows=(px["recon_own"], px["b_lo"], px["b_cnt"]) if px is not None else (recon, 0, B),
+                    l0_src=(val, 0, B * kk))
 
     # ------------------------------------------------------------------ BatchTopK path
     def _forward_batchtopk(self, batch, h, bf16):
@@ -716,7 +828,8 @@ class StepEngine:
             val.zero_()
             row_start.zero_()
             row_cnt.zero_()
-        self._call("clt_dead_update", mod.last_active, self.fired, None, B, int(mod.tokens_till_dead), L, F, s)
+        self._call("clt_dead_update", mod.last_active, self.fired, None, B, int(mod.tokens_till_dead), L, F,
+                   self._dead_count(dev), s)
         self._call("clt_sparse_decoder_fwd", idx, val, row_start, row_cnt, npl, W_op, bias, recon, B, L, D, F, 1,
                    crosslayer, int(k <= 8 * world), int(bf16), self.status, s)
         if world > 1:
@@ -727,7 +840,7 @@ class StepEngine:
         self._call("clt_finalize_loss", acc[2:4], None, out[0:1], out[1:5], 1.0 / (B * L * D), 0.0, 0.0, 0.0, s)
         return dict(kind="batchtopk", bf16=bf16, batch=batch, B=B, L=L, D=D, F=F, k=1, crosslayer=crosslayer, out=out,
                     stats=(mu_i, sd_i, mu_o, sd_o), in_code=in_code, aux=None, aux_scale=0.0, idx=idx, val=val,
-                    npl=npl, etok=etok)
+                    npl=npl, etok=etok, recon_rows=(recon, 0, B), l0_src=(val, 0, npl))
 
     def _backward_topk(self, c, gscale):
         model = self.module.model
@@ -814,13 +927,25 @@ class _StepFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         eng: StepEngine = ctx.engine
+        fp = eng.flat
+        # After an earlier backward a parameter's .grad usually IS its slice of the flat gradient buffer
+        # (autograd keeps the tensor it was handed).  The kernels overwrite that buffer, so gradients that
+        # are being accumulated (no zero_grad between two backwards, or zero_grad(set_to_none=False)) are
+        # saved first and handed back as the increment: autograd then adds the old values onto the new
+        # ones in place and .grad stays the flat slice.
+        base = fp.grad.data_ptr()
+        aliased = [p.grad is not None and p.grad.data_ptr() == base + 4 * fp.offsets[id(p)] for p in fp.params]
+        saved = fp.grad.clone() if any(aliased) else None
         eng.backward(ctx.step_ctx, grad_out)
         grads = []
-        for p in eng.flat.params:
-            gv = eng.flat.view_of(p, eng.flat.grad)
-            # a parameter that already holds a gradient would be accumulated into in place;
-            # hand it a copy so the flat buffer can be reused by the next step
-            grads.append(gv.clone() if p.grad is not None else gv)
+        for p, al in zip(fp.params, aliased):
+            gv = fp.view_of(p, fp.grad)
+            if al:
+                grads.append(fp.view_of(p, saved))
+            else:
+                # a gradient held in a tensor of the caller's own is accumulated into in place:
+                # hand it a copy so the flat buffer can be reused by the next step
+                grads.append(gv.clone() if p.grad is not None else gv)
         return (None, None, *grads)
 
 
@@ -834,6 +959,38 @@ class FusedAdam(torch.optim.Optimizer):
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, decoupled=decoupled))
         self.engine = engine
         self._step = 0
+        self._linked_to = None      # the FlatParams whose moment buffers self.state points into
+
+    # ---- checkpoint resume -------------------------------------------------------------------
+    def load_state_dict(self, state_dict):
+        """Restore moments and step count (the layout of ``torch.optim.Adam.state_dict()``: per parameter
+        ``exp_avg``, ``exp_avg_sq``, ``step``).  The loaded moments are copied into the flat moment
+        buffers the kernel reads — at once when the flat buffers exist, else at the first step."""
+        super().load_state_dict(state_dict)
+        steps = [int(st["step"]) for st in self.state.values() if "step" in st]
+        self._step = max(steps) if steps else 0
+        self._linked_to = None
+        fp = self.engine.flat
+        if fp is not None and fp.is_packed():
+            self._link_state(fp)
+
+    def _link_state(self, fp: "FlatParams"):
+        """Make ``self.state[p]['exp_avg' / 'exp_avg_sq']`` views of the flat moment buffers, carrying over
+        moments that live in tensors of their own (loaded from a checkpoint, or created by the
+        per-parameter path)."""
+        fp.ensure_moments()
+        for group in self.param_groups:
+            for p in group["params"]:
+                if id(p) not in fp.offsets:
+                    continue
+                st = self.state[p]
+                for key, buf in (("exp_avg", fp.exp_avg), ("exp_avg_sq", fp.exp_avg_sq)):
+                    view = fp.view_of(p, buf)
+                    cur = st.get(key)
+                    if cur is not None and cur.data_ptr() != view.data_ptr():
+                        view.copy_(cur.to(view.dtype))
+                    st[key] = view
+        self._linked_to = fp
 
     def _flat_ready(self, group) -> bool:
         fp = self.engine.flat
@@ -859,15 +1016,12 @@ class FusedAdam(torch.optim.Optimizer):
                     int(group["decoupled"]), self._step, s)
             if len(self.param_groups) == 1 and self._flat_ready(group):
                 fp = self.engine.flat
-                fp.ensure_moments()
+                if self._linked_to is not fp or fp.exp_avg is None:
+                    self._link_state(fp)
                 self.engine._call("clt_adam_step", fp.flat, fp.grad, fp.exp_avg, fp.exp_avg_sq, fp.shadow, fp.numel,
                                   *args)
                 for p in group["params"]:
-                    st = self.state[p]
-                    if "exp_avg" not in st:
-                        st["exp_avg"] = fp.view_of(p, fp.exp_avg)
-                        st["exp_avg_sq"] = fp.view_of(p, fp.exp_avg_sq)
-                    st["step"] = self._step
+                    self.state[p]["step"] = self._step
                 continue
             # general path: one launch per parameter (still the CUDA kernel)
             fp = self.engine.flat

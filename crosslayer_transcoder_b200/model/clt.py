@@ -191,14 +191,14 @@ class CrossLayerTranscoder(SerializableModule):
         self._is_folded = True
         self.input_standardizer = self.output_standardizer = None
 
-    def save_pretrained(self, directory: Path, fold_standardizers: bool = True):
+    def save_pretrained(self, directory: Path, fold_standardizers: bool = True, reference_class_paths: bool = False):
         from safetensors.torch import save_file
 
         directory = Path(directory)
         directory.mkdir(parents=True, exist_ok=True)
         if fold_standardizers:
             self.fold()
-        cfg = self.to_config()
+        cfg = self.config_for_export(reference_class_paths)
         cfg["is_folded"] = self._is_folded
         (directory / "config.yaml").write_text(yaml.dump({"model": cfg}))
         save_file({k: v.contiguous() for k, v in self.state_dict().items()}, directory / "checkpoint.safetensors")

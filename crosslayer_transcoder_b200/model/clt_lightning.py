@@ -96,16 +96,46 @@ class CrossLayerTranscoderModule(_Base):
         return self.model(acts_norm)
 
     def configure_model(self):
-        """Nothing to shard or compile here: feature-axis sharding is set up by constructing the
-        module on each rank with its own feature slice (see ``parallel.py``)."""
+        """Feature-axis sharding of an unsharded module (reference clt_lightning.py:100-119, which applies
+        its DTensor plan when ``trainer.num_devices > 1``): with more than one device and an initialised
+        process group, every rank keeps its contiguous slice of the feature axis of the encoder, the
+        nonlinearity's thresholds, the decoder blocks and ``last_active`` (``parallel.shard_module``) and
+        joins the group (``parallel.attach``).  A module that was built from a shard and attached by hand
+        is left as it is.  ``compile`` is accepted and ignored: the step is already a fixed sequence of
+        kernels."""
+        import torch.distributed as dist
+
+        from .. import parallel
+
+        if getattr(self, "tp_world", 1) > 1:
+            return
+        n_dev = int(getattr(self.trainer, "num_devices", 1) or 1)
+        if n_dev > 1 and dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            parallel.shard_module(self, dist.get_rank(), dist.get_world_size())
+            parallel.attach(self)
 
     def _run_step(self, batch, batch_idx):
         if batch_idx == 0:
             self.model.initialize_standardizers(batch)
         loss = self._engine.forward(batch, self._hyper())
         terms = self._engine.last_terms
+        self.log("metrics/dead_features", self._engine.dead_fraction())
         self.log("training/loss", loss.detach())
+        if self.log_metrics_every and batch_idx % self.log_metrics_every == 0:
+            self.log_training_metrics(batch_idx)
         return loss, terms
+
+    def log_training_metrics(self, batch_idx=0):
+        """The scalar part of the reference's ``log_training_metrics`` (clt_lightning.py:131-199), computed
+        on the device by ``StepEngine.training_metrics`` from the buffers of the step that just ran — no
+        ``features.cpu()``.  Histograms, tables and the W&B-specific plots are left to the caller."""
+        if not hasattr(self, "tokens_seen"):
+            self.tokens_seen = 0
+        B = int(self._engine._last_ctx["B"])
+        self.tokens_seen += B * self.log_metrics_every
+        self.log("training/tokens_seen", self.tokens_seen)
+        for name, value in self._engine.training_metrics().items():
+            self.log(name, value)
 
     def training_step(self, batch, batch_idx):
         loss, _ = self._run_step(batch, batch_idx)
@@ -113,6 +143,10 @@ class CrossLayerTranscoderModule(_Base):
 
     def validation_step(self, batch, batch_idx):
         pass
+
+    def on_train_epoch_end(self):
+        """A blocking look at the device status word (``training_step`` itself only polls it)."""
+        self._engine.check_status("at the end of the epoch")
 
     def configure_optimizers(self):
         b1 = 0.9 if self.beta1 is None else self.beta1
@@ -170,5 +204,7 @@ class TopKCrossLayerTranscoderModule(CrossLayerTranscoderModule):
 
     def training_step(self, batch, batch_idx):
         loss, terms = self._run_step(batch, batch_idx)
-        self.log("training/aux_loss", terms[3])
+        # the reference logs the unscaled mean (clt_lightning.py:554); the step's summand carries the scale
+        scale = float(self.aux_loss_scale)
+        self.log("training/aux_loss", terms[3] / scale if scale != 0.0 else terms[3])
         return loss

@@ -16,12 +16,28 @@ import yaml
 from torch import nn
 
 
+_OWN_PACKAGE = "crosslayer_transcoder_b200"
+_REFERENCE_PACKAGE = "crosslayer_transcoder"
+
+#: when set (``save_pretrained(..., reference_class_paths=True)``), configs name the reference's classes
+#: (``crosslayer_transcoder.model...``) so that the reference's own ``from_pretrained`` can read them
+_emit_reference_paths = False
+
+
 def _class_path(obj) -> str:
-    return f"{type(obj).__module__}.{type(obj).__name__}"
+    mod = type(obj).__module__
+    if _emit_reference_paths and mod.startswith(_OWN_PACKAGE + "."):
+        mod = _REFERENCE_PACKAGE + mod[len(_OWN_PACKAGE):]
+    return f"{mod}.{type(obj).__name__}"
 
 
 def _resolve(path: str):
+    """Class named by a config's ``class_path``.  Paths into the reference package
+    (``crosslayer_transcoder.model.clt.Encoder`` ...), as written by the reference's ``save_pretrained``,
+    resolve to this package's classes of the same name, so its checkpoints load here unchanged."""
     mod, _, name = path.rpartition(".")
+    if mod == _REFERENCE_PACKAGE or mod.startswith(_REFERENCE_PACKAGE + "."):
+        mod = _OWN_PACKAGE + mod[len(_REFERENCE_PACKAGE):]
     return getattr(importlib.import_module(mod), name)
 
 
@@ -44,12 +60,22 @@ class SerializableModule(nn.Module):
             kwargs[key] = val
         return cls(**kwargs)
 
-    def save_pretrained(self, directory: Union[Path, str]) -> None:
+    def config_for_export(self, reference_class_paths: bool = False) -> Dict[str, Any]:
+        """``to_config()``; with ``reference_class_paths`` every ``class_path`` names the reference's class."""
+        global _emit_reference_paths
+        prev = _emit_reference_paths
+        _emit_reference_paths = bool(reference_class_paths)
+        try:
+            return self.to_config()
+        finally:
+            _emit_reference_paths = prev
+
+    def save_pretrained(self, directory: Union[Path, str], reference_class_paths: bool = False) -> None:
         from safetensors.torch import save_file
 
         directory = Path(directory)
         directory.mkdir(parents=True, exist_ok=True)
-        (directory / "config.yaml").write_text(yaml.dump({"model": self.to_config()}))
+        (directory / "config.yaml").write_text(yaml.dump({"model": self.config_for_export(reference_class_paths)}))
         save_file({k: v.contiguous() for k, v in self.state_dict().items()}, directory / "checkpoint.safetensors")
 
     @classmethod

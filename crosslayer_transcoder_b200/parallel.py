@@ -53,6 +53,43 @@ def attach(module, group: Optional[dist.ProcessGroup] = None, fused="auto") -> N
                 raise
 
 
+def shard_module(module, rank: int, world: int) -> None:
+    """Cut an unsharded training module down to ``rank``'s feature slice, in place: ``encoder.W`` /
+    ``encoder.b``, the JumpReLU ``theta``, every decoder block and the ``last_active`` counters keep
+    ``[lo, hi)`` of the feature axis (the placement of the reference's plan:
+    crosslayer_transcoder/model/parallel.py:186-192, 235-246, 303-310); ``decoder.b``, the standardizers
+    and the BatchTopK thresholds stay replicated.  Call it before the optimizer is created."""
+    from torch import nn
+
+    from .engine import StepEngine
+
+    model = module.model
+    enc, dec, nl = model.encoder, model.decoder, model.nonlinearity
+    lo, hi = feature_shard(enc.d_features, rank, world)
+
+    def cut(owner, name, axis):
+        t = getattr(owner, name)
+        new = t.detach().narrow(axis, lo, hi - lo).clone()
+        if isinstance(t, nn.Parameter):
+            setattr(owner, name, nn.Parameter(new, requires_grad=t.requires_grad))
+        else:
+            setattr(owner, name, new)
+
+    cut(enc, "W", 2)
+    cut(enc, "b", 1)
+    if dec.crosslayer:
+        for t in range(dec.n_layers):
+            cut(dec, f"W_{t}", 1)
+    else:
+        cut(dec, "W", 1)
+    if isinstance(getattr(nl, "theta", None), nn.Parameter):
+        cut(nl, "theta", 2)
+        nl.d_features = hi - lo
+    enc.d_features = dec.d_features = hi - lo
+    cut(module, "last_active", 1)
+    module._engine = StepEngine(module)         # flat buffers are rebuilt for the new shapes
+
+
 def _symm():
     """torch's symmetric-memory module, set up for plain peer pointers (no NVLink multicast binding:
     the kernels here use peer loads / stores / reductions only)."""

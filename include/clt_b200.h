@@ -150,9 +150,10 @@ int clt_norm_coef(const float* dnorm, const float* norm, float* out, int count, 
 
 /* update_dead_features (clt_lightning.py:282-288): last_active[fired]=0; last_active+=B;
  * dead = last_active > limit (dead may be NULL).  fired_bits is [L, ceil(F/32)] words, one bit
- * per feature, and is cleared for the next step. */
+ * per feature, and is cleared for the next step.  dead_count (one int, may be NULL) receives the
+ * number of dead features, the numerator of the logged metrics/dead_features (clt_lightning.py:287). */
 int clt_dead_update(int64_t* last_active, uint32_t* fired_bits, uint8_t* dead, int64_t B, int64_t limit, int L,
-                    int F, clt_stream_t stream);
+                    int F, int* dead_count, clt_stream_t stream);
 
 /* ---- TopK path --------------------------------------------------------------------------- */
 
@@ -300,6 +301,23 @@ int clt_batchtopk_collect(const void* z, const float* b_enc, uint64_t* state, co
                           int* status, clt_stream_t stream);
 /* threshold[g] <- (1 - e) threshold[g] + e * smallest kept value of group g (topk.py:94-95, 131-132). */
 int clt_batchtopk_threshold_update(uint64_t* state, float* threshold, float e, int groups, clt_stream_t stream);
+
+/* ---- training metrics ---------------------------------------------------------------------- */
+
+/* The sums behind the reconstruction metrics of log_training_metrics (clt_lightning.py:131-199),
+ * taken on the device instead of after a copy of the features to the host.  For the n_rows tokens
+ * b_lo .. b_lo + n_rows - 1 (recon_rows [n_rows, L, D] fp32 holds their normalised reconstructions;
+ * batch is the whole [B, 2, L, D] batch) and every (layer, dim) c:
+ *   out[c, 0..5] += sum yn, sum yn^2, sum (yn - r)^2, sum (y - (r sd + mu))^2, sum r, sum r^2
+ * with yn = (y - mu) / sd the standardised target.  out [L, D, 6] fp32 is accumulated into (zero it
+ * first; feature-shard ranks that each hold some of the rows add theirs and sum over the ranks). */
+int clt_recon_stats(const float* recon_rows, const void* batch, int in_dtype, const float* mu_out,
+                    const float* sd_out, float* out, int b_lo, int n_rows, int L, int D, clt_stream_t stream);
+
+/* out[l] += number of positive elements of x[l, 0 .. n_per_layer) (x: dtype 0 fp32 / 1 fp16 / 2 bf16): the
+ * L0 counts of clt_lightning.py:187-199 from the dense features [L, B, F] or from a sparse value list
+ * [L, npl].  out: L 64-bit counters, accumulated into. */
+int clt_count_active(const void* x, int dtype, int64_t n_per_layer, int L, uint64_t* out, clt_stream_t stream);
 
 /* torch.optim.Adam / AdamW step (clt_lightning.py:339-352) over one flat fp32 buffer; `step`
  * counts from 1.  shadow_bf16 (may be NULL) receives the bf16 copy of the new parameters. */

@@ -60,15 +60,44 @@ def test_scaled_backward_scales_every_gradient():
 
 
 def test_gradient_accumulation_keeps_earlier_gradients():
-    """A second backward without zero_grad adds to the first (the flat gradient buffer is reused, so the
-    step hands out copies when a parameter already holds a gradient)."""
+    """A second backward on ANOTHER batch without zero_grad adds to the first.  After the first backward
+    every .grad is its slice of the flat gradient buffer, which the second backward's kernels overwrite:
+    the step must carry the earlier values over."""
+    spec = _spec()
+    batch, w, la = spec_inputs(spec)
+    batch2, _, _ = spec_inputs(spec, seed=77)
+    dev = torch.device("cuda:0")
+    b1, b2 = batch.to(dev), batch2.to(dev)
+    singles = []
+    for b in (b1, b2):
+        mod = build_module(spec, w, dev)
+        mod.model.initialize_standardizers(b1)
+        mod.training_step(b, 1).backward()
+        singles.append([g.detach().clone() for g in module_grad_list(mod)])
+    assert rel_err(singles[1][0], singles[0][0]) > 1e-2          # the two batches give different gradients
+    mod = build_module(spec, w, dev)
+    mod.model.initialize_standardizers(b1)
+    mod.training_step(b1, 1).backward()
+    mod.training_step(b2, 2).backward()
+    for a, g1, g2 in zip(module_grad_list(mod), *singles):
+        assert rel_err(a, g1 + g2) < 1e-5
+    # the accumulated gradients still sit in the flat buffer, so the one-launch Adam path stays available
+    opt = mod.configure_optimizers()
+    assert opt._flat_ready(opt.param_groups[0])
+
+
+def test_zero_grad_in_place_does_not_double_count():
+    """zero_grad(set_to_none=False) leaves zero-filled .grad tensors that alias the flat buffer; the next
+    backward must produce G, not 2 G."""
     spec = _spec()
     batch, w, la = spec_inputs(spec)
     dev = torch.device("cuda:0")
-    mod = build_module(spec, w, dev)
     b = batch.to(dev)
+    mod = build_module(spec, w, dev)
+    opt = mod.configure_optimizers()
     mod.training_step(b, 0).backward()
     g1 = [g.detach().clone() for g in module_grad_list(mod)]
+    opt.zero_grad(set_to_none=False)
     mod.training_step(b, 1).backward()
     for a, g in zip(module_grad_list(mod), g1):
-        assert rel_err(a, 2 * g) < 1e-5
+        assert rel_err(a, g) < 1e-5

@@ -58,7 +58,8 @@ def test_golden_topk_step(prec):
         assert ((feat > 0) != (g["feat"] > 0)).float().mean() < 1e-3  # and almost always with the reference's
     assert torch.equal(mod.last_active.cpu(), g["last_active_out"])
     assert rel_err(loss.cpu(), g["loss"]) < tol
-    assert rel_err(mod._engine.last_terms[3].cpu() / spec.aux_loss_scale, g["logged"]["training/aux_loss"]) < tol
+    assert rel_err(mod.logged["training/aux_loss"].cpu(), g["logged"]["training/aux_loss"]) < tol
+    assert rel_err(mod.logged["metrics/dead_features"].cpu(), g["logged"]["metrics/dead_features"]) < 1e-6
     for a, b in zip(module_grad_list(mod), golden_grad_list(g)):
         assert rel_err(a.cpu(), b) < tol
     if prec == "fp32":
