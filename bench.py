@@ -5,8 +5,8 @@
 Prints ONE JSON line (rank 0).  ``value`` is training tokens/s with the batch already
 resident in HBM; ``e2e`` is the same metric through the public module API with the batch
 copied from pinned host memory and the loss read back every step; ``roofline`` describes
-the kernel with the largest share of the timed region; ``cpu_baseline`` is the CPU oracle
-(a restatement of the reference's step) timed on this host on a bounded sample.
+the kernel with the largest share of the timed region; ``cpu_baseline`` is the reference's own
+training step (unmodified modules, CPU PyTorch) timed on this host on a bounded sample.
 
 For N > 1 launch with ``python -m torch.distributed.run --nproc-per-node N bench.py --gpus N``:
 the feature axis is sharded over the ranks, every rank sees the same batch (strong scaling).
@@ -106,6 +106,41 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------
 # workload construction
 # --------------------------------------------------------------------------------------
+STATIONARY_TOKENS_TILL_DEAD = 10 ** 12      # no live feature can cross this during a benchmark run
+
+
+def bench_spec(spec):
+    """The workload as the benchmark runs it: the TopK configuration's seeded dead features stay dead and no
+    live feature dies during the run (``tokens_till_dead`` far beyond the tokens of the run), so every step
+    does the same work."""
+    if spec.kind == "topk":
+        return synthetic.scaled(spec, tokens_till_dead=STATIONARY_TOKENS_TILL_DEAD)
+    return spec
+
+
+def draw_weights(mod_enc, mod_dec, spec, dev, lo: int, hi: int):
+    """Seeded weights of the benchmark configurations, identical for every number of ranks: each encoder
+    layer and each decoder block is drawn whole from its own seed on the device and this rank keeps its
+    feature slice ``[lo, hi)``.  (The loss after the same number of steps therefore agrees across 1/2/4/8
+    GPUs up to summation order.)"""
+    L, D, F = spec.n_layers, spec.d_acts, spec.d_features
+    g = torch.Generator(device=dev)
+    with torch.no_grad():
+        for l in range(L):
+            g.manual_seed(1234 + l)
+            full = (torch.rand(D, F, device=dev, generator=g) * 2 - 1) / D ** 0.5
+            mod_enc.W[l].copy_(full[:, lo:hi])
+        bound = (L * F) ** -0.5 if spec.crosslayer else F ** -0.5
+        p = 0
+        for w in mod_dec.blocks():
+            for s_ in range(w.shape[0]):
+                g.manual_seed(100_000 + p)
+                full = (torch.rand(F, D, device=dev, generator=g) * 2 - 1) * bound
+                w[s_].copy_(full[lo:hi])
+                p += 1
+        del full
+
+
 def build_on_device(spec: synthetic.WorkloadSpec, dev, rank: int, world: int, exchange: str = "auto"):
     """The package's training module for this rank's feature shard, weights drawn on the device."""
     import crosslayer_transcoder_b200.model as M
@@ -125,13 +160,9 @@ def build_on_device(spec: synthetic.WorkloadSpec, dev, rank: int, world: int, ex
             nl = M.BatchTopK(k=spec.k, e=spec.e)
         model = M.CrossLayerTranscoder(nl, enc, dec, M.DimensionwiseInputStandardizer(L, D),
                                        M.DimensionwiseOutputStandardizer(L, D))
-    g = torch.Generator(device=dev).manual_seed(1234 + rank)
-    with torch.no_grad():
-        enc.W.copy_((torch.rand(enc.W.shape, device=dev, generator=g) * 2 - 1) / D ** 0.5)
-        bound = (L * F) ** -0.5 if spec.crosslayer else F ** -0.5
-        for w in dec.blocks():
-            w.copy_((torch.rand(w.shape, device=dev, generator=g) * 2 - 1) * bound)
-    common = dict(model=model, learning_rate=spec.lr, tokens_till_dead=spec.tokens_till_dead)
+    draw_weights(enc, dec, spec, dev, lo, hi)
+    common = dict(model=model, learning_rate=spec.lr, tokens_till_dead=spec.tokens_till_dead,
+                  log_metrics_every=0)      # the metrics block is not part of the timed step
     if spec.kind == "jumprelu":
         mod = M.JumpReLUCrossLayerTranscoderModule(lambda_sparsity=spec.lambda_sparsity, c_sparsity=spec.c_sparsity,
                                                    use_tanh=spec.use_tanh, pre_actv_loss=spec.pre_actv_loss, **common)
@@ -157,38 +188,50 @@ def build_on_device(spec: synthetic.WorkloadSpec, dev, rank: int, world: int, ex
     return mod
 
 
-def algorithmic_work(spec, Fl: int, n_params: int, batch_bytes_per_elem: int, nd_pad: int = 0):
-    """Per-launch algorithmic FLOPs / bytes of every entry point, for this rank's shard.
-    Dense contractions: 2 M N K.  HBM-bound kernels: the bytes the operation has to move once
-    (gathers count every row they fetch; L2-resident re-reads are not counted)."""
+def algorithmic_work(spec, world: int, Fl: int, n_params: int, batch_bytes_per_elem: int, nd_pad: int = 0,
+                     fused_exchange: bool = False):
+    """Per-launch algorithmic FLOPs / bytes of every entry point ON THIS RANK (feature shard Fl = F / world).
+    Dense contractions: 2 M N K.  HBM-bound kernels: the bytes the operation has to move once.  Gathers have
+    two figures: the token-major count (every fetched row counted, L2 hits included) and the lower bound
+    with perfect row reuse, min(rows fetched, rows that exist); the fraction reported is of the lower bound.
+    Returns {entry point: (bound, amount)} or (bound, amount, token_major_amount)."""
     B, L, D = spec.batch, spec.n_layers, spec.d_acts
     P = L * (L + 1) // 2 if spec.crosslayer else L
     e = 2 if spec.bf16 else 4
     Fd = nd_pad if spec.kind == "topk" else Fl        # width of the dense decoder-side contractions
-    if spec.kind == "batchtopk":
-        k = max(spec.k, 1)
     enc = 2.0 * B * L * D * Fl
     dec = 2.0 * B * P * Fd * D
     bld = float(B) * L * D
+    own = bld / world if fused_exchange else bld       # rows whose loss this rank computes
     k = max(spec.k, 1)
-    rows = float(B) * k * P                            # decoder rows fetched by the sparse forward
+    rows = float(B) * k * P / world                    # decoder rows fetched by the sparse forward (expected per shard)
+    rows_unique = min(rows, float(P) * Fl)
+    ent = float(L) * B * k / world                     # selected entries on this shard (expected)
+    aux = 1 if spec.k_aux else 0
+    sparse_fwd = ("hbm", rows_unique * D * e + bld * 4, rows * D * e + bld * 4)
     work = {
         "clt_encoder_fwd_act": ("tensor", enc), "clt_encoder_fwd_store": ("tensor", enc),
         "clt_encoder_dense_bwd_dw": ("tensor", 2.0 * B * L * D * Fd if spec.kind == "topk" else enc),
-        "clt_decoder_dense_fwd": ("tensor", dec),
+        "clt_decoder_dense_fwd": ("tensor", dec), "clt_decoder_dense_fwd_push": ("tensor", dec),
         "clt_decoder_dense_bwd_dfeat": ("tensor", dec), "clt_decoder_dense_bwd_dw": ("tensor", dec),
         "clt_decoder_dense_bwd_dfeat_raw": ("tensor", dec),
         "clt_act_fwd": ("hbm", float(B) * L * Fl * e * 2), "clt_act_bwd": ("hbm", float(B) * L * Fl * e * 3),
         "clt_adam_step": ("hbm", n_params * (28.0 + (2 if spec.bf16 else 0))),
         "clt_prep_input": ("hbm", bld * (batch_bytes_per_elem + e)),
-        "clt_loss_fwd": ("hbm", bld * (4 + batch_bytes_per_elem + (4 if spec.k_aux else 0))),
-        "clt_loss_bwd": ("hbm", bld * (4 + batch_bytes_per_elem + e + ((4 + e) if spec.k_aux else 0))),
+        "clt_loss_fwd": ("hbm", own * (4 + batch_bytes_per_elem + 4 * aux)),
+        "clt_loss_bwd": ("hbm", bld * (4 + batch_bytes_per_elem + e + (4 + e) * aux)),
+        # owned rows read locally; the gradient rows written once into every rank's buffer
+        "clt_loss_bwd_push": ("hbm", own * (4 + batch_bytes_per_elem + 4 * aux) + own * world * e * (1 + aux)),
+        "clt_sum_slots": ("hbm", own * 4 * (world + 1)),
         "clt_dec_norms": ("hbm", float(P) * Fl * D * 4),
         "clt_select_topk": ("hbm", float(L) * B * Fl * e + float(L) * B * k * 8),
         "clt_select_aux": ("hbm", float(L) * B * nd_pad * e * 2),
-        "clt_sparse_decoder_fwd": ("hbm", rows * D * e + bld * 4),
+        "clt_aux_count": ("hbm", float(L) * B * nd_pad * e),
+        "clt_topk_threshold": ("hbm", float(L) * B * k * 4 * world + float(L) * B * 4),
+        "clt_topk_apply_threshold": ("hbm", float(L) * B * k * 8 * 2),
+        "clt_sparse_decoder_fwd": sparse_fwd, "clt_sparse_decoder_fwd_push": sparse_fwd,
         "clt_sparse_bwd_dec": ("hbm", float(P) * Fl * D * (e + 4)),
-        "clt_sparse_bwd_enc": ("hbm", float(L) * D * Fl * 4 + float(L) * B * k * D * e),
+        "clt_sparse_bwd_enc": ("hbm", float(L) * D * Fl * 4 + ent * D * e),
         "clt_gather_rows": ("hbm", float(P) * nd_pad * D * e * 2),
         "clt_scatter_rows": ("hbm", float(P) * nd_pad * D * 4 * 3),
         "clt_scatter_cols": ("hbm", float(L) * nd_pad * D * 4 * 3),
@@ -200,17 +243,22 @@ def algorithmic_work(spec, Fl: int, n_params: int, batch_bytes_per_elem: int, nd
 
 
 # --------------------------------------------------------------------------------------
-# CPU arm: the oracle port of the reference's step on the host cores
+# CPU arm: the reference's own training step on the host cores
 # --------------------------------------------------------------------------------------
-def cpu_sample_spec(spec):
-    """A bounded sample of the workload for the CPU: same B, D, F and step structure, two layers."""
-    return synthetic.scaled(spec, n_layers=2, name=spec.name + "_cpu_sample")
+def dense_flops(s) -> float:
+    """Dense work of the REFERENCE's step (it runs every decoder product densely; the TopK module runs the
+    decoder a second time for the auxiliary loss): what its step time scales with."""
+    Pn = s.n_layers * (s.n_layers + 1) // 2 if s.crosslayer else s.n_layers
+    passes = 2.0 if (s.kind == "topk" and s.k_aux) else 1.0
+    return 4.0 * s.batch * s.n_layers * s.d_acts * s.d_features + passes * 6.0 * s.batch * Pn * s.d_features * s.d_acts
 
 
-def time_cpu_oracle(spec, steps: int, warmup: int):
+def time_cpu_port(spec, steps: int = 1, warmup: int = 1):
+    """Fallback when the reference modules are not on this machine: the oracle restatement of the step
+    (``oracle/clt_oracle.py``) on the same 2-layer sample."""
     from oracle import clt_oracle as O
 
-    sample = cpu_sample_spec(spec)
+    sample = synthetic.scaled(spec, n_layers=2, name=spec.name + "_cpu_sample")
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     batch = synthetic.make_batch(sample, seed=5)
@@ -247,32 +295,108 @@ def time_cpu_oracle(spec, steps: int, warmup: int):
         dt = time.perf_counter() - t0
         if i >= warmup:
             times.append(dt)
-    # the sample has 2 of the workload's layers; dense work per layer pair grows with the number of
-    # decoder blocks, so scale the step time by the dense-FLOP ratio of the full workload
-    def flops(s):
-        Pn = s.n_layers * (s.n_layers + 1) // 2 if s.crosslayer else s.n_layers
-        return 4.0 * s.batch * s.n_layers * s.d_acts * s.d_features + 6.0 * s.batch * Pn * s.d_features * s.d_acts
-    scale = flops(spec) / flops(sample)
+    scale = dense_flops(spec) / dense_flops(sample)
     t_med = statistics.median(times)
-    return {"tokens_per_s": spec.batch / (t_med * scale), "cores": cores, "sample_step_s": t_med, "scale": scale,
-            "sample": f"{sample.n_layers} of {spec.n_layers} layers at full B/D/F, step time scaled by the dense-FLOP "
-                      f"ratio {scale:.1f} (extrapolated)"}
+    return {"cores": cores, "kind": "port", "sample_step_s": t_med, "scale": scale, "full": False,
+            "tokens_per_s": spec.batch / (t_med * scale), "step_s": t_med, "steps": steps, "warmup": warmup,
+            "sample": f"CPU restatement of the reference step (the reference modules are not on this machine); "
+                      f"2 of {spec.n_layers} layers at full B/D/F timed ({t_med:.2f} s per step), step time scaled "
+                      f"by the dense-work ratio {scale:.1f} (extrapolated)"}
+
+
+def _run_ref_step(workload: str, override: str, steps: int, warmup: int, mem_limit_gb: float, timeout_s: float):
+    """One run of ``oracle/ref_step.py`` in a child process (its own address-space limit and time limit);
+    returns its JSON, or {"error": ...}."""
+    cmd = [sys.executable, "-m", "oracle.ref_step", "--workload", workload, "--steps", str(steps), "--warmup",
+           str(warmup), "--device", "cpu"]
+    if override:
+        cmd += ["--override", override]
+    if mem_limit_gb > 0:
+        cmd += ["--mem-limit-gb", f"{mem_limit_gb:.1f}"]
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s, cwd=str(ROOT))
+    except subprocess.TimeoutExpired:
+        return {"error": f"no result within {timeout_s:.0f} s"}
+    for ln in reversed(r.stdout.strip().splitlines()):
+        if ln.startswith("{"):
+            return json.loads(ln)
+    return {"error": f"exit code {r.returncode}: {r.stderr.strip().splitlines()[-1] if r.stderr.strip() else ''}"[:300]}
+
+
+def host_mem_available_gb() -> float:
+    try:
+        for ln in Path("/proc/meminfo").read_text().splitlines():
+            if ln.startswith("MemAvailable:"):
+                return float(ln.split()[1]) / 1e6
+    except OSError:
+        pass
+    return 0.0
+
+
+def time_cpu_reference(spec, workload: str, override: str, full_budget_s: float):
+    """The unmodified reference step on the host cores.  First a bounded sample (2 layers, everything else
+    as in the workload; one warm-up step and one timed step).  If the sample predicts that ONE full-shape
+    step fits ``full_budget_s`` and the host has the memory, the full workload is timed as it is (no
+    extrapolation); otherwise the sample's step time is scaled by the dense-work ratio and labelled so."""
+    from oracle import ref_import
+
+    kind = "reference"
+    if not ref_import.available():
+        return time_cpu_port(spec)
+    over = (override + "," if override else "") + "n_layers=2"
+    sample_spec = synthetic.scaled(spec, n_layers=2)
+    s = _run_ref_step(workload, over, 1, 1, 0.0, 600)
+    if "error" in s:
+        return {"error": "sample: " + s["error"]}
+    scale = dense_flops(spec) / dense_flops(sample_spec)
+    predicted = s["step_s"] * scale
+    out = {"cores": s["cores"], "kind": kind, "sample_step_s": s["step_s"], "scale": scale, "full": False,
+           "tokens_per_s": spec.batch / predicted, "step_s": s["step_s"], "steps": 1, "warmup": 1,
+           "sample": f"unmodified reference modules; 2 of {spec.n_layers} layers at full B/D/F timed "
+                     f"({s['step_s']:.2f} s per step), step time scaled by the dense-work ratio {scale:.1f} "
+                     f"(extrapolated)"}
+    # memory of the full shape: fp32 p/g/m/v, plus the sample's activation footprint grown with the layer
+    # count (dense [B, L, F] intermediates) and the block count (per-target operand copies); errs high
+    def n_par(sp):
+        Pn = sp.n_layers * (sp.n_layers + 1) // 2 if sp.crosslayer else sp.n_layers
+        return sp.n_layers * sp.d_acts * sp.d_features + Pn * sp.d_features * sp.d_acts
+
+    Pf = spec.n_layers * (spec.n_layers + 1) // 2 if spec.crosslayer else spec.n_layers
+    act_sample = max(0.0, s["maxrss_gb"] - 16.0 * n_par(sample_spec) / 1e9)
+    need_gb = 16.0 * n_par(spec) / 1e9 + act_sample * (0.5 * spec.n_layers / 2 + 0.5 * Pf / (3 if spec.crosslayer else 2))
+    avail = host_mem_available_gb()
+    if full_budget_s > 0 and spec.n_layers > 2 and predicted <= full_budget_s and need_gb < 0.8 * avail:
+        wu = 1 if 2 * predicted <= full_budget_s else 0
+        k = max(1, min(3, int(full_budget_s / max(predicted, 1e-3)) - wu))
+        f = _run_ref_step(workload, override, k, wu, 0.9 * avail, 1.6 * full_budget_s + 60)
+        if "error" not in f:
+            out.update(full=True, tokens_per_s=f["tokens_per_s"], step_s=f["step_s"], steps=k, warmup=wu,
+                       sample=f"unmodified reference modules at the full workload shape, median of {k} step(s) "
+                              f"after {wu} warm-up ({f['step_s']:.2f} s per step, no extrapolation)")
+        else:
+            out["sample"] += f"; the full-shape run gave: {f['error']}"
+    return out
 
 
 # --------------------------------------------------------------------------------------
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=0,
+                    help="timed steps; 0 (default) = as many as fill about 3 s of device time")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(synthetic.WORKLOADS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-gpu"],
+                    help="ours: this package; reference: the unmodified reference step on the host cores; "
+                         "reference-gpu: the same unmodified reference modules on cuda:0 (eager PyTorch)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", choices=["nccl", "fused", "auto"], default="auto",
                     help="feature shards: sum the partial reconstructions with NCCL, or fused into the kernels "
-                         "over peer memory (JumpReLU and TopK steps); auto = fused where available")
+                         "over peer memory; auto = fused where available")
     ap.add_argument("--override", default="", help="comma-separated field=value changes to the workload "
                     "(reduced shapes for profiler captures; the result is then not a benchmark value)")
+    ap.add_argument("--ref-full-budget-s", type=float, default=150.0,
+                    help="--impl reference: time the full workload shape if one step is predicted to fit this")
     args = ap.parse_args()
     spec = synthetic.WORKLOADS[args.workload]
     if args.override:
@@ -281,27 +405,53 @@ def main():
             k, v = kv.split("=")
             over[k] = type(getattr(spec, k))(v)
         spec = synthetic.scaled(spec, name=spec.name + "[" + args.override + "]", **over)
+    spec = bench_spec(spec)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     config = {"workload": spec.name, "kind": spec.kind, "decoder": "crosslayer" if spec.crosslayer else "per-layer",
               "n_layers": spec.n_layers, "d_acts": spec.d_acts, "d_features": spec.d_features,
               "batch_tokens": spec.batch, "sharding": f"d_features/{world}",
-              "l2": "inputs_larger_than_l2 (batch and activations are hundreds of MB to GB per step)"}
+              "l2": "inputs_larger_than_l2 (batch and activations are hundreds of MB to GB per step)",
+              "weights": "seeded per layer / decoder block, identical for every number of GPUs"}
+    if spec.kind == "topk":
+        config["dead_features"] = (f"{spec.dead_fraction:.0%} seeded dead (last_active beyond tokens_till_dead), their "
+                                   "encoder bias set to -1 so they stay dead; b_enc = 0 elsewhere; no feature dies "
+                                   "during the run (stationary work per step)")
+    dtype_name = "bf16" if spec.bf16 else "fp32"
 
-    if args.impl == "reference":
+    if args.impl in ("reference", "reference-gpu"):
         if rank != 0:
             return
-        steps = max(1, min(args.steps, 3))
-        r = time_cpu_oracle(spec, steps=steps, warmup=min(args.warmup, 1))
-        line = {"impl": "reference", "metric": METRIC, "value": r["tokens_per_s"], "unit": UNIT, "n_gpus": args.gpus,
-                "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": 1e3 * r["sample_step_s"] * r["scale"],
-                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "bf16" if spec.bf16 else "fp32", "data": "synthetic", "config": config,
-                "cpu_baseline": {"value": r["tokens_per_s"], "unit": UNIT, "cores": r["cores"], "kind": "port",
-                                 "sample": r["sample"]},
-                "e2e": {"value": r["tokens_per_s"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
+        base = {"impl": "reference", "metric": METRIC, "unit": UNIT, "n_gpus": args.gpus, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": dtype_name, "data": "synthetic", "config": config}
+        if args.impl == "reference-gpu":
+            from oracle import ref_step
+
+            try:
+                r = ref_step.time_reference(spec, steps=max(1, min(args.steps or 3, 5)), warmup=1, device="cuda:0")
+            except Exception as e:          # typically torch.OutOfMemoryError at the full shapes
+                print(json.dumps({"impl": "reference", "unavailable": f"reference on cuda:0: {type(e).__name__}: "
+                                  f"{str(e).splitlines()[0][:160]}"}))
+                return
+            base.update(value=r["tokens_per_s"], steps=r["steps"], warmup=r["warmup"], ms_per_step=1e3 * r["step_s"],
+                        reference_device="cuda:0 (eager PyTorch, bf16 autocast, torch.optim.Adam(fused=True))",
+                        last_loss=r["loss"])
+            print(json.dumps(base))
+            return
+        r = time_cpu_reference(spec, args.workload, args.override, args.ref_full_budget_s)
+        if r is None or "error" in r:
+            why = "the reference modules are not available (oracle/_ref missing)" if r is None else r["error"]
+            print(json.dumps({"impl": "reference", "unavailable": why}))
+            return
+        base.update(value=r["tokens_per_s"], steps=r["steps"], warmup=r["warmup"], ms_per_step=1e3 * r["step_s"],
+                    cpu_baseline={"value": r["tokens_per_s"], "unit": UNIT, "cores": r["cores"], "kind": r["kind"],
+                                  "sample": r["sample"], "full_shape": r["full"]},
+                    e2e={"value": r["tokens_per_s"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
+        if not r["full"]:
+            base["note"] = ("ms_per_step is the timed 2-layer sample's step; value = batch_tokens / (ms_per_step x "
+                            f"{r['scale']:.1f})")
+        print(json.dumps(base))
         return
 
     import torch.distributed as dist
@@ -319,8 +469,9 @@ def main():
         torch.cuda.synchronize()
 
     mod = build_on_device(spec, dev, rank, world, args.exchange)
+    fused_exchange = bool(getattr(mod, "tp_fused", False))
     if world > 1:
-        config["exchange"] = "fused into the kernels over peer memory" if getattr(mod, "tp_fused", False) else "nccl"
+        config["exchange"] = "fused into the kernels over peer memory" if fused_exchange else "nccl"
     opt = mod.configure_optimizers()
     eng = mod._engine
     # fp16 activations (the reference's storage dtype), drawn on the device (same on every rank), with a pinned
@@ -337,9 +488,24 @@ def main():
         opt.step()
         return loss
 
-    for i in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for i in range(warmup):
         step(batch_dev, i)
     eng.check_status("warm-up")
+    steps = args.steps
+    if steps <= 0:
+        # as many steps as fill about 3 s: time two more (untimed for the result) to size the region
+        barrier()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for i in range(2):
+            step(batch_dev, 50 + i)
+        c1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([c0.elapsed_time(c1) / 2], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        steps = int(min(2000, max(20, 3000.0 / max(float(t), 1e-3))))
 
     # ---- device-resident timing, per-kernel events collected in the same region --------------
     sampler = ClockSampler(local_rank)
@@ -350,7 +516,7 @@ def main():
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(args.steps):
+    for i in range(steps):
         step(batch_dev, 100 + i)
     e1.record()
     barrier()
@@ -358,6 +524,7 @@ def main():
     prof = eng.profile_summary()
     eng.profile = None
     launches = eng.launches - launches0
+    nd_pad = int(getattr(eng, "last_nd_pad", 0))      # width of the compacted dead-feature operands in those launches
     clocks = sampler.stop() if rank == 0 else None
     eng.check_status("timed region")
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
@@ -411,9 +578,9 @@ def main():
     loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
     loss_ready = [torch.cuda.Event(), torch.cuda.Event()]
     last = 0.0
-    for i in range(args.steps):
+    for i in range(steps):
         slot = i & 1
-        if i + 1 < args.steps:
+        if i + 1 < steps:
             upload(slot ^ 1)
         torch.cuda.current_stream().wait_event(ready[slot])
         loss = step(views[slot], 200 + i)
@@ -423,8 +590,8 @@ def main():
         if i > 0:
             loss_ready[slot ^ 1].synchronize()
             last = float(loss_host[slot ^ 1])
-    loss_ready[(args.steps - 1) & 1].synchronize()
-    last = float(loss_host[(args.steps - 1) & 1])
+    loss_ready[(steps - 1) & 1].synchronize()
+    last = float(loss_host[(steps - 1) & 1])
     t1.record()
     barrier()
     e2e_ms = t0.elapsed_time(t1)
@@ -437,21 +604,29 @@ def main():
     if rank == 0:
         peaks = load_peaks()
         Fl = spec.d_features // world
-        a_aux = eng.ws.buf.get("a_aux")
-        work = algorithmic_work(spec, Fl, eng.flat.numel, batch_host.element_size(),
-                                nd_pad=int(a_aux.shape[-1]) if a_aux is not None else 0)
+        work = algorithmic_work(spec, world, Fl, eng.flat.numel, batch_host.element_size(), nd_pad=nd_pad,
+                                fused_exchange=fused_exchange)
         kernels = {}
+        flags = []
         for name, st in prof.items():
-            bound, amount = work.get(name, (None, None))
+            w = work.get(name)
             entry = {"launches": st["launches"], "ms_avg": round(st["ms_avg"], 4),
                      "share": round(st["ms_total"] / ms, 4)}
-            if bound == "tensor":
-                ach = amount / (st["ms_avg"] * 1e-3) / 1e12
-                entry.update(bound="tensor", achieved=round(ach, 1), unit="TFLOP/s",
-                             frac=round(ach / peaks["bf16_tflops"], 4))
-            elif bound == "hbm":
-                ach = amount / (st["ms_avg"] * 1e-3) / 1e9
-                entry.update(bound="hbm", achieved=round(ach, 1), unit="GB/s", frac=round(ach / peaks["hbm_gbs"], 4))
+            if w is not None:
+                bound, amount = w[0], w[1]
+                per_s = amount / (st["ms_avg"] * 1e-3)
+                if bound == "tensor":
+                    ach, peak, unit, limit = per_s / 1e12, peaks["bf16_tflops"], "TFLOP/s", 1.4
+                else:
+                    ach, peak, unit, limit = per_s / 1e9, peaks["hbm_gbs"], "GB/s", 1.2
+                entry.update(bound=bound, achieved=round(ach, 1), unit=unit, frac=round(ach / peak, 4))
+                if len(w) > 2:      # gathers: the figure above counts every distinct row once
+                    tm = w[2] / (st["ms_avg"] * 1e-3) / 1e9
+                    entry["counts"] = "each distinct decoder row once (lower bound with perfect reuse)"
+                    entry["token_major"] = {"achieved": round(tm, 1), "unit": "GB/s", "frac": round(tm / peak, 4),
+                                            "counts": "every fetched row, L2 hits included"}
+                if ach / peak > limit:
+                    flags.append(f"{name}: {ach / peak:.2f} of peak exceeds {limit}")
             kernels[name] = entry
         top = max((k for k in kernels if "bound" in kernels[k]), key=lambda k: kernels[k]["share"])
         tk = kernels[top]
@@ -459,19 +634,27 @@ def main():
                     "peak": peaks["bf16_tflops"] if tk["bound"] == "tensor" else peaks["hbm_gbs"],
                     "unit": tk["unit"], "frac": tk["frac"], "peak_source": peaks["source"],
                     "traffic": (NCU_TRAFFIC_PER_UNIT[top] * eng.flat.numel if top in NCU_TRAFFIC_PER_UNIT else None)}
-        line = {"metric": METRIC, "value": spec.batch * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
-                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+        line = {"metric": METRIC, "value": spec.batch * steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+                "steps": steps, "warmup": warmup, "ms_per_step": ms / steps,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "bf16" if spec.bf16 else "fp32", "data": "synthetic", "config": config,
+                "dtype": dtype_name, "data": "synthetic", "config": config,
                 "clocks": clocks,
-                "e2e": {"value": spec.batch * args.steps / (e2e_ms * 1e-3), "unit": UNIT,
+                "e2e": {"value": spec.batch * steps / (e2e_ms * 1e-3), "unit": UNIT,
                         "h2d_bytes_per_step": batch_host.numel() * batch_host.element_size() // world,
-                        "d2h_bytes_per_step": 4, "last_loss": last},
-                "gpu_launches": launches, "roofline": roofline, "kernels": kernels}
+                        "d2h_bytes_per_step": 8, "last_loss": last},
+                "last_loss": last, "gpu_launches": launches, "roofline": roofline, "kernels": kernels,
+                "accounting_ok": not flags}
+        if flags:
+            line["accounting_flags"] = flags
+            print("bench.py: work-model check failed: " + "; ".join(flags), file=sys.stderr)
         if world == 1 and not args.no_cpu_baseline:
-            r = time_cpu_oracle(spec, steps=1, warmup=1)
-            line["cpu_baseline"] = {"value": r["tokens_per_s"], "unit": UNIT, "cores": r["cores"], "kind": "port",
-                                    "sample": r["sample"]}
+            r = time_cpu_reference(spec, args.workload, args.override, 0.0)       # the bounded sample only
+            if r is not None and "error" not in r:
+                line["cpu_baseline"] = {"value": r["tokens_per_s"], "unit": UNIT, "cores": r["cores"], "kind": r["kind"],
+                                        "sample": r["sample"], "sample_step_s": r["sample_step_s"]}
+            else:
+                line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
+                                        "sample": "unavailable: " + ("oracle/_ref missing" if r is None else r["error"])}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -623,7 +623,7 @@ __global__ void topk_apply_threshold_kernel(int* __restrict__ idx, float* __rest
       const int slot = n_out + __popc(bal & ((1u << lane) - 1u));  // slot <= j: never overtakes the reads
       vr[slot] = v;
       ir[slot] = f;
-      if (fired_bits != nullptr) atomicOr(fired_bits + (size_t)l * words + f / 32, 1u << (f & 31));
+      if (fired_bits != nullptr && f >= 0 && f < F) atomicOr(fired_bits + (size_t)l * words + f / 32, 1u << (f & 31));
     }
     n_out += __popc(bal);
     __syncwarp();

@@ -678,6 +678,7 @@ class StepEngine:
             else:
                 nd = int(n_dead.max())                  # host read: sizes the compacted contractions
             nd_pad = max(64, _round_up(nd, 64))
+            self.last_nd_pad = nd_pad
             a_aux = ws.get("a_aux", (L, B, nd_pad), T, dev)
             if exchange:
                 # offer this shard's k_aux best dead values per row; the gather runs while the main

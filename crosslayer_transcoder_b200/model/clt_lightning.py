@@ -119,9 +119,13 @@ class CrossLayerTranscoderModule(_Base):
             self.model.initialize_standardizers(batch)
         loss = self._engine.forward(batch, self._hyper())
         terms = self._engine.last_terms
-        self.log("metrics/dead_features", self._engine.dead_fraction())
+        periodic = bool(self.log_metrics_every) and batch_idx % self.log_metrics_every == 0
+        if getattr(self, "tp_world", 1) == 1 or periodic:
+            # every step as the reference does (clt_lightning.py:287); feature shards need a collective
+            # for the mean over all shards and log it with the periodic metrics only
+            self.log("metrics/dead_features", self._engine.dead_fraction())
         self.log("training/loss", loss.detach())
-        if self.log_metrics_every and batch_idx % self.log_metrics_every == 0:
+        if periodic:
             self.log_training_metrics(batch_idx)
         return loss, terms
 

@@ -8,8 +8,9 @@ exactly as they are; three small stand-in modules (``lightning``,
 ``torchmetrics``, ``nnsight``) are enough for
 ``crosslayer_transcoder/model/clt_lightning.py`` too.
 
-Used only where the reference tree exists (the development container): by
-``tests/golden/make_golden.py`` and ``tests/test_oracle_vs_reference.py``.
+Used by ``tests/golden/make_golden.py``, ``tests/test_oracle_vs_reference.py`` and the benchmark's
+reference arm (``oracle/ref_step.py``); the sources come from the reference tree, or from the
+unmodified mirror ``oracle/make_ref.py`` makes of it.
 """
 from __future__ import annotations
 
@@ -21,7 +22,17 @@ from pathlib import Path
 
 import torch
 
-REF_ROOT = Path(os.environ.get("CLT_REFERENCE_ROOT", "/root/reference"))
+def _find_root() -> Path:
+    """The reference tree itself where it exists, else the unmodified mirror of its model package that
+    ``oracle/make_ref.py`` leaves under ``oracle/_ref/`` (which travels to machines without the tree)."""
+    cands = [Path(os.environ.get("CLT_REFERENCE_ROOT", "/root/reference")), Path(__file__).resolve().parent / "_ref"]
+    for c in cands:
+        if (c / "crosslayer_transcoder" / "model" / "clt.py").exists():
+            return c
+    return cands[0]
+
+
+REF_ROOT = _find_root()
 
 
 def available() -> bool:
@@ -57,6 +68,9 @@ def _shim_lightning():
 
         def save_hyperparameters(self, *a, **k):
             pass
+
+        def lr_schedulers(self):
+            return None
 
     class Callback:
         pass

@@ -23,6 +23,7 @@ sys.path.insert(0, str(ROOT))
 
 from crosslayer_transcoder_b200 import synthetic  # noqa: E402
 from oracle import ref_import  # noqa: E402  (only main() needs the reference)
+from oracle.ref_step import build_reference_module  # noqa: E402
 
 HERE = Path(__file__).resolve().parent
 
@@ -43,44 +44,6 @@ def cases():
             S(f"batchtopk_clt_{sfx}", kind="batchtopk", crosslayer=True, bf16=bf16, k=3, e=0.1, lr=1e-3, **base),
         ]
     return out
-
-
-def build_reference_module(ref, spec, weights, last_active):
-    clt, jr, tk, st, cl = ref.clt, ref.jumprelu, ref.topk, ref.standardize, ref.clt_lightning
-    L, D, F = spec.n_layers, spec.d_acts, spec.d_features
-    enc = clt.Encoder(D, F, L)
-    dec = (clt.CrosslayerDecoder if spec.crosslayer else clt.Decoder)(D, F, L)
-    if spec.kind == "jumprelu":
-        nl = jr.JumpReLU(theta=spec.theta, bandwidth=spec.bandwidth, n_layers=L, d_features=F)
-    elif spec.kind == "topk":
-        nl = tk.PerLayerTopK(k=spec.k)
-    else:
-        nl = tk.BatchTopK(k=spec.k, e=spec.e)
-    model = clt.CrossLayerTranscoder(nl, enc, dec, st.DimensionwiseInputStandardizer(L, D),
-                                     st.DimensionwiseOutputStandardizer(L, D))
-    with torch.no_grad():
-        enc.W.copy_(weights["W_enc"])
-        enc.b.copy_(weights["b_enc"])
-        dec.b.copy_(weights["b_dec"])
-        if spec.crosslayer:
-            for t in range(L):
-                dec.get_parameter(f"W_{t}").copy_(weights["W_dec"][t])
-        else:
-            dec.W.copy_(weights["W_dec"])
-    common = dict(model=model, learning_rate=spec.lr, log_metrics_every=10 ** 9)
-    if spec.kind == "jumprelu":
-        mod = cl.JumpReLUCrossLayerTranscoderModule(lambda_sparsity=spec.lambda_sparsity, c_sparsity=spec.c_sparsity,
-                                                    use_tanh=spec.use_tanh, pre_actv_loss=spec.pre_actv_loss, **common)
-        mod.trainer.max_steps = 1
-        mod.global_step = 1          # lambda ramp factor global_step / max_steps = 1
-    elif spec.kind == "topk":
-        mod = cl.TopKCrossLayerTranscoderModule(topk_aux=tk.PerLayerTopK(k=spec.k_aux),
-                                                tokens_till_dead=spec.tokens_till_dead,
-                                                aux_loss_scale=spec.aux_loss_scale, **common)
-        mod.last_active.copy_(last_active)
-    else:
-        mod = cl.CrossLayerTranscoderModule(**common)
-    return mod
 
 
 def case_inputs(spec):
