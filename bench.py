@@ -216,7 +216,7 @@ def algorithmic_work(spec, world: int, Fl: int, n_params: int, batch_bytes_per_e
         "clt_decoder_dense_bwd_dfeat": ("tensor", dec), "clt_decoder_dense_bwd_dw": ("tensor", dec),
         "clt_decoder_dense_bwd_dfeat_raw": ("tensor", dec),
         "clt_act_fwd": ("hbm", float(B) * L * Fl * e * 2), "clt_act_bwd": ("hbm", float(B) * L * Fl * e * 3),
-        "clt_adam_step": ("hbm", n_params * (28.0 + (2 if spec.bf16 else 0))),
+        "clt_adam_step": ("hbm", n_params * (28.0 + (2 if spec.bf16 else 0))),      # n_params: see the caller
         "clt_prep_input": ("hbm", bld * (batch_bytes_per_elem + e)),
         "clt_loss_fwd": ("hbm", own * (4 + batch_bytes_per_elem + 4 * aux)),
         "clt_loss_bwd": ("hbm", bld * (4 + batch_bytes_per_elem + e + (4 + e) * aux)),
@@ -231,6 +231,8 @@ def algorithmic_work(spec, world: int, Fl: int, n_params: int, batch_bytes_per_e
         "clt_topk_apply_threshold": ("hbm", float(L) * B * k * 8 * 2),
         "clt_sparse_decoder_fwd": sparse_fwd, "clt_sparse_decoder_fwd_push": sparse_fwd,
         "clt_sparse_bwd_dec": ("hbm", float(P) * Fl * D * (e + 4)),
+        # read p, m, v; write p, m, v (+ the bf16 copy): the gradient and the operand copy never touch memory
+        "clt_sparse_bwd_dec_adam": ("hbm", float(P) * Fl * D * (24 + (2 if spec.bf16 else 0))),
         "clt_sparse_bwd_enc": ("hbm", float(L) * D * Fl * 4 + ent * D * e),
         "clt_gather_rows": ("hbm", float(P) * nd_pad * D * e * 2),
         "clt_scatter_rows": ("hbm", float(P) * nd_pad * D * 4 * 3),
@@ -395,6 +397,9 @@ def main():
                          "over peer memory; auto = fused where available")
     ap.add_argument("--override", default="", help="comma-separated field=value changes to the workload "
                     "(reduced shapes for profiler captures; the result is then not a benchmark value)")
+    ap.add_argument("--no-fuse-optimizer", action="store_true",
+                    help="TopK / BatchTopK workloads: keep the decoder's Adam update in the optimizer kernel "
+                         "instead of applying it inside the sparse decoder backward (module.fuse_optimizer)")
     ap.add_argument("--ref-full-budget-s", type=float, default=150.0,
                     help="--impl reference: time the full workload shape if one step is predicted to fit this")
     args = ap.parse_args()
@@ -472,6 +477,13 @@ def main():
     fused_exchange = bool(getattr(mod, "tp_fused", False))
     if world > 1:
         config["exchange"] = "fused into the kernels over peer memory" if fused_exchange else "nccl"
+    if spec.kind in ("topk", "batchtopk") and not args.no_fuse_optimizer:
+        mod.fuse_optimizer = True
+        config["optimizer"] = ("Adam; the decoder's update is applied inside the sparse decoder backward "
+                               "(module.fuse_optimizer=True: same result as the separate optimizer kernel, the "
+                               "decoder gradient is never stored), the other parameters in the optimizer kernel")
+    else:
+        config["optimizer"] = "Adam, one kernel over the flat parameter buffer"
     opt = mod.configure_optimizers()
     eng = mod._engine
     # fp16 activations (the reference's storage dtype), drawn on the device (same on every rank), with a pinned
@@ -604,7 +616,13 @@ def main():
     if rank == 0:
         peaks = load_peaks()
         Fl = spec.d_features // world
-        work = algorithmic_work(spec, world, Fl, eng.flat.numel, batch_host.element_size(), nd_pad=nd_pad,
+        n_adam = eng.flat.numel
+        if getattr(mod, "fuse_optimizer", False):
+            # the optimizer kernel runs twice per step, before and after the decoder blocks; its per-launch
+            # average covers half of the remaining parameters
+            n_dec = sum((w.numel() + 63) // 64 * 64 for w in mod.model.decoder.blocks())
+            n_adam = (eng.flat.numel - n_dec) / 2.0
+        work = algorithmic_work(spec, world, Fl, n_adam, batch_host.element_size(), nd_pad=nd_pad,
                                 fused_exchange=fused_exchange)
         kernels = {}
         flags = []
@@ -633,7 +651,7 @@ def main():
         roofline = {"kernel": top, "bound": tk["bound"], "achieved": tk["achieved"],
                     "peak": peaks["bf16_tflops"] if tk["bound"] == "tensor" else peaks["hbm_gbs"],
                     "unit": tk["unit"], "frac": tk["frac"], "peak_source": peaks["source"],
-                    "traffic": (NCU_TRAFFIC_PER_UNIT[top] * eng.flat.numel if top in NCU_TRAFFIC_PER_UNIT else None)}
+                    "traffic": (NCU_TRAFFIC_PER_UNIT[top] * n_adam if top in NCU_TRAFFIC_PER_UNIT else None)}
         line = {"metric": METRIC, "value": spec.batch * steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
                 "steps": steps, "warmup": warmup, "ms_per_step": ms / steps,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None,

@@ -1,6 +1,7 @@
 // HBM-bound kernels of the training step that are not contractions:
 // standardise + cast of the input batch, reconstruction loss forward and
 // backward, decoder row norms, the dead-feature counters and the fused Adam step.
+#include "adam.cuh"
 #include "common.cuh"
 #include "kernels.h"
 
@@ -815,24 +816,6 @@ int dead_update(long long* last_active, unsigned* fired_bits, unsigned char* dea
 // Fused Adam over one flat fp32 buffer, optionally refreshing the bf16 copy that
 // the tensor-core kernels read.  28 bytes of traffic per parameter (+2 for the copy).
 // ---------------------------------------------------------------------------------
-struct AdamScalars {
-  float lr, beta1, beta2, eps, inv_bc1, inv_sqrt_bc2, weight_decay;
-  int decoupled;
-};
-
-__device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, const AdamScalars& a) {
-  if (a.weight_decay != 0.f) {
-    if (a.decoupled)
-      p *= 1.f - a.lr * a.weight_decay;
-    else
-      g = fmaf(a.weight_decay, p, g);
-  }
-  m = a.beta1 * m + (1.f - a.beta1) * g;
-  v = a.beta2 * v + (1.f - a.beta2) * g * g;
-  const float denom = sqrtf(v) * a.inv_sqrt_bc2 + a.eps;
-  p -= (a.lr * a.inv_bc1) * (m / denom);
-}
-
 __global__ void __launch_bounds__(256) adam_kernel(float* __restrict__ p, const float* __restrict__ g,
                                                    float* __restrict__ m, float* __restrict__ v,
                                                    __nv_bfloat16* __restrict__ shadow, long long n, AdamScalars a) {
@@ -872,12 +855,7 @@ int adam_step(float* p, const float* g, float* m, float* v, void* shadow_bf16, l
   CLT_CHECK_ARG(step >= 1, "adam_step: step counts from 1 (got %lld)", step);
   CLT_CHECK_ARG(((uintptr_t)p | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) % 16 == 0,
                 "adam_step: buffers must be 16-byte aligned");
-  AdamScalars a;
-  a.lr = lr, a.beta1 = beta1, a.beta2 = beta2, a.eps = eps, a.weight_decay = weight_decay, a.decoupled = decoupled;
-  const double bc1 = 1.0 - pow((double)beta1, (double)step);
-  const double bc2 = 1.0 - pow((double)beta2, (double)step);
-  a.inv_bc1 = (float)(1.0 / bc1);
-  a.inv_sqrt_bc2 = (float)(1.0 / sqrt(bc2));
+  const AdamScalars a = make_adam_scalars(lr, beta1, beta2, eps, weight_decay, decoupled, step);
   const int threads = 256;
   const long long want = (n / 4 + threads - 1) / threads + 1;
   const long long cap = (long long)num_sms * 8;

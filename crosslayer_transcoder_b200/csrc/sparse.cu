@@ -210,12 +210,12 @@ sparse_dec_fwd_warp_kernel(const int* __restrict__ idx, const float* __restrict_
       if (lane < m) {
         my_v = __ldg(val + e0 + j0 + lane);
         my_f = __ldg(idx + e0 + j0 + lane);
-        if (my_f < 0 || my_f >= F) {
-          report_status(status, kBadIndex);
-          my_v = 0.f, my_f = 0;
-        }
       }
       const int valid = __popc(__ballot_sync(0xffffffffu, my_v != 0.f));  // valid slots come first
+      if (my_v != 0.f && (my_f < 0 || my_f >= F)) {  // skip this entry only: it contributes 0 * row 0
+        report_status(status, kBadIndex);
+        my_v = 0.f, my_f = 0;
+      }
       for (int j = 0; j < valid; j += 2) {
         const bool two = j + 1 < valid;
         const float v0 = __shfl_sync(0xffffffffu, my_v, j);

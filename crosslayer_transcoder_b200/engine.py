@@ -113,6 +113,8 @@ class StepEngine:
         self.profile: Optional[dict] = None
         # the device status word is copied to pinned host memory after every backward and looked at,
         # without waiting, when the next steps begin
+        self.optimizer = None                     # the FusedAdam of configure_optimizers (for fuse_optimizer)
+        self.decoder_updated = False              # set by a backward that stepped the decoder itself
         self._status_host: Optional[torch.Tensor] = None
         self._status_evt = [None, None]
         self._status_pending = [False, False]
@@ -883,7 +885,7 @@ class StepEngine:
             self._call("clt_loss_bwd", recon, aux_recon if aux is not None else None, c["batch"], c["in_code"],
                        mu_o, sd_o, gs, c["aux_scale"] if aux is not None else 0.0, drecon, daux, int(bf16),
                        gview(dec.b), B, L, D, s)
-        W_op, _, dW_dec = self._dec_flat(bf16)
+        W_op, W_master, dW_dec = self._dec_flat(bf16)
         idx, val = c["idx"], c["val"]
         npl, etok = c.get("npl", B * k), c.get("etok")       # entry slots per layer, token of each entry
         col_ptr = ws.get("col_ptr", (L, F + 1), torch.int32, dev)
@@ -891,11 +893,11 @@ class StepEngine:
         ent = ws.get("ent", (L, npl), torch.int32, dev)
         dval = ws.get("dval", (L, npl), torch.float32, dev)
         self._call("clt_csc_build", idx, val, col_ptr, cursor, ent, npl, L, F, self.status, s)
-        self._call("clt_sparse_bwd_dec", col_ptr, ent, val, etok, npl, W_op, drecon, dW_dec, dval, B, L, D, F, k, cross,
-                   int(bf16), s)
-        self._call("clt_sparse_bwd_enc", col_ptr, ent, dval, etok, npl, xn, gview(enc.W), gview(enc.b), B, L, D, F, k,
-                   int(bf16), s)
+        fuse_opt = self._fused_optimizer(F)
+        dW_c = dpre_c = db_c = None
         if aux is not None:
+            # auxiliary path, decoder side first: its compact weight gradient is an input of the fused
+            # decoder backward + optimizer kernel
             nd_pad, a_aux, w_c = aux["nd_pad"], aux["a_aux"], aux["w_c"]
             dl, n_dead = aux["dead_list"], aux["n_dead"]
             P = w_c.shape[0]
@@ -909,10 +911,59 @@ class StepEngine:
             dW_c = ws.get("dW_c", (P, nd_pad, D), torch.float32, dev)
             self._call("clt_decoder_dense_bwd_dw", a_aux, daux, dW_c, None, None, B, L, D, nd_pad, cross, int(bf16),
                        self.status, s)
-            self._call("clt_scatter_rows", dW_c, dl, n_dead, dW_dec, L, F, D, nd_pad, cross, s)
+        if fuse_opt:
+            # the decoder rows are updated as their gradients are formed: no gradient buffer, no separate
+            # optimizer pass over the decoder (the optimizer's step() then covers the other parameters)
+            opt = self.optimizer
+            fp = self.flat
+            if opt._linked_to is not fp or fp.exp_avg is None:
+                opt._link_state(fp)
+            grp = opt.param_groups[0]
+            o0 = fp.offsets[id(dec.blocks()[0])]
+            n = W_master.numel()
+            m_dec, v_dec = fp.exp_avg[o0:o0 + n], fp.exp_avg_sq[o0:o0 + n]
+            dead_pos = None
+            if aux is not None:
+                dead_pos = ws.get("dead_pos", (L, F), torch.int32, dev)
+                self._call("clt_dead_positions", aux["dead_list"], aux["n_dead"], dead_pos, L, F, s)
+            b1, b2 = grp["betas"]
+            self._call("clt_sparse_bwd_dec_adam", col_ptr, ent, val, etok, npl, W_master, m_dec, v_dec,
+                       W_op if bf16 else None, drecon, dval, dW_c if aux is not None else None, dead_pos,
+                       aux["nd_pad"] if aux is not None else 0, B, L, D, F, k, cross, int(bf16), float(grp["lr"]),
+                       float(b1), float(b2), float(grp["eps"]), float(grp["weight_decay"]), int(grp["decoupled"]),
+                       opt._step + 1, s)
+            self.decoder_updated = True
+        else:
+            self._call("clt_sparse_bwd_dec", col_ptr, ent, val, etok, npl, W_op, drecon, dW_dec, dval, B, L, D, F, k,
+                       cross, int(bf16), s)
+            if aux is not None:
+                self._call("clt_scatter_rows", dW_c, aux["dead_list"], aux["n_dead"], dW_dec, L, F, D, aux["nd_pad"],
+                           cross, s)
+        self._call("clt_sparse_bwd_enc", col_ptr, ent, dval, etok, npl, xn, gview(enc.W), gview(enc.b), B, L, D, F, k,
+                   int(bf16), s)
+        if aux is not None:
+            nd_pad, dl, n_dead = aux["nd_pad"], aux["dead_list"], aux["n_dead"]
             dWe_c = ws.get("dWe_c", (L, D, nd_pad), torch.float32, dev)
             self._call("clt_encoder_dense_bwd_dw", xn, dpre_c, dWe_c, B, L, D, nd_pad, int(bf16), self.status, s)
             self._call("clt_scatter_cols", dWe_c, db_c, dl, n_dead, gview(enc.W), gview(enc.b), L, D, F, nd_pad, s)
+
+    def _fused_optimizer(self, F: int) -> bool:
+        """Apply the optimizer to the decoder inside the sparse backward?  Opt-in
+        (``module.fuse_optimizer = True``): the decoder blocks then never get a ``.grad`` (so no gradient
+        clipping, accumulation or unscaling on them) and are already updated when ``backward()`` returns;
+        ``optimizer.step()`` updates the remaining parameters.  Needs the optimizer that
+        ``configure_optimizers()`` returned (one parameter group) and d_features % 8 == 0."""
+        if not getattr(self.module, "fuse_optimizer", False):
+            return False
+        opt = getattr(self, "optimizer", None)
+        if opt is None:
+            raise CltError("module.fuse_optimizer needs the optimizer returned by configure_optimizers()")
+        if len(opt.param_groups) != 1:
+            raise CltError("module.fuse_optimizer supports a single parameter group")
+        if getattr(self, "decoder_updated", False):
+            raise CltError("module.fuse_optimizer: a second backward() before optimizer.step() would update the "
+                           "decoder twice (gradient accumulation is not available in this mode)")
+        return F % 8 == 0 and self.flat.is_packed()
 
 
 class _StepFunction(torch.autograd.Function):
@@ -938,10 +989,15 @@ class _StepFunction(torch.autograd.Function):
         aliased = [p.grad is not None and p.grad.data_ptr() == base + 4 * fp.offsets[id(p)] for p in fp.params]
         saved = fp.grad.clone() if any(aliased) else None
         eng.backward(ctx.step_ctx, grad_out)
+        updated = set()
+        if getattr(eng, "decoder_updated", False):
+            updated = {id(w) for w in eng.module.model.decoder.blocks()}
         grads = []
         for p, al in zip(fp.params, aliased):
             gv = fp.view_of(p, fp.grad)
-            if al:
+            if id(p) in updated:
+                grads.append(None)             # already stepped by the fused decoder backward
+            elif al:
                 grads.append(fp.view_of(p, saved))
             else:
                 # a gradient held in a tensor of the caller's own is accumulated into in place:
@@ -959,6 +1015,7 @@ class FusedAdam(torch.optim.Optimizer):
                  decoupled=False):
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, decoupled=decoupled))
         self.engine = engine
+        engine.optimizer = self
         self._step = 0
         self._linked_to = None      # the FlatParams whose moment buffers self.state points into
 
@@ -1003,6 +1060,29 @@ class FusedAdam(torch.optim.Optimizer):
                 return False
         return True
 
+    def _step_around_decoder(self, group, args):
+        eng, fp = self.engine, self.engine.flat
+        blocks = eng.module.model.decoder.blocks()
+        skip = {id(w) for w in blocks}
+        base = fp.grad.data_ptr()
+        for p in group["params"]:
+            if id(p) in skip:
+                continue
+            if p.grad is None or p.grad.data_ptr() != base + 4 * fp.offsets[id(p)]:
+                raise CltError("module.fuse_optimizer: the gradients of the other parameters must be the ones the "
+                               "fused backward produced (no clipping / replacing of .grad in this mode)")
+        if self._linked_to is not fp or fp.exp_avg is None:
+            self._link_state(fp)
+        o0 = fp.offsets[id(blocks[0])]
+        o1 = o0 + sum(_round_up(w.numel()) for w in blocks)
+        for lo, hi in ((0, o0), (o1, fp.numel)):
+            if hi > lo:
+                eng._call("clt_adam_step", fp.flat[lo:hi], fp.grad[lo:hi], fp.exp_avg[lo:hi], fp.exp_avg_sq[lo:hi],
+                          fp.shadow[lo:hi] if fp.shadow is not None else None, hi - lo, *args)
+        for p in group["params"]:
+            self.state[p]["step"] = self._step
+        eng.decoder_updated = False
+
     @torch.no_grad()
     def step(self, closure=None):
         loss = None
@@ -1015,6 +1095,11 @@ class FusedAdam(torch.optim.Optimizer):
             b1, b2 = group["betas"]
             args = (float(group["lr"]), float(b1), float(b2), float(group["eps"]), float(group["weight_decay"]),
                     int(group["decoupled"]), self._step, s)
+            if getattr(self.engine, "decoder_updated", False):
+                # the sparse backward already stepped the decoder blocks (module.fuse_optimizer): update what
+                # lies before and after them in the flat buffer
+                self._step_around_decoder(group, args)
+                continue
             if len(self.param_groups) == 1 and self._flat_ready(group):
                 fp = self.engine.flat
                 if self._linked_to is not fp or fp.exp_avg is None:

@@ -67,6 +67,9 @@ class CrossLayerTranscoderModule(_Base):
         self.precision = "auto"
         #: fuse the (Jump)ReLU into the contraction epilogues: "auto" (by d_acts), True or False
         self.fuse_activation = "auto"
+        #: TopK / BatchTopK steps: apply Adam to the decoder inside the sparse backward (see
+        #: StepEngine._fused_optimizer).  Off by default because the decoder blocks then have no ``.grad``.
+        self.fuse_optimizer = False
         self._engine = StepEngine(self)
 
     # ---- nonlinearity -> step kind -----------------------------------------------------

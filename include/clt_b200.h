@@ -254,6 +254,27 @@ int clt_sparse_bwd_dec(const int* col_ptr, const int* ent, const float* val, con
                        const void* W_dec, const void* drecon, float* dW, float* dval, int B, int L, int D, int F,
                        int k, int crosslayer, int bf16, clt_stream_t stream);
 
+/* clt_sparse_bwd_dec with the optimizer applied in the same pass (opt-in, module.fuse_optimizer): every
+ * decoder row's gradient is formed in registers (plus, for dead features, row dead_pos[s, f] of the
+ * auxiliary loss's compact gradient dW_aux [P, nd_pad, D]; both may be NULL) and the torch.optim.Adam /
+ * AdamW update (clt_lightning.py:339-352) is applied to the row at once: W_master, exp_avg, exp_avg_sq
+ * [P, F, D] fp32 are updated in place and shadow_bf16 (the operand copy; NULL with bf16 = 0) is
+ * refreshed.  The gradient is never stored and the operand copy never read (the dot products use the
+ * rounded master weights, which equal it): 26 bytes per parameter instead of 6 + 30.  Rows of features
+ * nobody selected get the zero-gradient update, so the result equals the separate kernels'.  Needs
+ * F % 8 == 0.  dval as in clt_sparse_bwd_dec.  `step` counts from 1.  The update uses approximate square
+ * root and division (relative error about 2^-22 on a step of at most lr). */
+int clt_sparse_bwd_dec_adam(const int* col_ptr, const int* ent, const float* val, const int* etok, int64_t npl,
+                            float* W_master, float* exp_avg, float* exp_avg_sq, void* shadow_bf16,
+                            const void* drecon, float* dval, const float* dW_aux, const int* dead_pos, int nd_pad,
+                            int B, int L, int D, int F, int k, int crosslayer, int bf16, float lr, float beta1,
+                            float beta2, float eps, float weight_decay, int decoupled, int64_t step,
+                            clt_stream_t stream);
+
+/* dead_pos[l, f] = j where dead_list[l][j] == f (j < n_dead[l]), -1 for live features: the inverse of
+ * clt_dead_compact's lists, [L, F]. */
+int clt_dead_positions(const int* dead_list, const int* n_dead, int* dead_pos, int L, int F, clt_stream_t stream);
+
 /* Backward of the encoder on the selected features (autograd of clt.py:157-165 through the TopK
  * scatter): dW_enc[l,:,f] = sum_{e: idx[e] = f} dval[e] xn[l,b(e),:], db_enc[l,f] = sum dval[e]; every
  * element of both is written. */

@@ -124,7 +124,34 @@ def test_c3_slice_crosslayer_topk_with_aux():
     assert rel_err(mod.logged["training/aux_loss"].cpu(), ref.terms["aux"]) < TOL
     # dead-feature counters: a feature whose only activations are the near-tie entries may differ
     assert (mod.last_active.cpu() != ref.last_active).float().mean() < 1e-3
-    _check_grads(mod, ref_grads)
+    # Features are sparse here (a few activations each), so ONE near-tie entry that falls the other way
+    # changes that feature's whole gradient column.  Gradients are therefore compared on the features
+    # whose selections (main and auxiliary) agree in every token, which must be almost all of them; the
+    # loss, the decoder bias gradient and the counters above cover the rest.
+    aux = mod._engine._last_ctx["aux"]
+    a_aux, dl, nd = aux["a_aux"].float().cpu(), aux["dead_list"].long().cpu(), aux["n_dead"].cpu()
+    aux_here = torch.zeros(Ln, B, spec.d_features)
+    for l in range(Ln):
+        n = int(nd[l])
+        aux_here[l, :, dl[l, :n]] = a_aux[l, :, :n]
+    aux_here = aux_here.permute(1, 0, 2)
+    differs = (((feat > 0) != (ref.feat > 0)) | ((aux_here > 0) != (ref.aux_feat > 0))).any(dim=0)      # [L, F]
+    print(f"c3 slice: {int(differs.sum())} of {differs.numel()} features have a selection that differs in some token")
+    assert differs.float().mean() < 2e-3
+    same = ~differs
+    g_here, names = module_grad_list(mod), ["W_enc", "b_enc"] + [f"W_dec[{t}]" for t in range(Ln)] + ["b_dec"]
+    for name, a, b in zip(names, g_here, ref_grads):
+        a = a.cpu()
+        if name == "W_enc":                      # [L, D, F]: feature columns
+            m = same.unsqueeze(1).expand_as(b)
+        elif name == "b_enc":                    # [L, F]
+            m = same
+        elif name.startswith("W_dec"):           # [(t+1), F, D]: rows of the source layers' features
+            m = same[: b.shape[0]].unsqueeze(-1).expand_as(b)
+        else:
+            m = torch.ones_like(b, dtype=torch.bool)
+        e = float((a - b)[m].abs().max() / b[m].abs().max())
+        assert e < TOL, f"{name}: {e}"
 
 
 def test_c4_slice_crosslayer_batchtopk():

@@ -101,3 +101,88 @@ def test_zero_grad_in_place_does_not_double_count():
     mod.training_step(b, 1).backward()
     for a, g in zip(module_grad_list(mod), g1):
         assert rel_err(a, g) < 1e-5
+
+
+FUSED_CASES = [
+    # kind, precision, d_acts  (a decoder row is split into 256-column parts; 520 and 2056 leave the last one ragged)
+    ("topk", "fp32", 64), ("topk", "bf16", 64), ("batchtopk", "fp32", 64), ("batchtopk", "bf16", 64),
+    ("topk", "fp32", 520), ("topk", "fp32", 2056), ("topk", "bf16", 2048), ("batchtopk", "bf16", 2048),
+]
+
+
+@pytest.mark.parametrize("kind,prec,D", FUSED_CASES)
+def test_fused_optimizer_equals_separate_kernels(kind, prec, D):
+    """module.fuse_optimizer applies Adam to the decoder inside the sparse backward.  After ONE step the
+    decoder's parameters, moments and bf16 operand copy must be where the separate backward + optimizer
+    kernels leave them to rounding (its gradient does not depend on the order of any atomic addition:
+    dead features with an auxiliary gradient and features nobody selected included); after three steps
+    everything must still agree to the accuracy the optimizer allows (the encoder gradient is summed by
+    atomics whose order differs from run to run, and Adam turns differences of gradients near eps into
+    differences of about lr / 100)."""
+    bf16 = prec == "bf16"
+    if kind == "topk":
+        spec = synthetic.WorkloadSpec("fo", 3, D, 256, 90, "topk", True, bf16, rank_u=8, n_outlier=1, k=4, k_aux=16,
+                                      aux_loss_scale=1 / 32, tokens_till_dead=500, dead_fraction=0.25, lr=1e-2)
+    else:
+        spec = synthetic.WorkloadSpec("fo", 3, D, 256, 90, "batchtopk", True, bf16, rank_u=8, n_outlier=1, k=3, e=0.1,
+                                      lr=1e-2)
+    batch, w, la = spec_inputs(spec)
+    dev = torch.device("cuda:0")
+    b = batch.to(dev)
+    runs = []
+    for fuse in (False, True):
+        mod = build_module(spec, w, dev, last_active=la)
+        mod.optimizer = "adamw" if D == 64 and kind == "topk" else "adam"
+        mod.fuse_optimizer = fuse
+        opt = mod.configure_optimizers()
+        losses, first = [], None
+        for i in range(3):
+            opt.zero_grad()
+            loss = mod.training_step(b, i)
+            loss.backward()
+            if fuse:
+                assert all(wb.grad is None for wb in mod.model.decoder.blocks())
+                assert mod.model.encoder.W.grad is not None
+            opt.step()
+            losses.append(float(loss.detach()))
+            if i == 0:
+                fp = mod._engine.flat
+                o0 = fp.offsets[id(mod.model.decoder.blocks()[0])]
+                o1 = o0 + sum(x.numel() for x in mod.model.decoder.blocks())
+                first = dict(p=fp.flat[o0:o1].clone(), m=fp.exp_avg[o0:o1].clone(), v=fp.exp_avg_sq[o0:o1].clone(),
+                             sh=None if fp.shadow is None else fp.shadow[o0:o1].float().clone())
+        mod._engine.check_status()
+        fp = mod._engine.flat
+        runs.append(dict(losses=losses, first=first, p=fp.flat.clone(), m=fp.exp_avg.clone(), v=fp.exp_avg_sq.clone(),
+                         sh=None if fp.shadow is None else fp.shadow.float().clone(),
+                         la=mod.last_active.clone(), steps=[opt.state[p]["step"] for p in mod.parameters()]))
+    a, f = runs
+    # the decoder after one step: moments to rounding; parameters to what Adam allows (where |g| is near eps
+    # the step lr g / (|g| + eps) turns the last bits of g into a visible difference, between two runs of
+    # the separate kernels just as much)
+    for key in ("m", "v"):          # (the order of a feature's entries, hence of the fp32 sums, varies from run to run)
+        assert rel_err(f["first"][key], a["first"][key]) < (1e-4 if bf16 else 1e-5), key
+    dp = (f["first"]["p"] - a["first"]["p"]).abs()
+    assert float(dp.max()) < 5e-3 * spec.lr and float((dp > 1e-7).float().mean()) < 0.05
+    assert a["losses"] == pytest.approx(f["losses"], rel=1e-5)
+    assert torch.equal(a["la"], f["la"]) and a["steps"] == f["steps"] == [3] * len(a["steps"])
+    for key in ("p", "m", "v"):
+        assert rel_err(f[key], a[key]) < (1e-2 if bf16 else 1e-3), key
+    if bf16:
+        assert torch.equal(f["sh"], f["p"].bfloat16().float())      # the operand copy follows the master weights
+
+
+def test_fused_optimizer_refuses_a_second_backward():
+    spec = synthetic.WorkloadSpec("fo2", 2, 64, 256, 50, "topk", True, False, rank_u=8, n_outlier=1, k=4, k_aux=0)
+    batch, w, la = spec_inputs(spec)
+    dev = torch.device("cuda:0")
+    mod = build_module(spec, w, dev, last_active=la)
+    mod.topk_aux.k = 0
+    mod.fuse_optimizer = True
+    opt = mod.configure_optimizers()
+    mod.training_step(batch.to(dev), 0).backward()
+    with pytest.raises(RuntimeError, match="twice"):
+        mod.training_step(batch.to(dev), 1).backward()
+    opt.step()
+    mod.training_step(batch.to(dev), 2).backward()      # after the optimizer step the next backward is fine
+    opt.step()
