@@ -545,63 +545,95 @@ def main():
     ms = float(t)
 
     # ---- end to end: pinned host batch -> device every step (prefetched on a copy stream), loss read back
-    copy_stream = torch.cuda.Stream()
-    if world > 1:
-        from crosslayer_transcoder_b200 import parallel
-
-        # the uploads' all-gather shares the step's communicator: measured at 8 GPUs, a second communicator
-        # whose kernels run beside the step's own collectives cost more (548 K tokens/s end to end) than
-        # queueing on one (708 K)
-        upload_group = dist.group.WORLD
-        chunk = (spec.batch + world - 1) // world
-        shape = (world * chunk, *batch_dev.shape[1:])
-        bufs = [torch.empty(shape, dtype=batch_dev.dtype, device=dev) for _ in range(2)]
-    else:
-        bufs = [torch.empty_like(batch_dev), torch.empty_like(batch_dev)]
-    ready = [torch.cuda.Event(), torch.cuda.Event()]
-    freed = [torch.cuda.Event(), torch.cuda.Event()]
-    views = [None, None]
-
-    def upload(slot):
-        with torch.cuda.stream(copy_stream):
-            copy_stream.wait_event(freed[slot])
-            if world > 1:
-                # every rank holds the batch on the host; each uploads 1/R of the rows and the rest
-                # arrives over NVLink
-                views[slot] = parallel.upload_batch(batch_host, bufs[slot], upload_group)
-            else:
-                bufs[slot].copy_(batch_host, non_blocking=True)
-                views[slot] = bufs[slot]
-            ready[slot].record(copy_stream)
-
-    for f in freed:
-        f.record()
-    # untimed: one upload per slot, so that the upload communicator exists and the pinned pages are mapped
-    upload(0)
-    upload(1)
-    torch.cuda.synchronize()
-    barrier()
-    t0 = torch.cuda.Event(enable_timing=True)
-    t1 = torch.cuda.Event(enable_timing=True)
-    t0.record()
-    upload(0)
-    # the loss of every step is copied to pinned host memory inside the timed region; the host looks at a
-    # step's value one step later, so that reading it does not drain the launch queue
     loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
     loss_ready = [torch.cuda.Event(), torch.cuda.Event()]
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
     last = 0.0
-    for i in range(steps):
-        slot = i & 1
-        if i + 1 < steps:
-            upload(slot ^ 1)
-        torch.cuda.current_stream().wait_event(ready[slot])
-        loss = step(views[slot], 200 + i)
-        freed[slot].record()
-        loss_host[slot:slot + 1].copy_(loss.detach().reshape(1), non_blocking=True)   # device -> host, every step
-        loss_ready[slot].record()
-        if i > 0:
-            loss_ready[slot ^ 1].synchronize()
-            last = float(loss_host[slot ^ 1])
+    row_bytes = batch_host[0].numel() * batch_host.element_size()
+    if world > 1 and eng.has_fused_exchange():
+        # every rank uploads its own token rows and copies their input halves into the peers' buffers;
+        # the step's last collective orders the copies (parallel.ShardedBatchUploader)
+        from crosslayer_transcoder_b200 import parallel
+
+        up = parallel.ShardedBatchUploader(mod, batch_host.shape, batch_host.dtype, dev)
+        h2d_bytes = (up.hi - up.lo) * row_bytes
+        config["upload"] = "each rank uploads B/N token rows and copies their input halves to the peers (NVLink)"
+        for _ in range(2):                         # untimed: maps the pinned pages, touches both buffers
+            up.upload(batch_host, full=True)
+            up.fence()
+            up.take()
+            up.release()
+        barrier()
+        t0.record()
+        up.upload(batch_host)                      # the first step's batch: ordered by an explicit fence
+        up.fence()
+        for i in range(steps):
+            slot = i & 1
+            b = up.take()
+            if i + 1 < steps:
+                up.upload(batch_host)
+            loss = step(b, 200 + i)
+            up.release()
+            loss_host[slot:slot + 1].copy_(loss.detach().reshape(1), non_blocking=True)   # device -> host, every step
+            loss_ready[slot].record()
+            if i > 0:
+                loss_ready[slot ^ 1].synchronize()
+                last = float(loss_host[slot ^ 1])
+        eng.before_last_collective = None
+    else:
+        copy_stream = torch.cuda.Stream()
+        if world > 1:
+            from crosslayer_transcoder_b200 import parallel
+
+            # NCCL form: every rank needs the whole batch; each uploads 1/N of the rows and the slices are
+            # all-gathered over NVLink on the step's communicator
+            upload_group = dist.group.WORLD
+            chunk = (spec.batch + world - 1) // world
+            shape = (world * chunk, *batch_dev.shape[1:])
+            bufs = [torch.empty(shape, dtype=batch_dev.dtype, device=dev) for _ in range(2)]
+            h2d_bytes = chunk * row_bytes
+            config["upload"] = "each rank uploads B/N token rows, NCCL all-gather of the slices"
+        else:
+            bufs = [torch.empty_like(batch_dev), torch.empty_like(batch_dev)]
+            h2d_bytes = spec.batch * row_bytes
+        ready = [torch.cuda.Event(), torch.cuda.Event()]
+        freed = [torch.cuda.Event(), torch.cuda.Event()]
+        views = [None, None]
+
+        def upload(slot):
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(freed[slot])
+                if world > 1:
+                    views[slot] = parallel.upload_batch(batch_host, bufs[slot], upload_group)
+                else:
+                    bufs[slot].copy_(batch_host, non_blocking=True)
+                    views[slot] = bufs[slot]
+                ready[slot].record(copy_stream)
+
+        for f in freed:
+            f.record()
+        # untimed: one upload per slot, so that the pinned pages are mapped
+        upload(0)
+        upload(1)
+        torch.cuda.synchronize()
+        barrier()
+        t0.record()
+        upload(0)
+        # the loss of every step is copied to pinned host memory inside the timed region; the host looks at a
+        # step's value one step later, so that reading it does not drain the launch queue
+        for i in range(steps):
+            slot = i & 1
+            if i + 1 < steps:
+                upload(slot ^ 1)
+            torch.cuda.current_stream().wait_event(ready[slot])
+            loss = step(views[slot], 200 + i)
+            freed[slot].record()
+            loss_host[slot:slot + 1].copy_(loss.detach().reshape(1), non_blocking=True)   # device -> host, every step
+            loss_ready[slot].record()
+            if i > 0:
+                loss_ready[slot ^ 1].synchronize()
+                last = float(loss_host[slot ^ 1])
     loss_ready[(steps - 1) & 1].synchronize()
     last = float(loss_host[(steps - 1) & 1])
     t1.record()
@@ -658,7 +690,7 @@ def main():
                 "dtype": dtype_name, "data": "synthetic", "config": config,
                 "clocks": clocks,
                 "e2e": {"value": spec.batch * steps / (e2e_ms * 1e-3), "unit": UNIT,
-                        "h2d_bytes_per_step": batch_host.numel() * batch_host.element_size() // world,
+                        "h2d_bytes_per_step": h2d_bytes,
                         "d2h_bytes_per_step": 8, "last_loss": last},
                 "last_loss": last, "gpu_launches": launches, "roofline": roofline, "kernels": kernels,
                 "accounting_ok": not flags}

@@ -479,11 +479,18 @@ template <class T>
 __global__ void __launch_bounds__(kSelThreads)
 select_aux_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, const int* __restrict__ dead_list,
                   const int* __restrict__ n_dead, T* __restrict__ a_out, float* __restrict__ cand_out,
-                  const float* __restrict__ thr, int mode, int B, int F, int k_aux, int nd_pad) {
+                  const float* __restrict__ thr, int mode, int B, int F, int k_aux, int nd_pad,
+                  const int* __restrict__ row_count, int* status) {
   extern __shared__ float cand[];  // pre-activations of the dead features of this row
   const int row = blockIdx.x;
   const int l = row / B;
   const int nd = min(n_dead[l], nd_pad);
+  if (threadIdx.x == 0) {
+    // the caller sized the compact operands (nd_pad) and chose the mode from counts of an earlier step:
+    // more dead features than columns, or a row that needed the candidate exchange, is reported
+    if (n_dead[l] > nd_pad) report_status(status, kOverflow);
+    if (mode == 0 && row_count != nullptr && row_count[row] > k_aux) report_status(status, kOverflow);
+  }
   const T* zr = z + (size_t)row * F;
   const float* br = b_enc + (size_t)l * F;
   const int* dl = dead_list + (size_t)l * F;
@@ -678,7 +685,7 @@ int clt_dead_compact(const uint8_t* dead, int* dead_list, int* n_dead, int L, in
 
 int clt_select_aux(const void* z, const float* b_enc, const int* dead_list, const int* n_dead, void* a_out,
                    float* cand_out, const float* thr, int mode, int B, int L, int F, int k_aux, int nd_pad, int bf16,
-                   clt_stream_t stream) {
+                   const int* row_count, int* status, clt_stream_t stream) {
   CLT_CHECK_ARG(B > 0 && L > 0 && F > 0 && nd_pad > 0, "select_aux: bad dims B=%d L=%d F=%d nd_pad=%d", B, L, F, nd_pad);
   CLT_CHECK_ARG(k_aux >= 1, "select_aux: k_aux=%d must be positive", k_aux);
   CLT_CHECK_ARG(mode >= 0 && mode <= 2, "select_aux: unknown mode %d", mode);
@@ -694,12 +701,13 @@ int clt_select_aux(const void* z, const float* b_enc, const int* dead_list, cons
     auto kern = select_aux_kernel<__nv_bfloat16>;
     CLT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<(unsigned)rows, kSelThreads, smem, s>>>((const __nv_bfloat16*)z, b_enc, dead_list, n_dead,
-                                                   (__nv_bfloat16*)a_out, cand_out, thr, mode, B, F, k_aux, nd_pad);
+                                                   (__nv_bfloat16*)a_out, cand_out, thr, mode, B, F, k_aux, nd_pad,
+                                                   row_count, status);
   } else {
     auto kern = select_aux_kernel<float>;
     CLT_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<(unsigned)rows, kSelThreads, smem, s>>>((const float*)z, b_enc, dead_list, n_dead, (float*)a_out, cand_out,
-                                                   thr, mode, B, F, k_aux, nd_pad);
+                                                   thr, mode, B, F, k_aux, nd_pad, row_count, status);
   }
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;

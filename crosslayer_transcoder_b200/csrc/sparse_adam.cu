@@ -261,10 +261,10 @@ int launch(const int* col_ptr, const int* ent, const float* val, const int* etok
 
 // dead_pos[l, f] = position of feature f in dead_list[l] (j < n_dead[l]), -1 for live features
 __global__ void dead_pos_kernel(const int* __restrict__ dead_list, const int* __restrict__ n_dead,
-                                int* __restrict__ dead_pos, int F) {
+                                int* __restrict__ dead_pos, int F, int nd_pad) {
   const int l = blockIdx.y;
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j < n_dead[l]) {
+  if (j < min(n_dead[l], nd_pad)) {
     const int f = dead_list[(size_t)l * F + j];
     if (f >= 0 && f < F) dead_pos[(size_t)l * F + f] = j;
   }
@@ -277,13 +277,14 @@ using namespace clt;
 
 extern "C" {
 
-int clt_dead_positions(const int* dead_list, const int* n_dead, int* dead_pos, int L, int F, clt_stream_t stream) {
-  CLT_CHECK_ARG(dead_list && n_dead && dead_pos && L > 0 && F > 0, "dead_positions: bad arguments");
+int clt_dead_positions(const int* dead_list, const int* n_dead, int* dead_pos, int L, int F, int nd_pad,
+                       clt_stream_t stream) {
+  CLT_CHECK_ARG(dead_list && n_dead && dead_pos && L > 0 && F > 0 && nd_pad > 0, "dead_positions: bad arguments");
   CLT_CHECK_ARG(L <= 65535, "dead_positions: too many layers");
   cudaStream_t s = (cudaStream_t)stream;
   CLT_CHECK_CUDA(cudaMemsetAsync(dead_pos, 0xff, sizeof(int) * (size_t)L * F, s));
   dim3 grid((F + 255) / 256, L);
-  dead_pos_kernel<<<grid, 256, 0, s>>>(dead_list, n_dead, dead_pos, F);
+  dead_pos_kernel<<<grid, 256, 0, s>>>(dead_list, n_dead, dead_pos, F, nd_pad);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

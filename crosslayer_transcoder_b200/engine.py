@@ -114,6 +114,9 @@ class StepEngine:
         # the device status word is copied to pinned host memory after every backward and looked at,
         # without waiting, when the next steps begin
         self.optimizer = None                     # the FusedAdam of configure_optimizers (for fuse_optimizer)
+        #: feature shards, fused exchange: called right before the last collective of a step (the all-reduce
+        #: of the decoder-bias gradient); parallel.ShardedBatchUploader orders its peer copies through it
+        self.before_last_collective = None
         self.decoder_updated = False              # set by a backward that stepped the decoder itself
         self._status_host: Optional[torch.Tensor] = None
         self._status_evt = [None, None]
@@ -356,6 +359,12 @@ class StepEngine:
                         drecon=drecon, daux=daux, token=torch.zeros(1, dtype=torch.float32, device=dev))
         return self._px
 
+    def has_fused_exchange(self) -> bool:
+        """Does this module's step run the exchange fused into the kernels (token rows owned by ranks)?"""
+        mod = self.module
+        return bool(getattr(mod, "tp_fused", False)) and getattr(mod, "tp_world", 1) > 1 and \
+            mod._kind() in ("jumprelu", "relu", "topk") and mod.model.encoder.d_acts % 8 == 0
+
     def _sum_slots(self, px, which: int):
         """Add the per-source slots of the owned rows (0: main, 1: auxiliary reconstruction)."""
         n = px["recon_own"].numel()
@@ -565,6 +574,8 @@ class StepEngine:
                 self._call("clt_loss_bwd_push", px["recon_own"], None, c["batch"], c["in_code"], mu_o, sd_o, gs, 0.0,
                            px["drecon"].bases, None, self.module.tp_world, int(bf16), gview(dec.b), B, px["b_lo"],
                            px["b_cnt"], L, D, s)
+            if self.before_last_collective is not None:
+                self.before_last_collective()
             all_reduce_sum(gview(dec.b), self.module.tp_group)   # partial bias gradients; orders the ranks
         else:
             self._call("clt_loss_bwd", recon, None, c["batch"], c["in_code"], mu_o, sd_o, gs, 0.0, drecon, None,
@@ -675,11 +686,10 @@ class StepEngine:
                 cnt = ws.get("aux_cnt", (L, B), torch.int32, dev)
                 self._call("clt_aux_count", z, enc.b.data, dead_list, n_dead, cnt, B, L, F, int(bf16), s)
                 all_reduce_sum(cnt, group)
-                both = torch.stack([n_dead.max(), cnt.max()]).tolist()   # ONE host read for both sizes
-                nd, exchange = int(both[0]), int(both[1]) > k_aux          # (same values on every rank for cnt)
+                nd_pad, exchange = self._aux_sizes(n_dead, cnt, k_aux)
             else:
-                nd = int(n_dead.max())                  # host read: sizes the compacted contractions
-            nd_pad = max(64, _round_up(nd, 64))
+                cnt = None
+                nd_pad, exchange = self._aux_sizes(n_dead, None, k_aux)
             self.last_nd_pad = nd_pad
             a_aux = ws.get("a_aux", (L, B, nd_pad), T, dev)
             if exchange:
@@ -687,7 +697,7 @@ class StepEngine:
                 # decoder works
                 cand = ws.get("aux_cand", (L, B, k_aux), torch.float32, dev)
                 self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, None, cand, None, 1, B, L, F, k_aux,
-                           nd_pad, int(bf16), s)
+                           nd_pad, int(bf16), None, self.status, s)
                 cand_all = ws.get("aux_cand_all", (world, L, B, k_aux), torch.float32, dev)
                 h_gather = all_gather(cand_all, cand, group, async_op=True)
         def main_decoder():
@@ -708,13 +718,13 @@ class StepEngine:
         if k_aux > 0:
             if not exchange:
                 self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, a_aux, None, None, 0, B, L, F, k_aux,
-                           nd_pad, int(bf16), s)
+                           nd_pad, int(bf16), cnt, self.status, s)
             else:
                 h_gather.wait()
                 thr_aux = ws.get("thr_aux", (L, B), torch.float32, dev)
                 self._call("clt_topk_threshold", cand_all, thr_aux, L * B, world, k_aux, s)
                 self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, a_aux, None, thr_aux, 2, B, L, F, k_aux,
-                           nd_pad, int(bf16), s)
+                           nd_pad, int(bf16), None, self.status, s)
             P = W_op.shape[0]
             w_c = ws.get("w_c", (P, nd_pad, D), T, dev)
             self._call("clt_gather_rows", W_op, dead_list, n_dead, w_c, L, F, D, nd_pad, crosslayer, int(bf16), s)
@@ -880,6 +890,8 @@ class StepEngine:
                            sd_o, gs, c["aux_scale"] if aux is not None else 0.0, px["drecon"].bases,
                            px["daux"].bases if aux is not None else None, self.module.tp_world, int(bf16),
                            gview(dec.b), B, b_lo, b_cnt, L, D, s)
+            if self.before_last_collective is not None:
+                self.before_last_collective()
             all_reduce_sum(gview(dec.b), self.module.tp_group)
         else:
             self._call("clt_loss_bwd", recon, aux_recon if aux is not None else None, c["batch"], c["in_code"],
@@ -925,7 +937,7 @@ class StepEngine:
             dead_pos = None
             if aux is not None:
                 dead_pos = ws.get("dead_pos", (L, F), torch.int32, dev)
-                self._call("clt_dead_positions", aux["dead_list"], aux["n_dead"], dead_pos, L, F, s)
+                self._call("clt_dead_positions", aux["dead_list"], aux["n_dead"], dead_pos, L, F, aux["nd_pad"], s)
             b1, b2 = grp["betas"]
             self._call("clt_sparse_bwd_dec_adam", col_ptr, ent, val, etok, npl, W_master, m_dec, v_dec,
                        W_op if bf16 else None, drecon, dval, dW_c if aux is not None else None, dead_pos,
@@ -946,6 +958,37 @@ class StepEngine:
             dWe_c = ws.get("dWe_c", (L, D, nd_pad), torch.float32, dev)
             self._call("clt_encoder_dense_bwd_dw", xn, dpre_c, dWe_c, B, L, D, nd_pad, int(bf16), self.status, s)
             self._call("clt_scatter_cols", dWe_c, db_c, dl, n_dead, gview(enc.W), gview(enc.b), L, D, F, nd_pad, s)
+
+    def _aux_sizes(self, n_dead: torch.Tensor, cnt, k_aux: int):
+        """(nd_pad, exchange) for the auxiliary path: the column count of the compact dead-feature operands
+        and, on feature shards, whether some row has more than k_aux positive dead values in total (then
+        the shards must exchange candidates).  Both depend on device values.  The first two steps read
+        them (one blocking host read each); afterwards every step copies its values to pinned memory
+        without waiting and decisions use the values of the step before last, which have always arrived
+        when the next-but-one step is enqueued: the launch queue is never drained.  Dead counts move
+        slowly, so the operands get 1/8 headroom and the exchange switches on at 3/4 of k_aux; if a step
+        outgrows either all the same, ``clt_select_aux`` reports it through the status word.  Every rank
+        takes the same decisions (the row counts are summed over the ranks before they are used)."""
+        st = getattr(self, "_aux_hist", None)
+        if st is None:
+            st = self._aux_hist = dict(step=0, host=torch.zeros(2, 2, dtype=torch.int32).pin_memory(),
+                                       evt=[torch.cuda.Event(), torch.cuda.Event()], cap=0)
+        i = st["step"]
+        st["step"] = i + 1
+        cur = torch.stack([n_dead.max(), cnt.max() if cnt is not None else n_dead.new_zeros(())]).to(torch.int32)
+        slot = i & 1
+        if i < 2:
+            nd, cmax = (int(x) for x in cur.tolist())          # blocking: the first two steps only
+        else:
+            st["evt"][slot].synchronize()                       # the copy made two steps ago into this slot
+            nd, cmax = int(st["host"][slot, 0]), int(st["host"][slot, 1])
+        st["host"][slot].copy_(cur, non_blocking=True)
+        st["evt"][slot].record()
+        want = max(64, _round_up(nd + (nd + 7) // 8 if i >= 2 else nd, 64))
+        if want > st["cap"] or want < st["cap"] // 2:
+            st["cap"] = want
+        exchange = cnt is not None and (cmax > k_aux if i < 2 else 4 * cmax > 3 * k_aux)
+        return st["cap"], exchange
 
     def _fused_optimizer(self, F: int) -> bool:
         """Apply the optimizer to the decoder inside the sparse backward?  Opt-in

@@ -116,6 +116,13 @@ class PeerBuffer:
         if off < 0 or off + self.local.numel() * self.local.element_size() > int(self.handle.buffer_size):
             raise RuntimeError("symmetric-memory tensor lies outside its registered buffer")
         self.bases = torch.tensor([int(p) + off for p in self.handle.buffer_ptrs], dtype=torch.int64)
+        self._offset_bytes = off
+
+    def peer(self, rank: int) -> torch.Tensor:
+        """Rank ``rank``'s copy as a tensor of THIS device (its storage is the peer's memory, mapped here):
+        plain copies into it travel over NVLink."""
+        return self.handle.get_buffer(rank, tuple(self.local.shape), self.local.dtype,
+                                      self._offset_bytes // self.local.element_size())
 
 
 def all_reduce_sum(buf: torch.Tensor, group, async_op: bool = False):
@@ -145,6 +152,102 @@ def upload_batch(batch_host: torch.Tensor, staging: torch.Tensor, group) -> torc
         mine[: hi - lo].copy_(batch_host[lo:hi], non_blocking=True)
     all_gather(staging.view(world, c, *staging.shape[1:]), mine, group)
     return staging[:B]
+
+
+class ShardedBatchUploader:
+    """Batch ingestion for a feature-shard group that uses the exchange fused into the kernels
+    (``attach(module)`` with ``module.tp_fused``): every rank holds the pinned host batch ``[B, 2, L, D]``
+    (what the reference's loader hands every tensor-parallel rank,
+    crosslayer_transcoder/data/shared_memory.py:168-214), but each row crosses PCIe only once and NVLink
+    carries only what the step reads.
+
+    Rank r copies its own token rows ``[r c, (r+1) c)`` (c = ceil(B / R), both halves) host-to-device into
+    its double-buffered device batch and copies the INPUT half of those rows into every peer's buffer
+    (device-to-device copies on a side stream, no collective, no communicator): in this exchange form a
+    rank standardises and encodes all tokens but computes the loss only for its own rows, so the target
+    half of the other rows is never read.  ``full=True`` pushes both halves (for the first batch, from
+    which the standardizers take their statistics).
+
+    Ordering between the ranks costs no extra collective.  The pushes of batch i+1 are enqueued while step
+    i runs; the step's own last collective (the all-reduce of the decoder-bias gradient in backward) is
+    made to wait for this rank's pushes (``StepEngine.before_last_collective``), so when that collective
+    has completed on a rank, every peer's rows for batch i+1 have landed in its buffer.  Conversely a
+    buffer is overwritten only after the step that read it has finished on every rank, which the same
+    collective of that step guarantees.
+
+        up = ShardedBatchUploader(module, batch_host.shape, batch_host.dtype, device)
+        up.upload(first, full=True); up.fence()     # then, per step:
+        batch = up.take()                           # current stream waits for the newest upload
+        up.upload(next_host_batch)                  # prefetch while the step runs
+        loss = module.training_step(batch, i); loss.backward(); opt.step()
+        up.release()                                # the step's work on `batch` is enqueued
+    """
+
+    def __init__(self, module, shape, dtype, device):
+        if not getattr(module, "tp_fused", False) or not module._engine.has_fused_exchange():
+            raise RuntimeError("ShardedBatchUploader needs a module attached with the fused exchange "
+                               "(and a step kind that has it)")
+        self.module, self.group = module, module.tp_group
+        self.world, self.rank = module.tp_world, module.tp_rank
+        B = shape[0]
+        self.B, self.c = B, (B + self.world - 1) // self.world
+        self.lo, self.hi = min(self.rank * self.c, B), min((self.rank + 1) * self.c, B)
+        self.bufs = [PeerBuffer(tuple(shape), dtype, device, self.group) for _ in range(2)]
+        self.peers = [[b.peer(r) for r in range(self.world)] for b in self.bufs]
+        self.stream = torch.cuda.Stream(device=device)
+        self.pushed = [torch.cuda.Event(), torch.cuda.Event()]
+        self.freed = [torch.cuda.Event(), torch.cuda.Event()]
+        for e in self.freed:
+            e.record()
+        self._next, self._ready, self._in_use = 0, [], []
+        module._engine.before_last_collective = self._join
+
+    def upload(self, batch_host: torch.Tensor, full: bool = False) -> None:
+        slot = self._next
+        self._next ^= 1
+        lo, hi = self.lo, self.hi
+        with torch.cuda.stream(self.stream):
+            self.stream.wait_event(self.freed[slot])
+            if hi > lo:
+                mine = self.bufs[slot].local[lo:hi]
+                mine.copy_(batch_host[lo:hi], non_blocking=True)
+                for r in range(self.world):
+                    if r == self.rank:
+                        continue
+                    dst = self.peers[slot][r][lo:hi]
+                    if full:
+                        dst.copy_(mine, non_blocking=True)
+                    else:
+                        dst[:, 0].copy_(mine[:, 0], non_blocking=True)
+            self.pushed[slot].record(self.stream)
+        self._ready.append(slot)
+
+    def _join(self):
+        """Called by the engine right before the last collective of a step: this rank takes part in it
+        only after its pushes of the next batch have been written."""
+        for slot in self._ready:
+            torch.cuda.current_stream().wait_event(self.pushed[slot])
+
+    def fence(self) -> None:
+        """Stream-ordered barrier for a batch that no step's collective has ordered yet (the first one): the
+        current stream waits for this rank's pushes, then a one-element all-reduce waits for everyone's."""
+        self._join()
+        if not hasattr(self, "_token"):
+            self._token = torch.zeros(1, dtype=torch.float32, device=self.bufs[0].local.device)
+        all_reduce_sum(self._token, self.group)
+
+    def take(self) -> torch.Tensor:
+        """The oldest uploaded batch not yet handed out; the current stream waits for this rank's part of it.
+        (The peers' parts are ordered by the previous step's last collective; before the first step the
+        caller calls ``fence()`` once.)"""
+        slot = self._ready.pop(0)
+        torch.cuda.current_stream().wait_event(self.pushed[slot])
+        self._in_use.append(slot)
+        return self.bufs[slot].local[: self.B]
+
+    def release(self) -> None:
+        slot = self._in_use.pop(0)
+        self.freed[slot].record()
 
 
 # --------------------------------------------------------------------------------------------------

@@ -173,10 +173,13 @@ int clt_dead_compact(const uint8_t* dead, int* dead_list, int* n_dead, int L, in
  * largest positive dead pre-activations of the row (ties with the k_aux-th are all kept), else 0;
  * [L, B, nd_pad] in T, columns j >= n_dead[l] are 0.
  * mode 0: as above.  mode 1 (feature shards): write only cand_out [L, B, k_aux], this shard's k_aux
- * best values per row (0-padded).  mode 2: a_out from the exchanged per-row threshold thr [L, B]. */
+ * best values per row (0-padded).  mode 2: a_out from the exchanged per-row threshold thr [L, B].
+ * The caller may size nd_pad and pick the mode from the counts of an earlier step: a layer with more dead
+ * features than nd_pad, or (mode 0, row_count [L, B] = positive dead values per row summed over the
+ * shards, may be NULL) a row with more than k_aux of them, writes the overflow code to `status`. */
 int clt_select_aux(const void* z, const float* b_enc, const int* dead_list, const int* n_dead, void* a_out,
                    float* cand_out, const float* thr, int mode, int B, int L, int F, int k_aux, int nd_pad,
-                   int bf16, clt_stream_t stream);
+                   int bf16, const int* row_count, int* status, clt_stream_t stream);
 
 /* cnt[l, b] = number of positive pre-activations among the dead features of the row (feature shards
  * sum these to see whether any row needs the candidate exchange of the auxiliary selection). */
@@ -271,9 +274,10 @@ int clt_sparse_bwd_dec_adam(const int* col_ptr, const int* ent, const float* val
                             float beta2, float eps, float weight_decay, int decoupled, int64_t step,
                             clt_stream_t stream);
 
-/* dead_pos[l, f] = j where dead_list[l][j] == f (j < n_dead[l]), -1 for live features: the inverse of
- * clt_dead_compact's lists, [L, F]. */
-int clt_dead_positions(const int* dead_list, const int* n_dead, int* dead_pos, int L, int F, clt_stream_t stream);
+/* dead_pos[l, f] = j where dead_list[l][j] == f (j < min(n_dead[l], nd_pad)), -1 for every other feature:
+ * the inverse of clt_dead_compact's lists, [L, F], restricted to the columns the compact operands hold. */
+int clt_dead_positions(const int* dead_list, const int* n_dead, int* dead_pos, int L, int F, int nd_pad,
+                       clt_stream_t stream);
 
 /* Backward of the encoder on the selected features (autograd of clt.py:157-165 through the TopK
  * scatter): dW_enc[l,:,f] = sum_{e: idx[e] = f} dval[e] xn[l,b(e),:], db_enc[l,f] = sum dval[e]; every
