@@ -363,7 +363,8 @@ class StepEngine:
         """Does this module's step run the exchange fused into the kernels (token rows owned by ranks)?"""
         mod = self.module
         return bool(getattr(mod, "tp_fused", False)) and getattr(mod, "tp_world", 1) > 1 and \
-            mod._kind() in ("jumprelu", "relu", "topk") and mod.model.encoder.d_acts % 8 == 0
+            mod._kind() in ("jumprelu", "relu", "topk", "batchtopk", "perlayer_batchtopk") and \
+            mod.model.encoder.d_acts % 8 == 0
 
     def _sum_slots(self, px, which: int):
         """Add the per-source slots of the owned rows (0: main, 1: auxiliary reconstruction)."""
@@ -843,17 +844,37 @@ class StepEngine:
             row_cnt.zero_()
         self._call("clt_dead_update", mod.last_active, self.fired, None, B, int(mod.tokens_till_dead), L, F,
                    self._dead_count(dev), s)
-        self._call("clt_sparse_decoder_fwd", idx, val, row_start, row_cnt, npl, W_op, bias, recon, B, L, D, F, 1,
-                   crosslayer, int(k <= 8 * world), int(bf16), self.status, s)
-        if world > 1:
+        px = None
+        if world > 1 and getattr(mod, "tp_fused", False) and D % 8 == 0:
+            # exchange fused into the kernels: the sparse decoder stores its partial rows into the owning
+            # ranks' slots, the loss runs on the owned rows (see _peer_exchange)
             from .parallel import all_reduce_sum
 
-            all_reduce_sum(rbuf[:n_rec], group)
-        self._call("clt_loss_fwd", recon, None, batch, in_code, mu_o, sd_o, acc[2:4], B, L, D, s)
+            px = self._peer_exchange(B, L, D, T, dev)
+            self._call("clt_sparse_decoder_fwd_push", idx, val, row_start, row_cnt, npl, W_op, bias,
+                       px["recon_bases"], px["rpr"], world, rank, B, L, D, F, 1, crosslayer, int(k <= 8 * world),
+                       int(bf16), self.status, s)
+            self._rank_barrier(px)                      # every rank's rows have landed in the owners' slots
+            self._sum_slots(px, 0)
+            b_lo, b_cnt = px["b_lo"], px["b_cnt"]
+            if b_cnt > 0:
+                self._call("clt_loss_fwd", px["recon_own"], None, batch[b_lo:b_lo + b_cnt], in_code, mu_o, sd_o,
+                           acc[2:4], b_cnt, L, D, s)
+            all_reduce_sum(acc[2:4], group)             # loss sums of all owners
+        else:
+            self._call("clt_sparse_decoder_fwd", idx, val, row_start, row_cnt, npl, W_op, bias, recon, B, L, D, F, 1,
+                       crosslayer, int(k <= 8 * world), int(bf16), self.status, s)
+            if world > 1:
+                from .parallel import all_reduce_sum
+
+                all_reduce_sum(rbuf[:n_rec], group)
+            self._call("clt_loss_fwd", recon, None, batch, in_code, mu_o, sd_o, acc[2:4], B, L, D, s)
         self._call("clt_finalize_loss", acc[2:4], None, out[0:1], out[1:5], 1.0 / (B * L * D), 0.0, 0.0, 0.0, s)
         return dict(kind="batchtopk", bf16=bf16, batch=batch, B=B, L=L, D=D, F=F, k=1, crosslayer=crosslayer, out=out,
                     stats=(mu_i, sd_i, mu_o, sd_o), in_code=in_code, aux=None, aux_scale=0.0, idx=idx, val=val,
-                    npl=npl, etok=etok, recon_rows=(recon, 0, B), l0_src=(val, 0, npl))
+                    npl=npl, etok=etok, px=px,
+                    recon_rows=(px["recon_own"], px["b_lo"], px["b_cnt"]) if px is not None else (recon, 0, B),
+                    l0_src=(val, 0, npl))
 
     def _backward_topk(self, c, gscale):
         model = self.module.model

@@ -13,7 +13,7 @@ ROOT = Path(__file__).resolve().parents[1]
 
 CASES = [(k, p, "nccl") for k in ("jumprelu", "topk", "batchtopk") for p in ("fp32", "bf16")]
 # exchange fused into the kernels over peer memory
-CASES += [(k, p, "fused") for k in ("jumprelu", "topk") for p in ("fp32", "bf16")]
+CASES += [(k, p, "fused") for k in ("jumprelu", "topk", "batchtopk") for p in ("fp32", "bf16")]
 
 
 @pytest.mark.parametrize("kind,prec,mode", CASES)
