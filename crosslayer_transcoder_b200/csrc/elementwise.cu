@@ -780,20 +780,21 @@ int norm_coef(const float* dnorm, const float* n, float* out, int count, cudaStr
 // selection kernels); the words are cleared here for the next step.
 // ---------------------------------------------------------------------------------
 __global__ void dead_update_kernel(long long* last_active, unsigned* fired_bits, unsigned char* dead, long long B,
-                                   long long limit, int F, int* dead_count) {
+                                   long long limit, int F, int* dead_count, int* soon_dead) {
   const int l = blockIdx.y;
   const int f = blockIdx.x * blockDim.x + threadIdx.x;  // a warp covers one 32-feature word
   const int words = (F + 31) / 32;
   unsigned word = 0u;
   if (f < F) word = fired_bits[(size_t)l * words + f / 32];
   __syncwarp();
-  bool is_dead = false;
+  bool is_dead = false, is_soon = false;
   if (f < F) {
     const size_t i = (size_t)l * F + f;
     long long v = ((word >> (f & 31)) & 1u) ? 0 : last_active[i];
     v += B;
     last_active[i] = v;
     is_dead = v > limit;
+    is_soon = v + 2 * B > limit;   // dead within the next two steps unless it fires
     if (dead != nullptr) dead[i] = is_dead ? 1 : 0;
     if ((f & 31) == 0) fired_bits[(size_t)l * words + f / 32] = 0u;
   }
@@ -801,13 +802,18 @@ __global__ void dead_update_kernel(long long* last_active, unsigned* fired_bits,
     const int n = __popc(__ballot_sync(0xffffffffu, is_dead));
     if ((threadIdx.x & 31) == 0 && n) atomicAdd(dead_count, n);
   }
+  if (soon_dead != nullptr) {
+    const int n = __popc(__ballot_sync(0xffffffffu, is_soon));
+    if ((threadIdx.x & 31) == 0 && n) atomicAdd(soon_dead + l, n);
+  }
 }
 int dead_update(long long* last_active, unsigned* fired_bits, unsigned char* dead, long long B, long long limit, int L,
-                int F, int* dead_count, cudaStream_t s) {
+                int F, int* dead_count, int* soon_dead, cudaStream_t s) {
   if (L <= 0 || F <= 0) return 0;
   if (dead_count != nullptr) CLT_CHECK_CUDA(cudaMemsetAsync(dead_count, 0, sizeof(int), s));
+  if (soon_dead != nullptr) CLT_CHECK_CUDA(cudaMemsetAsync(soon_dead, 0, sizeof(int) * L, s));
   dim3 grid((F + 255) / 256, L);
-  dead_update_kernel<<<grid, 256, 0, s>>>(last_active, fired_bits, dead, B, limit, F, dead_count);
+  dead_update_kernel<<<grid, 256, 0, s>>>(last_active, fired_bits, dead, B, limit, F, dead_count, soon_dead);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -163,8 +163,9 @@ int clt_norm_coef(const float* dnorm, const float* norm, float* out, int count, 
 }
 
 int clt_dead_update(int64_t* last_active, uint32_t* fired_bits, uint8_t* dead, int64_t B, int64_t limit, int L, int F,
-                    int* dead_count, clt_stream_t stream) {
-  return dead_update((long long*)last_active, fired_bits, dead, B, limit, L, F, dead_count, (cudaStream_t)stream);
+                    int* dead_count, int* soon_dead, clt_stream_t stream) {
+  return dead_update((long long*)last_active, fired_bits, dead, B, limit, L, F, dead_count, soon_dead,
+                     (cudaStream_t)stream);
 }
 
 int clt_adam_step(float* p, const float* g, float* m, float* v, void* shadow_bf16, int64_t n, float lr, float beta1,

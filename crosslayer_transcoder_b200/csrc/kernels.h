@@ -28,7 +28,7 @@ int act_bwd(const void* g, const void* z, const float* b_enc, const float* theta
 int dec_norms(const float* W, float* out, int L, int F, int D, int crosslayer, cudaStream_t s);
 int norm_coef(const float* dnorm, const float* n, float* out, int count, cudaStream_t s);
 int dead_update(long long* last_active, unsigned* fired_bits, unsigned char* dead, long long B, long long limit, int L,
-                int F, int* dead_count, cudaStream_t s);
+                int F, int* dead_count, int* soon_dead, cudaStream_t s);
 int adam_step(float* p, const float* g, float* m, float* v, void* shadow_bf16, long long n, float lr, float beta1,
               float beta2, float eps, float weight_decay, int decoupled, long long step, int num_sms, cudaStream_t s);
 int cast_bf16(const float* src, void* dst, long long n, cudaStream_t s);

@@ -433,6 +433,212 @@ select_topk_warp_kernel(const T* __restrict__ z, const float* __restrict__ b_enc
 }
 
 // ---------------------------------------------------------------------------------------
+// Main selection for long rows in ONE sweep: a warp streams its row once and keeps a running
+// candidate list in shared memory.
+//
+//   * A value joins the list when its key is at least tau (tau starts at the smallest positive key).
+//   * When the list could overflow, the warp finds the k-th largest key T of the list (bisection on the
+//     key bits over values held in registers), keeps the k best entries and raises tau to T + 1: from
+//     then on only values that would displace one of the k held ones join (a value equal to the current
+//     k-th is interchangeable with it).  After the first few hundred elements tau sits near the row's
+//     final threshold and almost nothing joins any more: k (1 + ln(F / 256)) entries in expectation.
+//   * At the end of the row one more such step leaves exactly min(k, #positive) entries.
+//
+// A CTA is 8 independent warps = 8 consecutive tokens of one layer (no CTA-wide barrier).  The row is
+// read exactly once, 256 columns per step with the next step's values already requested; the fp32 bias
+// comes through L1, which the warps of the CTAs resident on an SM share because they walk the same
+// layer's bias at about the same pace.  The filter is one floating-point compare per element
+// (pre >= tau with tau > 0 also rejects everything that is not positive).  k <= kStreamCap - 256.
+// ---------------------------------------------------------------------------------------
+constexpr int kStreamWarps = 8;
+constexpr int kStreamMinF = 2048;   // shorter rows keep the one-warp-per-row two-sweep kernel
+constexpr int kStreamCap = 512;
+
+template <class T>
+struct ChunkLoader;
+template <>
+struct ChunkLoader<__nv_bfloat16> {
+  using Raw = uint4;  // 8 values
+  __device__ static __forceinline__ Raw load(const __nv_bfloat16* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
+  __device__ static __forceinline__ void unpack(const Raw& t, float (&o)[8]) {
+    o[0] = __uint_as_float(t.x << 16), o[1] = __uint_as_float(t.x & 0xffff0000u);
+    o[2] = __uint_as_float(t.y << 16), o[3] = __uint_as_float(t.y & 0xffff0000u);
+    o[4] = __uint_as_float(t.z << 16), o[5] = __uint_as_float(t.z & 0xffff0000u);
+    o[6] = __uint_as_float(t.w << 16), o[7] = __uint_as_float(t.w & 0xffff0000u);
+  }
+};
+template <>
+struct ChunkLoader<float> {
+  struct Raw {
+    float4 a, b;
+  };
+  __device__ static __forceinline__ Raw load(const float* p) {
+    Raw r;
+    r.a = __ldcs(reinterpret_cast<const float4*>(p));
+    r.b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+    return r;
+  }
+  __device__ static __forceinline__ void unpack(const Raw& r, float (&o)[8]) {
+    o[0] = r.a.x, o[1] = r.a.y, o[2] = r.a.z, o[3] = r.a.w, o[4] = r.b.x, o[5] = r.b.y, o[6] = r.b.z, o[7] = r.b.w;
+  }
+};
+
+// Keep the k best of the n entries of a warp's candidate list (n <= kStreamCap, n > k); returns the k-th
+// largest key.  Entries equal to it are kept in list order until k are held.
+__device__ __forceinline__ unsigned stream_keep_top(float* cv, int* ci, int n, int k) {
+  const int lane = threadIdx.x & 31;
+  constexpr int kPer = kStreamCap / 32;
+  unsigned key[kPer];
+#pragma unroll
+  for (int q = 0; q < kPer; ++q) key[q] = (lane + 32 * q) < n ? __float_as_uint(cv[lane + 32 * q]) : 0u;
+  unsigned Tk = 0u;
+  for (int bit = 30; bit >= 0; --bit) {
+    const unsigned trial = Tk | (1u << bit);
+    int c = 0;
+#pragma unroll
+    for (int q = 0; q < kPer; ++q) c += key[q] >= trial ? 1 : 0;
+    c = __reduce_add_sync(0xffffffffu, c);
+    if (c >= k) Tk = trial;
+  }
+  int n_gt = 0;
+#pragma unroll
+  for (int q = 0; q < kPer; ++q) n_gt += key[q] > Tk ? 1 : 0;
+  n_gt = __reduce_add_sync(0xffffffffu, n_gt);
+  int ties_left = k - n_gt, n_out = 0;
+#pragma unroll
+  for (int q = 0; q < kPer; ++q) {   // in-place: an entry never moves to a later position
+    const int c = lane + 32 * q;
+    const bool gt = key[q] > Tk, tie = key[q] == Tk && key[q] != 0u;
+    const unsigned tb = __ballot_sync(0xffffffffu, tie);
+    const bool take = gt || (tie && __popc(tb & ((1u << lane) - 1u)) < ties_left);
+    const unsigned bal = __ballot_sync(0xffffffffu, take);
+    const float v = c < n ? cv[c] : 0.f;
+    const int f = c < n ? ci[c] : 0;
+    __syncwarp();
+    if (take) {
+      const int slot = n_out + __popc(bal & ((1u << lane) - 1u));
+      cv[slot] = v;
+      ci[slot] = f;
+    }
+    __syncwarp();
+    n_out += __popc(bal);
+    ties_left -= min(ties_left, __popc(tb));
+  }
+  return Tk;
+}
+
+template <class T>
+__global__ void __launch_bounds__(kStreamWarps * 32, 4)
+select_topk_stream_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, int* __restrict__ idx_out,
+                          float* __restrict__ val_out, unsigned* __restrict__ fired_bits, int B, int F, int k) {
+  __shared__ float c_val[kStreamWarps][kStreamCap];
+  __shared__ int c_idx[kStreamWarps][kStreamCap];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int l = blockIdx.y;
+  const int b = blockIdx.x * kStreamWarps + warp;
+  if (b >= B) return;                       // warps are independent: no CTA-wide barrier below
+  const size_t row = (size_t)l * B + b;
+  const T* zr = z + row * F;
+  const float* br = b_enc + (size_t)l * F;  // read through L1: the 8 warps of a CTA walk the same layer's bias
+  float* cv = c_val[warp];
+  int* ci = c_idx[warp];
+  float tau = __uint_as_float(1u);          // smallest positive value: every positive value qualifies at first
+  int count = 0;
+  using CL = ChunkLoader<T>;
+  // 256 columns per step (8 per lane); the next step's row values are requested before this step's are used
+  const int n_steps = F / 256;              // whole steps; the ragged end (F % 256, a multiple of 8) follows
+  const int i_last = n_steps * 256 + 8 * lane;
+  typename CL::Raw cur, nxt;
+  float4 b0c, b1c, b0n, b1n;
+  auto fetch = [&](int i, typename CL::Raw& r, float4& c0, float4& c1) {
+    r = CL::load(zr + i);
+    c0 = __ldg(reinterpret_cast<const float4*>(br + i));
+    c1 = __ldg(reinterpret_cast<const float4*>(br + i) + 1);
+  };
+  auto consume = [&](int i, const typename CL::Raw& r, const float4& c0, const float4& c1) {
+    float v[8];
+    CL::unpack(r, v);
+    v[0] += c0.x, v[1] += c0.y, v[2] += c0.z, v[3] += c0.w;
+    v[4] += c1.x, v[5] += c1.y, v[6] += c1.z, v[7] += c1.w;
+    bool any = false;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) any |= v[q] >= tau;
+    if (__any_sync(0xffffffffu, any)) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const bool hit = v[q] >= tau;
+        const unsigned bal = __ballot_sync(0xffffffffu, hit);
+        if (hit) {
+          const int slot = count + __popc(bal & ((1u << lane) - 1u));
+          cv[slot] = v[q];
+          ci[slot] = i + q;
+        }
+        count += __popc(bal);
+      }
+      __syncwarp();
+      if (count > kStreamCap - 256) {       // the next 256 elements could overflow the list
+        if (count > k) {
+          tau = __uint_as_float(stream_keep_top(cv, ci, count, k) + 1u);
+          count = k;
+        }
+        __syncwarp();
+      }
+    }
+  };
+  if (n_steps > 0) fetch(8 * lane, cur, b0c, b1c);
+#pragma unroll 2
+  for (int st = 0; st < n_steps; ++st) {
+    const int i = st * 256 + 8 * lane;
+    if (st + 1 < n_steps) fetch(i + 256, nxt, b0n, b1n);
+    consume(i, cur, b0c, b1c);
+    cur = nxt, b0c = b0n, b1c = b1n;
+  }
+  if (i_last < F) fetch(i_last, cur, b0c, b1c);
+  {
+    // ragged end (F % 256 columns): lanes beyond F contribute nothing (their values are forced below tau)
+    const bool in = i_last < F;
+    if (__any_sync(0xffffffffu, in)) {
+      float v[8];
+      if (in) {
+        CL::unpack(cur, v);
+        v[0] += b0c.x, v[1] += b0c.y, v[2] += b0c.z, v[3] += b0c.w;
+        v[4] += b1c.x, v[5] += b1c.y, v[6] += b1c.z, v[7] += b1c.w;
+      } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) v[q] = 0.f;
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const bool hit = v[q] >= tau;
+        const unsigned bal = __ballot_sync(0xffffffffu, hit);
+        if (hit) {
+          const int slot = count + __popc(bal & ((1u << lane) - 1u));
+          cv[slot] = v[q];
+          ci[slot] = i_last + q;
+        }
+        count += __popc(bal);
+      }
+      __syncwarp();
+    }
+  }
+  if (count > k) {
+    stream_keep_top(cv, ci, count, k);
+    count = k;
+  }
+  __syncwarp();
+  int* io = idx_out + row * k;
+  float* vo = val_out + row * k;
+  const int words = (F + 31) / 32;
+  for (int j = lane; j < k; j += 32) {
+    const bool live = j < count;
+    const int f = live ? ci[j] : 0;
+    io[j] = f;
+    vo[j] = live ? cv[j] : 0.f;
+    if (live && fired_bits != nullptr) atomicOr(fired_bits + (size_t)l * words + f / 32, 1u << (f & 31));
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // Dead-feature list per layer: dead_list[l, 0..n_dead[l]) = ascending indices with dead != 0.
 // One CTA per layer.
 // ---------------------------------------------------------------------------------------
@@ -657,6 +863,19 @@ int clt_select_topk(const void* z, const float* b_enc, int* idx_out, float* val_
   cudaStream_t s = (cudaStream_t)stream;
   const bool warp_rows = k <= 64 && F % 8 == 0 && F >= 512 && F <= 8192;   // short rows: one warp each
   const unsigned wblocks = (unsigned)((rows + 7) / 8);
+  if (F % 8 == 0 && F >= kStreamMinF && k <= kStreamCap - 256 && L <= 65535 &&
+      ((uintptr_t)z | (uintptr_t)b_enc) % 16 == 0) {
+    // long rows: one streaming sweep per row, the bias staged once per 8 rows
+    dim3 grid((B + kStreamWarps - 1) / kStreamWarps, L);
+    if (bf16)
+      select_topk_stream_kernel<__nv_bfloat16><<<grid, kStreamWarps * 32, 0, s>>>(
+          (const __nv_bfloat16*)z, b_enc, idx_out, val_out, fired_bits, B, F, k);
+    else
+      select_topk_stream_kernel<float><<<grid, kStreamWarps * 32, 0, s>>>((const float*)z, b_enc, idx_out, val_out,
+                                                                          fired_bits, B, F, k);
+    CLT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+  }
   if (bf16) {
     if (warp_rows)
       select_topk_warp_kernel<__nv_bfloat16><<<wblocks, 256, 0, s>>>((const __nv_bfloat16*)z, b_enc, idx_out, val_out,

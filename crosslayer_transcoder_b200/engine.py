@@ -476,7 +476,7 @@ class StepEngine:
         self._call("clt_finalize_loss", acc[2:4], acc[0:2], out[0:1], out[1:5], 1.0 / (B * L * D), lam / B,
                    pal / (B * L), 0.0, s)
         self._call("clt_dead_update", mod.last_active, self.fired, None, B, int(mod.tokens_till_dead), L, F,
-                   self._dead_count(dev), s)
+                   self._dead_count(dev), None, s)
         return dict(kind=h["kind"], bf16=bf16, batch=batch, B=B, L=L, D=D, F=F, crosslayer=crosslayer, lam=lam,
                     pal=pal, c=float(h.get("c_sparsity", 1.0)), use_tanh=int(h.get("use_tanh", True)),
                     bandwidth=self._bandwidth(nl) if h["kind"] == "jumprelu" else 1.0, out=out,
@@ -667,8 +667,9 @@ class StepEngine:
             idx.zero_()
             val.zero_()
         dead = ws.get("dead", (L, F), torch.uint8, dev)
+        soon = ws.get("soon_dead", (L,), torch.int32, dev)
         self._call("clt_dead_update", mod.last_active, self.fired, dead, B, int(mod.tokens_till_dead), L, F,
-                   self._dead_count(dev), s)
+                   self._dead_count(dev), soon, s)
         aux = None
         aux_recon = None
         aux_scale = float(h.get("aux_loss_scale", 0.0))
@@ -687,10 +688,10 @@ class StepEngine:
                 cnt = ws.get("aux_cnt", (L, B), torch.int32, dev)
                 self._call("clt_aux_count", z, enc.b.data, dead_list, n_dead, cnt, B, L, F, int(bf16), s)
                 all_reduce_sum(cnt, group)
-                nd_pad, exchange = self._aux_sizes(n_dead, cnt, k_aux)
+                nd_pad, exchange = self._aux_sizes(n_dead, soon, cnt, k_aux)
             else:
                 cnt = None
-                nd_pad, exchange = self._aux_sizes(n_dead, None, k_aux)
+                nd_pad, exchange = self._aux_sizes(n_dead, soon, None, k_aux)
             self.last_nd_pad = nd_pad
             a_aux = ws.get("a_aux", (L, B, nd_pad), T, dev)
             if exchange:
@@ -843,7 +844,7 @@ class StepEngine:
             row_start.zero_()
             row_cnt.zero_()
         self._call("clt_dead_update", mod.last_active, self.fired, None, B, int(mod.tokens_till_dead), L, F,
-                   self._dead_count(dev), s)
+                   self._dead_count(dev), None, s)
         px = None
         if world > 1 and getattr(mod, "tp_fused", False) and D % 8 == 0:
             # exchange fused into the kernels: the sparse decoder stores its partial rows into the owning
@@ -980,36 +981,39 @@ class StepEngine:
             self._call("clt_encoder_dense_bwd_dw", xn, dpre_c, dWe_c, B, L, D, nd_pad, int(bf16), self.status, s)
             self._call("clt_scatter_cols", dWe_c, db_c, dl, n_dead, gview(enc.W), gview(enc.b), L, D, F, nd_pad, s)
 
-    def _aux_sizes(self, n_dead: torch.Tensor, cnt, k_aux: int):
+    def _aux_sizes(self, n_dead: torch.Tensor, soon_dead: torch.Tensor, cnt, k_aux: int):
         """(nd_pad, exchange) for the auxiliary path: the column count of the compact dead-feature operands
         and, on feature shards, whether some row has more than k_aux positive dead values in total (then
-        the shards must exchange candidates).  Both depend on device values.  The first two steps read
-        them (one blocking host read each); afterwards every step copies its values to pinned memory
-        without waiting and decisions use the values of the step before last, which have always arrived
-        when the next-but-one step is enqueued: the launch queue is never drained.  Dead counts move
-        slowly, so the operands get 1/8 headroom and the exchange switches on at 3/4 of k_aux; if a step
-        outgrows either all the same, ``clt_select_aux`` reports it through the status word.  Every rank
-        takes the same decisions (the row counts are summed over the ranks before they are used)."""
+        the shards must exchange candidates).  Both depend on device values; reading them every step would
+        drain the launch queue.  The first two steps do read them (one blocking host read each).  From
+        then on every step copies its values to pinned memory without waiting and a step uses what the
+        step before last left there, which has always arrived when it is needed:
+
+        * nd_pad from ``soon_dead`` of two steps ago, the number of features that were dead or within two
+          steps of the limit then.  A feature leaves that set only by firing, so it bounds the dead count of
+          this step from above whatever happens in between: the operands are never too small, and in
+          steady state the bound is the dead count itself.
+        * the exchange switches on when the largest row count of two steps ago exceeds 3/4 of k_aux; should
+          a row outgrow k_aux within two steps all the same, ``clt_select_aux`` reports it through the
+          status word.  Every rank takes the same decision (the counts are summed over the ranks first)."""
         st = getattr(self, "_aux_hist", None)
         if st is None:
             st = self._aux_hist = dict(step=0, host=torch.zeros(2, 2, dtype=torch.int32).pin_memory(),
-                                       evt=[torch.cuda.Event(), torch.cuda.Event()], cap=0)
+                                       evt=[torch.cuda.Event(), torch.cuda.Event()])
         i = st["step"]
         st["step"] = i + 1
-        cur = torch.stack([n_dead.max(), cnt.max() if cnt is not None else n_dead.new_zeros(())]).to(torch.int32)
+        cmax_t = cnt.max() if cnt is not None else n_dead.new_zeros(())
         slot = i & 1
         if i < 2:
-            nd, cmax = (int(x) for x in cur.tolist())          # blocking: the first two steps only
+            nd, cmax = (int(x) for x in torch.stack([n_dead.max(), cmax_t]).tolist())   # blocking: first two steps only
+            exchange = cnt is not None and cmax > k_aux
         else:
             st["evt"][slot].synchronize()                       # the copy made two steps ago into this slot
             nd, cmax = int(st["host"][slot, 0]), int(st["host"][slot, 1])
-        st["host"][slot].copy_(cur, non_blocking=True)
+            exchange = cnt is not None and 4 * cmax > 3 * k_aux
+        st["host"][slot].copy_(torch.stack([soon_dead.max(), cmax_t]).to(torch.int32), non_blocking=True)
         st["evt"][slot].record()
-        want = max(64, _round_up(nd + (nd + 7) // 8 if i >= 2 else nd, 64))
-        if want > st["cap"] or want < st["cap"] // 2:
-            st["cap"] = want
-        exchange = cnt is not None and (cmax > k_aux if i < 2 else 4 * cmax > 3 * k_aux)
-        return st["cap"], exchange
+        return max(64, _round_up(nd, 64)), exchange
 
     def _fused_optimizer(self, F: int) -> bool:
         """Apply the optimizer to the decoder inside the sparse backward?  Opt-in

@@ -151,9 +151,12 @@ int clt_norm_coef(const float* dnorm, const float* norm, float* out, int count, 
 /* update_dead_features (clt_lightning.py:282-288): last_active[fired]=0; last_active+=B;
  * dead = last_active > limit (dead may be NULL).  fired_bits is [L, ceil(F/32)] words, one bit
  * per feature, and is cleared for the next step.  dead_count (one int, may be NULL) receives the
- * number of dead features, the numerator of the logged metrics/dead_features (clt_lightning.py:287). */
+ * number of dead features, the numerator of the logged metrics/dead_features (clt_lightning.py:287).
+ * soon_dead ([L] ints, may be NULL) receives per layer the number of features with last_active + 2 B > limit:
+ * an upper bound of that layer's dead count in this and the next two steps (a feature only leaves the set
+ * by firing), from which a caller can size the auxiliary path's operands ahead of time. */
 int clt_dead_update(int64_t* last_active, uint32_t* fired_bits, uint8_t* dead, int64_t B, int64_t limit, int L,
-                    int F, int* dead_count, clt_stream_t stream);
+                    int F, int* dead_count, int* soon_dead, clt_stream_t stream);
 
 /* ---- TopK path --------------------------------------------------------------------------- */
 
