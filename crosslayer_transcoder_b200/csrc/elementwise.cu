@@ -29,7 +29,8 @@ __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 v) { retu
 // ---------------------------------------------------------------------------------
 template <class TIn, class TOut>
 __global__ void prep_input_kernel(const TIn* __restrict__ batch, const float* __restrict__ mu,
-                                  const float* __restrict__ sd, TOut* __restrict__ xn, int B, int L, int D) {
+                                  const float* __restrict__ sd, TOut* __restrict__ xn, int B, int L, int D,
+                                  int halves) {
   const long long total = (long long)B * L * D;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -37,8 +38,8 @@ __global__ void prep_input_kernel(const TIn* __restrict__ batch, const float* __
     const long long r = i / D;
     const int l = (int)(r % L);
     const long long b = r / L;
-    const float x = to_float<TIn>(batch[((b * 2 + 0) * L + l) * D + d]);
-    const float v = (x - mu[l * D + d]) / sd[l * D + d];
+    const float x = to_float<TIn>(batch[((b * halves + 0) * L + l) * D + d]);
+    const float v = mu != nullptr ? (x - mu[l * D + d]) / sd[l * D + d] : x;
     xn[((long long)l * B + b) * D + d] = from_float<TOut>(v);
   }
 }
@@ -89,7 +90,8 @@ __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const fl
 // same as prep_input_kernel, 8 consecutive d per thread (needs D % 8 == 0)
 template <class TIn, class TOut>
 __global__ void prep_input_vec_kernel(const TIn* __restrict__ batch, const float* __restrict__ mu,
-                                      const float* __restrict__ sd, TOut* __restrict__ xn, int B, int L, int D) {
+                                      const float* __restrict__ sd, TOut* __restrict__ xn, int B, int L, int D,
+                                      int halves) {
   const int dv = D / 8;
   const long long total = (long long)B * L * dv;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -99,42 +101,44 @@ __global__ void prep_input_vec_kernel(const TIn* __restrict__ batch, const float
     const int l = (int)(r % L);
     const long long b = r / L;
     float x[8], m[8], s[8];
-    load8<TIn>(batch + ((b * 2 + 0) * L + l) * D + d, x);
-    load8<float>(mu + l * D + d, m);
-    load8<float>(sd + l * D + d, s);
+    load8<TIn>(batch + ((b * halves + 0) * L + l) * D + d, x);
+    if (mu != nullptr) {
+      load8<float>(mu + l * D + d, m);
+      load8<float>(sd + l * D + d, s);
 #pragma unroll
-    for (int q = 0; q < 8; ++q) x[q] = (x[q] - m[q]) / s[q];
+      for (int q = 0; q < 8; ++q) x[q] = (x[q] - m[q]) / s[q];
+    }
     store8<TOut>(xn + ((long long)l * B + b) * D + d, x);
   }
 }
 
 template <class TIn, class TOut>
 static int prep_input_t(const void* batch, const float* mu, const float* sd, void* xn, int B, int L, int D,
-                        cudaStream_t s) {
+                        int halves, cudaStream_t s) {
   const int threads = 256;
-  if (D % 8 == 0 && ((uintptr_t)batch | (uintptr_t)xn | (uintptr_t)mu | (uintptr_t)sd) % 16 == 0) {
+  if (D % 8 == 0 && ((uintptr_t)batch | (uintptr_t)xn | (uintptr_t)mu | (uintptr_t)sd) % 16 == 0) {  // (NULL statistics pass)
     const long long total = (long long)B * L * (D / 8);
     const int blocks = (int)min((total + threads - 1) / threads, (long long)148 * 16);
-    prep_input_vec_kernel<TIn, TOut><<<blocks, threads, 0, s>>>((const TIn*)batch, mu, sd, (TOut*)xn, B, L, D);
+    prep_input_vec_kernel<TIn, TOut><<<blocks, threads, 0, s>>>((const TIn*)batch, mu, sd, (TOut*)xn, B, L, D, halves);
   } else {
     const long long total = (long long)B * L * D;
     const int blocks = (int)min((total + threads - 1) / threads, (long long)148 * 16);
-    prep_input_kernel<TIn, TOut><<<blocks, threads, 0, s>>>((const TIn*)batch, mu, sd, (TOut*)xn, B, L, D);
+    prep_input_kernel<TIn, TOut><<<blocks, threads, 0, s>>>((const TIn*)batch, mu, sd, (TOut*)xn, B, L, D, halves);
   }
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
 
 int prep_input(const void* batch, int in_dtype, const float* mu, const float* sd, void* xn, int out_bf16, int B, int L,
-               int D, cudaStream_t s) {
+               int D, int halves, cudaStream_t s) {
   if (B <= 0) return 0;
   switch (in_dtype * 2 + (out_bf16 ? 1 : 0)) {
-    case 0: return prep_input_t<float, float>(batch, mu, sd, xn, B, L, D, s);
-    case 1: return prep_input_t<float, __nv_bfloat16>(batch, mu, sd, xn, B, L, D, s);
-    case 2: return prep_input_t<__half, float>(batch, mu, sd, xn, B, L, D, s);
-    case 3: return prep_input_t<__half, __nv_bfloat16>(batch, mu, sd, xn, B, L, D, s);
-    case 4: return prep_input_t<__nv_bfloat16, float>(batch, mu, sd, xn, B, L, D, s);
-    case 5: return prep_input_t<__nv_bfloat16, __nv_bfloat16>(batch, mu, sd, xn, B, L, D, s);
+    case 0: return prep_input_t<float, float>(batch, mu, sd, xn, B, L, D, halves, s);
+    case 1: return prep_input_t<float, __nv_bfloat16>(batch, mu, sd, xn, B, L, D, halves, s);
+    case 2: return prep_input_t<__half, float>(batch, mu, sd, xn, B, L, D, halves, s);
+    case 3: return prep_input_t<__half, __nv_bfloat16>(batch, mu, sd, xn, B, L, D, halves, s);
+    case 4: return prep_input_t<__nv_bfloat16, float>(batch, mu, sd, xn, B, L, D, halves, s);
+    case 5: return prep_input_t<__nv_bfloat16, __nv_bfloat16>(batch, mu, sd, xn, B, L, D, halves, s);
   }
   set_error("prep_input: unknown input dtype %d", in_dtype);
   return 1;

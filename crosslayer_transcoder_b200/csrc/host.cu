@@ -96,7 +96,7 @@ int clt_device_check(void) {
 
 int clt_prep_input(const void* batch, int in_dtype, const float* mu, const float* sd, void* xn, int bf16, int B, int L,
                    int D, clt_stream_t stream) {
-  return prep_input(batch, in_dtype, mu, sd, xn, bf16, B, L, D, (cudaStream_t)stream);
+  return prep_input(batch, in_dtype, mu, sd, xn, bf16, B, L, D, 2, (cudaStream_t)stream);
 }
 
 int clt_loss_fwd(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu_out,

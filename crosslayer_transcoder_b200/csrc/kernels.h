@@ -8,7 +8,7 @@ int device_sm_count();
 
 // elementwise.cu
 int prep_input(const void* batch, int in_dtype, const float* mu, const float* sd, void* xn, int out_bf16, int B, int L,
-               int D, cudaStream_t s);
+               int D, int halves, cudaStream_t s);
 int loss_fwd(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu, const float* sd,
              float* acc, int B, int L, int D, cudaStream_t s);
 int sum_slots(const float* slots, float* out, int n_slots, long long n, cudaStream_t s);

@@ -148,7 +148,7 @@ class StepEngine:
 
     def _precision(self, batch) -> bool:
         """True for the bf16 tensor-core path.  ``module.precision`` forces it ("bf16" / "fp32");
-        "auto" follows the autocast state the trainer set up (bf16-mixed -> bf16)."""
+        "auto" follows the autocast state the trainer set up (bf16-mixed and 16-mixed -> bf16 operands)."""
         mode = getattr(self.module, "precision", "auto")
         if mode == "bf16":
             return True
@@ -156,9 +156,13 @@ class StepEngine:
             return False
         if torch.is_autocast_enabled("cuda"):
             dt = torch.get_autocast_dtype("cuda")
-            if dt == torch.bfloat16:
+            if dt in (torch.bfloat16, torch.float16):
+                # fp16 autocast (the reference's default "16-mixed", config/default.yaml:13) also runs on the
+                # bf16 tensor-core path: the operands are rounded to bf16 (fp32 exponent range, so nothing can
+                # overflow under a GradScaler's loss scale), which stays inside the bf16 parity bar against
+                # the reference's fp16 run; the scale itself reaches the kernels as the loss gradient.
                 return True
-            raise NotImplementedError(f"autocast dtype {dt} is not supported by the fused step (bf16 or fp32 only)")
+            raise NotImplementedError(f"autocast dtype {dt} is not supported by the fused step")
         return False
 
     def prepare(self, device: torch.device, bf16: bool):
@@ -488,47 +492,155 @@ class StepEngine:
     @torch.no_grad()
     def infer(self, acts: torch.Tensor):
         """``(pre_actvs [B,L,F], features [B,L,F], recons_norm [B,L,D], recons [B,L,D])`` of
-        ``CrossLayerTranscoder.forward`` (reference crosslayer_transcoder/model/clt.py:403-425) with the two
-        contractions on this library's kernels: the encoder product through ``clt_encoder_fwd_store``, the
-        (crosslayer) decoder sum through ``clt_decoder_dense_fwd``.  Standardizers and the nonlinearity are
-        the module's own element-wise PyTorch code.  No autograd graph is built.  On feature shards the
-        partial reconstructions are summed over the ranks; the returned features are the rank's slice, and
-        nonlinearities that rank across the whole feature axis (TopK, BatchTopK) are refused there."""
+        ``CrossLayerTranscoder.forward`` (reference crosslayer_transcoder/model/clt.py:403-425) on this
+        library's kernels from end to end: standardise + cast (``clt_prep_acts``), encoder contraction
+        (``clt_encoder_fwd_store``), the nonlinearity — (Jump)ReLU by ``clt_act_fwd``, PerLayerTopK by
+        ``clt_select_topk``, BatchTopK / PerLayerBatchTopK by the histogram select, each exactly what the
+        module's ``forward(..., layer="all")`` computes, running-threshold update included — the dense or
+        sparse decoder, and the output de-standardisation (``clt_destandardize``).  The token-major fp32
+        tensors of the return value are written by ``clt_export_blf`` / ``clt_scatter_features``.  No
+        autograd graph is built.  On feature shards the partial reconstructions are summed over the ranks;
+        the returned features are the rank's slice, and nonlinearities that rank across the whole feature
+        axis (TopK, BatchTopK) are refused there."""
         if not acts.is_cuda:
             raise CltError("the kernel forward runs on CUDA tensors only (no CPU fallback)")
         if acts.dim() != 3:
             raise CltError(f"expected acts [batch, n_layers, d_acts], got {tuple(acts.shape)}")
+        if acts.dtype not in DTYPE_CODE:
+            raise CltError(f"unsupported activation dtype {acts.dtype}")
         mod, model = self.module, self.module.model
-        enc, dec = model.encoder, model.decoder
+        enc, dec, nl = model.encoder, model.decoder, model.nonlinearity
         B, L, D, F = acts.shape[0], enc.n_layers, enc.d_acts, enc.d_features
         if acts.shape[1] != L or acts.shape[2] != D:
             raise CltError(f"acts {tuple(acts.shape)} do not match n_layers={L}, d_acts={D}")
+        acts = acts.contiguous()
         bf16 = self._precision(acts)
         dev = acts.device
         self.prepare(dev, bf16)
+        kind = mod._kind()
         world, group = getattr(mod, "tp_world", 1), getattr(mod, "tp_group", None)
-        if world > 1 and mod._kind() not in ("jumprelu", "relu"):
+        if world > 1 and kind not in ("jumprelu", "relu"):
             raise NotImplementedError("the kernel forward on feature shards supports element-wise nonlinearities only")
         T = torch.bfloat16 if bf16 else torch.float32
         s = stream_ptr()
-        x = model.input_standardizer(acts.float()) if model.input_standardizer is not None else acts.float()
-        xn = x.permute(1, 0, 2).to(T).contiguous()
+        f32 = lambda t: t.detach().float().contiguous()
+        ins, outs = model.input_standardizer, model.output_standardizer
+        if ins is not None and not ins.is_initialized:
+            raise ValueError("Standardizer not initialized")
+        xn = torch.empty(L, B, D, dtype=T, device=dev)
+        self._call("clt_prep_acts", acts, DTYPE_CODE[acts.dtype], f32(ins.mean) if ins is not None else None,
+                   f32(ins.std) if ins is not None else None, xn, int(bf16), B, L, D, s)
         z = torch.empty(L, B, F, dtype=T, device=dev)
         self._call("clt_encoder_fwd_store", xn, self._operand(enc.W, bf16), z, B, L, D, F, int(bf16), self.status, s)
-        pre_actvs = z.permute(1, 0, 2).float() + enc.b.data
-        features = model.nonlinearity(pre_actvs)
-        feat = features.permute(1, 0, 2).to(T).contiguous()
-        W_op, _, _ = self._dec_flat(bf16)
+        pre_actvs = torch.empty(B, L, F, dtype=torch.float32, device=dev)
+        self._call("clt_export_blf", z, enc.b.data, pre_actvs, B, L, F, int(bf16), s)
+        features = torch.empty(B, L, F, dtype=torch.float32, device=dev)
         recon = torch.empty(B, L, D, dtype=torch.float32, device=dev)
-        first_rank = getattr(mod, "tp_rank", 0) == 0
-        self._call("clt_decoder_dense_fwd", feat, W_op, dec.b.data if first_rank else None, recon, B, L, D, F,
-                   1 if dec.crosslayer else 0, int(bf16), self.status, s)
-        if world > 1:
-            from .parallel import all_reduce_sum
+        W_op, _, _ = self._dec_flat(bf16)
+        crosslayer = 1 if dec.crosslayer else 0
+        bias = dec.b.data if getattr(mod, "tp_rank", 0) == 0 else None
+        if kind in ("jumprelu", "relu"):
+            feat = torch.empty(L, B, F, dtype=T, device=dev)
+            scratch = torch.zeros(2, dtype=torch.float32, device=dev)
+            theta = nl.theta.data if kind == "jumprelu" else None
+            self._call("clt_act_fwd", z, enc.b.data, theta, None, feat, None, scratch, 1.0, 0, 0, B, L, F, int(bf16), s)
+            self._call("clt_export_blf", feat, None, features, B, L, F, int(bf16), s)
+            self._call("clt_decoder_dense_fwd", feat, W_op, bias, recon, B, L, D, F, crosslayer, int(bf16),
+                       self.status, s)
+            if world > 1:
+                from .parallel import all_reduce_sum
 
-            all_reduce_sum(recon, group)
-        recons = model.output_standardizer(recon) if model.output_standardizer is not None else recon
+                all_reduce_sum(recon, group)
+        elif kind == "topk":
+            k = int(nl.k)
+            assert k <= F                                   # reference topk.py:56
+            if k == 0:
+                features.zero_()
+                recon.copy_(dec.b.data.float().unsqueeze(0).expand(B, L, D))
+            else:
+                idx = torch.empty(L, B, k, dtype=torch.int32, device=dev)
+                val = torch.empty(L, B, k, dtype=torch.float32, device=dev)
+                self._call("clt_select_topk", z, enc.b.data, idx, val, None, B, L, F, k, int(bf16), s)
+                self._call("clt_scatter_features", idx, val, None, features, B, L, F, k, B * k, self.status, s)
+                self._call("clt_sparse_decoder_fwd", idx, val, None, None, B * k, W_op, bias, recon, B, L, D, F, k,
+                           crosslayer, 0, int(bf16), self.status, s)
+        else:
+            k = int(nl.k)
+            assert k <= F                                   # reference topk.py:80, 113
+            if nl.e is None and k > 0:
+                raise TypeError("BatchTopK needs its EMA rate `e` (reference topk.py:95)")
+            idx, val, etok, row_start, row_cnt, npl = self._batchtopk_select(z, kind, k, B, L, F, bf16, dev, fired=None)
+            self._call("clt_scatter_features", idx, val, etok, features, B, L, F, 1, npl, self.status, s)
+            self._call("clt_sparse_decoder_fwd", idx, val, row_start, row_cnt, npl, W_op, bias, recon, B, L, D, F, 1,
+                       crosslayer, 0, int(bf16), self.status, s)
+        if outs is not None:
+            if not outs.is_initialized:
+                raise ValueError("Standardizer not initialized")
+            recons = torch.empty_like(recon)
+            self._call("clt_destandardize", recon, f32(outs.mean), f32(outs.std), recons, B, L, D, s)
+        else:
+            recons = recon
         return pre_actvs, features, recon, recons
+
+    @torch.no_grad()
+    def encode_layer(self, acts_norm: torch.Tensor, layer: int) -> torch.Tensor:
+        """``Encoder.forward_layer`` (reference clt.py:134-145): ``acts_norm [..., D] @ W[layer] + b[layer]``
+        on the contraction kernel, fp32 ``[..., F]`` out."""
+        enc = self.module.model.encoder
+        lead, D, F = acts_norm.shape[:-1], enc.d_acts, enc.d_features
+        x = acts_norm.reshape(-1, D).contiguous()
+        if x.dtype not in DTYPE_CODE:
+            x = x.float()
+        B = x.shape[0]
+        bf16 = self._precision(x)
+        dev = x.device
+        self.prepare(dev, bf16)
+        T = torch.bfloat16 if bf16 else torch.float32
+        s = stream_ptr()
+        xn = torch.empty(1, B, D, dtype=T, device=dev)
+        self._call("clt_prep_acts", x, DTYPE_CODE[x.dtype], None, None, xn, int(bf16), B, 1, D, s)
+        z = torch.empty(1, B, F, dtype=T, device=dev)
+        self._call("clt_encoder_fwd_store", xn, self._operand(enc.W, bf16)[layer:layer + 1], z, B, 1, D, F, int(bf16),
+                   self.status, s)
+        out = torch.empty(B, 1, F, dtype=torch.float32, device=dev)
+        self._call("clt_export_blf", z, enc.b.data[layer:layer + 1] if enc.bias else None, out, B, 1, F, int(bf16), s)
+        return out.reshape(*lead, F)
+
+    @torch.no_grad()
+    def decode_layer(self, features: torch.Tensor, layer: int) -> torch.Tensor:
+        """``Decoder.forward_layer`` / ``CrosslayerDecoder.forward_layer`` (reference clt.py:216-231, 304-317):
+        the reconstruction of target ``layer`` from ``features [..., F]`` (per-layer decoder; a 4-D input
+        ``[batch, seq, L, F]`` is cut to its ``layer``) or ``[..., layer + 1, F]`` (crosslayer decoder: the
+        features of the source layers 0..layer), as one contraction over the concatenated source axis."""
+        dec = self.module.model.decoder
+        D, F = dec.d_acts, dec.d_features
+        if dec.crosslayer:
+            n_src = layer + 1
+            if features.shape[-2] != n_src or features.shape[-1] != F:
+                raise CltError(f"expected features [..., {n_src}, {F}], got {tuple(features.shape)}")
+            lead = features.shape[:-2]
+            w = dec.get_parameter(f"W_{layer}")
+        else:
+            if features.ndim == 4:
+                features = features[:, :, layer, :]
+            n_src, lead = 1, features.shape[:-1]
+            w = dec.W
+        K = n_src * F
+        x = features.reshape(-1, K).float().contiguous()
+        B = x.shape[0]
+        bf16 = self._precision(x)
+        dev = x.device
+        self.prepare(dev, bf16)
+        T = torch.bfloat16 if bf16 else torch.float32
+        s = stream_ptr()
+        feat = torch.empty(1, B, K, dtype=T, device=dev)
+        self._call("clt_import_blf", x, feat, B, 1, K, int(bf16), s)
+        w_op = self._operand(w, bf16)
+        w_op = w_op.reshape(1, K, D) if dec.crosslayer else w_op[layer:layer + 1]
+        recon = torch.empty(B, 1, D, dtype=torch.float32, device=dev)
+        self._call("clt_decoder_dense_fwd", feat, w_op, dec.b.data[layer:layer + 1], recon, B, 1, D, K, 0, int(bf16),
+                   self.status, s)
+        return recon.reshape(*lead, D)
 
     # ------------------------------------------------------------------ backward
     def backward(self, ctx: dict, gscale: torch.Tensor):
@@ -801,6 +913,52 @@ class StepEngine:
         W_op, _, _ = self._dec_flat(bf16)
         self._call("clt_prep_input", batch, in_code, mu_i, sd_i, xn, int(bf16), B, L, D, s)
         self._call("clt_encoder_fwd_store", xn, self._operand(enc.W, bf16), z, B, L, D, F, int(bf16), self.status, s)
+        idx, val, etok, row_start, row_cnt, npl = self._batchtopk_select(z, h["kind"], k, B, L, F, bf16, dev,
+                                                                          fired=self.fired)
+        self._call("clt_dead_update", mod.last_active, self.fired, None, B, int(mod.tokens_till_dead), L, F,
+                   self._dead_count(dev), None, s)
+        px = None
+        if world > 1 and getattr(mod, "tp_fused", False) and D % 8 == 0:
+            # exchange fused into the kernels: the sparse decoder stores its partial rows into the owning
+            # ranks' slots, the loss runs on the owned rows (see _peer_exchange)
+            from .parallel import all_reduce_sum
+
+            px = self._peer_exchange(B, L, D, T, dev)
+            self._call("clt_sparse_decoder_fwd_push", idx, val, row_start, row_cnt, npl, W_op, bias,
+                       px["recon_bases"], px["rpr"], world, rank, B, L, D, F, 1, crosslayer, int(k <= 8 * world),
+                       int(bf16), self.status, s)
+            self._rank_barrier(px)                      # every rank's rows have landed in the owners' slots
+            self._sum_slots(px, 0)
+            b_lo, b_cnt = px["b_lo"], px["b_cnt"]
+            if b_cnt > 0:
+                self._call("clt_loss_fwd", px["recon_own"], None, batch[b_lo:b_lo + b_cnt], in_code, mu_o, sd_o,
+                           acc[2:4], b_cnt, L, D, s)
+            all_reduce_sum(acc[2:4], group)             # loss sums of all owners
+        else:
+            self._call("clt_sparse_decoder_fwd", idx, val, row_start, row_cnt, npl, W_op, bias, recon, B, L, D, F, 1,
+                       crosslayer, int(k <= 8 * world), int(bf16), self.status, s)
+            if world > 1:
+                from .parallel import all_reduce_sum
+
+                all_reduce_sum(rbuf[:n_rec], group)
+            self._call("clt_loss_fwd", recon, None, batch, in_code, mu_o, sd_o, acc[2:4], B, L, D, s)
+        self._call("clt_finalize_loss", acc[2:4], None, out[0:1], out[1:5], 1.0 / (B * L * D), 0.0, 0.0, 0.0, s)
+        return dict(kind="batchtopk", bf16=bf16, batch=batch, B=B, L=L, D=D, F=F, k=1, crosslayer=crosslayer, out=out,
+                    stats=(mu_i, sd_i, mu_o, sd_o), in_code=in_code, aux=None, aux_scale=0.0, idx=idx, val=val,
+                    npl=npl, etok=etok, px=px,
+                    recon_rows=(px["recon_own"], px["b_lo"], px["b_cnt"]) if px is not None else (recon, 0, B),
+                    l0_src=(val, 0, npl))
+
+    def _batchtopk_select(self, z, kind, k, B, L, F, bf16, dev, fired):
+        """BatchTopK / PerLayerBatchTopK selection on the stored contraction output ``z`` (reference
+        topk.py:76-96, 109-133): threshold by the three-level histogram select, survivors collected into
+        per-layer entry lists, running threshold updated.  Returns (idx, val, etok, row_start, row_cnt, npl)."""
+        mod = self.module
+        enc, nl = mod.model.encoder, mod.model.nonlinearity
+        ws, s = self.ws, stream_ptr()
+        world, group = getattr(mod, "tp_world", 1), getattr(mod, "tp_group", None)
+        rank = getattr(mod, "tp_rank", 0)
+        h = {"kind": kind}
         # BatchTopK: one selection over the whole batch (all layers, all feature shards);
         # PerLayerBatchTopK: one per layer
         groups = L if h["kind"] == "perlayer_batchtopk" else 1
@@ -837,45 +995,13 @@ class StepEngine:
                 quota = (state[:, 3] - before).clamp(min=0).minimum(state[:, 5]).contiguous()
             fill = ws.get("bt_fill", (L,), torch.int32, dev)
             self._call("clt_batchtopk_collect", z, enc.b.data, state, quota, idx, val, etok, row_start, row_cnt, fill,
-                       self.fired, groups, B, L, F, npl, int(bf16), self.status, s)
+                       fired, groups, B, L, F, npl, int(bf16), self.status, s)
             self._call("clt_batchtopk_threshold_update", state, nl.threshold, float(nl.e), groups, s)
         else:
             val.zero_()
             row_start.zero_()
             row_cnt.zero_()
-        self._call("clt_dead_update", mod.last_active, self.fired, None, B, int(mod.tokens_till_dead), L, F,
-                   self._dead_count(dev), None, s)
-        px = None
-        if world > 1 and getattr(mod, "tp_fused", False) and D % 8 == 0:
-            # exchange fused into the kernels: the sparse decoder stores its partial rows into the owning
-            # ranks' slots, the loss runs on the owned rows (see _peer_exchange)
-            from .parallel import all_reduce_sum
-
-            px = self._peer_exchange(B, L, D, T, dev)
-            self._call("clt_sparse_decoder_fwd_push", idx, val, row_start, row_cnt, npl, W_op, bias,
-                       px["recon_bases"], px["rpr"], world, rank, B, L, D, F, 1, crosslayer, int(k <= 8 * world),
-                       int(bf16), self.status, s)
-            self._rank_barrier(px)                      # every rank's rows have landed in the owners' slots
-            self._sum_slots(px, 0)
-            b_lo, b_cnt = px["b_lo"], px["b_cnt"]
-            if b_cnt > 0:
-                self._call("clt_loss_fwd", px["recon_own"], None, batch[b_lo:b_lo + b_cnt], in_code, mu_o, sd_o,
-                           acc[2:4], b_cnt, L, D, s)
-            all_reduce_sum(acc[2:4], group)             # loss sums of all owners
-        else:
-            self._call("clt_sparse_decoder_fwd", idx, val, row_start, row_cnt, npl, W_op, bias, recon, B, L, D, F, 1,
-                       crosslayer, int(k <= 8 * world), int(bf16), self.status, s)
-            if world > 1:
-                from .parallel import all_reduce_sum
-
-                all_reduce_sum(rbuf[:n_rec], group)
-            self._call("clt_loss_fwd", recon, None, batch, in_code, mu_o, sd_o, acc[2:4], B, L, D, s)
-        self._call("clt_finalize_loss", acc[2:4], None, out[0:1], out[1:5], 1.0 / (B * L * D), 0.0, 0.0, 0.0, s)
-        return dict(kind="batchtopk", bf16=bf16, batch=batch, B=B, L=L, D=D, F=F, k=1, crosslayer=crosslayer, out=out,
-                    stats=(mu_i, sd_i, mu_o, sd_o), in_code=in_code, aux=None, aux_scale=0.0, idx=idx, val=val,
-                    npl=npl, etok=etok, px=px,
-                    recon_rows=(px["recon_own"], px["b_lo"], px["b_cnt"]) if px is not None else (recon, 0, B),
-                    l0_src=(val, 0, npl))
+        return idx, val, etok, row_start, row_cnt, npl
 
     def _backward_topk(self, c, gscale):
         model = self.module.model

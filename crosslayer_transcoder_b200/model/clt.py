@@ -6,8 +6,10 @@ arguments, parameter names and shapes (crosslayer_transcoder/model/clt.py:115-46
     decoder.b [L, D]
 
 The training step does not call these ``forward`` methods: it runs the fused CUDA
-path of ``crosslayer_transcoder_b200.engine`` on the same parameters.  The eager
-definitions below serve inference-style calls (``layer=i``), folding and export.
+path of ``crosslayer_transcoder_b200.engine`` on the same parameters.  The per-layer
+``forward_layer`` calls run on the same kernels when the stack belongs to a training
+module and the input is on the GPU; otherwise, and for folding and export, the eager
+definitions below apply.
 """
 from __future__ import annotations
 
@@ -30,6 +32,16 @@ class _Layered(SerializableModule):
         self.d_acts, self.d_features, self.n_layers = d_acts, d_features, n_layers
         self._is_folded = False
 
+    def _engine(self):
+        """The fused-step engine of the training module that owns this layer stack (set by
+        ``CrossLayerTranscoderModule``), or None: with it the per-layer forwards run on the CUDA kernels."""
+        return self.__dict__.get("_kernel_engine")
+
+    def __getstate__(self):
+        state = dict(self.__dict__)
+        state.pop("_kernel_engine", None)      # device buffers and events of the engine are not part of the module
+        return state
+
 
 class Encoder(_Layered):
     def __init__(self, d_acts: int, d_features: int, n_layers: int):
@@ -47,6 +59,9 @@ class Encoder(_Layered):
 
     @torch.no_grad()
     def forward_layer(self, acts_norm, layer: int):
+        eng = self._engine()
+        if eng is not None and acts_norm.is_cuda:
+            return eng.encode_layer(acts_norm, layer)
         return acts_norm @ self.W[layer] + self.b[layer]
 
     def forward(self, acts_norm, layer="all"):
@@ -86,6 +101,9 @@ class Decoder(_Layered):
 
     @torch.no_grad()
     def forward_layer(self, features, layer: int):
+        eng = self._engine()
+        if eng is not None and features.is_cuda:
+            return eng.decode_layer(features, layer)
         if features.ndim == 4:
             features = features[:, :, layer, :]
         return features @ self.W[layer] + self.b[layer]
@@ -127,6 +145,9 @@ class CrosslayerDecoder(_Layered):
 
     @torch.no_grad()
     def forward_layer(self, features, layer: int):
+        eng = self._engine()
+        if eng is not None and features.is_cuda:
+            return eng.decode_layer(features, layer)
         return torch.einsum("bqsf,sfd->bqd", features, self.get_parameter(f"W_{layer}")) + self.b[layer]
 
     def forward(self, features, layer="all"):

@@ -71,6 +71,9 @@ class CrossLayerTranscoderModule(_Base):
         #: StepEngine._fused_optimizer).  Off by default because the decoder blocks then have no ``.grad``.
         self.fuse_optimizer = False
         self._engine = StepEngine(self)
+        # per-layer forwards of the encoder / decoder (validation-time calls) run on the engine's kernels
+        model.encoder.__dict__["_kernel_engine"] = self._engine
+        model.decoder.__dict__["_kernel_engine"] = self._engine
 
     # ---- nonlinearity -> step kind -----------------------------------------------------
     def _kind(self) -> str:

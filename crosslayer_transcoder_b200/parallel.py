@@ -88,6 +88,7 @@ def shard_module(module, rank: int, world: int) -> None:
     enc.d_features = dec.d_features = hi - lo
     cut(module, "last_active", 1)
     module._engine = StepEngine(module)         # flat buffers are rebuilt for the new shapes
+    enc.__dict__["_kernel_engine"] = dec.__dict__["_kernel_engine"] = module._engine
 
 
 def _symm():

@@ -330,6 +330,28 @@ int clt_batchtopk_collect(const void* z, const float* b_enc, uint64_t* state, co
 /* threshold[g] <- (1 - e) threshold[g] + e * smallest kept value of group g (topk.py:94-95, 131-132). */
 int clt_batchtopk_threshold_update(uint64_t* state, float* threshold, float e, int groups, clt_stream_t stream);
 
+/* ---- inference forward --------------------------------------------------------------------- */
+
+/* CrossLayerTranscoder.forward without gradients (clt.py:403-425) and the per-layer forward_layer calls
+ * (clt.py:134-145, 216-231, 304-317) run on the contraction / selection / decoder entry points above; the
+ * entry points below move between the module surface's token-major fp32 tensors and the kernels'
+ * layer-major operands.
+ * clt_prep_acts: xn[l,b,:] = T((acts[b,l,:] - mu[l]) / sd[l]) for acts [B, L, D] (mu = sd = NULL: cast only).
+ * clt_export_blf: out[b,l,:] = src[l,b,:] (+ bias[l,:]), src [L, B, F] in T, out [B, L, F] fp32.
+ * clt_import_blf: dst[l,b,:] = T(src[b,l,:]).
+ * clt_destandardize: out = recon * sd + mu (DimensionwiseOutputStandardizer.forward, standardize.py:88-98).
+ * clt_scatter_features: dense [B, L, F] fp32 zeroed, then dense[token(e), l, idx[e]] = val[e] for the valid
+ * entries of the lists idx / val [L, npl] (etok NULL: token = slot / k, npl = B k). */
+int clt_prep_acts(const void* acts, int in_dtype, const float* mu, const float* sd, void* xn, int bf16, int B,
+                  int L, int D, clt_stream_t stream);
+int clt_export_blf(const void* src, const float* bias, float* out, int B, int L, int64_t F, int bf16,
+                   clt_stream_t stream);
+int clt_import_blf(const float* src, void* dst, int B, int L, int64_t F, int bf16, clt_stream_t stream);
+int clt_destandardize(const float* recon, const float* mu, const float* sd, float* out, int B, int L, int D,
+                      clt_stream_t stream);
+int clt_scatter_features(const int* idx, const float* val, const int* etok, float* dense, int B, int L, int F,
+                         int k, int64_t npl, int* status, clt_stream_t stream);
+
 /* ---- training metrics ---------------------------------------------------------------------- */
 
 /* The sums behind the reconstruction metrics of log_training_metrics (clt_lightning.py:131-199),

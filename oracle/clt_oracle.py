@@ -30,9 +30,12 @@ Tensor = torch.Tensor
 # --------------------------------------------------------------------------- #
 # helpers
 # --------------------------------------------------------------------------- #
-def _autocast(bf16: bool):
+def _autocast(bf16):
     """bf16 runs restate the reference's ``precision: bf16-mixed`` trainer flag
-    (config/default.yaml:13) with CPU autocast; fp32 runs use no autocast."""
+    (config/default.yaml:13) with CPU autocast; ``"fp16"`` restates its default ``16-mixed``; fp32 runs
+    use no autocast."""
+    if bf16 == "fp16":
+        return torch.autocast("cpu", dtype=torch.float16)
     if bf16:
         return torch.autocast("cpu", dtype=torch.bfloat16)
     return contextlib.nullcontext()
@@ -181,7 +184,7 @@ class Params:
 @dataclass
 class Hyper:
     kind: str = "jumprelu"          # jumprelu | relu | topk | batchtopk | perlayer_batchtopk
-    bf16: bool = False
+    bf16: object = False            # False: fp32, True: bf16 autocast, "fp16": fp16 autocast
     # JumpReLU module (clt_lightning.py:396-409)
     bandwidth: float = 1.0
     lambda_sparsity: float = 0.0    # already multiplied by global_step/max_steps (clt_lightning.py:411-418)

@@ -62,3 +62,37 @@ def test_kernel_forward_needs_cuda_without_grad():
     n0 = mod._engine.launches
     out = mod(batch[:, 0].to(dev))
     assert mod._engine.launches == n0 and out[3].requires_grad
+
+
+@pytest.mark.parametrize("prec", ["fp32", "bf16"])
+@pytest.mark.parametrize("cross", [True, False], ids=["crosslayer", "per_layer"])
+def test_forward_layer_runs_on_the_kernels(cross, prec):
+    """``encoder(x, layer=i)`` / ``decoder(features, layer=i)`` (what the reference's replacement-model metric
+    calls, crosslayer_transcoder/model/clt.py:134-145, 216-231, 304-317) on the contraction kernels against the
+    eager definitions, with the reference's [batch, seq, ...] shapes."""
+    bf16 = prec == "bf16"
+    dev = torch.device("cuda:0")
+    L, D, F = 3, 64, 192
+    spec = synthetic.WorkloadSpec("fl", L, D, F, 8, "jumprelu", cross, bf16, rank_u=8, n_outlier=1)
+    batch, w, la = spec_inputs(spec)
+    mod = build_module(spec, w, dev, last_active=la)
+    enc, dec = mod.model.encoder, mod.model.decoder
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(5, 7, D, generator=g).to(dev)
+    tol = 2e-2 if bf16 else 1e-4
+    n0 = mod._engine.launches
+    for layer in (0, L - 1):
+        got = enc(x, layer=layer)
+        want = x @ enc.W[layer] + enc.b[layer]
+        assert got.shape == want.shape and rel_err(got, want) < tol
+        if cross:
+            feats = torch.relu(torch.randn(5, 7, layer + 1, F, generator=g)).to(dev)
+            want = torch.einsum("bqsf,sfd->bqd", feats, dec.get_parameter(f"W_{layer}")) + dec.b[layer]
+        else:
+            feats = torch.relu(torch.randn(5, 7, L, F, generator=g)).to(dev)
+            want = feats[:, :, layer, :] @ dec.W[layer] + dec.b[layer]
+        got = dec(feats, layer=layer)
+        assert got.shape == want.shape and rel_err(got, want) < tol
+    assert mod._engine.launches >= n0 + 12
+    mod._engine.check_status("forward_layer")
+    assert torch.equal(enc.cpu()(x.cpu(), layer=0), x.cpu() @ enc.W[0] + enc.b[0])      # CPU tensors: eager definition

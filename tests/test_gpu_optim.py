@@ -186,3 +186,37 @@ def test_fused_optimizer_refuses_a_second_backward():
     opt.step()
     mod.training_step(batch.to(dev), 2).backward()      # after the optimizer step the next backward is fine
     opt.step()
+
+
+def test_fp16_mixed_with_grad_scaler_runs_on_the_bf16_path():
+    """The reference's default precision is ``16-mixed`` (fp16 autocast + GradScaler).  Under fp16 autocast the
+    fused step computes with bf16 operands; loss and unscaled gradients must stay within the bf16 parity bar
+    of the reference arithmetic run in fp16, the scaler must find no inf / nan, and the step must train."""
+    from oracle import clt_oracle as O
+    from tests.helpers import oracle_for_spec
+
+    spec = synthetic.WorkloadSpec("amp16", 3, 128, 512, 200, "jumprelu", True, True, rank_u=16, n_outlier=2,
+                                  lambda_sparsity=4e-4, pre_actv_loss=3e-6, lr=1e-3)
+    batch, w, la = spec_inputs(spec)
+    P, H, stats, kw = oracle_for_spec(spec, batch, w, la)
+    H.bf16 = "fp16"
+    ref, ref_grads = O.step_with_grads(P, batch, stats, H, **kw)
+    dev = torch.device("cuda:0")
+    mod = build_module(spec, w, dev)
+    mod.precision = "auto"
+    opt = mod.configure_optimizers()
+    scaler = torch.amp.GradScaler("cuda", init_scale=1024.0)
+    b = batch.to(dev).half()
+    before = mod.model.encoder.W.detach().clone()
+    with torch.autocast("cuda", dtype=torch.float16):
+        loss = mod.training_step(b, 0)
+    scaler.scale(loss).backward()
+    scaler.unscale_(opt)
+    assert rel_err(loss.detach().cpu(), ref.loss) < 2e-2
+    for a, g in zip(module_grad_list(mod), ref_grads):
+        assert rel_err(a.cpu(), g) < 2e-2
+    scaler.step(opt)
+    scaler.update()
+    assert scaler.get_scale() == 1024.0                       # no inf / nan was found
+    assert not torch.equal(mod.model.encoder.W.detach(), before)
+    mod._engine.check_status()
