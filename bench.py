@@ -37,7 +37,8 @@ DEFAULT_WORKLOAD = "c3_clt_topk_bf16"
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the dominant kernels from
 # the ncu captures summarised under profiles/; None where no capture has been taken.
 # Adam: 29.83 B/parameter (profiles/adam_kernel_c3_4layer.md), scaled by the parameter count at run time.
-NCU_TRAFFIC_PER_UNIT = {"clt_adam_step": 29.83}
+# Fused decoder backward + Adam: 26.45 B/decoder parameter (profiles/sparse_bwd_dec_adam_kernel_c3_4layer.md).
+NCU_TRAFFIC_PER_UNIT = {"clt_adam_step": 29.83, "clt_sparse_bwd_dec_adam": 26.45}
 
 
 def load_peaks():
@@ -236,7 +237,6 @@ def algorithmic_work(spec, world: int, Fl: int, n_params: int, batch_bytes_per_e
         "clt_sparse_bwd_enc": ("hbm", float(L) * D * Fl * 4 + ent * D * e),
         "clt_gather_rows": ("hbm", float(P) * nd_pad * D * e * 2),
         "clt_scatter_rows": ("hbm", float(P) * nd_pad * D * 4 * 3),
-        "clt_scatter_cols": ("hbm", float(L) * nd_pad * D * 4 * 3),
         "clt_csc_build": ("hbm", float(L) * B * k * 8 * 2 + float(L) * Fl * 4 * 3),
         "clt_batchtopk_hist": ("hbm", float(L) * B * Fl * e),
         "clt_batchtopk_collect": ("hbm", float(L) * B * Fl * e + float(L) * B * k * 12),
@@ -649,6 +649,7 @@ def main():
         peaks = load_peaks()
         Fl = spec.d_features // world
         n_adam = eng.flat.numel
+        n_dec_params = sum(w.numel() for w in mod.model.decoder.blocks())
         if getattr(mod, "fuse_optimizer", False):
             # the optimizer kernel runs twice per step, before and after the decoder blocks; its per-launch
             # average covers half of the remaining parameters
@@ -683,7 +684,8 @@ def main():
         roofline = {"kernel": top, "bound": tk["bound"], "achieved": tk["achieved"],
                     "peak": peaks["bf16_tflops"] if tk["bound"] == "tensor" else peaks["hbm_gbs"],
                     "unit": tk["unit"], "frac": tk["frac"], "peak_source": peaks["source"],
-                    "traffic": (NCU_TRAFFIC_PER_UNIT[top] * n_adam if top in NCU_TRAFFIC_PER_UNIT else None)}
+                    "traffic": (NCU_TRAFFIC_PER_UNIT[top] * (n_dec_params if top == "clt_sparse_bwd_dec_adam" else n_adam)
+                                if top in NCU_TRAFFIC_PER_UNIT else None)}
         line = {"metric": METRIC, "value": spec.batch * steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
                 "steps": steps, "warmup": warmup, "ms_per_step": ms / steps,
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None,

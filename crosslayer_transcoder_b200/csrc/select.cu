@@ -533,6 +533,7 @@ select_topk_stream_kernel(const T* __restrict__ z, const float* __restrict__ b_e
                           float* __restrict__ val_out, unsigned* __restrict__ fired_bits, int B, int F, int k) {
   __shared__ float c_val[kStreamWarps][kStreamCap];
   __shared__ int c_idx[kStreamWarps][kStreamCap];
+  __shared__ int c_cnt[kStreamWarps];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int l = blockIdx.y;
   const int b = blockIdx.x * kStreamWarps + warp;
@@ -543,7 +544,9 @@ select_topk_stream_kernel(const T* __restrict__ z, const float* __restrict__ b_e
   float* cv = c_val[warp];
   int* ci = c_idx[warp];
   float tau = __uint_as_float(1u);          // smallest positive value: every positive value qualifies at first
-  int count = 0;
+  int* cnt = &c_cnt[warp];
+  if (lane == 0) *cnt = 0;
+  __syncwarp();
   using CL = ChunkLoader<T>;
   // 256 columns per step (8 per lane); the next step's row values are requested before this step's are used
   const int n_steps = F / 256;              // whole steps; the ragged end (F % 256, a multiple of 8) follows
@@ -563,26 +566,30 @@ select_topk_stream_kernel(const T* __restrict__ z, const float* __restrict__ b_e
     bool any = false;
 #pragma unroll
     for (int q = 0; q < 8; ++q) any |= v[q] >= tau;
-    if (__any_sync(0xffffffffu, any)) {
+    if (any) {
+      // append (only lanes with hits run this): a shared-memory counter hands out the slots.  A step adds at
+      // most 256 entries and the list is trimmed whenever it holds more than kStreamCap - 256, so it fits.
+      int mine = 0;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) mine += v[q] >= tau ? 1 : 0;
+      int slot = atomicAdd(cnt, mine);
 #pragma unroll
       for (int q = 0; q < 8; ++q) {
-        const bool hit = v[q] >= tau;
-        const unsigned bal = __ballot_sync(0xffffffffu, hit);
-        if (hit) {
-          const int slot = count + __popc(bal & ((1u << lane) - 1u));
+        if (v[q] >= tau) {
           cv[slot] = v[q];
           ci[slot] = i + q;
+          ++slot;
         }
-        count += __popc(bal);
+      }
+    }
+    __syncwarp();
+    const int count = *reinterpret_cast<volatile int*>(cnt);
+    if (count > kStreamCap - 256) {        // the next step could overflow the list: keep the k best, raise tau
+      if (count > k) {
+        tau = __uint_as_float(stream_keep_top(cv, ci, count, k) + 1u);
+        if (lane == 0) *cnt = k;
       }
       __syncwarp();
-      if (count > kStreamCap - 256) {       // the next 256 elements could overflow the list
-        if (count > k) {
-          tau = __uint_as_float(stream_keep_top(cv, ci, count, k) + 1u);
-          count = k;
-        }
-        __syncwarp();
-      }
     }
   };
   if (n_steps > 0) fetch(8 * lane, cur, b0c, b1c);
@@ -594,33 +601,13 @@ select_topk_stream_kernel(const T* __restrict__ z, const float* __restrict__ b_e
     cur = nxt, b0c = b0n, b1c = b1n;
   }
   if (i_last < F) fetch(i_last, cur, b0c, b1c);
-  {
-    // ragged end (F % 256 columns): lanes beyond F contribute nothing (their values are forced below tau)
-    const bool in = i_last < F;
-    if (__any_sync(0xffffffffu, in)) {
-      float v[8];
-      if (in) {
-        CL::unpack(cur, v);
-        v[0] += b0c.x, v[1] += b0c.y, v[2] += b0c.z, v[3] += b0c.w;
-        v[4] += b1c.x, v[5] += b1c.y, v[6] += b1c.z, v[7] += b1c.w;
-      } else {
-#pragma unroll
-        for (int q = 0; q < 8; ++q) v[q] = 0.f;
-      }
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        const bool hit = v[q] >= tau;
-        const unsigned bal = __ballot_sync(0xffffffffu, hit);
-        if (hit) {
-          const int slot = count + __popc(bal & ((1u << lane) - 1u));
-          cv[slot] = v[q];
-          ci[slot] = i_last + q;
-        }
-        count += __popc(bal);
-      }
-      __syncwarp();
-    }
+  if (__any_sync(0xffffffffu, i_last < F)) {
+    // ragged end (F % 256 columns): lanes beyond F have nothing to add
+    if (i_last < F) consume(i_last, cur, b0c, b1c);
+    else consume(i_last, typename CL::Raw{}, make_float4(-1.f, -1.f, -1.f, -1.f), make_float4(-1.f, -1.f, -1.f, -1.f));
   }
+  __syncwarp();
+  int count = *reinterpret_cast<volatile int*>(cnt);
   if (count > k) {
     stream_keep_top(cv, ci, count, k);
     count = k;

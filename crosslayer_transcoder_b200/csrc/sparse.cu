@@ -592,7 +592,8 @@ template <class T>
 __global__ void __launch_bounds__(256)
 sparse_bwd_enc_kernel(const int* __restrict__ col_ptr, const int* __restrict__ ent, const float* __restrict__ dval,
                       const int* __restrict__ etok, long long npl_, const T* __restrict__ xn, float* __restrict__ dW,
-                      float* __restrict__ db, int B, int D, int F, int k) {
+                      float* __restrict__ db, int B, int D, int F, int k, const float* __restrict__ dW_aux,
+                      const float* __restrict__ db_aux, const int* __restrict__ dead_pos, int nd_pad) {
   const int l = blockIdx.y, f0 = blockIdx.x * kEncFB, d0 = blockIdx.z * 768;
   const int* cp = col_ptr + (size_t)l * (F + 1);
   const size_t npl = (size_t)npl_;
@@ -653,6 +654,21 @@ sparse_bwd_enc_kernel(const int* __restrict__ col_ptr, const int* __restrict__ e
       if ((int)threadIdx.x == q) bsum += bs;
     }
   }
+  // gradient of the auxiliary dead-feature loss (dense contraction over the compact dead features): added
+  // here, so that no separate read-modify-write pass over the scattered columns is needed
+  if (dW_aux != nullptr) {
+#pragma unroll
+    for (int q = 0; q < kEncFB; ++q) {
+      const int pos = f0 + q < F ? __ldg(dead_pos + (size_t)l * F + f0 + q) : -1;   // CTA-uniform
+      if (pos < 0) continue;
+#pragma unroll
+      for (int i = 0; i < 3; ++i) {
+        const int d = d0 + threadIdx.x + 256 * i;
+        if (d < D) acc[i][q] += __ldg(dW_aux + ((size_t)l * D + d) * nd_pad + pos);
+      }
+      if ((int)threadIdx.x == q) bsum += __ldg(db_aux + (size_t)l * nd_pad + pos);
+    }
+  }
   const bool vec = (F % 4 == 0) && (f0 + kEncFB <= F);
 #pragma unroll
   for (int i = 0; i < 3; ++i) {
@@ -710,21 +726,6 @@ __global__ void scatter_rows_kernel(const float* __restrict__ src, const int* __
     x.x += y.x, x.y += y.y, x.z += y.z, x.w += y.w;
     o[i] = x;
   }
-}
-
-// dW_enc[l, d, dead_list[l][j]] += src[l, d, j];  db_enc[l, dead_list[l][j]] += db_src[l, j]
-// blockDim (32, 8): x walks the dead features (coalesced reads of src), y walks input dims.
-__global__ void scatter_cols_kernel(const float* __restrict__ src, const float* __restrict__ db_src,
-                                    const int* __restrict__ dead_list, const int* __restrict__ n_dead,
-                                    float* __restrict__ dW, float* __restrict__ db, int D, int F, int nd_pad) {
-  const int l = blockIdx.y;
-  const int nd = n_dead[l];
-  const int j = blockIdx.x * 32 + threadIdx.x;
-  if (j >= nd) return;
-  const int f = dead_list[(size_t)l * F + j];
-  for (int d = blockIdx.z * 8 + threadIdx.y; d < D; d += 8 * gridDim.z)
-    dW[((size_t)l * D + d) * F + f] += src[((size_t)l * D + d) * nd_pad + j];
-  if (blockIdx.z == 0 && threadIdx.y == 0) db[(size_t)l * F + f] += db_src[(size_t)l * nd_pad + j];
 }
 
 template <class T>
@@ -920,18 +921,24 @@ int clt_sparse_bwd_dec(const int* col_ptr, const int* ent, const float* val, con
 }
 
 int clt_sparse_bwd_enc(const int* col_ptr, const int* ent, const float* dval, const int* etok, int64_t npl,
-                       const void* xn, float* dW_enc, float* db_enc, int B, int L, int D, int F, int k, int bf16,
+                       const void* xn, float* dW_enc, float* db_enc, const float* dW_aux, const float* db_aux,
+                       const int* dead_pos, int nd_pad, int B, int L, int D, int F, int k, int bf16,
                        clt_stream_t stream) {
   CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && F > 0 && k > 0 && npl > 0, "sparse_bwd_enc: bad dims");
   CLT_CHECK_ARG(col_ptr && ent && dval && xn && dW_enc && db_enc, "sparse_bwd_enc: null pointer");
+  CLT_CHECK_ARG((dW_aux == nullptr) == (db_aux == nullptr) && (dW_aux == nullptr) == (dead_pos == nullptr),
+                "sparse_bwd_enc: dW_aux, db_aux and dead_pos go together");
+  CLT_CHECK_ARG(dW_aux == nullptr || nd_pad > 0, "sparse_bwd_enc: nd_pad=%d", nd_pad);
   dim3 grid((F + kEncFB - 1) / kEncFB, L, (D + 767) / 768);
   CLT_CHECK_ARG(grid.y <= 65535 && grid.z <= 65535, "sparse_bwd_enc: grid too large");
   if (bf16)
     sparse_bwd_enc_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>(
-        col_ptr, ent, dval, etok, npl, (const __nv_bfloat16*)xn, dW_enc, db_enc, B, D, F, k);
+        col_ptr, ent, dval, etok, npl, (const __nv_bfloat16*)xn, dW_enc, db_enc, B, D, F, k, dW_aux, db_aux, dead_pos,
+        nd_pad);
   else
     sparse_bwd_enc_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(col_ptr, ent, dval, etok, npl,
-                                                                        (const float*)xn, dW_enc, db_enc, B, D, F, k);
+                                                                        (const float*)xn, dW_enc, db_enc, B, D, F, k,
+                                                                        dW_aux, db_aux, dead_pos, nd_pad);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }
@@ -958,16 +965,6 @@ int clt_scatter_rows(const float* src, const int* dead_list, const int* n_dead, 
   const int P = crosslayer ? L * (L + 1) / 2 : L;
   dim3 grid(nd_pad, P);
   scatter_rows_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(src, dead_list, n_dead, dW_dec, F, D, nd_pad, crosslayer);
-  CLT_CHECK_CUDA(cudaGetLastError());
-  return 0;
-}
-
-int clt_scatter_cols(const float* src, const float* db_src, const int* dead_list, const int* n_dead, float* dW_enc,
-                     float* db_enc, int L, int D, int F, int nd_pad, clt_stream_t stream) {
-  CLT_CHECK_ARG(L > 0 && F > 0 && D > 0 && nd_pad > 0, "scatter_cols: bad dims");
-  dim3 grid((nd_pad + 31) / 32, L, 16), block(32, 8);
-  scatter_cols_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, db_src, dead_list, n_dead, dW_enc, db_enc, D, F,
-                                                                nd_pad);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -1054,8 +1054,12 @@ class StepEngine:
         dval = ws.get("dval", (L, npl), torch.float32, dev)
         self._call("clt_csc_build", idx, val, col_ptr, cursor, ent, npl, L, F, self.status, s)
         fuse_opt = self._fused_optimizer(F)
-        dW_c = dpre_c = db_c = None
+        dW_c = dpre_c = db_c = dead_pos = None
         if aux is not None:
+            # position of every dead feature in the compact operands: the feature-major kernels below add the
+            # auxiliary loss's compact gradients through it
+            dead_pos = ws.get("dead_pos", (L, F), torch.int32, dev)
+            self._call("clt_dead_positions", aux["dead_list"], aux["n_dead"], dead_pos, L, F, aux["nd_pad"], s)
             # auxiliary path, decoder side first: its compact weight gradient is an input of the fused
             # decoder backward + optimizer kernel
             nd_pad, a_aux, w_c = aux["nd_pad"], aux["a_aux"], aux["w_c"]
@@ -1082,10 +1086,6 @@ class StepEngine:
             o0 = fp.offsets[id(dec.blocks()[0])]
             n = W_master.numel()
             m_dec, v_dec = fp.exp_avg[o0:o0 + n], fp.exp_avg_sq[o0:o0 + n]
-            dead_pos = None
-            if aux is not None:
-                dead_pos = ws.get("dead_pos", (L, F), torch.int32, dev)
-                self._call("clt_dead_positions", aux["dead_list"], aux["n_dead"], dead_pos, L, F, aux["nd_pad"], s)
             b1, b2 = grp["betas"]
             self._call("clt_sparse_bwd_dec_adam", col_ptr, ent, val, etok, npl, W_master, m_dec, v_dec,
                        W_op if bf16 else None, drecon, dval, dW_c if aux is not None else None, dead_pos,
@@ -1099,13 +1099,14 @@ class StepEngine:
             if aux is not None:
                 self._call("clt_scatter_rows", dW_c, aux["dead_list"], aux["n_dead"], dW_dec, L, F, D, aux["nd_pad"],
                            cross, s)
-        self._call("clt_sparse_bwd_enc", col_ptr, ent, dval, etok, npl, xn, gview(enc.W), gview(enc.b), B, L, D, F, k,
-                   int(bf16), s)
+        dWe_c = None
         if aux is not None:
-            nd_pad, dl, n_dead = aux["nd_pad"], aux["dead_list"], aux["n_dead"]
+            nd_pad = aux["nd_pad"]
             dWe_c = ws.get("dWe_c", (L, D, nd_pad), torch.float32, dev)
             self._call("clt_encoder_dense_bwd_dw", xn, dpre_c, dWe_c, B, L, D, nd_pad, int(bf16), self.status, s)
-            self._call("clt_scatter_cols", dWe_c, db_c, dl, n_dead, gview(enc.W), gview(enc.b), L, D, F, nd_pad, s)
+        self._call("clt_sparse_bwd_enc", col_ptr, ent, dval, etok, npl, xn, gview(enc.W), gview(enc.b), dWe_c,
+                   db_c if aux is not None else None, dead_pos, aux["nd_pad"] if aux is not None else 0, B, L, D, F,
+                   k, int(bf16), s)
 
     def _aux_sizes(self, n_dead: torch.Tensor, soon_dead: torch.Tensor, cnt, k_aux: int):
         """(nd_pad, exchange) for the auxiliary path: the column count of the compact dead-feature operands

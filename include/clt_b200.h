@@ -284,22 +284,23 @@ int clt_dead_positions(const int* dead_list, const int* n_dead, int* dead_pos, i
 
 /* Backward of the encoder on the selected features (autograd of clt.py:157-165 through the TopK
  * scatter): dW_enc[l,:,f] = sum_{e: idx[e] = f} dval[e] xn[l,b(e),:], db_enc[l,f] = sum dval[e]; every
- * element of both is written. */
+ * element of both is written.  With dW_aux [L, D, nd_pad], db_aux [L, nd_pad] and dead_pos [L, F] (all three or
+ * none) the auxiliary loss's compact encoder gradients are added for the dead features in the same pass:
+ * dW_enc[l,:,f] += dW_aux[l,:,dead_pos[l,f]], db_enc likewise (no separate scatter pass over the columns). */
 int clt_sparse_bwd_enc(const int* col_ptr, const int* ent, const float* dval, const int* etok, int64_t npl,
-                       const void* xn, float* dW_enc, float* db_enc, int B, int L, int D, int F, int k, int bf16,
+                       const void* xn, float* dW_enc, float* db_enc, const float* dW_aux, const float* db_aux,
+                       const int* dead_pos, int nd_pad, int B, int L, int D, int F, int k, int bf16,
                        clt_stream_t stream);
 
 /* Compaction helpers of the auxiliary dead-feature path (clt_lightning.py:544-549 run as dense
  * contractions over the dead features only):
  * gather_rows : out[p, j, :] = W_dec[p, dead_list[s(p)][j], :]              (T, [P, nd_pad, D])
  * scatter_rows: dW_dec[p, dead_list[s(p)][j], :] += src[p, j, :]            (fp32)
- * scatter_cols: dW_enc[l, :, dead_list[l][j]] += src[l, :, j]; db_enc likewise (fp32) */
+ * (the compact encoder gradients are added inside clt_sparse_bwd_enc) */
 int clt_gather_rows(const void* W_dec, const int* dead_list, const int* n_dead, void* out, int L, int F, int D,
                     int nd_pad, int crosslayer, int bf16, clt_stream_t stream);
 int clt_scatter_rows(const float* src, const int* dead_list, const int* n_dead, float* dW_dec, int L, int F,
                      int D, int nd_pad, int crosslayer, clt_stream_t stream);
-int clt_scatter_cols(const float* src, const float* db_src, const int* dead_list, const int* n_dead,
-                     float* dW_enc, float* db_enc, int L, int D, int F, int nd_pad, clt_stream_t stream);
 
 /* ---- BatchTopK path ---------------------------------------------------------------------- */
 
