@@ -396,8 +396,35 @@ __global__ void sum_slots_kernel(const float4* __restrict__ slots, float4* __res
   }
 }
 
-int sum_slots(const float* slots, float* out, int n_slots, long long n, cudaStream_t s) {
+// same with bf16 slots: 8 values per thread
+__global__ void sum_slots_bf16_kernel(const uint4* __restrict__ slots, float4* __restrict__ out, int n_slots,
+                                      long long n8) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < n_slots; ++s) {
+      const uint4 t = __ldcs(slots + (long long)s * n8 + i);
+      const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        a[2 * j] += __uint_as_float(w[j] << 16);
+        a[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+      }
+    }
+    out[2 * i] = make_float4(a[0], a[1], a[2], a[3]);
+    out[2 * i + 1] = make_float4(a[4], a[5], a[6], a[7]);
+  }
+}
+
+int sum_slots(const void* slots, float* out, int n_slots, long long n, int slots_bf16, cudaStream_t s) {
   if (n <= 0) return 0;
+  if (slots_bf16) {
+    const long long n8 = n / 8;
+    const int blocks = (int)min((n8 + 255) / 256, (long long)148 * 16);
+    sum_slots_bf16_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const uint4*>(slots), reinterpret_cast<float4*>(out),
+                                                 n_slots, n8);
+    CLT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+  }
   const long long n4 = n / 4;
   const int blocks = (int)min((n4 + 255) / 256, (long long)148 * 16);
   sum_slots_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const float4*>(slots), reinterpret_cast<float4*>(out),

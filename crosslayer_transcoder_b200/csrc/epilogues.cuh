@@ -327,6 +327,7 @@ struct DecOutPush {
     int rows_per_rank;
     long long ld, zstride;                    // row and slab strides inside a slot
     long long slot_offset;                    // this rank's slot, in elements
+    int slot_bf16;                            // slots hold bf16 partial sums (half the bytes over NVLink)
   };
   struct State {};
   static constexpr int kColArrays = 1;
@@ -335,10 +336,21 @@ struct DecOutPush {
     return p.bias != nullptr ? __ldg(p.bias + (size_t)z * N + n) : 0.f;
   }
   __device__ static void init(State&) {}
-  __device__ static __forceinline__ float* row_ptr(const Params& p, int row, int z) {
+  // element offset of (row, slab z) inside the owner's buffer, and the owner's base address
+  __device__ static __forceinline__ size_t row_off(const Params& p, int row, int z, unsigned long long& base) {
     const int o = row / p.rows_per_rank;
-    return reinterpret_cast<float*>(p.bases[o]) + p.slot_offset + (size_t)(row - o * p.rows_per_rank) * p.ld +
-           (size_t)z * p.zstride;
+    base = p.bases[o];
+    return (size_t)p.slot_offset + (size_t)(row - o * p.rows_per_rank) * p.ld + (size_t)z * p.zstride;
+  }
+  __device__ static __forceinline__ float* row_ptr(const Params& p, int row, int z) {
+    unsigned long long base;
+    const size_t off = row_off(p, row, z, base);
+    return reinterpret_cast<float*>(base) + off;
+  }
+  __device__ static __forceinline__ __nv_bfloat16* row_ptr_bf16(const Params& p, int row, int z) {
+    unsigned long long base;
+    const size_t off = row_off(p, row, z, base);
+    return reinterpret_cast<__nv_bfloat16*>(base) + off;
   }
   template <int CS>
   __device__ static void apply(const Params& p, State&, int z, int row, bool row_ok, int n0, int M, int N,
@@ -347,6 +359,34 @@ struct DecOutPush {
     for (int i = 0; i < 32; ++i) v[i] += colp[i];
     const int lane = threadIdx.x & 31;
     const int row0 = row - lane;
+    if (p.slot_bf16) {
+      if (n0 + 32 <= N && p.ld % 8 == 0 && p.zstride % 8 == 0 && N % 8 == 0) {
+        // 32 values of a row = 64 bytes of bf16: one pass through the staging buffer, 8 rows x 64 bytes per store
+        uint4* mine = reinterpret_cast<uint4*>(stage + lane * kStageRow);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint4 t;
+          t.x = pack_bf16x2(v[8 * i], v[8 * i + 1]), t.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+          t.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), t.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+          mine[i] = t;
+        }
+        __syncwarp();
+        const int piece = lane & 3;
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int r = it * 8 + (lane >> 2);
+          const uint4 t = *reinterpret_cast<const uint4*>(stage + r * kStageRow + piece * 16);
+          if (row0 + r < M) *reinterpret_cast<uint4*>(row_ptr_bf16(p, row0 + r, z) + n0 + piece * 8) = t;
+        }
+        __syncwarp();
+      } else if (row_ok) {
+        __nv_bfloat16* o = row_ptr_bf16(p, row, z) + n0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (n0 + i < N) o[i] = __float2bfloat16_rn(v[i]);
+      }
+      return;
+    }
     if (n0 + 32 <= N && p.ld % 4 == 0 && p.zstride % 4 == 0 && N % 4 == 0) {
       float4* mine = reinterpret_cast<float4*>(stage + lane * kStageRow);
       const int piece = lane & 3;

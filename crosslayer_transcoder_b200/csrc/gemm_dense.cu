@@ -101,8 +101,8 @@ int clt_decoder_dense_fwd(const void* feat, const void* W_dec, const float* b_de
 }
 
 int clt_decoder_dense_fwd_push(const void* feat, const void* W_dec, const float* b_dec, const uint64_t* rank_bases,
-                               int rows_per_rank, int n_ranks, int my_slot, int B, int L, int D, int F, int crosslayer,
-                               int bf16, int* status, clt_stream_t stream) {
+                               int rows_per_rank, int n_ranks, int my_slot, int slot_bf16, int B, int L, int D, int F,
+                               int crosslayer, int bf16, int* status, clt_stream_t stream) {
   CLT_CHECK_ARG(dims_ok(B, L, D, F), "decoder_dense_fwd_push: bad dims B=%d L=%d D=%d F=%d", B, L, D, F);
   CLT_CHECK_ARG(feat && W_dec && rank_bases, "decoder_dense_fwd_push: null pointer");
   CLT_CHECK_ARG(n_ranks > 0 && n_ranks <= epi::kMaxPushRanks && rows_per_rank > 0 &&
@@ -120,6 +120,7 @@ int clt_decoder_dense_fwd_push(const void* feat, const void* W_dec, const float*
   p.ld = (long long)L * D;
   p.zstride = (long long)D;
   p.slot_offset = (long long)my_slot * rows_per_rank * L * D;
+  p.slot_bf16 = slot_bf16 ? 1 : 0;
   return run_gemm<epi::DecOutPush, epi::DecOutPush>(g, a, b, p, p, bf16, status, (cudaStream_t)stream);
 }
 

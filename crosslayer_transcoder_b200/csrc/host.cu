@@ -117,9 +117,10 @@ int clt_loss_bwd(const float* recon, const float* aux, const void* batch, int in
                   (cudaStream_t)stream);
 }
 
-int clt_sum_slots(const float* slots, float* out, int n_slots, int64_t n, clt_stream_t stream) {
-  CLT_CHECK_ARG(slots && out && n_slots > 0 && n >= 0 && n % 4 == 0, "sum_slots: bad arguments (n %% 4 == 0)");
-  return sum_slots(slots, out, n_slots, (long long)n, (cudaStream_t)stream);
+int clt_sum_slots(const void* slots, float* out, int n_slots, int64_t n, int slots_bf16, clt_stream_t stream) {
+  CLT_CHECK_ARG(slots && out && n_slots > 0 && n >= 0 && n % (slots_bf16 ? 8 : 4) == 0,
+                "sum_slots: bad arguments (n must be a multiple of 4, of 8 for bf16 slots)");
+  return sum_slots(slots, out, n_slots, (long long)n, slots_bf16, (cudaStream_t)stream);
 }
 
 int clt_loss_bwd_push(const float* recon_own, const float* aux_own, const void* batch, int in_dtype,

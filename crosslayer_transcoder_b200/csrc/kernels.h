@@ -11,7 +11,7 @@ int prep_input(const void* batch, int in_dtype, const float* mu, const float* sd
                int D, int halves, cudaStream_t s);
 int loss_fwd(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu, const float* sd,
              float* acc, int B, int L, int D, cudaStream_t s);
-int sum_slots(const float* slots, float* out, int n_slots, long long n, cudaStream_t s);
+int sum_slots(const void* slots, float* out, int n_slots, long long n, int slots_bf16, cudaStream_t s);
 int loss_bwd_push(const float* recon, const float* aux, const void* batch, int in_dtype, const float* mu,
                   const float* sd, const float* gscale, float aux_scale, const unsigned long long* drecon_ptrs,
                   const unsigned long long* daux_ptrs, int n_ranks, int out_bf16, float* db_dec, int B, int b_lo,

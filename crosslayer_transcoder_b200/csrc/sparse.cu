@@ -83,12 +83,24 @@ struct PushDst {
   unsigned long long bases[kMaxPushRanks];  // address of each rank's buffer
   int rows_per_rank;                        // 0 = plain store to `recon`
   long long slot_offset;                    // this rank's slot: slot * rows_per_rank * L * D elements
+  int slot_bf16;                            // slots hold bf16 partial sums (half the bytes over NVLink)
 };
 
 __device__ __forceinline__ float* push_row(const PushDst& p, float* recon, int b, int t, int L, int D) {
   if (p.rows_per_rank == 0) return recon + ((size_t)b * L + t) * D;
   const int o = b / p.rows_per_rank;
   return reinterpret_cast<float*>(p.bases[o]) + p.slot_offset + ((size_t)(b - o * p.rows_per_rank) * L + t) * D;
+}
+__device__ __forceinline__ __nv_bfloat16* push_row_bf16(const PushDst& p, int b, int t, int L, int D) {
+  const int o = b / p.rows_per_rank;
+  return reinterpret_cast<__nv_bfloat16*>(p.bases[o]) + p.slot_offset +
+         ((size_t)(b - o * p.rows_per_rank) * L + t) * D;
+}
+__device__ __forceinline__ void store8_bf16(__nv_bfloat16* o, const float (&v)[8]) {
+  uint4 t;
+  t.x = pack_bf16x2(v[0], v[1]), t.y = pack_bf16x2(v[2], v[3]);
+  t.z = pack_bf16x2(v[4], v[5]), t.w = pack_bf16x2(v[6], v[7]);
+  *reinterpret_cast<uint4*>(o) = t;
 }
 
 // =========================================================================================
@@ -151,6 +163,19 @@ sparse_dec_fwd_kernel(const int* __restrict__ idx, const float* __restrict__ val
     }
   }
   __syncthreads();
+  if (push.rows_per_rank != 0 && push.slot_bf16) {  // bf16 slots: 8 columns = one 16-byte store (D % 8 == 0)
+    __nv_bfloat16* ob = push_row_bf16(push, b, t, L, D);
+    for (int d = 8 * threadIdx.x; d < D; d += 8 * 128) {
+      float sum[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        sum[q] = red[d + q] + red[D + d + q] + red[2 * D + d + q] + red[3 * D + d + q];
+        if (b_dec != nullptr) sum[q] += __ldg(b_dec + (size_t)t * D + d + q);
+      }
+      store8_bf16(ob + d, sum);
+    }
+    return;
+  }
   float* out = push_row(push, recon, b, t, L, D);
   if (D % 4 == 0) {  // 16-byte stores (always the case for pushed rows: D % 8 == 0 there)
     for (int d = 4 * threadIdx.x; d < D; d += 4 * 128) {
@@ -242,6 +267,22 @@ sparse_dec_fwd_warp_kernel(const int* __restrict__ idx, const float* __restrict_
       }
       if (valid < m) break;
     }
+  }
+  if (push.rows_per_rank != 0 && push.slot_bf16) {
+    __nv_bfloat16* ob = push_row_bf16(push, b, t, L, D);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nvec) {
+        float bb[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (b_dec != nullptr) Vec8<float>::load(b_dec + (size_t)t * D + 8 * c, bb);
+        float o8[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) o8[q] = acc[i][q] + bb[q];
+        store8_bf16(ob + 8 * c, o8);
+      }
+    }
+    return;
   }
   float* out = push_row(push, recon, b, t, L, D);
 #pragma unroll
@@ -731,7 +772,7 @@ __global__ void scatter_rows_kernel(const float* __restrict__ src, const int* __
 template <class T>
 int launch_dec_fwd(const int* idx, const float* val, const int* row_start, const int* row_cnt, long long npl,
                    const void* W, const float* b_dec, float* recon, int B, int L, int D, int F, int k, int crosslayer,
-                   int short_rows, int* status, cudaStream_t s, PushDst push = PushDst{{0ull}, 0, 0}) {
+                   int short_rows, int* status, cudaStream_t s, PushDst push = PushDst{{0ull}, 0, 0, 0}) {
   const int vpl = (D / 8 + 31) / 32;
   dim3 grid(B, L);
   const size_t smem = 4 * (size_t)D * sizeof(float);
@@ -822,8 +863,8 @@ int clt_sparse_decoder_fwd(const int* idx, const float* val, const int* row_star
 
 int clt_sparse_decoder_fwd_push(const int* idx, const float* val, const int* row_start, const int* row_cnt, int64_t npl,
                                 const void* W_dec, const float* b_dec, const uint64_t* rank_bases, int rows_per_rank,
-                                int n_ranks, int my_slot, int B, int L, int D, int F, int k, int crosslayer,
-                                int short_rows, int bf16, int* status, clt_stream_t stream) {
+                                int n_ranks, int my_slot, int slot_bf16, int B, int L, int D, int F, int k,
+                                int crosslayer, int short_rows, int bf16, int* status, clt_stream_t stream) {
   CLT_CHECK_ARG(B > 0 && L > 0 && D > 0 && F > 0 && k > 0, "sparse_decoder_fwd_push: bad dims B=%d L=%d D=%d F=%d k=%d",
                 B, L, D, F, k);
   CLT_CHECK_ARG(D % 8 == 0, "sparse_decoder_fwd_push: d_acts=%d must be a multiple of 8", D);
@@ -841,6 +882,7 @@ int clt_sparse_decoder_fwd_push(const int* idx, const float* val, const int* row
   CLT_CHECK_ARG(my_slot >= 0 && my_slot < n_ranks, "sparse_decoder_fwd_push: slot %d of %d", my_slot, n_ranks);
   push.rows_per_rank = rows_per_rank;
   push.slot_offset = (long long)my_slot * rows_per_rank * L * D;
+  push.slot_bf16 = slot_bf16 ? 1 : 0;
   if (bf16)
     return launch_dec_fwd<__nv_bfloat16>(idx, val, row_start, row_cnt, npl, W_dec, b_dec, nullptr, B, L, D, F, k,
                                          crosslayer, short_rows, status, (cudaStream_t)stream, push);

@@ -342,24 +342,28 @@ class StepEngine:
         decoder kernels store into them); ``recon_own`` / ``aux_own`` are their sums (``_sum_slots``);
         ``drecon`` / ``daux`` [L, B, D] receive every owner's gradient rows (the loss backward writes
         them into all ranks' copies)."""
-        key = (B, L, D, T, dev)
+        mod = self.module
+        # bf16 steps exchange the partial rows as bf16 (half the NVLink bytes; the owner sums them in fp32);
+        # module.tp_bf16_partials = False keeps fp32 slots
+        slot_bf16 = T == torch.bfloat16 and bool(getattr(mod, "tp_bf16_partials", True)) and D % 8 == 0
+        key = (B, L, D, T, dev, slot_bf16)
         px = getattr(self, "_px", None)
         if px is not None and px["key"] == key:
             return px
         from .parallel import PeerBuffer
 
-        mod = self.module
         world, rank, group = mod.tp_world, mod.tp_rank, mod.tp_group
         rpr = (B + world - 1) // world
         b_lo = min(B, rank * rpr)
         b_cnt = max(0, min(B, b_lo + rpr) - b_lo)
         # [0] main, [1] auxiliary reconstruction; one slot per source rank
-        slots = PeerBuffer((2, world, rpr, L, D), torch.float32, dev, group)
+        slots = PeerBuffer((2, world, rpr, L, D), torch.bfloat16 if slot_bf16 else torch.float32, dev, group)
         own = torch.empty(2, rpr, L, D, dtype=torch.float32, device=dev)
         drecon = PeerBuffer((L, B, D), T, dev, group)
         daux = PeerBuffer((L, B, D), T, dev, group)
         self._px = dict(key=key, rpr=rpr, b_lo=b_lo, b_cnt=b_cnt, slots=slots, recon_own=own[0], aux_own=own[1],
-                        recon_bases=slots.bases, aux_bases=slots.bases + world * rpr * L * D * 4,
+                        recon_bases=slots.bases, slot_bf16=int(slot_bf16),
+                        aux_bases=slots.bases + world * rpr * L * D * (2 if slot_bf16 else 4),
                         drecon=drecon, daux=daux, token=torch.zeros(1, dtype=torch.float32, device=dev))
         return self._px
 
@@ -374,7 +378,7 @@ class StepEngine:
         """Add the per-source slots of the owned rows (0: main, 1: auxiliary reconstruction)."""
         n = px["recon_own"].numel()
         self._call("clt_sum_slots", px["slots"].local[which], px["recon_own"] if which == 0 else px["aux_own"],
-                   self.module.tp_world, n, stream_ptr())
+                   self.module.tp_world, n, px["slot_bf16"], stream_ptr())
 
     def _rank_barrier(self, px):
         """Order the ranks on the compute stream: a one-element all-reduce.  After it, every kernel that
@@ -459,8 +463,8 @@ class StepEngine:
 
             px = self._peer_exchange(B, L, D, T, dev)
             self._call("clt_decoder_dense_fwd_push", feat, W_op, dec.b.data if first_rank else None,
-                       px["recon_bases"], px["rpr"], world, mod.tp_rank, B, L, D, F, crosslayer, int(bf16),
-                       self.status, s)
+                       px["recon_bases"], px["rpr"], world, mod.tp_rank, px["slot_bf16"], B, L, D, F, crosslayer,
+                       int(bf16), self.status, s)
             self._rank_barrier(px)                      # every rank's tiles have landed in the owners' slots
             self._sum_slots(px, 0)
             b_lo, b_cnt = px["b_lo"], px["b_cnt"]
@@ -817,8 +821,8 @@ class StepEngine:
         def main_decoder():
             if px is not None:
                 self._call("clt_sparse_decoder_fwd_push", idx, val, None, None, B * kk, W_op, bias,
-                           px["recon_bases"], px["rpr"], world, mod.tp_rank, B, L, D, F, kk, crosslayer,
-                           int(kk <= 8 * world), int(bf16), self.status, s)
+                           px["recon_bases"], px["rpr"], world, mod.tp_rank, px["slot_bf16"], B, L, D, F, kk,
+                           crosslayer, int(kk <= 8 * world), int(bf16), self.status, s)
                 return
             self._call("clt_sparse_decoder_fwd", idx, val, None, None, B * kk, W_op, bias, recon, B, L, D, F, kk,
                        crosslayer, int(kk <= 8 * world), int(bf16), self.status, s)
@@ -846,7 +850,7 @@ class StepEngine:
             if px is not None:
                 # the contraction's epilogue adds each tile to the owning ranks' buffers
                 self._call("clt_decoder_dense_fwd_push", a_aux, w_c, bias, px["aux_bases"], px["rpr"], world,
-                           mod.tp_rank, B, L, D, nd_pad, crosslayer, int(bf16), self.status, s)
+                           mod.tp_rank, px["slot_bf16"], B, L, D, nd_pad, crosslayer, int(bf16), self.status, s)
             else:
                 self._call("clt_decoder_dense_fwd", a_aux, w_c, bias, aux_recon, B, L, D, nd_pad, crosslayer,
                            int(bf16), self.status, s)
@@ -925,8 +929,8 @@ class StepEngine:
 
             px = self._peer_exchange(B, L, D, T, dev)
             self._call("clt_sparse_decoder_fwd_push", idx, val, row_start, row_cnt, npl, W_op, bias,
-                       px["recon_bases"], px["rpr"], world, rank, B, L, D, F, 1, crosslayer, int(k <= 8 * world),
-                       int(bf16), self.status, s)
+                       px["recon_bases"], px["rpr"], world, rank, px["slot_bf16"], B, L, D, F, 1, crosslayer,
+                       int(k <= 8 * world), int(bf16), self.status, s)
             self._rank_barrier(px)                      # every rank's rows have landed in the owners' slots
             self._sum_slots(px, 0)
             b_lo, b_cnt = px["b_lo"], px["b_cnt"]

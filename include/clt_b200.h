@@ -73,8 +73,8 @@ int clt_decoder_dense_fwd(const void* feat, const void* W_dec, const float* b_de
  * buffers (16-byte stores, over NVLink for the peers) while the tensor cores work on the next tile.
  * Replaces the DTensor all-reduce after the decoder (crosslayer_transcoder/model/parallel.py:157-339). */
 int clt_decoder_dense_fwd_push(const void* feat, const void* W_dec, const float* b_dec, const uint64_t* rank_bases,
-                               int rows_per_rank, int n_ranks, int my_slot, int B, int L, int D, int F, int crosslayer,
-                               int bf16, int* status, clt_stream_t stream);
+                               int rows_per_rank, int n_ranks, int my_slot, int slot_bf16, int B, int L, int D, int F,
+                               int crosslayer, int bf16, int* status, clt_stream_t stream);
 
 /* Reconstruction MSE (clt_lightning.py:303-304) and, with aux != NULL, the TopK auxiliary
  * loss (clt_lightning.py:548-551).  acc[0] += sum diff^2, acc[1] += sum (aux + diff)^2. */
@@ -222,12 +222,16 @@ int clt_sparse_decoder_fwd(const int* idx, const float* val, const int* row_star
  * DTensor all-reduce after the decoder (crosslayer_transcoder/model/parallel.py:157-339). */
 int clt_sparse_decoder_fwd_push(const int* idx, const float* val, const int* row_start, const int* row_cnt,
                                 int64_t npl, const void* W_dec, const float* b_dec, const uint64_t* rank_bases,
-                                int rows_per_rank, int n_ranks, int my_slot, int B, int L, int D, int F, int k,
-                                int crosslayer, int short_rows, int bf16, int* status, clt_stream_t stream);
+                                int rows_per_rank, int n_ranks, int my_slot, int slot_bf16, int B, int L, int D,
+                                int F, int k, int crosslayer, int short_rows, int bf16, int* status,
+                                clt_stream_t stream);
 
-/* out[i] = sum_s slots[s n + i], i < n (n % 4 == 0): the owner's local reduction of the slots the ranks
- * filled with the *_push entry points.  No reference counterpart (part of the fused exchange). */
-int clt_sum_slots(const float* slots, float* out, int n_slots, int64_t n, clt_stream_t stream);
+/* out[i] = sum_s slots[s n + i], i < n (n % 4 == 0; n % 8 == 0 for bf16 slots): the owner's local reduction
+ * of the slots the ranks filled with the *_push entry points.  No reference counterpart (part of the fused
+ * exchange).  slot_bf16 / slots_bf16 != 0 (both *_push entry points and this one): the slots hold the partial
+ * rows rounded to bf16, which halves the bytes every rank sends over NVLink; the sum is taken in fp32.  (Under
+ * bf16 autocast the reference's decoder product is itself rounded to bf16 before it is summed over the ranks.) */
+int clt_sum_slots(const void* slots, float* out, int n_slots, int64_t n, int slots_bf16, clt_stream_t stream);
 
 /* Feature-major copy of the selection: col_ptr [L, F+1], ent [L, npl] (entry slots grouped by
  * feature).  cursor [L, F] is scratch. */

@@ -34,8 +34,8 @@ def test_sparse_decoder_push_matches_plain(bf16, short_rows):
                bf16, status, stream_ptr())
     rpr = (B + R - 1) // R
     bufs = [torch.zeros(R, rpr, L, D, device=dev) for _ in range(R)]      # owner buffers: one slot per source
-    lib().call("clt_sparse_decoder_fwd_push", idx, val, None, None, B * k, W, bias, _bases(bufs), rpr, R, 1, B, L, D, F,
-               k, 1, short_rows, bf16, status, stream_ptr())
+    lib().call("clt_sparse_decoder_fwd_push", idx, val, None, None, B * k, W, bias, _bases(bufs), rpr, R, 1, 0, B, L, D,
+               F, k, 1, short_rows, bf16, status, stream_ptr())
     torch.cuda.synchronize()
     assert int(status) == 0
     got = torch.cat([b[1] for b in bufs], 0)                    # slot 1 of every owner
@@ -43,13 +43,25 @@ def test_sparse_decoder_push_matches_plain(bf16, short_rows):
     assert float(got[B:].abs().sum()) == 0.0                    # rows past B stay untouched
     assert all(float(b[0].abs().sum()) == 0.0 and float(b[2].abs().sum()) == 0.0 for b in bufs)   # other slots too
     # a second source fills another slot; the owner's sum of its slots is the reduced reconstruction
-    lib().call("clt_sparse_decoder_fwd_push", idx, val, None, None, B * k, W, None, _bases(bufs), rpr, R, 2, B, L, D, F,
-               k, 1, short_rows, bf16, status, stream_ptr())
+    lib().call("clt_sparse_decoder_fwd_push", idx, val, None, None, B * k, W, None, _bases(bufs), rpr, R, 2, 0, B, L, D,
+               F, k, 1, short_rows, bf16, status, stream_ptr())
     own = [torch.empty(rpr, L, D, device=dev) for _ in range(R)]
     for b, o in zip(bufs, own):
-        lib().call("clt_sum_slots", b, o, R, rpr * L * D, stream_ptr())
+        lib().call("clt_sum_slots", b, o, R, rpr * L * D, 0, stream_ptr())
     torch.cuda.synchronize()
     assert torch.allclose(torch.cat(own, 0)[:B], 2 * recon - bias, rtol=1e-6, atol=1e-6)
+    # bf16 slots: the same partial rows rounded to bf16 (half the bytes), summed in fp32 by the owner
+    hb = [torch.zeros(R, rpr, L, D, device=dev, dtype=torch.bfloat16) for _ in range(R)]
+    for slot, bb in ((0, bias), (2, None)):
+        lib().call("clt_sparse_decoder_fwd_push", idx, val, None, None, B * k, W, bb, _bases(hb), rpr, R, slot, 1, B, L,
+                   D, F, k, 1, short_rows, bf16, status, stream_ptr())
+    for b, o in zip(hb, own):
+        lib().call("clt_sum_slots", b, o, R, rpr * L * D, 1, stream_ptr())
+    torch.cuda.synchronize()
+    assert int(status) == 0
+    assert torch.equal(torch.cat([b[0] for b in hb], 0)[:B], recon.bfloat16())
+    want = recon.bfloat16().float() + (recon - bias).bfloat16().float()
+    assert torch.allclose(torch.cat(own, 0)[:B], want, rtol=1e-6, atol=1e-6)
 
 
 @pytest.mark.parametrize("bf16", [0, 1])
@@ -70,7 +82,7 @@ def test_dense_decoder_push_matches_plain(bf16):
     lib().call("clt_decoder_dense_fwd", feat, W, bias, recon, B, L, D, F, 1, bf16, status, stream_ptr())
     rpr = (B + R - 1) // R
     bufs = [torch.zeros(R, rpr, L, D, device=dev) for _ in range(R)]
-    lib().call("clt_decoder_dense_fwd_push", feat, W, bias, _bases(bufs), rpr, R, 2, B, L, D, F, 1, bf16, status,
+    lib().call("clt_decoder_dense_fwd_push", feat, W, bias, _bases(bufs), rpr, R, 2, 0, B, L, D, F, 1, bf16, status,
                stream_ptr())
     torch.cuda.synchronize()
     assert int(status) == 0
