@@ -381,6 +381,70 @@ def time_cpu_reference(spec, workload: str, override: str, full_budget_s: float)
 
 
 # --------------------------------------------------------------------------------------
+def time_ingest(spec, dev, batches: int = 10) -> dict:
+    """Batch ingestion from the reference's activation store, both ways, on this machine: the reference's own
+    consumer (``SharedActivationBuffer.get_activations`` on one CPU thread, then the upload of the pageable
+    batch it returns) against the device-side consumer (``data.SharedBufferBatches``: the GPU gathers the
+    same choice of rows from the registered shared mapping).  ms per batch of ``spec.batch`` rows."""
+    import shutil
+
+    from crosslayer_transcoder_b200 import data
+    from oracle import ref_import
+
+    shm_mod = ref_import.load_shared_memory()
+    if shm_mod is None:
+        return {"unavailable": "the reference's shared_memory.py is not present (oracle/_ref missing)"}
+    B, L, D = spec.batch, spec.n_layers, spec.d_acts
+    n = 3 * B
+    need = n * 2 * L * D * 2
+    if shutil.disk_usage("/dev/shm").free < need + (256 << 20):
+        return {"unavailable": f"/dev/shm has less than {need >> 20} MiB free"}
+    store = shm_mod.SharedActivationBuffer(buffer_size=n, n_in_out=2, n_layers=L, activation_dim=D,
+                                           dtype=torch.float16, generation_batch_size=1, max_sequence_length=64,
+                                           batch_size=B)
+    try:
+        chunk = torch.randn(500, 2, L, D).half()
+        for i in range(0, n, 500):
+            store.buffer_tensor[i:i + 500] = chunk[: min(500, n - i)]
+        store.validity_tensor.fill_(True)
+        t_get, t_all = [], []
+        for _ in range(batches):
+            t0 = time.perf_counter()
+            x = store.get_activations(B)
+            t1 = time.perf_counter()
+            x.to(dev)
+            torch.cuda.synchronize()
+            t2 = time.perf_counter()
+            t_get.append(t1 - t0)
+            t_all.append(t2 - t0)
+            store.validity_tensor.fill_(True)
+        t_get.sort()
+        t_all.sort()
+        out = {"rows_per_batch": B, "bytes_per_batch": B * 2 * L * D * 2,
+               "reference_get_activations_ms": 1e3 * t_get[len(t_get) // 2],
+               "reference_with_upload_ms": 1e3 * t_all[len(t_all) // 2]}
+        for mode in ("mapped", "staged"):
+            src = data.SharedBufferBatches(store, B, device=dev, depth=2, mode=mode)
+            try:
+                for _ in range(3):
+                    next(src)
+                    store.validity_tensor.fill_(True)
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for _ in range(batches):
+                    next(src)
+                    store.validity_tensor.fill_(True)
+                torch.cuda.synchronize()
+                out[f"device_consumer_{mode}_ms"] = 1e3 * (time.perf_counter() - t0) / batches
+                src.gather.check()
+            finally:
+                src.close()
+        out["mapped_gather_GBps"] = out["bytes_per_batch"] / out["device_consumer_mapped_ms"] / 1e6
+        return out
+    finally:
+        store.cleanup()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -400,6 +464,9 @@ def main():
     ap.add_argument("--no-fuse-optimizer", action="store_true",
                     help="TopK / BatchTopK workloads: keep the decoder's Adam update in the optimizer kernel "
                          "instead of applying it inside the sparse decoder backward (module.fuse_optimizer)")
+    ap.add_argument("--ingest", action="store_true",
+                    help="1 GPU: also time batch ingestion from the reference's shared-memory activation store "
+                         "(its own consumer vs the device-side one) and add an `ingest` object to the line")
     ap.add_argument("--ref-full-budget-s", type=float, default=150.0,
                     help="--impl reference: time the full workload shape if one step is predicted to fit this")
     args = ap.parse_args()
@@ -707,6 +774,11 @@ def main():
             else:
                 line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
                                         "sample": "unavailable: " + ("oracle/_ref missing" if r is None else r["error"])}
+        if world == 1 and args.ingest:
+            try:
+                line["ingest"] = time_ingest(spec, dev)
+            except Exception as e:
+                line["ingest"] = {"unavailable": f"{type(e).__name__}: {str(e).splitlines()[0][:160]}"}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

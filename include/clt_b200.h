@@ -357,6 +357,22 @@ int clt_destandardize(const float* recon, const float* mu, const float* sd, floa
 int clt_scatter_features(const int* idx, const float* val, const int* etok, float* dense, int B, int L, int F,
                          int k, int64_t npl, int* status, clt_stream_t stream);
 
+/* ---- batch ingestion ----------------------------------------------------------------------- */
+
+/* The reference's activation store keeps `[buffer_size, 2, L, D]` rows in host shared memory and its
+ * get_activations (crosslayer_transcoder/data/shared_memory.py:168-214) gathers a random batch of valid
+ * rows into a new pageable tensor on one CPU thread.  Replacement: map the store into the device's
+ * address space once (clt_host_register: cudaHostRegister, mapped + portable; *device_ptr is the address
+ * the kernels use; clt_host_unregister before the mapping goes away), then per batch
+ *   dst[i, :] = src[rows[i], :]     (clt_gather_batch_rows; rows: n_rows 64-bit indices in device memory)
+ * read by the GPU over PCIe with 16-byte loads.  src may equally be device memory.  row_bytes must be a
+ * multiple of 16 and both buffers 16-byte aligned; a row index outside [0, n_src_rows) is skipped and
+ * status (may be NULL) set to 0x20. */
+int clt_host_register(void* host_ptr, int64_t bytes, void** device_ptr);
+int clt_host_unregister(void* host_ptr);
+int clt_gather_batch_rows(const void* src, const int64_t* rows, void* dst, int64_t row_bytes, int n_rows,
+                          int64_t n_src_rows, int* status, clt_stream_t stream);
+
 /* ---- training metrics ---------------------------------------------------------------------- */
 
 /* The sums behind the reconstruction metrics of log_training_metrics (clt_lightning.py:131-199),

@@ -11,6 +11,8 @@ own packaging cannot be used offline (its build backend, hatchling, is not insta
 byte-for-byte mirror of
 
     crosslayer_transcoder/model/*.py      crosslayer_transcoder/metrics/*.py
+    crosslayer_transcoder/data/shared_memory.py   (the activation store whose consumer the ingestion tests
+                                                   and the benchmark's ingestion comparison run against)
 
 ``oracle/ref_import.py`` imports them from the reference tree when it is present and from this mirror
 otherwise.
@@ -25,6 +27,7 @@ from pathlib import Path
 SRC = Path(os.environ.get("CLT_REFERENCE_ROOT", "/root/reference"))
 DST = Path(__file__).resolve().parent / "_ref"
 SUBDIRS = ("model", "metrics")
+FILES = ("data/shared_memory.py",)
 
 
 def make(verbose: bool = True) -> bool:
@@ -39,8 +42,12 @@ def make(verbose: bool = True) -> bool:
         out.mkdir(parents=True, exist_ok=True)
         for f in sorted((base / sub).glob("*.py")):
             shutil.copyfile(f, out / f.name)
+    for rel in FILES:
+        out = DST / "crosslayer_transcoder" / rel
+        out.parent.mkdir(parents=True, exist_ok=True)
+        shutil.copyfile(base / rel, out)
     if verbose:
-        print(f"mirrored {', '.join(SUBDIRS)} of {base} into {DST}")
+        print(f"mirrored {', '.join(SUBDIRS + FILES)} of {base} into {DST}")
     return True
 
 

@@ -133,3 +133,20 @@ def load(with_lightning: bool = False) -> types.SimpleNamespace:
         ns.clt_lightning = importlib.import_module("crosslayer_transcoder.model.clt_lightning")
     _loaded[key] = ns
     return ns
+
+
+def load_shared_memory():
+    """The reference's ``crosslayer_transcoder/data/shared_memory.py`` as a stand-alone module (it imports
+    only torch, numpy and the standard library), or None where neither the tree nor the mirror has it."""
+    import importlib.util
+
+    if "ref_shared_memory" in sys.modules:
+        return sys.modules["ref_shared_memory"]
+    path = REF_ROOT / "crosslayer_transcoder" / "data" / "shared_memory.py"
+    if not path.exists():
+        return None
+    spec = importlib.util.spec_from_file_location("ref_shared_memory", path)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["ref_shared_memory"] = mod
+    spec.loader.exec_module(mod)
+    return mod
