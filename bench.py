@@ -386,11 +386,14 @@ def time_ingest(spec, dev, batches: int = 10) -> dict:
     consumer (``SharedActivationBuffer.get_activations`` on one CPU thread, then the upload of the pageable
     batch it returns) against the device-side consumer (``data.SharedBufferBatches``: the GPU gathers the
     same choice of rows from the registered shared mapping).  ms per batch of ``spec.batch`` rows."""
+    import faulthandler
+    import gc
     import shutil
 
     from crosslayer_transcoder_b200 import data
     from oracle import ref_import
 
+    faulthandler.enable()           # a crash in native code names the Python frame it came from
     shm_mod = ref_import.load_shared_memory()
     if shm_mod is None:
         return {"unavailable": "the reference's shared_memory.py is not present (oracle/_ref missing)"}
@@ -439,6 +442,8 @@ def time_ingest(spec, dev, batches: int = 10) -> dict:
                 src.gather.check()
             finally:
                 src.close()
+                del src
+                gc.collect()
         out["mapped_gather_GBps"] = out["bytes_per_batch"] / out["device_consumer_mapped_ms"] / 1e6
         return out
     finally:
@@ -779,7 +784,7 @@ def main():
                 line["ingest"] = time_ingest(spec, dev)
             except Exception as e:
                 line["ingest"] = {"unavailable": f"{type(e).__name__}: {str(e).splitlines()[0][:160]}"}
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 

@@ -7,8 +7,7 @@
   thread and invalidates them; Lightning then uploads that tensor.  Here the choice of rows is the same
   (same calls on torch's CPU generator, so the same rows for the same seed), but the rows are moved by the
   GPU: the shared mapping is registered with the CUDA driver once and ``clt_gather_batch_rows`` reads the
-  chosen rows over PCIe straight into a device batch, on a side stream and a background thread, one batch
-  ahead of the step.
+  chosen rows over PCIe straight into a device batch, on a side stream, one batch ahead of the step.
 * ``TensorBatches`` / ``TensorDataModule`` iterate a ``[n_samples, 2, L, D]`` tensor like
   ``InfiniteTensorDataset`` / ``TensorDataModule`` (crosslayer_transcoder/data/tensor_datamodule.py:14-121):
   the tensor lives in HBM when it fits (the default on a 180 GB device), else in registered host memory,
@@ -20,8 +19,6 @@ until the iterator has been advanced ``depth`` more times.
 from __future__ import annotations
 
 import ctypes
-import queue
-import threading
 import time
 from typing import Iterator, Optional
 
@@ -123,8 +120,13 @@ class SharedBufferBatches:
     ``mode="staged"``: a CPU ``index_select`` into pinned memory, then one host-to-device copy (for stores
     whose memory cannot be registered, e.g. under a locked-memory limit).
 
-    The rows of a batch are invalidated only after the GPU has read them, and the buffer lock is held until
-    then, so generator processes cannot overwrite a row that is still being read."""
+    One batch is always in flight: ``__next__`` hands out the batch whose gather was launched by the previous
+    call and launches the next one on a side stream before it returns, so the gather runs under the step
+    that consumes the current batch.  Rows are chosen under the buffer lock and stay VALID while the GPU
+    reads them — generator processes only refill invalid rows, so they cannot overwrite a row in flight —
+    and are invalidated once the gather has completed (one consumer per store, as in the reference).  No
+    thread is used: the host work per batch is the row choice (``nonzero`` + ``randperm``), which runs
+    while the device executes the step that was just enqueued."""
 
     def __init__(self, store, batch_size: Optional[int] = None, device="cuda", depth: int = 2, mode: str = "mapped",
                  timeout: float = 1000.0):
@@ -139,8 +141,8 @@ class SharedBufferBatches:
             self.device = torch.device("cuda", torch.cuda.current_device())
         buf = store.buffer_tensor
         row_shape = tuple(buf.shape[1:])
-        # one more slot than the caller may hold, so the next batch can be gathered while those are in use
-        self.n_slots = depth + 1
+        self.depth = depth
+        self.n_slots = depth + 1           # `depth` batches with the caller, one in flight
         with torch.cuda.device(self.device):
             if mode == "mapped":
                 self.mapping = HostMapping(buf)
@@ -151,49 +153,9 @@ class SharedBufferBatches:
                                for _ in range(self.n_slots)]
                 src = 0
             self.gather = _RowGather(src, buf.shape[0], row_shape, buf.dtype, self.device, self.n_slots, batch_size)
-        self.depth = depth
-        self._ready: "queue.Queue" = queue.Queue()
-        self._free: "queue.Queue" = queue.Queue()
-        for slot in range(self.n_slots):
-            self._free.put(slot)
+        self._slot = 0
         self._held = []
-        self._stop = threading.Event()
-        self._thread = threading.Thread(target=self._produce, daemon=True)
-        self._thread.start()
-
-    # -- producer thread -----------------------------------------------------------------------
-    def _free_slot(self) -> Optional[int]:
-        while not self._stop.is_set():
-            try:
-                return self._free.get(timeout=0.1)
-            except queue.Empty:
-                pass
-        return None
-
-    def _produce(self):
-        try:
-            torch.cuda.set_device(self.device)
-            while True:
-                slot = self._free_slot()                # a slot the consumer has released (or never had)
-                if slot is None:
-                    return
-                t0 = time.time()
-                while True:
-                    with self.store.buffer_lock:
-                        rows = draw_rows(self.store, self.batch_size)
-                        if rows is not None:
-                            ev = self._move(slot, rows)
-                            ev.synchronize()            # rows are read; only now may they be refilled
-                            retire_rows(self.store, rows)
-                            break
-                    if self._stop.is_set():
-                        return
-                    if time.time() - t0 > self.timeout:
-                        raise TimeoutError("Timeout waiting for valid indices")
-                    time.sleep(0.01)
-                self._ready.put((slot, None))
-        except BaseException as e:                      # handed to the consumer
-            self._ready.put((None, e))
+        self._flight = None                # (slot, rows) of the gather in flight
 
     def _move(self, slot: int, rows: torch.Tensor) -> torch.cuda.Event:
         g = self.gather
@@ -206,7 +168,34 @@ class SharedBufferBatches:
             g.done[slot].record(g.stream)
         return g.done[slot]
 
-    # -- consumer ------------------------------------------------------------------------------
+    def _launch(self, block: bool) -> bool:
+        """Choose the next batch's rows and start moving them; with ``block`` wait (up to ``timeout``) for
+        the store to hold enough valid rows, as ``get_activations`` does."""
+        t0 = time.time()
+        while True:
+            with self.store.buffer_lock:
+                rows = draw_rows(self.store, self.batch_size)
+                if rows is not None:
+                    slot = self._slot
+                    self._slot = (slot + 1) % self.n_slots
+                    self._move(slot, rows)
+                    self._flight = (slot, rows)
+                    return True
+            if not block:
+                return False
+            if time.time() - t0 > self.timeout:
+                raise TimeoutError("Timeout waiting for valid indices")
+            time.sleep(0.01)
+
+    def _land(self) -> int:
+        """Wait for the gather in flight, invalidate its rows, return its slot."""
+        slot, rows = self._flight
+        self._flight = None
+        self.gather.done[slot].synchronize()
+        with self.store.buffer_lock:
+            retire_rows(self.store, rows)
+        return slot
+
     def __iter__(self) -> Iterator[torch.Tensor]:
         return self
 
@@ -214,27 +203,22 @@ class SharedBufferBatches:
         cur = torch.cuda.current_stream(self.device)
         # the batch handed out `depth` calls ago is released; work already enqueued on it still runs first
         if len(self._held) >= self.depth:
-            old = self._held.pop(0)
-            self.gather.freed[old].record(cur)
-            self._free.put(old)
-        slot, err = self._ready.get()
-        if err is not None:
-            raise err
+            self.gather.freed[self._held.pop(0)].record(cur)
+        if self._flight is None:
+            self._launch(block=True)
+        slot = self._land()
         cur.wait_event(self.gather.done[slot])
         self._held.append(slot)
+        self._launch(block=False)          # the next batch, if the store can supply it already
         return self.gather.out[slot]
 
     def close(self):
-        self._stop.set()
-        try:
-            while True:
-                self._ready.get_nowait()
-        except queue.Empty:
-            pass
-        self._thread.join(timeout=5.0)
+        if self._flight is not None:
+            self._land()
         torch.cuda.synchronize(self.device)
         if self.mapping is not None:
             self.mapping.close()
+            self.mapping = None
 
     def __del__(self):
         try:

@@ -5,6 +5,8 @@ the same kernels over NVLink is tests/test_gpu_multi.py."""
 import pytest
 import torch
 
+from tests.helpers import rel_err
+
 pytestmark = pytest.mark.gpu
 
 
@@ -60,7 +62,9 @@ def test_sparse_decoder_push_matches_plain(bf16, short_rows):
     torch.cuda.synchronize()
     assert int(status) == 0
     assert torch.equal(torch.cat([b[0] for b in hb], 0)[:B], recon.bfloat16())
-    want = recon.bfloat16().float() + (recon - bias).bfloat16().float()
+    second = torch.cat([b[2] for b in hb], 0)[:B].float()           # partial rows without the bias
+    assert rel_err(second, recon - bias) < 1e-2                     # (one bf16 rounding)
+    want = recon.bfloat16().float() + second
     assert torch.allclose(torch.cat(own, 0)[:B], want, rtol=1e-6, atol=1e-6)
 
 
