@@ -223,7 +223,8 @@ def algorithmic_work(spec, world: int, Fl: int, n_params: int, batch_bytes_per_e
         "clt_loss_bwd": ("hbm", bld * (4 + batch_bytes_per_elem + e + (4 + e) * aux)),
         # owned rows read locally; the gradient rows written once into every rank's buffer
         "clt_loss_bwd_push": ("hbm", own * (4 + batch_bytes_per_elem + 4 * aux) + own * world * e * (1 + aux)),
-        "clt_sum_slots": ("hbm", own * 4 * (world + 1)),
+        # the owner reads its R slots (bf16 on the bf16 path, fp32 otherwise) and writes the fp32 sum
+        "clt_sum_slots": ("hbm", own * (e * world + 4)),
         "clt_dec_norms": ("hbm", float(P) * Fl * D * 4),
         "clt_select_topk": ("hbm", float(L) * B * Fl * e + float(L) * B * k * 8),
         "clt_select_aux": ("hbm", float(L) * B * nd_pad * e * 2),
