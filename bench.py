@@ -190,7 +190,7 @@ def build_on_device(spec: synthetic.WorkloadSpec, dev, rank: int, world: int, ex
 
 
 def algorithmic_work(spec, world: int, Fl: int, n_params: int, batch_bytes_per_elem: int, nd_pad: int = 0,
-                     fused_exchange: bool = False):
+                     fused_exchange: bool = False, candidate_list: bool = True):
     """Per-launch algorithmic FLOPs / bytes of every entry point ON THIS RANK (feature shard Fl = F / world).
     Dense contractions: 2 M N K.  HBM-bound kernels: the bytes the operation has to move once.  Gathers have
     two figures: the token-major count (every fetched row counted, L2 hits included) and the lower bound
@@ -239,9 +239,15 @@ def algorithmic_work(spec, world: int, Fl: int, n_params: int, batch_bytes_per_e
         "clt_gather_rows": ("hbm", float(P) * nd_pad * D * e * 2),
         "clt_scatter_rows": ("hbm", float(P) * nd_pad * D * 4 * 3),
         "clt_csc_build": ("hbm", float(L) * B * k * 8 * 2 + float(L) * Fl * 4 * 3),
+        # the one sweep of the selection's steady state; the full-sweep entry points (clt_batchtopk_hist,
+        # clt_batchtopk_collect) are enqueued every step and return at once unless a step falls back to them,
+        # so they carry no work model when the candidate list is in use
+        "clt_batchtopk_candidates": ("hbm", float(L) * B * Fl * e),
         "clt_batchtopk_hist": ("hbm", float(L) * B * Fl * e),
         "clt_batchtopk_collect": ("hbm", float(L) * B * Fl * e + float(L) * B * k * 12),
     }
+    if candidate_list:
+        del work["clt_batchtopk_hist"], work["clt_batchtopk_collect"]
     return work
 
 
@@ -592,6 +598,15 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         steps = int(min(2000, max(20, 3000.0 / max(float(t), 1e-3))))
 
+    # host time to ENQUEUE a step (the launch queue is empty at the start and 6 steps do not fill it): if this
+    # approaches ms_per_step the run is bound by the host's launch path, not by the device
+    barrier()
+    h0 = time.perf_counter()
+    for i in range(6):
+        step(batch_dev, 60 + i)
+    host_issue_ms = (time.perf_counter() - h0) * 1e3 / 6
+    torch.cuda.synchronize()
+
     # ---- device-resident timing, per-kernel events collected in the same region --------------
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -729,7 +744,8 @@ def main():
             n_dec = sum((w.numel() + 63) // 64 * 64 for w in mod.model.decoder.blocks())
             n_adam = (eng.flat.numel - n_dec) / 2.0
         work = algorithmic_work(spec, world, Fl, n_adam, batch_host.element_size(), nd_pad=nd_pad,
-                                fused_exchange=fused_exchange)
+                                fused_exchange=fused_exchange,
+                                candidate_list=bool(getattr(mod, "batchtopk_candidates", True)))
         kernels = {}
         flags = []
         for name, st in prof.items():
@@ -767,7 +783,8 @@ def main():
                 "e2e": {"value": spec.batch * steps / (e2e_ms * 1e-3), "unit": UNIT,
                         "h2d_bytes_per_step": h2d_bytes,
                         "d2h_bytes_per_step": 8, "last_loss": last},
-                "last_loss": last, "gpu_launches": launches, "roofline": roofline, "kernels": kernels,
+                "last_loss": last, "gpu_launches": launches, "host_issue_ms_per_step": host_issue_ms,
+                "roofline": roofline, "kernels": kernels,
                 "accounting_ok": not flags}
         if flags:
             line["accounting_flags"] = flags

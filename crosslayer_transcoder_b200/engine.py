@@ -975,19 +975,40 @@ class StepEngine:
         row_cnt = ws.get("bt_row_cnt", (L, B), torch.int32, dev)
         if n_keep > 0:
             state = ws.get("bt_state", (groups, 8), torch.int64, dev, zero=True)
-            hist_l = ws.get("bt_hist_local", (groups, 2048), torch.int64, dev)
-            hist = ws.get("bt_hist", (groups, 2048), torch.int64, dev) if world > 1 else hist_l
+            # histograms [groups, 2048] followed by the "candidate list invalid" word, so that feature shards
+            # sum the flag together with the counters
+            nh = groups * 2048
+            hbuf_l = ws.get("bt_hist_local", (nh + 8,), torch.int64, dev, zero=True)
+            hbuf = ws.get("bt_hist", (nh + 8,), torch.int64, dev) if world > 1 else hbuf_l
+            hist_l, inval_l, hist, inval = hbuf_l[:nh], hbuf_l[nh:], hbuf[:nh], hbuf[nh:]
+            # steady state: one sweep of z collects everything at or above 0.9 of the last threshold, and the
+            # radix levels and the collection read that list; the full sweeps below are enqueued as well and
+            # return at once unless this step cannot trust its list
+            use_list = bool(getattr(mod, "batchtopk_candidates", True))
+            if use_list:
+                cap = int(min(L * B * F, max(8 * k * B * L, 65536), 2 ** 31 - 1))
+                cand_feat = ws.get("bt_cand_feat", (cap,), torch.int32, dev)
+                cand_val = ws.get("bt_cand_val", (cap,), torch.float32, dev)
+                cand_row = ws.get("bt_cand_row", (cap,), torch.int32, dev)
+                cand_fill = ws.get("bt_cand_fill", (1,), torch.int32, dev)
+                cand_start = ws.get("bt_cand_start", (L, B), torch.int32, dev)
+                cand_cnt = ws.get("bt_cand_cnt", (L, B), torch.int32, dev)
+                self._call("clt_batchtopk_candidates", z, enc.b.data, state, cand_feat, cand_val, cand_row, cand_fill,
+                           cand_start, cand_cnt, inval_l, groups, B, L, F, cap, int(bf16), s)
             # level 0, its retry without the guessed floor (returns at once unless requested), levels 1, 2
             for level, retry in ((0, 0), (0, 1), (1, 0), (2, 0)):
-                self._call("clt_batchtopk_hist", z, enc.b.data, state, hist_l, level, retry, groups, B, L, F,
-                           int(bf16), s)
+                self._call("clt_batchtopk_hist", z, enc.b.data, state, hist_l, inval_l if use_list else None, level,
+                           retry, groups, B, L, F, int(bf16), s)
+                if use_list and not retry:
+                    self._call("clt_batchtopk_hist_list", cand_val, cand_row, cand_fill, state, hist_l, inval_l, level,
+                               groups, B, cap, s)
                 if world > 1:
                     from .parallel import all_reduce_sum
 
-                    hist.copy_(hist_l)
-                    all_reduce_sum(hist, group)
-                self._call("clt_batchtopk_pick", hist, hist_l if world > 1 else None, state, level, retry, groups,
-                           n_keep, s)
+                    hbuf.copy_(hbuf_l)
+                    all_reduce_sum(hbuf, group)
+                self._call("clt_batchtopk_pick", hist, hist_l if world > 1 else None, state,
+                           inval if use_list else None, level, retry, groups, n_keep, s)
             quota = None
             if world > 1:
                 # elements equal to the threshold are kept in rank order until the global count is reached
@@ -1000,6 +1021,9 @@ class StepEngine:
             fill = ws.get("bt_fill", (L,), torch.int32, dev)
             self._call("clt_batchtopk_collect", z, enc.b.data, state, quota, idx, val, etok, row_start, row_cnt, fill,
                        fired, groups, B, L, F, npl, int(bf16), self.status, s)
+            if use_list:
+                self._call("clt_batchtopk_filter", cand_feat, cand_val, cand_start, cand_cnt, state, quota, idx, val,
+                           etok, row_start, row_cnt, fill, fired, groups, B, L, F, npl, self.status, s)
             self._call("clt_batchtopk_threshold_update", state, nl.threshold, float(nl.e), groups, s)
         else:
             val.zero_()

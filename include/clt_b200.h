@@ -315,15 +315,43 @@ int clt_scatter_rows(const float* src, const int* dead_list, const int* n_dead, 
  * histogram of the elements inside the bucket chosen so far, feature shards sum their histograms,
  * clt_batchtopk_pick chooses the next bucket (n_keep = elements kept per group).
  * state: [groups, 8] 64-bit words of device memory, zero before the first step ([2] threshold key
- * after level 2, [3] kept elements equal to it, [5] this rank's count of them, [7] half of the last
- * threshold: the first level only looks at elements above it).  If that floor turns out too high
- * the pick kernel requests a retry: always enqueue the level-0 pair a second time with retry = 1
- * before levels 1 and 2; it returns at once when no retry is pending.  hist_local (may be NULL) is
- * this rank's own histogram when hist holds the sum over shards. */
-int clt_batchtopk_hist(const void* z, const float* b_enc, const uint64_t* state, uint64_t* hist, int level,
-                       int retry, int groups, int B, int L, int F, int bf16, clt_stream_t stream);
-int clt_batchtopk_pick(const uint64_t* hist, const uint64_t* hist_local, uint64_t* state, int level, int retry,
-                       int groups, int64_t n_keep, clt_stream_t stream);
+ * after level 2, [3] kept elements equal to it, [5] this rank's count of them, [6] result code in the
+ * low bits and 16 = "this step runs on full sweeps of z", [7] 0.9 of the last threshold: the first level
+ * only looks at elements at or above it).  If that floor turns out too high the pick kernel requests a
+ * retry: always enqueue the level-0 pair a second time with retry = 1 before levels 1 and 2; it returns
+ * at once when no retry is pending.  hist_local (may be NULL) is this rank's own histogram when hist
+ * holds the sum over shards.
+ *
+ * Candidate list (one sweep of z per step in steady state).  clt_batchtopk_candidates sweeps z once and
+ * writes every element at or above the floor to cand_feat / cand_val / cand_row [cap] (one segment per
+ * (layer, token) row, largest value first: cand_row_start / cand_row_cnt [L, B]; cand_fill: one int).  It
+ * sets *list_invalid (one 64-bit word, zeroed by the call) when there is no floor yet, a row holds more
+ * than 2048 candidates or the list is full.  Then, per level, BOTH clt_batchtopk_hist (given
+ * list_invalid) and clt_batchtopk_hist_list are enqueued: at level 0 the former runs only if this rank's
+ * list is invalid, the latter only if it is valid; clt_batchtopk_pick at level 0 looks at list_invalid
+ * SUMMED OVER THE SHARDS (sum it together with the histogram) and, if it is non-zero or the floor proves
+ * too high, marks the step for full sweeps; at levels 1 and 2 each kernel runs on the path chosen.
+ * Likewise clt_batchtopk_collect (full sweeps) and clt_batchtopk_filter (candidate list; same outputs)
+ * are both enqueued, in this order (collect's call zeroes layer_fill and val).  list_invalid = NULL in
+ * clt_batchtopk_hist / _pick: no candidate list, always full sweeps. */
+int clt_batchtopk_hist(const void* z, const float* b_enc, const uint64_t* state, uint64_t* hist,
+                       const uint64_t* list_invalid, int level, int retry, int groups, int B, int L, int F,
+                       int bf16, clt_stream_t stream);
+int clt_batchtopk_pick(const uint64_t* hist, const uint64_t* hist_local, uint64_t* state,
+                       const uint64_t* list_invalid, int level, int retry, int groups, int64_t n_keep,
+                       clt_stream_t stream);
+int clt_batchtopk_candidates(const void* z, const float* b_enc, const uint64_t* state, int* cand_feat,
+                             float* cand_val, int* cand_row, int* cand_fill, int* cand_row_start,
+                             int* cand_row_cnt, uint64_t* list_invalid, int groups, int B, int L, int F,
+                             int64_t cap, int bf16, clt_stream_t stream);
+int clt_batchtopk_hist_list(const float* cand_val, const int* cand_row, const int* cand_fill,
+                            const uint64_t* state, uint64_t* hist, const uint64_t* list_invalid, int level,
+                            int groups, int B, int64_t cap, clt_stream_t stream);
+int clt_batchtopk_filter(const int* cand_feat, const float* cand_val, const int* cand_row_start,
+                         const int* cand_row_cnt, uint64_t* state, const int64_t* tie_quota, int* idx,
+                         float* val, int* etok, int* row_start, int* row_cnt, int* layer_fill,
+                         uint32_t* fired_bits, int groups, int B, int L, int F, int64_t npl, int* status,
+                         clt_stream_t stream);
 /* Collect the survivors into per-layer entry lists idx / val / etok [L, npl] with the segment of
  * token b at row_start[l,b] .. + row_cnt[l,b]; layer_fill [L] receives the list lengths.  tie_quota
  * (device int64 per group, may be NULL = all kept ties are this rank's) bounds the elements equal to
