@@ -28,7 +28,7 @@
 //
 // Candidate list (steady state: ONE sweep of z per step instead of five).  The threshold moves little from
 // step to step, so the first pass keeps every element at or above the floor — a few times n_keep
-// elements — in a compact list (feature, value, row; one segment per row, largest value first), and the
+// elements — in a compact list (feature, value, row; one segment per row, in a fixed scrambled order), and the
 // three radix levels and the final collection read that list instead of z.  Whenever the list cannot be
 // trusted — no floor yet, a row or the list overflowed on any rank, fewer than n_keep elements above the
 // floor — the first pick sets bit 4 of state[6] and the same step falls back to the full sweeps, which the
@@ -313,7 +313,7 @@ bt_collect_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, u64*
 }
 
 // First pass of the candidate path.  One CTA per (layer, token) row: ONE sweep; every element at or above
-// the group's floor goes to shared memory, is sorted by value and written as the row's segment of the
+// the group's floor goes to shared memory, is put in a fixed order and written as the row's segment of the
 // global candidate list (segment reserved with one atomic).  No floor yet, more than kRowCand candidates in
 // a row or a full list: *invalid = 1 and the step falls back to the full sweeps.
 template <class T>
@@ -372,22 +372,28 @@ bt_candidates_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, c
     return;
   }
   if (cnt > 1) {
-    // largest value first, equal values by feature (bitonic, in shared memory): a fixed order, and one that
-    // is not correlated with the decoder's addresses (rows in feature order make the CTAs of the token-major
-    // decoder gather sweep the same address range in step: 3.6 ms against 3.2 ms on the 16-layer workload)
+    // a fixed order unrelated to addresses and values: ascending hash of the feature (bitonic, in shared
+    // memory).  Rows in feature order make the warps of the token-major decoder gather sweep the same
+    // address range in step, rows in value order make them all start with the most popular features: 3.6 ms
+    // either way against 3.2 ms in arrival order on the 16-layer workload.
+    const unsigned salt = (unsigned)row * 0x9E3779B1u;
+    auto key = [&](int f) -> unsigned long long {
+      return f == 0x7fffffff ? (1ull << 32) : (unsigned long long)((unsigned)f * 2654435761u + salt);
+    };
     int n2 = 2;
     while (n2 < cnt) n2 <<= 1;
-    for (int j = cnt + threadIdx.x; j < n2; j += blockDim.x) s_feat[j] = 0x7fffffff, s_val[j] = -1.f;
+    for (int j = cnt + threadIdx.x; j < n2; j += blockDim.x) s_feat[j] = 0x7fffffff, s_val[j] = 0.f;
     __syncthreads();
     for (int size = 2; size <= n2; size <<= 1) {
       for (int stride = size >> 1; stride > 0; stride >>= 1) {
         for (int t = threadIdx.x; t < (n2 >> 1); t += blockDim.x) {
           const int i = ((t / stride) * (stride << 1)) + (t & (stride - 1)), j = i + stride;
           const bool up = (i & size) == 0;
-          const float va = s_val[i], vc = s_val[j];
           const int a = s_feat[i], c = s_feat[j];
-          const bool after = va < vc || (va == vc && a > c);     // entry i belongs after entry j
-          if (after == up) s_feat[i] = c, s_feat[j] = a, s_val[i] = vc, s_val[j] = va;
+          if ((key(a) > key(c)) == up) {
+            const float va = s_val[i], vc = s_val[j];
+            s_feat[i] = c, s_feat[j] = a, s_val[i] = vc, s_val[j] = va;
+          }
         }
         __syncthreads();
       }
@@ -451,8 +457,8 @@ bt_list_hist_kernel(const float* __restrict__ cand_val, const int* __restrict__ 
   }
 }
 
-// Survivors from the candidate list.  One warp per (layer, token) row: the row's candidates (sorted by
-// value) above the threshold, plus ties while the quota lasts, are written in order as the row's segment
+// Survivors from the candidate list.  One warp per (layer, token) row: the row's candidates (in their
+// fixed order) above the threshold, plus ties while the quota lasts, are written in order as the row's segment
 // of the layer's entry list.  Same outputs as bt_collect_kernel.
 __global__ void __launch_bounds__(256)
 bt_filter_kernel(const int* __restrict__ cand_feat, const float* __restrict__ cand_val,

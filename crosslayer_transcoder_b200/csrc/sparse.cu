@@ -199,6 +199,12 @@ sparse_dec_fwd_kernel(const int* __restrict__ idx, const float* __restrict__ val
   }
 }
 
+// Measured effects of order on this gather (12-layer, 32768-feature, k = 32 workload unless said otherwise):
+// target layers in ascending order, tokens fastest (below) 1.99 ms, longest target layers first 2.26 ms; one
+// warp per (token, layer) 1.99 ms, one CTA 2.34 ms (four times fewer tokens in flight per decoder block);
+// entry lists in feature order or, for the short ragged lists of the batch-wide selection, in value order cost
+// 10 % (16-layer BatchTopK workload: 3.6 ms against 3.2-3.3 ms in arrival or scrambled order).
+//
 // Same computation with one WARP per (token, target layer) and no shared-memory reduction: for
 // short entry lists (a feature shard keeps only a few of a row's k slots) the per-CTA overhead of
 // the kernel above dominates.  Entries are fetched 32 at a time, rows two at a time.

@@ -324,7 +324,7 @@ int clt_scatter_rows(const float* src, const int* dead_list, const int* n_dead, 
  *
  * Candidate list (one sweep of z per step in steady state).  clt_batchtopk_candidates sweeps z once and
  * writes every element at or above the floor to cand_feat / cand_val / cand_row [cap] (one segment per
- * (layer, token) row, largest value first: cand_row_start / cand_row_cnt [L, B]; cand_fill: one int).  It
+ * (layer, token) row, in a fixed scrambled order: cand_row_start / cand_row_cnt [L, B]; cand_fill: one int).  It
  * sets *list_invalid (one 64-bit word, zeroed by the call) when there is no floor yet, a row holds more
  * than 2048 candidates or the list is full.  Then, per level, BOTH clt_batchtopk_hist (given
  * list_invalid) and clt_batchtopk_hist_list are enqueued: at level 0 the former runs only if this rank's

@@ -156,42 +156,3 @@ def _check_selection(dev, L, B, F, ks):
                                                       ((f[..., 1:] > f[..., :-1]) | (v[..., 1:] == 0)))).all())
             tv, ti = torch.topk(z[0, 0], k)
             assert torch.equal(v[0, 0], tv) and torch.equal(f[0, 0].long(), ti)
-
-
-@pytest.mark.parametrize("L,B,F,ks", [(3, 120, 16384, (32, 256)), (2, 40, 32768, (1, 32)), (2, 11, 8200, (32,))])
-def test_selection_long_bf16_rows(L, B, F, ks):
-    """Long bf16 rows with a non-zero bias (the one-CTA-per-row kernel): all-negative rows, rows with few
-    positives, masses of nearly equal values (candidate-list overflow -> radix select), a row length
-    that is not a multiple of the per-sweep stride, and the fired-feature bits."""
-    from crosslayer_transcoder_b200._lib import lib, stream_ptr
-
-    dev = torch.device("cuda:0")
-    lib().check_device()
-    g = torch.Generator().manual_seed(1)
-    z = torch.randn(L, B, F, generator=g).bfloat16()
-    bias = 0.3 * torch.randn(L, F, generator=g)
-    z[1, 3] = -4.0                                                   # all negative after the bias
-    z[0, 1, 40:] = -4.0                                              # at most 40 positives
-    # masses of equal pre-activations: where z is positive, make z + bias the same value
-    zt = z.clone()
-    zt[0, 2] = torch.where(z[0, 2] > 0, (0.5 - bias[0]).bfloat16(), z[0, 2])
-    pre = zt.float() + bias[:, None, :]
-    zb, bb = zt.to(dev), bias.to(dev)
-    for k in ks:
-        idx = torch.full((L, B, k), -1, dtype=torch.int32, device=dev)
-        val = torch.full((L, B, k), -1.0, device=dev)
-        fired = torch.zeros(L, (F + 31) // 32, dtype=torch.int32, device=dev)
-        lib().call("clt_select_topk", zb, bb, idx, val, fired, B, L, F, k, 1, stream_ptr())
-        torch.cuda.synchronize()
-        assert int(idx.min()) >= 0 and int(idx.max()) < F
-        dense = torch.zeros(L, B, F).scatter_add_(2, idx.long().cpu(), val.cpu())
-        ref = O.per_layer_topk(pre.permute(1, 0, 2).contiguous(), k).permute(1, 0, 2)
-        # rows with values repeated at the k-th place may pick any of the equal ones
-        kth = ref.topk(k, dim=-1).values[..., -1:]
-        tie_row = ((pre == kth) & (kth > 0)).sum(-1) > 1
-        assert torch.equal(dense[~tie_row], ref[~tie_row])
-        assert torch.equal(dense[tie_row].sort(dim=-1).values, ref[tie_row].sort(dim=-1).values)
-        assert float(dense[1, 3].abs().sum()) == 0.0
-        bits = fired.cpu().numpy().view("uint32")
-        got = torch.from_numpy(((bits[:, :, None] >> torch.arange(32).numpy()[None, None, :]) & 1).reshape(L, -1)[:, :F].astype("bool"))
-        assert torch.equal(got, (dense > 0).any(dim=1))
