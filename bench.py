@@ -598,13 +598,14 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         steps = int(min(2000, max(20, 3000.0 / max(float(t), 1e-3))))
 
-    # host time to ENQUEUE a step (the launch queue is empty at the start and 6 steps do not fill it): if this
-    # approaches ms_per_step the run is bound by the host's launch path, not by the device
+    # host time to ENQUEUE a step, over two steps from an empty launch queue (from the third step on, the TopK
+    # step waits for the sizes the step before last copied to the host, i.e. for the device): if this approaches
+    # ms_per_step the run is bound by the host's launch path, not by the device
     barrier()
     h0 = time.perf_counter()
-    for i in range(6):
+    for i in range(2):
         step(batch_dev, 60 + i)
-    host_issue_ms = (time.perf_counter() - h0) * 1e3 / 6
+    host_issue_ms = (time.perf_counter() - h0) * 1e3 / 2
     torch.cuda.synchronize()
 
     # ---- device-resident timing, per-kernel events collected in the same region --------------

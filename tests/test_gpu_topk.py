@@ -148,7 +148,7 @@ def _check_selection(dev, L, B, F, ks):
         assert torch.equal(dense[~tie_row], ref[~tie_row])
         assert torch.equal(dense[tie_row].sort(dim=-1).values, ref[tie_row].sort(dim=-1).values)
         assert (dense >= 0).all() and float(dense[1, 3].abs().sum()) == 0.0
-        if F >= 2048 and k <= 256:
+        if F >= 2048 and k <= 256 and (F > 8192 or k > 64):
             # the one-sweep kernel hands the entries out as torch.topk does: largest value first (equal values
             # by feature), unused slots (value 0) last
             v, f = val.cpu(), idx.cpu()
