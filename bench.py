@@ -647,7 +647,8 @@ def main():
 
         up = parallel.ShardedBatchUploader(mod, batch_host.shape, batch_host.dtype, dev)
         h2d_bytes = (up.hi - up.lo) * row_bytes
-        config["upload"] = "each rank uploads B/N token rows and copies their input halves to the peers (NVLink)"
+        config["upload"] = ("each rank uploads B/N token rows and copies their input halves to the peers (NVLink); "
+                            + ("joined at the end of backward" if up.late_join else "joined at the step's last collective"))
         for _ in range(2):                         # untimed: maps the pinned pages, touches both buffers
             up.upload(batch_host, full=True)
             up.fence()
@@ -669,7 +670,7 @@ def main():
             if i > 0:
                 loss_ready[slot ^ 1].synchronize()
                 last = float(loss_host[slot ^ 1])
-        eng.before_last_collective = None
+        up.detach()
     else:
         copy_stream = torch.cuda.Stream()
         if world > 1:

@@ -203,7 +203,10 @@ sparse_dec_fwd_kernel(const int* __restrict__ idx, const float* __restrict__ val
 // target layers in ascending order, tokens fastest (below) 1.99 ms, longest target layers first 2.26 ms; one
 // warp per (token, layer) 1.99 ms, one CTA 2.34 ms (four times fewer tokens in flight per decoder block);
 // entry lists in feature order or, for the short ragged lists of the batch-wide selection, in value order cost
-// 10 % (16-layer BatchTopK workload: 3.6 ms against 3.2-3.3 ms in arrival or scrambled order).
+// 10 % (16-layer BatchTopK workload: 3.6 ms against 3.2-3.3 ms in arrival or scrambled order).  Two variants of
+// the warp form were measured and dropped: four rows in flight per warp instead of two (2.29 ms against
+// 1.99 ms: fewer resident warps), and the columns of a wide row (D = 2048) split over two warps (4.6 ms against
+// 3.3 ms: the halves of a decoder row are then fetched at different times).
 //
 // Same computation with one WARP per (token, target layer) and no shared-memory reduction: for
 // short entry lists (a feature shard keeps only a few of a row's k slots) the per-CTA overhead of
@@ -213,17 +216,12 @@ __global__ void __launch_bounds__(128)
 sparse_dec_fwd_warp_kernel(const int* __restrict__ idx, const float* __restrict__ val,
                            const int* __restrict__ row_start, const int* __restrict__ row_cnt, long long npl,
                            const T* __restrict__ W, const float* __restrict__ b_dec, float* __restrict__ recon, int B,
-                           int L, int D, int F, int k, int crosslayer, int* status, PushDst push, int nsplit) {
-  // wide rows are split over nsplit warps (each takes a contiguous range of columns of the same (token,
-  // layer) pair), so that a warp's accumulators and the rows it has in flight fit its registers
-  long long pair = blockIdx.x * 4ll + (threadIdx.x >> 5);
-  if (pair >= (long long)B * L * nsplit) return;
-  const int part = (int)(pair % nsplit);
-  pair /= nsplit;
+                           int L, int D, int F, int k, int crosslayer, int* status, PushDst push) {
+  const long long pair = blockIdx.x * 4ll + (threadIdx.x >> 5);
+  if (pair >= (long long)B * L) return;
   const int b = (int)(pair % B), t = (int)(pair / B);
   const int lane = threadIdx.x & 31;
-  const int nvec = D / 8 / nsplit;          // 8-column chunks of this warp's range
-  const int col0 = part * nvec * 8;         // its first column
+  const int nvec = D / 8;
   using V = Vec8<T>;
   float acc[VPL][8];
 #pragma unroll
@@ -252,37 +250,29 @@ sparse_dec_fwd_warp_kernel(const int* __restrict__ idx, const float* __restrict_
         report_status(status, kBadIndex);
         my_v = 0.f, my_f = 0;
       }
-      // two rows at a time: their loads are all in flight before the first is used.  Four at a time was slower
-      // (2.29 ms against 1.99 ms on the 12-layer, 32768-feature workload: fewer resident warps).
-      constexpr int kRows = 2;
-      for (int j = 0; j < valid; j += kRows) {
-        float vr[kRows];
-        const T* rr[kRows];
+      for (int j = 0; j < valid; j += 2) {
+        const bool two = j + 1 < valid;
+        const float v0 = __shfl_sync(0xffffffffu, my_v, j);
+        const float v1 = two ? __shfl_sync(0xffffffffu, my_v, j + 1) : 0.f;
+        const T* r0 = W + (p * F + __shfl_sync(0xffffffffu, my_f, j)) * D;
+        const T* r1 = W + (p * F + __shfl_sync(0xffffffffu, my_f, two ? j + 1 : j)) * D;
+        typename V::Raw x0[VPL], x1[VPL];
 #pragma unroll
-        for (int r = 0; r < kRows; ++r) {
-          const bool on = j + r < valid;
-          const int src = on ? j + r : j;
-          const float vv = __shfl_sync(0xffffffffu, my_v, src);
-          vr[r] = on ? vv : 0.f;
-          rr[r] = W + (p * F + __shfl_sync(0xffffffffu, my_f, src)) * D;
+        for (int i = 0; i < VPL; ++i) {
+          const int c = lane + 32 * i;
+          x0[i] = c < nvec ? V::load_raw(r0 + 8 * c) : V::zero();
+          x1[i] = (two && c < nvec) ? V::load_raw(r1 + 8 * c) : V::zero();
         }
-        typename V::Raw x[kRows][VPL];
 #pragma unroll
-        for (int r = 0; r < kRows; ++r)
+        for (int i = 0; i < VPL; ++i) {
+          float w[8];
+          V::unpack(x0[i], w);
 #pragma unroll
-          for (int i = 0; i < VPL; ++i) {
-            const int c = lane + 32 * i;
-            x[r][i] = (j + r < valid && c < nvec) ? V::load_raw(rr[r] + col0 + 8 * c) : V::zero();
-          }
+          for (int q = 0; q < 8; ++q) acc[i][q] = fmaf(v0, w[q], acc[i][q]);
+          V::unpack(x1[i], w);
 #pragma unroll
-        for (int r = 0; r < kRows; ++r)
-#pragma unroll
-          for (int i = 0; i < VPL; ++i) {
-            float w[8];
-            V::unpack(x[r][i], w);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) acc[i][q] = fmaf(vr[r], w[q], acc[i][q]);
-          }
+          for (int q = 0; q < 8; ++q) acc[i][q] = fmaf(v1, w[q], acc[i][q]);
+        }
       }
       if (valid < m) break;
     }
@@ -294,11 +284,11 @@ sparse_dec_fwd_warp_kernel(const int* __restrict__ idx, const float* __restrict_
       const int c = lane + 32 * i;
       if (c < nvec) {
         float bb[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        if (b_dec != nullptr) Vec8<float>::load(b_dec + (size_t)t * D + col0 + 8 * c, bb);
+        if (b_dec != nullptr) Vec8<float>::load(b_dec + (size_t)t * D + 8 * c, bb);
         float o8[8];
 #pragma unroll
         for (int q = 0; q < 8; ++q) o8[q] = acc[i][q] + bb[q];
-        store8_bf16(ob + col0 + 8 * c, o8);
+        store8_bf16(ob + 8 * c, o8);
       }
     }
     return;
@@ -309,8 +299,8 @@ sparse_dec_fwd_warp_kernel(const int* __restrict__ idx, const float* __restrict_
     const int c = lane + 32 * i;
     if (c < nvec) {
       float bb[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      if (b_dec != nullptr) Vec8<float>::load(b_dec + (size_t)t * D + col0 + 8 * c, bb);
-      float4* o = reinterpret_cast<float4*>(out + col0 + 8 * c);
+      if (b_dec != nullptr) Vec8<float>::load(b_dec + (size_t)t * D + 8 * c, bb);
+      float4* o = reinterpret_cast<float4*>(out + 8 * c);
       const float4 lo = make_float4(acc[i][0] + bb[0], acc[i][1] + bb[1], acc[i][2] + bb[2], acc[i][3] + bb[3]);
       const float4 hi = make_float4(acc[i][4] + bb[4], acc[i][5] + bb[5], acc[i][6] + bb[6], acc[i][7] + bb[7]);
       o[0] = lo;
@@ -792,21 +782,15 @@ template <class T>
 int launch_dec_fwd(const int* idx, const float* val, const int* row_start, const int* row_cnt, long long npl,
                    const void* W, const float* b_dec, float* recon, int B, int L, int D, int F, int k, int crosslayer,
                    int short_rows, int* status, cudaStream_t s, PushDst push = PushDst{{0ull}, 0, 0, 0}) {
-  int vpl = (D / 8 + 31) / 32;
+  const int vpl = (D / 8 + 31) / 32;
   dim3 grid(B, L);
   const size_t smem = 4 * (size_t)D * sizeof(float);
-  // one warp per (token, layer).  The kernel can split a row's columns over several warps; measured on the
-  // 16-layer, D = 2048 workload that is slower (4.6 ms against 3.3 ms with two warps per row: the halves of a
-  // decoder row are fetched at different times), so rows are not split.
-  const int nsplit = 1;
-  if (nsplit == 2) vpl = (D / 16 + 31) / 32;
-  const unsigned wgrid = (unsigned)(((long long)B * L * nsplit + 3) / 4);
+  const unsigned wgrid = (unsigned)(((long long)B * L + 3) / 4);
 #define CLT_DEC_FWD(V)                                                                                              \
   case V:                                                                                                           \
     if (short_rows) {                                                                                               \
       sparse_dec_fwd_warp_kernel<T, V><<<wgrid, 128, 0, s>>>(idx, val, row_start, row_cnt, npl, (const T*)W, b_dec, \
-                                                             recon, B, L, D, F, k, crosslayer, status, push,        \
-                                                             nsplit);                                               \
+                                                             recon, B, L, D, F, k, crosslayer, status, push);       \
       break;                                                                                                        \
     }                                                                                                               \
     CLT_CHECK_CUDA(cudaFuncSetAttribute(sparse_dec_fwd_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
@@ -815,11 +799,10 @@ int launch_dec_fwd(const int* idx, const float* val, const int* row_start, const
                                                         recon, B, L, D, F, k, crosslayer, status, push);            \
     break;
   switch (vpl) {
-    CLT_DEC_FWD(1) CLT_DEC_FWD(2) CLT_DEC_FWD(3) CLT_DEC_FWD(4) CLT_DEC_FWD(5) CLT_DEC_FWD(6) CLT_DEC_FWD(8)
-    CLT_DEC_FWD(9) CLT_DEC_FWD(12)
+    CLT_DEC_FWD(1) CLT_DEC_FWD(2) CLT_DEC_FWD(3) CLT_DEC_FWD(4) CLT_DEC_FWD(6) CLT_DEC_FWD(8) CLT_DEC_FWD(9)
+    CLT_DEC_FWD(12)
     default:
-      set_error("sparse decoder: d_acts=%d is not supported (needs D/256 in {1,2,3,4,5,6,8,9,12} after rounding up)",
-                D);
+      set_error("sparse decoder: d_acts=%d is not supported (needs D/256 in {1,2,3,4,6,8,9,12} after rounding up)", D);
       return 1;
   }
 #undef CLT_DEC_FWD

@@ -117,6 +117,7 @@ class StepEngine:
         #: feature shards, fused exchange: called right before the last collective of a step (the all-reduce
         #: of the decoder-bias gradient); parallel.ShardedBatchUploader orders its peer copies through it
         self.before_last_collective = None
+        self.after_backward = None          # called when the last kernel of a backward pass has been enqueued
         self.decoder_updated = False              # set by a backward that stepped the decoder itself
         self._status_host: Optional[torch.Tensor] = None
         self._status_evt = [None, None]
@@ -663,6 +664,8 @@ class StepEngine:
             self._backward_topk(ctx, gscale)
         else:
             raise NotImplementedError(ctx["kind"])
+        if self.after_backward is not None:
+            self.after_backward()
         self.post_status()
 
     def _zero_small_grads(self):

@@ -169,12 +169,15 @@ class ShardedBatchUploader:
     half of the other rows is never read.  ``full=True`` pushes both halves (for the first batch, from
     which the standardizers take their statistics).
 
-    Ordering between the ranks costs no extra collective.  The pushes of batch i+1 are enqueued while step
-    i runs; the step's own last collective (the all-reduce of the decoder-bias gradient in backward) is
-    made to wait for this rank's pushes (``StepEngine.before_last_collective``), so when that collective
-    has completed on a rank, every peer's rows for batch i+1 have landed in its buffer.  Conversely a
-    buffer is overwritten only after the step that read it has finished on every rank, which the same
-    collective of that step guarantees.
+    Ordering between the ranks.  The pushes of batch i+1 are enqueued while step i runs.  For small uploads
+    the step's own last collective (the all-reduce of the decoder-bias gradient, at the start of backward)
+    is made to wait for this rank's pushes (``StepEngine.before_last_collective``), so when that collective
+    has completed on a rank, every peer's rows for batch i+1 have landed in its buffer, at no extra cost.
+    An upload that may take longer than the forward pass (more than ``late_join_bytes`` per rank) would stall
+    that collective; it is joined at the END of backward instead (``StepEngine.after_backward``), by a
+    one-element all-reduce of its own, so that the copies have the whole step to finish.  Either way a buffer
+    is overwritten only after the step that read it has finished on every rank, which the same collective of
+    that step guarantees.
 
         up = ShardedBatchUploader(module, batch_host.shape, batch_host.dtype, device)
         up.upload(first, full=True); up.fence()     # then, per step:
@@ -183,6 +186,8 @@ class ShardedBatchUploader:
         loss = module.training_step(batch, i); loss.backward(); opt.step()
         up.release()                                # the step's work on `batch` is enqueued
     """
+
+    late_join_bytes = 48 << 20
 
     def __init__(self, module, shape, dtype, device):
         if not getattr(module, "tp_fused", False) or not module._engine.has_fused_exchange():
@@ -201,7 +206,12 @@ class ShardedBatchUploader:
         for e in self.freed:
             e.record()
         self._next, self._ready, self._in_use = 0, [], []
-        module._engine.before_last_collective = self._join
+        row_bytes = int(torch.Size(shape[1:]).numel()) * torch.empty((), dtype=dtype).element_size()
+        self.late_join = (self.hi - self.lo) * row_bytes > self.late_join_bytes
+        if self.late_join:
+            module._engine.after_backward = self._join_and_fence
+        else:
+            module._engine.before_last_collective = self._join
 
     def upload(self, batch_host: torch.Tensor, full: bool = False) -> None:
         slot = self._next
@@ -228,6 +238,18 @@ class ShardedBatchUploader:
         only after its pushes of the next batch have been written."""
         for slot in self._ready:
             torch.cuda.current_stream().wait_event(self.pushed[slot])
+
+    def _join_and_fence(self):
+        """Called by the engine when a backward pass has been enqueued (large uploads): wait for this rank's
+        pushes of the next batch, then a one-element all-reduce waits for everyone's."""
+        if self._ready:
+            self.fence()
+
+    def detach(self) -> None:
+        """Take the uploader's hooks out of the engine (its buffers stay valid until they are dropped)."""
+        eng = self.module._engine
+        eng.before_last_collective = None
+        eng.after_backward = None
 
     def fence(self) -> None:
         """Stream-ordered barrier for a batch that no step's collective has ordered yet (the first one): the

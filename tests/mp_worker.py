@@ -24,6 +24,76 @@ def shard_weights(w, lo, hi, crosslayer):
     return out
 
 
+def uploader_case(mod, spec, batch, dev, join):
+    """Three training steps fed by ``parallel.ShardedBatchUploader`` (every rank uploads its own token rows and
+    copies their input halves to the peers) against the same steps fed with whole device batches: same losses,
+    same parameters afterwards.  ``join``: "early" = ordered by the step's own last collective, "late" = by the
+    uploader's own all-reduce at the end of backward."""
+    import copy
+
+    if join == "late":
+        parallel.ShardedBatchUploader.late_join_bytes = 0
+    g = torch.Generator().manual_seed(123)
+    host = [(batch * (1.0 + 0.1 * i) + 0.01 * torch.randn(batch.shape, generator=g)).half().pin_memory()
+            for i in range(3)]
+    state0 = copy.deepcopy(mod.state_dict())
+    la0 = mod.last_active.clone() if hasattr(mod, "last_active") else None
+
+    def run(feed):
+        mod.load_state_dict(state0)
+        if la0 is not None:
+            mod.last_active.copy_(la0)
+        opt = mod.configure_optimizers()
+        losses = []
+        for i in range(3):
+            b = feed(i)
+            opt.zero_grad(set_to_none=True)
+            loss = mod.training_step(b, i)
+            loss.backward()
+            opt.step()
+            losses.append(float(loss))
+            feed.done()
+        mod._engine.check_status("uploader case")
+        return losses, [p.detach().clone() for p in mod.parameters()]
+
+    class Whole:
+        def __call__(self, i):
+            return host[i].to(dev)
+
+        def done(self):
+            pass
+
+    class Uploaded:
+        def __init__(self):
+            self.up = parallel.ShardedBatchUploader(mod, host[0].shape, host[0].dtype, dev)
+            assert self.up.late_join == (join == "late")
+            self.up.upload(host[0], full=True)
+            self.up.fence()
+
+        def __call__(self, i):
+            b = self.up.take()
+            if i + 1 < len(host):
+                self.up.upload(host[i + 1])
+            return b
+
+        def done(self):
+            self.up.release()
+
+    want_l, want_p = run(Whole())
+    feed = Uploaded()
+    got_l, got_p = run(feed)
+    feed.up.detach()
+    # (sums taken with atomics differ in their last bits from run to run)
+    ok = all(abs(a - b) <= 1e-5 * abs(b) for a, b in zip(got_l, want_l)) and all(
+        rel_err(a, b) < 1e-5 for a, b in zip(got_p, want_p))
+    if not ok:
+        print("uploader case FAILED", got_l, want_l)
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    dist.destroy_process_group()
+    sys.exit(0 if int(flag) else 1)
+
+
 def main():
     kind, prec = sys.argv[1], sys.argv[2]
     mode = sys.argv[3] if len(sys.argv) > 3 else "nccl"     # "fused": exchange fused into the kernels over peer memory
@@ -48,6 +118,8 @@ def main():
     mod = build_module(spec, shard_weights(w, lo, hi, spec.crosslayer), dev, last_active=la[:, lo:hi].contiguous())
     parallel.attach(mod, fused=(mode == "fused"))
     assert mod.tp_fused == (mode == "fused")
+    if mode == "fused" and len(sys.argv) > 4:
+        return uploader_case(mod, spec, batch, dev, sys.argv[4])
     loss = mod.training_step(batch.to(dev), 0)
     loss.backward()
     mod._engine.check_status("multi-GPU step")

@@ -237,7 +237,9 @@ def test_candidate_list_matches_full_sweeps(groups):
     g = torch.Generator().manual_seed(5)
     L, B, F, k = 3, 64, 4096, 6
     z = torch.randn(L, B, F, generator=g).to(dev)
-    b_enc = (0.1 * torch.randn(L, F, generator=g)).to(dev)
+    b_enc = 0.1 * torch.randn(L, F, generator=g)
+    b_enc[:, ::61] += 0.8                              # a few large biases
+    b_enc = b_enc.to(dev)
     n_keep = k * B * L
     full, _, code_full = _select(z, b_enc, n_keep, groups, 0.0, False)
     assert int((full != 0).sum()) == n_keep and bool((code_full == 16).all())

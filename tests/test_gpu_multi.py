@@ -25,3 +25,18 @@ def test_two_shards_match_unsharded_oracle(kind, prec, mode):
            "127.0.0.1", "--master-port", "29533", str(ROOT / "tests" / "mp_worker.py"), kind, prec, mode]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("join", ["early", "late"])
+@pytest.mark.parametrize("kind", ["topk", "batchtopk"])
+def test_sharded_batch_uploader_feeds_the_same_steps(kind, join):
+    """parallel.ShardedBatchUploader (each rank uploads its token rows, peers receive the input halves) against
+    whole device batches: identical losses and parameters over three optimizer steps, with both ways of ordering
+    the peer copies."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29534", str(ROOT / "tests" / "mp_worker.py"), kind, "bf16", "fused", join]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]

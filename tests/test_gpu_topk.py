@@ -132,17 +132,23 @@ def _check_selection(dev, L, B, F, ks):
 
     g = torch.Generator().manual_seed(0)
     z = torch.randn(L, B, F, generator=g)
-    z[1, 3] = -z[1, 3].abs() - 0.1                                   # an all-negative row
-    z[0, 1, F // 2:] = -1.0                                          # positives in half of the row only
-    z[0, 2] = torch.where(z[0, 2] > 0, torch.full_like(z[0, 2], 0.5), z[0, 2])   # masses of equal values
+    # a bias with a few large entries, in multiples of 2^-10 so that z = c - bias gives pre-activations exactly
+    # equal to c
+    bias_h = torch.round(0.05 * torch.randn(L, F, generator=g) * 1024) / 1024
+    bias_h[:, ::97] += 0.75
+    bias_h[0, 1] = -3.0
+    z[1, 3] = -z[1, 3].abs() - 1.5                                   # an all-negative row, bias included
+    z[0, 1, F // 2:] = -2.0                                          # positives in half of the row only
+    z[0, 2] = torch.where(z[0, 2] > 0, 0.5 - bias_h[0], z[0, 2] - 1.0)   # masses of equal pre-activations
     zb = z.to(dev)
-    bias = torch.zeros(L, F, device=dev)
+    bias = bias_h.to(dev)
+    pre = z + bias_h.unsqueeze(1)
     for k in ks:
         idx = torch.empty(L, B, k, dtype=torch.int32, device=dev)
         val = torch.empty(L, B, k, device=dev)
         lib().call("clt_select_topk", zb, bias, idx, val, None, B, L, F, k, 0, stream_ptr())
         dense = torch.zeros(L, B, F).scatter_add_(2, idx.long().cpu(), val.cpu())
-        ref = O.per_layer_topk(z.permute(1, 0, 2).contiguous(), k).permute(1, 0, 2)
+        ref = O.per_layer_topk(pre.permute(1, 0, 2).contiguous(), k).permute(1, 0, 2)
         tie_row = torch.zeros(L, B, dtype=torch.bool)
         tie_row[0, 2] = True                                         # which of the equal values win is unspecified
         assert torch.equal(dense[~tie_row], ref[~tie_row])
@@ -154,5 +160,5 @@ def _check_selection(dev, L, B, F, ks):
             v, f = val.cpu(), idx.cpu()
             assert bool(((v[..., 1:] < v[..., :-1]) | ((v[..., 1:] == v[..., :-1]) &
                                                       ((f[..., 1:] > f[..., :-1]) | (v[..., 1:] == 0)))).all())
-            tv, ti = torch.topk(z[0, 0], k)
+            tv, ti = torch.topk(pre[0, 0], k)
             assert torch.equal(v[0, 0], tv) and torch.equal(f[0, 0].long(), ti)
