@@ -1280,7 +1280,9 @@ class FusedAdam(torch.optim.Optimizer):
                 for key, buf in (("exp_avg", fp.exp_avg), ("exp_avg_sq", fp.exp_avg_sq)):
                     view = fp.view_of(p, buf)
                     cur = st.get(key)
-                    if cur is not None and cur.data_ptr() != view.data_ptr():
+                    if cur is None:
+                        view.zero_()        # a new optimizer starts from zero moments, whatever an earlier one left
+                    elif cur.data_ptr() != view.data_ptr():
                         view.copy_(cur.to(view.dtype))
                     st[key] = view
         self._linked_to = fp

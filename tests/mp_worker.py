@@ -83,11 +83,15 @@ def uploader_case(mod, spec, batch, dev, join):
     feed = Uploaded()
     got_l, got_p = run(feed)
     feed.up.detach()
-    # (sums taken with atomics differ in their last bits from run to run)
-    ok = all(abs(a - b) <= 1e-5 * abs(b) for a, b in zip(got_l, want_l)) and all(
-        rel_err(a, b) < 1e-5 for a, b in zip(got_p, want_p))
+    # Sums taken with atomics differ in their last bits from run to run, and Adam turns such a difference into a
+    # step of up to lr wherever a gradient is at the rounding level (two runs of the SAME feed differ that way
+    # too): the losses of all three steps must agree to 1e-4 — a wrong or stale row would move them by percents —
+    # and no parameter may differ by more than a few steps of lr.
+    ok = all(abs(a - b) <= 1e-4 * abs(b) for a, b in zip(got_l, want_l))
+    worst = max(float((a - b).abs().max()) for a, b in zip(got_p, want_p))
+    ok = ok and worst <= 3 * spec.lr
     if not ok:
-        print("uploader case FAILED", got_l, want_l)
+        print("uploader case FAILED", got_l, want_l, "max |dp|", worst)
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.destroy_process_group()

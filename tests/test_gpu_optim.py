@@ -44,6 +44,31 @@ def test_three_steps_match_torch_optim(optimizer):
         assert rel_err(p.detach().cpu(), t.detach()) < 1e-5
 
 
+def test_a_second_optimizer_starts_from_zero_moments():
+    """configure_optimizers() called again on a module that has trained: the new optimizer must not inherit the
+    moments the first one left in the flat buffers (torch.optim.Adam's would not either)."""
+    spec = _spec()
+    batch, w, la = spec_inputs(spec)
+    dev = torch.device("cuda:0")
+    mod = build_module(spec, w, dev)
+    b = batch.to(dev)
+    opt = mod.configure_optimizers()
+    for i in range(2):
+        opt.zero_grad()
+        mod.training_step(b, i).backward()
+        opt.step()
+    opt2 = mod.configure_optimizers()
+    opt2.zero_grad()
+    mod.training_step(b, 2).backward()
+    grads = [p.grad.detach().clone() for p in mod.parameters()]
+    opt2.step()
+    for p, g in zip(mod.parameters(), grads):
+        st = opt2.state[p]
+        assert int(st["step"]) == 1
+        assert rel_err(st["exp_avg"], 0.1 * g) < 1e-5               # (1 - beta1) g: nothing carried over
+        assert rel_err(st["exp_avg_sq"], 0.001 * g * g) < 1e-4
+
+
 def test_scaled_backward_scales_every_gradient():
     spec = _spec()
     batch, w, la = spec_inputs(spec)
