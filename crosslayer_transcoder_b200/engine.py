@@ -803,33 +803,8 @@ class StepEngine:
         aux_scale = float(h.get("aux_loss_scale", 0.0))
         pending = []                                    # collectives in flight (feature shards only)
         h_gather = None
-        if k_aux > 0:
-            dead_list = ws.get("dead_list", (L, F), torch.int32, dev)
-            n_dead = ws.get("n_dead", (L,), torch.int32, dev)
-            self._call("clt_dead_compact", dead, dead_list, n_dead, L, F, s)
-            exchange = False
-            if world > 1:
-                # a row whose positive dead values, summed over the shards, do not exceed k_aux keeps all
-                # of them: the candidate exchange is needed only if some row has more
-                from .parallel import all_gather, all_reduce_sum
+        main_early, h_cnt = False, None
 
-                cnt = ws.get("aux_cnt", (L, B), torch.int32, dev)
-                self._call("clt_aux_count", z, enc.b.data, dead_list, n_dead, cnt, B, L, F, int(bf16), s)
-                all_reduce_sum(cnt, group)
-                nd_pad, exchange = self._aux_sizes(n_dead, soon, cnt, k_aux)
-            else:
-                cnt = None
-                nd_pad, exchange = self._aux_sizes(n_dead, soon, None, k_aux)
-            self.last_nd_pad = nd_pad
-            a_aux = ws.get("a_aux", (L, B, nd_pad), T, dev)
-            if exchange:
-                # offer this shard's k_aux best dead values per row; the gather runs while the main
-                # decoder works
-                cand = ws.get("aux_cand", (L, B, k_aux), torch.float32, dev)
-                self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, None, cand, None, 1, B, L, F, k_aux,
-                           nd_pad, int(bf16), None, self.status, s)
-                cand_all = ws.get("aux_cand_all", (world, L, B, k_aux), torch.float32, dev)
-                h_gather = all_gather(cand_all, cand, group, async_op=True)
         def main_decoder():
             if px is not None:
                 self._call("clt_sparse_decoder_fwd_push", idx, val, None, None, B * kk, W_op, bias,
@@ -843,6 +818,41 @@ class StepEngine:
 
                 pending.append(all_reduce_sum(rbuf[:n_rec], group, async_op=True))
 
+        if k_aux > 0:
+            dead_list = ws.get("dead_list", (L, F), torch.int32, dev)
+            n_dead = ws.get("n_dead", (L,), torch.int32, dev)
+            self._call("clt_dead_compact", dead, dead_list, n_dead, L, F, s)
+            exchange = False
+            if world > 1:
+                # a row whose positive dead values, summed over the shards, do not exceed k_aux keeps all
+                # of them: the candidate exchange is needed only if some row has more
+                from .parallel import all_gather, all_reduce_sum
+
+                cnt = ws.get("aux_cnt", (L, B), torch.int32, dev)
+                self._call("clt_aux_count", z, enc.b.data, dead_list, n_dead, cnt, B, L, F, int(bf16), s)
+                if px is not None:
+                    # the sum of the counts travels while the main decoder's gather and push run
+                    h_cnt = all_reduce_sum(cnt, group, async_op=True)
+                    main_early = True
+                else:
+                    all_reduce_sum(cnt, group)
+            else:
+                cnt = None
+        if main_early:
+            main_decoder()
+            h_cnt.wait()
+        if k_aux > 0:
+            nd_pad, exchange = self._aux_sizes(n_dead, soon, cnt, k_aux)
+            self.last_nd_pad = nd_pad
+            a_aux = ws.get("a_aux", (L, B, nd_pad), T, dev)
+            if exchange:
+                # offer this shard's k_aux best dead values per row; the gather runs while the main
+                # decoder works
+                cand = ws.get("aux_cand", (L, B, k_aux), torch.float32, dev)
+                self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, None, cand, None, 1, B, L, F, k_aux,
+                           nd_pad, int(bf16), None, self.status, s)
+                cand_all = ws.get("aux_cand_all", (world, L, B, k_aux), torch.float32, dev)
+                h_gather = all_gather(cand_all, cand, group, async_op=True)
         if px is None:
             main_decoder()          # its all-reduce runs while the auxiliary path computes
         if k_aux > 0:
@@ -872,7 +882,8 @@ class StepEngine:
         if px is not None:
             from .parallel import all_reduce_sum
 
-            main_decoder()
+            if not main_early:
+                main_decoder()
             self._rank_barrier(px)                      # every rank's rows have landed in the owners' slots
             for h_ in pending:
                 h_.wait()

@@ -165,3 +165,39 @@ def test_tensor_datamodule_and_bad_rows(tmp_path):
     with pytest.raises(Exception, match="out of range"):
         gth.check()
     dm.teardown()
+
+
+@pytest.mark.gpu
+def test_training_step_consumes_store_batches():
+    """A module trains directly from the batches the device-side consumer yields: same loss as the same rows
+    indexed on the host and uploaded."""
+    from crosslayer_transcoder_b200 import synthetic
+    from tests.helpers import build_module, spec_inputs
+
+    spec = synthetic.WorkloadSpec("ingest", 3, 64, 256, 32, "jumprelu", True, False, rank_u=8, n_outlier=1,
+                                  lambda_sparsity=1e-4, pre_actv_loss=3e-6, lr=1e-3)
+    batch, w, la = spec_inputs(spec)
+    s = FakeStore(128, spec.n_layers, spec.d_acts)
+    try:
+        g = torch.Generator().manual_seed(2)
+        s.buffer_tensor.copy_(torch.randn(s.buffer_tensor.shape, generator=g))
+        s.buffer_tensor[:, 0, 0, 0] = torch.arange(128, dtype=torch.float32)
+        s.validity_tensor.fill_(True)
+        dev = torch.device("cuda:0")
+        mod = build_module(spec, w, dev)
+        twin = build_module(spec, w, dev)
+        src = data.SharedBufferBatches(s, batch_size=spec.batch, device="cuda:0")
+        try:
+            for i in range(2):
+                b = next(src)
+                ids = _ids(b)
+                loss = mod.training_step(b, i)
+                want = twin.training_step(s.buffer_tensor[ids].to(dev), i)
+                assert abs(float(loss) - float(want)) <= 1e-6 * abs(float(want))
+                loss.backward()
+                want.backward()
+            mod._engine.check_status("ingest")
+        finally:
+            src.close()
+    finally:
+        s.close()
