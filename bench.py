@@ -212,6 +212,10 @@ def algorithmic_work(spec, world: int, Fl: int, n_params: int, batch_bytes_per_e
     sparse_fwd = ("hbm", rows_unique * D * e + bld * 4, rows * D * e + bld * 4)
     work = {
         "clt_encoder_fwd_act": ("tensor", enc), "clt_encoder_fwd_store": ("tensor", enc),
+        # the auxiliary path's own encoder contraction over the compact dead columns, and the gather that builds
+        # its operand (touches most sectors of the encoder weights: counted as one read of them)
+        "clt_encoder_fwd_store[dead]": ("tensor", 2.0 * B * L * D * nd_pad),
+        "clt_gather_enc_cols": ("hbm", float(L) * D * Fl * e + float(L) * D * nd_pad * e),
         "clt_encoder_dense_bwd_dw": ("tensor", 2.0 * B * L * D * Fd if spec.kind == "topk" else enc),
         "clt_decoder_dense_fwd": ("tensor", dec), "clt_decoder_dense_fwd_push": ("tensor", dec),
         "clt_decoder_dense_bwd_dfeat": ("tensor", dec), "clt_decoder_dense_bwd_dw": ("tensor", dec),

@@ -744,6 +744,28 @@ sparse_bwd_enc_kernel(const int* __restrict__ col_ptr, const int* __restrict__ e
 // Compaction helpers of the auxiliary (dead-feature) path.
 // =========================================================================================
 // out[p, j, :] = W[p, dead_list[s(p)][j], :] for j < n_dead[s(p)], else 0
+// Compact encoder operands of the dead features, for the auxiliary path's own small contraction:
+//   Wc[l, d, j] = W_enc[l, d, dead_list[l][j]],  bc[l, j] = b_enc[l, dead_list[l][j]]     (j < n_dead[l])
+// Padding columns (j >= n_dead[l]) get weight 0 and bias -1: their pre-activation is -1, never positive.
+template <class T>
+__global__ void gather_enc_cols_kernel(const T* __restrict__ W, const float* __restrict__ b_enc,
+                                       const int* __restrict__ dead_list, const int* __restrict__ n_dead,
+                                       T* __restrict__ Wc, float* __restrict__ bc, int D, int F, int nd_pad) {
+  const int l = blockIdx.z;
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  if (j >= nd_pad) return;
+  const int f = j < n_dead[l] ? dead_list[(size_t)l * F + j] : -1;
+  if (blockIdx.y == 0) bc[(size_t)l * nd_pad + j] = f >= 0 ? __ldg(b_enc + (size_t)l * F + f) : -1.f;
+  for (int d = blockIdx.y; d < D; d += gridDim.y) {
+    const size_t r = (size_t)l * D + d;
+    T v;
+    if (f >= 0) v = W[r * F + f];
+    else if constexpr (sizeof(T) == 2) v = __float2bfloat16_rn(0.f);
+    else v = 0.f;
+    Wc[r * nd_pad + j] = v;
+  }
+}
+
 template <class T>
 __global__ void gather_rows_kernel(const T* __restrict__ W, const int* __restrict__ dead_list,
                                    const int* __restrict__ n_dead, T* __restrict__ out, int F, int D, int nd_pad,
@@ -990,6 +1012,21 @@ int clt_sparse_bwd_enc(const int* col_ptr, const int* ent, const float* dval, co
     sparse_bwd_enc_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>(col_ptr, ent, dval, etok, npl,
                                                                         (const float*)xn, dW_enc, db_enc, B, D, F, k,
                                                                         dW_aux, db_aux, dead_pos, nd_pad);
+  CLT_CHECK_CUDA(cudaGetLastError());
+  return 0;
+}
+
+int clt_gather_enc_cols(const void* W_enc, const float* b_enc, const int* dead_list, const int* n_dead, void* Wc,
+                        float* bc, int L, int D, int F, int nd_pad, int bf16, clt_stream_t stream) {
+  CLT_CHECK_ARG(L > 0 && F > 0 && D > 0 && nd_pad > 0, "gather_enc_cols: bad dims");
+  CLT_CHECK_ARG(W_enc && b_enc && dead_list && n_dead && Wc && bc, "gather_enc_cols: null pointer");
+  dim3 grid((nd_pad + 255) / 256, D < 64 ? D : 64, L);
+  if (bf16)
+    gather_enc_cols_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)W_enc, b_enc, dead_list, n_dead, (__nv_bfloat16*)Wc, bc, D, F, nd_pad);
+  else
+    gather_enc_cols_kernel<float><<<grid, 256, 0, (cudaStream_t)stream>>>((const float*)W_enc, b_enc, dead_list,
+                                                                         n_dead, (float*)Wc, bc, D, F, nd_pad);
   CLT_CHECK_CUDA(cudaGetLastError());
   return 0;
 }

@@ -125,9 +125,10 @@ class StepEngine:
         self._status_slot = 0
 
     # ------------------------------------------------------------------ setup
-    def _call(self, name, *args):
+    def _call(self, name, *args, tag: str = ""):
         """One C-ABI call = one kernel launch on the current stream.  With ``self.profile`` set to a
-        dict, CUDA events around the call collect per-entry-point device time."""
+        dict, CUDA events around the call collect per-entry-point device time (``tag`` keeps apart two uses
+        of one entry point with different shapes)."""
         if self.profile is None:
             lib().call(name, *args)
         else:
@@ -135,7 +136,7 @@ class StepEngine:
             e0.record()
             lib().call(name, *args)
             e1.record()
-            self.profile.setdefault(name, []).append((e0, e1))
+            self.profile.setdefault(name + tag, []).append((e0, e1))
         self.launches += 1
 
     def profile_summary(self) -> Dict[str, dict]:
@@ -822,6 +823,21 @@ class StepEngine:
             dead_list = ws.get("dead_list", (L, F), torch.int32, dev)
             n_dead = ws.get("n_dead", (L,), torch.int32, dev)
             self._call("clt_dead_compact", dead, dead_list, n_dead, L, F, s)
+            nd_pad = self._aux_width(n_dead)
+            self.last_nd_pad = nd_pad
+            # The dead features' pre-activations come from a small contraction of their own over the compact
+            # encoder columns (nd_pad of F columns: a tenth of the main one) instead of a second and third sweep
+            # of z, whose dead columns are spread over four fifths of its 32-byte sectors.
+            az, ab, alist, aF = z, enc.b.data, dead_list, F
+            if getattr(mod, "aux_compact_encoder", True) and nd_pad < F:
+                w_ec = ws.get("w_enc_c", (L, D, nd_pad), T, dev)
+                ab = ws.get("b_enc_c", (L, nd_pad), torch.float32, dev)
+                self._call("clt_gather_enc_cols", self._operand(enc.W, bf16), enc.b.data, dead_list, n_dead, w_ec, ab,
+                           L, D, F, nd_pad, int(bf16), s)
+                az = ws.get("z_c", (L, B, nd_pad), T, dev)
+                self._call("clt_encoder_fwd_store", xn, w_ec, az, B, L, D, nd_pad, int(bf16), self.status, s,
+                           tag="[dead]")
+                alist, aF = self._iota(L, nd_pad, dev), nd_pad
             exchange = False
             if world > 1:
                 # a row whose positive dead values, summed over the shards, do not exceed k_aux keeps all
@@ -829,7 +845,7 @@ class StepEngine:
                 from .parallel import all_gather, all_reduce_sum
 
                 cnt = ws.get("aux_cnt", (L, B), torch.int32, dev)
-                self._call("clt_aux_count", z, enc.b.data, dead_list, n_dead, cnt, B, L, F, int(bf16), s)
+                self._call("clt_aux_count", az, ab, alist, n_dead, cnt, B, L, aF, int(bf16), s)
                 if px is not None:
                     # the sum of the counts travels while the main decoder's gather and push run
                     h_cnt = all_reduce_sum(cnt, group, async_op=True)
@@ -842,14 +858,13 @@ class StepEngine:
             main_decoder()
             h_cnt.wait()
         if k_aux > 0:
-            nd_pad, exchange = self._aux_sizes(n_dead, soon, cnt, k_aux)
-            self.last_nd_pad = nd_pad
+            exchange = self._aux_exchange(soon, cnt, k_aux)
             a_aux = ws.get("a_aux", (L, B, nd_pad), T, dev)
             if exchange:
                 # offer this shard's k_aux best dead values per row; the gather runs while the main
                 # decoder works
                 cand = ws.get("aux_cand", (L, B, k_aux), torch.float32, dev)
-                self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, None, cand, None, 1, B, L, F, k_aux,
+                self._call("clt_select_aux", az, ab, alist, n_dead, None, cand, None, 1, B, L, aF, k_aux,
                            nd_pad, int(bf16), None, self.status, s)
                 cand_all = ws.get("aux_cand_all", (world, L, B, k_aux), torch.float32, dev)
                 h_gather = all_gather(cand_all, cand, group, async_op=True)
@@ -857,13 +872,13 @@ class StepEngine:
             main_decoder()          # its all-reduce runs while the auxiliary path computes
         if k_aux > 0:
             if not exchange:
-                self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, a_aux, None, None, 0, B, L, F, k_aux,
+                self._call("clt_select_aux", az, ab, alist, n_dead, a_aux, None, None, 0, B, L, aF, k_aux,
                            nd_pad, int(bf16), cnt, self.status, s)
             else:
                 h_gather.wait()
                 thr_aux = ws.get("thr_aux", (L, B), torch.float32, dev)
                 self._call("clt_topk_threshold", cand_all, thr_aux, L * B, world, k_aux, s)
-                self._call("clt_select_aux", z, enc.b.data, dead_list, n_dead, a_aux, None, thr_aux, 2, B, L, F, k_aux,
+                self._call("clt_select_aux", az, ab, alist, n_dead, a_aux, None, thr_aux, 2, B, L, aF, k_aux,
                            nd_pad, int(bf16), None, self.status, s)
             P = W_op.shape[0]
             w_c = ws.get("w_c", (P, nd_pad, D), T, dev)
@@ -1159,39 +1174,57 @@ class StepEngine:
                    db_c if aux is not None else None, dead_pos, aux["nd_pad"] if aux is not None else 0, B, L, D, F,
                    k, int(bf16), s)
 
-    def _aux_sizes(self, n_dead: torch.Tensor, soon_dead: torch.Tensor, cnt, k_aux: int):
-        """(nd_pad, exchange) for the auxiliary path: the column count of the compact dead-feature operands
-        and, on feature shards, whether some row has more than k_aux positive dead values in total (then
-        the shards must exchange candidates).  Both depend on device values; reading them every step would
-        drain the launch queue.  The first two steps do read them (one blocking host read each).  From
-        then on every step copies its values to pinned memory without waiting and a step uses what the
-        step before last left there, which has always arrived when it is needed:
-
-        * nd_pad from ``soon_dead`` of two steps ago, the number of features that were dead or within two
-          steps of the limit then.  A feature leaves that set only by firing, so it bounds the dead count of
-          this step from above whatever happens in between: the operands are never too small, and in
-          steady state the bound is the dead count itself.
-        * the exchange switches on when the largest row count of two steps ago exceeds 3/4 of k_aux; should
-          a row outgrow k_aux within two steps all the same, ``clt_select_aux`` reports it through the
-          status word.  Every rank takes the same decision (the counts are summed over the ranks first)."""
+    def _aux_state(self):
         st = getattr(self, "_aux_hist", None)
         if st is None:
             st = self._aux_hist = dict(step=0, host=torch.zeros(2, 2, dtype=torch.int32).pin_memory(),
                                        evt=[torch.cuda.Event(), torch.cuda.Event()])
+        return st
+
+    def _aux_width(self, n_dead: torch.Tensor) -> int:
+        """nd_pad, the column count of the compact dead-feature operands of the auxiliary path.  It depends on a
+        device value (the largest per-layer dead count); reading it every step would drain the launch queue.  The
+        first two steps do read it (one blocking host read each).  From then on every step copies its values to
+        pinned memory without waiting (``_aux_exchange``) and a step uses what the step before last left there,
+        which has always arrived when it is needed: ``soon_dead`` of two steps ago, the number of features that
+        were dead or within two steps of the limit then.  A feature leaves that set only by firing, so it bounds
+        the dead count of this step from above whatever happens in between: the operands are never too small, and
+        in steady state the bound is the dead count itself."""
+        st = self._aux_state()
+        i = st["step"]
+        if i < 2:
+            nd = int(n_dead.max())                              # blocking: first two steps only
+        else:
+            st["evt"][i & 1].synchronize()                      # the copy made two steps ago into this slot
+            nd = int(st["host"][i & 1, 0])
+        return max(64, _round_up(nd, 64))
+
+    def _aux_exchange(self, soon_dead: torch.Tensor, cnt, k_aux: int) -> bool:
+        """On feature shards: does some row have more than k_aux positive dead values in total (then the shards
+        must exchange candidates)?  Decided like the operand width: from the current counts in the first two
+        steps, afterwards from the largest row count of two steps ago, switching on at 3/4 of k_aux; should a row
+        outgrow k_aux within two steps all the same, ``clt_select_aux`` reports it through the status word.
+        Every rank takes the same decision (the counts are summed over the ranks first).  Also posts this step's
+        values for the step after next; call once per step, after ``_aux_width``."""
+        st = self._aux_state()
         i = st["step"]
         st["step"] = i + 1
-        cmax_t = cnt.max() if cnt is not None else n_dead.new_zeros(())
         slot = i & 1
+        cmax_t = cnt.max() if cnt is not None else soon_dead.new_zeros(())
         if i < 2:
-            nd, cmax = (int(x) for x in torch.stack([n_dead.max(), cmax_t]).tolist())   # blocking: first two steps only
-            exchange = cnt is not None and cmax > k_aux
+            exchange = cnt is not None and int(cmax_t) > k_aux   # blocking: first two steps only
         else:
-            st["evt"][slot].synchronize()                       # the copy made two steps ago into this slot
-            nd, cmax = int(st["host"][slot, 0]), int(st["host"][slot, 1])
-            exchange = cnt is not None and 4 * cmax > 3 * k_aux
+            exchange = cnt is not None and 4 * int(st["host"][slot, 1]) > 3 * k_aux
         st["host"][slot].copy_(torch.stack([soon_dead.max(), cmax_t]).to(torch.int32), non_blocking=True)
         st["evt"][slot].record()
-        return max(64, _round_up(nd, 64)), exchange
+        return exchange
+
+    def _iota(self, L: int, n: int, dev) -> torch.Tensor:
+        """[L, n] int32 rows 0, 1, ..., n-1: the "dead list" of operands that are already compact."""
+        t = getattr(self, "_iota_t", None)
+        if t is None or t.shape != (L, n) or t.device != dev:
+            t = self._iota_t = torch.arange(n, dtype=torch.int32, device=dev).repeat(L, 1).contiguous()
+        return t
 
     def _fused_optimizer(self, F: int) -> bool:
         """Apply the optimizer to the decoder inside the sparse backward?  Opt-in

@@ -303,6 +303,13 @@ int clt_sparse_bwd_enc(const int* col_ptr, const int* ent, const float* dval, co
  * (the compact encoder gradients are added inside clt_sparse_bwd_enc) */
 int clt_gather_rows(const void* W_dec, const int* dead_list, const int* n_dead, void* out, int L, int F, int D,
                     int nd_pad, int crosslayer, int bf16, clt_stream_t stream);
+/* Compact ENCODER operands of the dead features: Wc[l, d, j] = W_enc[l, d, dead_list[l][j]] (T, [L, D, nd_pad]),
+ * bc[l, j] = b_enc[l, dead_list[l][j]] (fp32, [L, nd_pad]); padding columns get weight 0 and bias -1.  With
+ * them the auxiliary path takes the dead features' pre-activations from a small contraction of its own
+ * (clt_encoder_fwd_store with F = nd_pad) instead of sweeping the full pre-activations a second time:
+ * clt_aux_count / clt_select_aux are then called on that compact output with dead_list = 0, 1, 2, ... */
+int clt_gather_enc_cols(const void* W_enc, const float* b_enc, const int* dead_list, const int* n_dead, void* Wc,
+                        float* bc, int L, int D, int F, int nd_pad, int bf16, clt_stream_t stream);
 int clt_scatter_rows(const float* src, const int* dead_list, const int* n_dead, float* dW_dec, int L, int F,
                      int D, int nd_pad, int crosslayer, clt_stream_t stream);
 
