@@ -709,15 +709,25 @@ select_aux_kernel(const T* __restrict__ z, const float* __restrict__ b_enc, cons
   const T* zr = z + (size_t)row * F;
   const float* br = b_enc + (size_t)l * F;
   const int* dl = dead_list + (size_t)l * F;
+  __shared__ int n_pos;
+  if (threadIdx.x == 0) n_pos = 0;
+  __syncthreads();
+  int mine = 0;
   for (int j = threadIdx.x; j < nd; j += kSelThreads) {
     const int f = __ldg(dl + j);
-    cand[j] = ld_as_float<T>(zr, f) + __ldg(br + f);
+    const float c = ld_as_float<T>(zr, f) + __ldg(br + f);
+    cand[j] = c;
+    mine += c > 0.f ? 1 : 0;
   }
+  mine = __reduce_add_sync(0xffffffffu, mine);
+  if ((threadIdx.x & 31) == 0 && mine > 0) atomicAdd(&n_pos, mine);
   __syncthreads();
   RowSelect sel{0u, 0};
   if (mode == 2) {
     sel.T = positive_key(thr[row]);
-  } else {
+  } else if (n_pos > k_aux) {
+    // (a row with at most k_aux positive values keeps all of them: threshold key 0, no select passes —
+    // the usual case, dead features are rarely positive)
     auto key_at = [&](int j) { return positive_key(cand[j]); };
     sel = radix_select(nd, k_aux, key_at);
   }
