@@ -747,6 +747,98 @@ sparse_bwd_enc_kernel(const int* __restrict__ col_ptr, const int* __restrict__ e
 // Compact encoder operands of the dead features, for the auxiliary path's own small contraction:
 //   Wc[l, d, j] = W_enc[l, d, dead_list[l][j]],  bc[l, j] = b_enc[l, dead_list[l][j]]     (j < n_dead[l])
 // Padding columns (j >= n_dead[l]) get weight 0 and bias -1: their pre-activation is -1, never positive.
+// The same computation with 16-byte loads: a thread owns 8 consecutive input dimensions (one 16-byte chunk of an
+// x row) and all kEncFB features of the CTA, 128 threads cover 1024 dimensions (blockIdx.z takes the next 1024).
+// An 8th of the load instructions of the kernel above for the same rows; needs D % 8 == 0.
+template <class T>
+__global__ void __launch_bounds__(128)
+sparse_bwd_enc_vec_kernel(const int* __restrict__ col_ptr, const int* __restrict__ ent, const float* __restrict__ dval,
+                          const int* __restrict__ etok, long long npl_, const T* __restrict__ xn,
+                          float* __restrict__ dW, float* __restrict__ db, int B, int D, int F, int k,
+                          const float* __restrict__ dW_aux, const float* __restrict__ db_aux,
+                          const int* __restrict__ dead_pos, int nd_pad) {
+  using V = Vec8<T>;
+  const int l = blockIdx.y, f0 = blockIdx.x * kEncFB;
+  const int d = (blockIdx.z * 128 + threadIdx.x) * 8;      // this thread's first input dimension
+  const bool on = d < D;
+  const int* cp = col_ptr + (size_t)l * (F + 1);
+  const size_t npl = (size_t)npl_;
+  constexpr int kCap = 512;
+  __shared__ float s_g[kCap];
+  __shared__ int s_tok[kCap];
+  __shared__ int s_cp[kEncFB + 1];
+  if (threadIdx.x <= kEncFB) s_cp[threadIdx.x] = __ldg(cp + min(f0 + (int)threadIdx.x, F));
+  __syncthreads();
+  const int e_begin = s_cp[0], e_end = s_cp[kEncFB];
+  float acc[kEncFB][8];
+#pragma unroll
+  for (int q = 0; q < kEncFB; ++q)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[q][i] = 0.f;
+  float bsum = 0.f;
+  const T* xl = xn + (size_t)l * B * D + d;
+  for (int c0 = e_begin; c0 < e_end; c0 += kCap) {
+    const int c1 = min(e_end, c0 + kCap);
+    __syncthreads();
+    for (int e = c0 + threadIdx.x; e < c1; e += 128) {
+      const int slot = __ldg(ent + (size_t)l * npl + e);
+      s_g[e - c0] = __ldg(dval + (size_t)l * npl + slot);
+      s_tok[e - c0] = etok != nullptr ? __ldg(etok + (size_t)l * npl + slot) : slot / k;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < kEncFB; ++q) {
+      const int eb = max(s_cp[q], c0), ee = min(s_cp[q + 1], c1);
+      float bs = 0.f;
+      for (int e = eb; e < ee; e += 2) {  // two rows of x in flight
+        const bool two = e + 1 < ee;
+        const float g0 = s_g[e - c0], g1 = two ? s_g[e + 1 - c0] : 0.f;
+        typename V::Raw r0 = V::zero(), r1 = V::zero();
+        if (on) {
+          r0 = V::load_raw(xl + (size_t)s_tok[e - c0] * D);
+          if (two) r1 = V::load_raw(xl + (size_t)s_tok[e + 1 - c0] * D);
+        }
+        float x0[8], x1[8];
+        V::unpack(r0, x0);
+        V::unpack(r1, x1);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[q][i] = fmaf(g1, x1[i], fmaf(g0, x0[i], acc[q][i]));
+        bs += g0 + g1;
+      }
+      if ((int)threadIdx.x == q) bsum += bs;
+    }
+  }
+  if (dW_aux != nullptr) {   // the auxiliary loss's compact gradient, for the dead features among these 8
+#pragma unroll
+    for (int q = 0; q < kEncFB; ++q) {
+      const int pos = f0 + q < F ? __ldg(dead_pos + (size_t)l * F + f0 + q) : -1;   // CTA-uniform
+      if (pos < 0) continue;
+      if (on) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[q][i] += __ldg(dW_aux + ((size_t)l * D + d + i) * nd_pad + pos);
+      }
+      if ((int)threadIdx.x == q) bsum += __ldg(db_aux + (size_t)l * nd_pad + pos);
+    }
+  }
+  if (on) {
+    const bool vec = (F % 4 == 0) && (f0 + kEncFB <= F);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float* o = dW + ((size_t)l * D + d + i) * F + f0;
+      if (vec) {
+        __stcs(reinterpret_cast<float4*>(o), make_float4(acc[0][i], acc[1][i], acc[2][i], acc[3][i]));
+        __stcs(reinterpret_cast<float4*>(o) + 1, make_float4(acc[4][i], acc[5][i], acc[6][i], acc[7][i]));
+      } else {
+#pragma unroll
+        for (int q = 0; q < kEncFB; ++q)
+          if (f0 + q < F) o[q] = acc[q][i];
+      }
+    }
+  }
+  if (blockIdx.z == 0 && threadIdx.x < kEncFB && f0 + (int)threadIdx.x < F)
+    db[(size_t)l * F + f0 + threadIdx.x] = bsum;
+}
+
 template <class T>
 __global__ void gather_enc_cols_kernel(const T* __restrict__ W, const float* __restrict__ b_enc,
                                        const int* __restrict__ dead_list, const int* __restrict__ n_dead,
@@ -1004,6 +1096,19 @@ int clt_sparse_bwd_enc(const int* col_ptr, const int* ent, const float* dval, co
   CLT_CHECK_ARG(dW_aux == nullptr || nd_pad > 0, "sparse_bwd_enc: nd_pad=%d", nd_pad);
   dim3 grid((F + kEncFB - 1) / kEncFB, L, (D + 767) / 768);
   CLT_CHECK_ARG(grid.y <= 65535 && grid.z <= 65535, "sparse_bwd_enc: grid too large");
+  static_assert(kEncFB == 8, "the vector form writes its 8 features as two float4");
+  if (D % 8 == 0 && (uintptr_t)xn % 16 == 0) {   // 16-byte loads of the x rows
+    dim3 vgrid(grid.x, L, (D / 8 + 127) / 128);
+    if (bf16)
+      sparse_bwd_enc_vec_kernel<__nv_bfloat16><<<vgrid, 128, 0, (cudaStream_t)stream>>>(
+          col_ptr, ent, dval, etok, npl, (const __nv_bfloat16*)xn, dW_enc, db_enc, B, D, F, k, dW_aux, db_aux, dead_pos,
+          nd_pad);
+    else
+      sparse_bwd_enc_vec_kernel<float><<<vgrid, 128, 0, (cudaStream_t)stream>>>(
+          col_ptr, ent, dval, etok, npl, (const float*)xn, dW_enc, db_enc, B, D, F, k, dW_aux, db_aux, dead_pos, nd_pad);
+    CLT_CHECK_CUDA(cudaGetLastError());
+    return 0;
+  }
   if (bf16)
     sparse_bwd_enc_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>(
         col_ptr, ent, dval, etok, npl, (const __nv_bfloat16*)xn, dW_enc, db_enc, B, D, F, k, dW_aux, db_aux, dead_pos,
