@@ -480,6 +480,8 @@ def main():
     ap.add_argument("--no-fuse-optimizer", action="store_true",
                     help="TopK / BatchTopK workloads: keep the decoder's Adam update in the optimizer kernel "
                          "instead of applying it inside the sparse decoder backward (module.fuse_optimizer)")
+    ap.add_argument("--gather-form", choices=["auto", "warp", "cta"], default="auto",
+                    help="form of the token-major decoder gather (module.decoder_gather_warp); auto = the engine's rule")
     ap.add_argument("--ingest", action="store_true",
                     help="1 GPU: also time batch ingestion from the reference's shared-memory activation store "
                          "(its own consumer vs the device-side one) and add an `ingest` object to the line")
@@ -567,6 +569,9 @@ def main():
                                "decoder gradient is never stored), the other parameters in the optimizer kernel")
     else:
         config["optimizer"] = "Adam, one kernel over the flat parameter buffer"
+    if args.gather_form != "auto":
+        mod.decoder_gather_warp = args.gather_form == "warp"
+        config["decoder_gather"] = args.gather_form
     opt = mod.configure_optimizers()
     eng = mod._engine
     # fp16 activations (the reference's storage dtype), drawn on the device (same on every rank), with a pinned

@@ -382,6 +382,11 @@ class StepEngine:
         self._call("clt_sum_slots", px["slots"].local[which], px["recon_own"] if which == 0 else px["aux_own"],
                    self.module.tp_world, n, px["slot_bf16"], stream_ptr())
 
+    def _gather_form(self, k: int, world: int, D: int) -> int:
+        """``_warp_rows`` unless ``module.decoder_gather_warp`` (True / False) forces a form."""
+        forced = getattr(self.module, "decoder_gather_warp", None)
+        return int(bool(forced)) if forced is not None else self._warp_rows(k, world, D)
+
     @staticmethod
     def _warp_rows(k: int, world: int, D: int) -> int:
         """Which form of the token-major decoder gather: 1 = one warp per (token, target layer), 0 = one CTA
@@ -810,10 +815,10 @@ class StepEngine:
             if px is not None:
                 self._call("clt_sparse_decoder_fwd_push", idx, val, None, None, B * kk, W_op, bias,
                            px["recon_bases"], px["rpr"], world, mod.tp_rank, px["slot_bf16"], B, L, D, F, kk,
-                           crosslayer, self._warp_rows(kk, world, D), int(bf16), self.status, s)
+                           crosslayer, self._gather_form(kk, world, D), int(bf16), self.status, s)
                 return
             self._call("clt_sparse_decoder_fwd", idx, val, None, None, B * kk, W_op, bias, recon, B, L, D, F, kk,
-                       crosslayer, self._warp_rows(kk, world, D), int(bf16), self.status, s)
+                       crosslayer, self._gather_form(kk, world, D), int(bf16), self.status, s)
             if world > 1:
                 from .parallel import all_reduce_sum
 
@@ -968,7 +973,7 @@ class StepEngine:
             px = self._peer_exchange(B, L, D, T, dev)
             self._call("clt_sparse_decoder_fwd_push", idx, val, row_start, row_cnt, npl, W_op, bias,
                        px["recon_bases"], px["rpr"], world, rank, px["slot_bf16"], B, L, D, F, 1, crosslayer,
-                       int(k <= 8 * world), int(bf16), self.status, s)
+                       self._gather_form(k, world, D), int(bf16), self.status, s)
             self._rank_barrier(px)                      # every rank's rows have landed in the owners' slots
             self._sum_slots(px, 0)
             b_lo, b_cnt = px["b_lo"], px["b_cnt"]
@@ -978,7 +983,7 @@ class StepEngine:
             all_reduce_sum(acc[2:4], group)             # loss sums of all owners
         else:
             self._call("clt_sparse_decoder_fwd", idx, val, row_start, row_cnt, npl, W_op, bias, recon, B, L, D, F, 1,
-                       crosslayer, int(k <= 8 * world), int(bf16), self.status, s)
+                       crosslayer, self._gather_form(k, world, D), int(bf16), self.status, s)
             if world > 1:
                 from .parallel import all_reduce_sum
 
